@@ -1,0 +1,371 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory (128B swizzle) ->
+// tcgen05.mma with the f32 accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+//   C[b] (+)= alpha * A[b] x B[b]      A: M x K,  B: K x N,  C: M x N (row-major, bf16 or f32)
+//
+// Either operand may be stored K-major (contraction index contiguous) or MN-major (the M / N index
+// contiguous); all four combinations run on the tensor core without a transpose pass, which is
+// what lets one kernel serve y = x @ W, dx = dy @ W^T and dW = x^T @ dy for weights stored
+// [in, out] (the layout of reference src/ttt/model.py:137-148).  A leading batch index (a 3-D
+// tensor map) gives the per-sequence fast-weight products (reference model.py:316-319, one weight
+// per sequence) in one launch.
+//
+// Roles of the 192 threads of a CTA (one CTA per SM, grid = min(tiles, SMs)):
+//   warp 0     TMA producer   (one elected lane)
+//   warp 1     MMA issuer     (one elected lane) and TMEM owner
+//   warps 2-5  epilogue       (TMEM lane quarter = warp index % 4)
+// Two accumulators of BN columns alternate so the epilogue of tile i overlaps the main loop of
+// tile i+1.  Every wait is bounded (ptx_sm100.cuh); on a timeout all roles leave through the
+// common exit, the status word says which wait gave up and TMEM is freed.
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+#include <cstdio>
+
+namespace dttt {
+
+constexpr int BM = 128;
+constexpr int BK = 64;   // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+struct GemmParams {
+  int M, N, K, batch;
+  int a_mn_major, b_mn_major;
+  long long ldc;        // elements
+  long long c_batch;    // elements
+  int c_is_f32;
+  int accumulate;       // C += result
+  float alpha;
+  void* C;
+  int* status;
+  int tiles_m, tiles_n;
+};
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int BAR_BYTES = 1024;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& b, int& tm, int& tn) {
+  int per_batch = p.tiles_m * p.tiles_n;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  // Bands of 16 m-tiles, n fastest inside a band: concurrently running CTAs share A rows and sweep B.
+  constexpr int GROUP = 16;
+  int band = t / (GROUP * p.tiles_n);
+  int first_m = band * GROUP;
+  int rows = min(GROUP, p.tiles_m - first_m);
+  int r = t - band * GROUP * p.tiles_n;
+  tm = first_m + (r % rows);
+  tn = r / rows;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                 const GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + L::STAGES * L::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty = full + L::STAGES;
+  uint64_t* acc_full = empty + L::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&mapA);
+    tma_prefetch_desc(&mapB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(tile, p, b, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t ph = (it / L::STAGES) & 1;
+          if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sA = smem + s * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_3d(sA, &mapA, &full[s], k0, m0, b);                 // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)                            // box {64 m, 64 k-rows}
+              tma_load_3d(sA + j * (BK * 128), &mapA, &full[s], m0 + j * 64, k0, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(sB, &mapB, &full[s], k0, n0, b);                 // box {64 k, BN rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * (BK * 128), &mapB, &full[s], n0 + j * 64, k0, b);
+          }
+        }
+      }
+      if (!ok) {
+        // Unwinding: give the copies already issued a bounded time to land before the CTA exits.
+        // (Every issued stage either completed its full barrier or is about to; nothing to free.)
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;   // bytes per UMMA_K
+      const uint32_t b_kstep = p.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(&acc_empty[acc], acc_ph ^ 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t ph = (it / L::STAGES) & 1;
+          if (!mbar_wait_bounded(&full[s], ph, abort_word, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t ad = make_smem_desc(sA + k * a_kstep, a_lbo, 1024);
+            const uint64_t bd = make_smem_desc(sB + k * b_kstep, b_lbo, 1024);
+            umma_f16(d_tmem, ad, bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);      // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      int b, tm, tn;
+      tile_coords(tile, p, b, tm, tn);
+      const int acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      // One lane waits, the warp follows its verdict: the tcgen05.ld below is warp-collective, so the
+      // decision to go on must be uniform across the warp.
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(&acc_full[acc], acc_ph, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + quarter * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row_ok && col < p.N) {
+          const bool full_chunk = (col + 32 <= p.N);
+          if (p.c_is_f32) {
+            float* out = reinterpret_cast<float*>(p.C) + row_off + col;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  float4 o = *reinterpret_cast<float4*>(out + j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(out + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += out[j];
+                out[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[j + q]) * p.alpha;
+                if (p.accumulate) {
+                  uint4 o = *reinterpret_cast<uint4*>(out + j);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float2 of = __bfloat1622float2(ob[q]);
+                    f[2 * q] += of.x; f[2 * q + 1] += of.y;
+                  }
+                }
+                uint4 v;
+                __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) vb[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(out[j]);
+                out[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  // ---------------------------------------------------------------- common exit
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 3-D bf16 tensor map {inner, outer, batch} with a 128B-swizzled box {64, box_outer, 1}.
+static int make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long batch,
+                    long long outer_stride_elems, long long batch_stride_elems, int box_outer) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * 2, (cuuint64_t)(batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+static int g_num_sms = 0;
+static bool g_attr_set[2] = {false, false};
+
+}  // namespace dttt
+
+using namespace dttt;
+
+// C[b] (+)= alpha * A[b] x B[b].
+//   a_mn_major = 0: A stored [M, K] (row stride lda);  1: A stored [K, M] (row stride lda).
+//   b_mn_major = 0: B stored [N, K] (row stride ldb);  1: B stored [K, N] (row stride ldb).
+// Strides are in elements; every row stride and base pointer must be a multiple of 16 bytes.
+// `status` is a device int (0 = fine; see ptx_sm100.cuh for the codes).  Returns 0 on a clean launch.
+extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch,
+                              long long lda, long long ldb, long long ldc, long long a_batch, long long b_batch,
+                              long long c_batch, int a_mn_major, int b_mn_major, int c_is_f32, int accumulate,
+                              float alpha, int* status, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (a_batch % 8) || (b_batch % 8))
+    return -2;
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int bn = (N > 128) ? 256 : 128;
+  CUtensorMap mapA, mapB;
+  int r;
+  if (!a_mn_major) r = make_map(&mapA, A, K, M, batch, lda, a_batch, BM);
+  else             r = make_map(&mapA, A, M, K, batch, lda, a_batch, BK);
+  if (r) return 100 + r;
+  if (!b_mn_major) r = make_map(&mapB, B, K, N, batch, ldb, b_batch, bn);
+  else             r = make_map(&mapB, B, N, K, batch, ldb, b_batch, BK);
+  if (r) return 200 + r;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.ldc = ldc; p.c_batch = c_batch; p.c_is_f32 = c_is_f32; p.accumulate = accumulate; p.alpha = alpha;
+  p.C = C; p.status = status;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + bn - 1) / bn;
+  long long tiles = (long long)batch * p.tiles_m * p.tiles_n;
+  int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
+  int grid = (int)(tiles < cap ? tiles : cap);
+  if (bn == 256) {
+    if (!g_attr_set[0]) {
+      cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
+      g_attr_set[0] = true;
+    }
+    gemm_bf16_kernel<256><<<grid, 192, SmemLayout<256>::TOTAL, stream>>>(mapA, mapB, p);
+  } else {
+    if (!g_attr_set[1]) {
+      cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
+      g_attr_set[1] = true;
+    }
+    gemm_bf16_kernel<128><<<grid, 192, SmemLayout<128>::TOTAL, stream>>>(mapA, mapB, p);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

@@ -1,0 +1,149 @@
+"""Matrix products on the tcgen05 GEMM kernel (``csrc/gemm_tcgen05.cu``), differentiable to any order.
+
+``mm(a, b, ta, tb)`` computes ``op(a) @ op(b)`` for 2-D or batched 3-D operands.  On a CUDA device
+with bf16 operands the product runs on the hand-written kernel for every transposition (the kernel
+reads K-major and MN-major tiles alike, so no operand is ever transposed in memory); elsewhere
+(CPU, f32 test configurations) it is ``torch.matmul``.  The backward of a product is two more
+products issued through the same differentiable entry point, so the meta-gradient (the outer
+gradient through the inner step, reference src/ttt/chunk_scan.py:604-625) differentiates it again
+without special code.
+
+Weights follow the reference layout ``[in, out]`` applied as ``x @ w`` (reference
+src/ttt/model.py:137-148).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+_FORCE_TORCH = False          # tests flip this to compare the kernel against torch.matmul
+LAUNCHES = 0                  # kernel launches issued by this module (bench accounting)
+
+
+def _kernel_ok(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and not _FORCE_TORCH
+
+
+def _as_rows(x: torch.Tensor) -> torch.Tensor:
+    """A view (or copy) whose last dim is contiguous, whose row/batch strides are multiples of 8
+    elements and whose base is 16-byte aligned: what a tensor map accepts."""
+    ok = x.stride(-1) == 1 and x.stride(-2) % 8 == 0 and x.data_ptr() % 16 == 0
+    if x.dim() == 3:
+        ok = ok and (x.stride(0) % 8 == 0 or x.shape[0] == 1)
+        # rows of one batch entry must not alias rows of the next in a way a 3-D map cannot express
+        ok = ok and x.stride(-2) >= x.shape[-1]
+    return x if ok else x.contiguous()
+
+
+def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: torch.dtype = torch.bfloat16,
+             out: Optional[torch.Tensor] = None, accumulate: bool = False, alpha: float = 1.0,
+             max_ctas: int = 0) -> torch.Tensor:
+    """One kernel launch, no autograd.  ``a``: ``[.., M, K]`` (``[.., K, M]`` with ``ta``), ``b``:
+    ``[.., K, N]`` (``[.., N, K]`` with ``tb``); 2-D or 3-D with equal batch; a 2-D operand is shared by
+    every batch entry of a 3-D one.  ``out`` (+ ``accumulate``) writes / adds into an existing tensor."""
+    global LAUNCHES
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, (a.dtype, b.dtype)
+    a, b = _as_rows(a), _as_rows(b)
+    M, K = (a.shape[-1], a.shape[-2]) if ta else (a.shape[-2], a.shape[-1])
+    Kb, N = (b.shape[-1], b.shape[-2]) if tb else (b.shape[-2], b.shape[-1])
+    assert K == Kb, f"contraction mismatch {tuple(a.shape)} ta={ta} x {tuple(b.shape)} tb={tb}"
+    batch = 1
+    if a.dim() == 3 or b.dim() == 3:
+        batch = a.shape[0] if a.dim() == 3 else b.shape[0]
+        if a.dim() == 3 and b.dim() == 3:
+            assert a.shape[0] == b.shape[0]
+    if a.dim() == 2 and b.dim() == 3 and not ta and not tb and False:
+        pass
+    a_batch = a.stride(0) if a.dim() == 3 else 0
+    b_batch = b.stride(0) if b.dim() == 3 else 0
+    if batch > 1 and a.dim() == 3 and b.dim() == 2 and not ta and a.is_contiguous():
+        # shared right operand: fold the batch into the rows
+        res = gemm_raw(a.reshape(-1, a.shape[-1]), b, False, tb, out_dtype,
+                       None if out is None else out.view(-1, out.shape[-1]), accumulate, alpha, max_ctas)
+        return res.view(batch, M, N)
+    if batch > 1 and (a_batch == 0 or b_batch == 0):
+        # a shared 2-D operand with a batched partner: a zero batch stride is a legal tensor-map stride
+        # only as an explicit expand; materialise the small side.
+        if a.dim() == 2:
+            a = a.unsqueeze(0).expand(batch, -1, -1).contiguous(); a_batch = a.stride(0)
+        if b.dim() == 2:
+            b = b.unsqueeze(0).expand(batch, -1, -1).contiguous(); b_batch = b.stride(0)
+    shape = (M, N) if batch == 1 and a.dim() == 2 and b.dim() == 2 else (batch, M, N)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape == torch.Size(shape) and out.stride(-1) == 1, (out.shape, shape)
+    c_batch = out.stride(0) if out.dim() == 3 else 0
+    st = _lib.status_tensor(a.device)
+    rc = _lib.lib().dttt_gemm_bf16(
+        ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+        M, N, K, batch, a.stride(-2), b.stride(-2), out.stride(-2), a_batch, b_batch, c_batch,
+        1 if ta else 0, 0 if tb else 1, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+        float(alpha), ctypes.c_void_p(st.data_ptr()), max_ctas, ctypes.c_void_p(_lib.stream_ptr()))
+    if rc != 0:
+        raise _lib.KernelError(f"dttt_gemm_bf16 launch failed rc={rc} for M={M} N={N} K={K} batch={batch} "
+                               f"ta={ta} tb={tb}")
+    LAUNCHES += 1
+    return out
+
+
+def _torch_mm(a, b, ta, tb, out_dtype):
+    x = a.transpose(-1, -2) if ta else a
+    y = b.transpose(-1, -2) if tb else b
+    if out_dtype is not None and out_dtype != x.dtype and x.dtype == torch.bfloat16:
+        return torch.matmul(x.float(), y.float()).to(out_dtype)
+    r = torch.matmul(x, y)
+    return r if out_dtype is None or r.dtype == out_dtype else r.to(out_dtype)
+
+
+class _MM(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, ta, tb, out_dtype):
+        ctx.save_for_backward(a, b)
+        ctx.ta, ctx.tb = ta, tb
+        return gemm_raw(a, b, ta, tb, out_dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        ta, tb = ctx.ta, ctx.tb
+        g = g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)
+        ga = gb = None
+        # y = op(a) op(b);  d op(a) = g op(b)^T,  d op(b) = op(a)^T g
+        if ctx.needs_input_grad[0]:
+            ga = mm(b, g, tb, True) if ta else mm(g, b, False, not tb)
+            if ga.dim() > a.dim():
+                ga = ga.sum(0)
+        if ctx.needs_input_grad[1]:
+            gb = mm(g, a, True, ta) if tb else mm(a, g, not ta, False)
+            if gb.dim() > b.dim():
+                gb = gb.sum(0)
+        return ga, gb, None, None, None
+
+
+def mm(a: torch.Tensor, b: torch.Tensor, ta: bool = False, tb: bool = False,
+       out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``op(a) @ op(b)``, differentiable (to any order); see the module docstring."""
+    if _kernel_ok(a) and _kernel_ok(b) and a.dim() >= 2 and b.dim() >= 2 and a.dim() <= 3 and b.dim() <= 3:
+        od = out_dtype or torch.bfloat16
+        if torch.is_grad_enabled() and (a.requires_grad or b.requires_grad):
+            return _MM.apply(a, b, ta, tb, od)
+        return gemm_raw(a, b, ta, tb, od)
+    return _torch_mm(a, b, ta, tb, out_dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w (+ bias)`` with ``w [in, out]``; ``x`` of any leading shape."""
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if w.dtype != x2.dtype:
+        w = w.to(x2.dtype)
+    y = mm(x2, w)
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    return y.view(*lead, w.shape[-1])
