@@ -1,0 +1,160 @@
+"""Chunk-window attention.
+
+Geometry (reference ``src/ttt/attention.py:5-10``): a chunk of ``C`` query slots attends to the clean
+keys of the previous ``W`` chunks plus the keys of its own chunk; inside the own chunk the pattern is
+``full`` (bidirectional), ``causal``, ``split:K`` or ``block:b``; the sub-block read adds the chunk's
+clean keys as a second own-chunk key set (``[C, 2C]`` pattern).  Window slots that precede the sequence
+start, or lie beyond ``reach`` chunks, are invalid.  The window is stored oldest chunk first, so the
+valid keys are always a *suffix* of the window followed by the own chunk: the fast path slices that
+suffix instead of masking, and batches all calls that share a valid length.
+
+``attend`` is the general entry point (explicit key validity, exact semantics of the reference's
+``attend_xla``, ``attention.py:181-201``).  ``attend_window`` is what the model calls.
+"""
+from __future__ import annotations
+
+from functools import lru_cache
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import reference as ref
+from .functional import staged, use_kernels
+
+
+# ------------------------------------------------------------------ geometry
+def window_gather(x: torch.Tensor, chunk: int, window: int, prev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [B, T, ...]`` -> ``[B, nc, window*chunk, ...]``: for chunk ``c`` the tokens of chunks
+    ``[c-window, c)``; ``prev [B, window*chunk, ...]`` is what precedes ``x`` (zeros when absent)."""
+    B, T = x.shape[:2]
+    nc, WC = T // chunk, window * chunk
+    if WC == 0:
+        return x.new_zeros((B, nc, 0) + tuple(x.shape[2:]))
+    pad = x.new_zeros((B, WC) + tuple(x.shape[2:])) if prev is None else prev.to(x.dtype)
+    xp = torch.cat([pad, x], dim=1)
+    idx = (torch.arange(nc, device=x.device)[:, None] * chunk + torch.arange(WC, device=x.device)[None, :])
+    return xp[:, idx]
+
+
+def valid_window_chunks(chunk_idx: int, window: int, reach: Optional[int]) -> int:
+    """How many of the newest window chunks chunk ``chunk_idx`` may see."""
+    n = min(chunk_idx, window)
+    return n if reach is None else min(n, reach)
+
+
+def key_validity(chunk_idx, chunk: int, window: int, reach=None, device=None) -> torch.Tensor:
+    """``[(window+1)*chunk]`` bool, as reference attention.py:109-120."""
+    j = torch.arange(window * chunk, device=device)
+    win = (chunk_idx - window + j // chunk) >= 0
+    if reach is not None:
+        win = win & (j // chunk >= window - reach)
+    return torch.cat([win, torch.ones(chunk, dtype=torch.bool, device=device)])
+
+
+def key_validity_all(nc: int, chunk: int, window: int, first: int = 0, reach=None, device=None) -> torch.Tensor:
+    return torch.stack([key_validity(first + c, chunk, window, reach, device) for c in range(nc)])
+
+
+@lru_cache(maxsize=64)
+def _own_mask_cpu(chunk: int, own: str) -> Optional[torch.Tensor]:
+    if own == "full":
+        return None
+    i = torch.arange(chunk)[:, None]
+    j = torch.arange(chunk)[None, :]
+    if own == "causal":
+        return j <= i
+    if own.startswith("split:"):
+        K = int(own.split(":")[1])
+        return (j < K) | ((i >= K) & (j <= i))
+    if own.startswith("block:"):
+        b = int(own.split(":")[1])
+        return (j // b) <= (i // b)
+    raise ValueError(f"own-chunk mode {own!r}")
+
+
+def own_mask_matrix(chunk: int, own: str, device=None) -> Optional[torch.Tensor]:
+    """``[C, C]`` bool own-chunk pattern (None for ``full``); reference attention.py:132-150."""
+    m = _own_mask_cpu(chunk, own)
+    return None if m is None else m.to(device)
+
+
+def read_mask_matrix(chunk: int, block: int, device=None) -> torch.Tensor:
+    """``[C, 2C]`` bool: the sub-block read over ``[clean own keys, noisy own keys]`` (attention.py:153-159)."""
+    i = torch.arange(chunk, device=device)[:, None] // block
+    j = torch.arange(chunk, device=device)[None, :] // block
+    return torch.cat([j < i, j == i], dim=1)
+
+
+# ------------------------------------------------------------------ general attention
+def _sdpa_fast(q, k, v, scale, causal_lower_right: bool):
+    """q [n, C, nh, d], k/v [n, K, nkv, d], every key valid; full pattern or causal aligned to the end of
+    the key axis (query i sees keys j <= i + K - C)."""
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if causal_lower_right and k.shape[1] != q.shape[1]:
+        from torch.nn.attention.bias import causal_lower_right as clr
+        o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=clr(q.shape[1], k.shape[1]), scale=scale,
+                                           enable_gqa=True)
+    else:
+        o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal_lower_right, scale=scale, enable_gqa=True)
+    return o.transpose(1, 2)
+
+
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_valid: Optional[torch.Tensor], scale: float,
+           own_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Exact masked attention, any order of differentiation (``ops.reference.attend``)."""
+    return ref.attend(q, k, v, key_valid, scale, own_mask)
+
+
+def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_win: torch.Tensor, v_win: torch.Tensor,
+                  n_valid: int, chunk: int, scale: float, own: str = "full", inner: bool = False,
+                  own_mask: Optional[torch.Tensor] = None,
+                  extra_own: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """One batch of chunk calls that all see the newest ``n_valid`` window chunks.
+
+    ``q [n, Cq, nh, d]``; ``k_own/v_own [n, Cq, nkv, d]``; ``k_win/v_win [n, Wc*C, nkv, d]`` (oldest first);
+    ``own``: the own-chunk pattern by name, or pass an explicit ``own_mask [Cq, M]``;
+    ``extra_own``: the chunk's clean K/V placed between the window and the own keys (sub-block read).
+    ``inner``: this call's backward will itself be differentiated.
+    """
+    WC = k_win.shape[1]
+    kw, vw = k_win[:, WC - n_valid * chunk:], v_win[:, WC - n_valid * chunk:]
+    parts_k = [kw] + ([extra_own[0].to(k_own.dtype)] if extra_own is not None else []) + [k_own]
+    parts_v = [vw] + ([extra_own[1].to(v_own.dtype)] if extra_own is not None else []) + [v_own]
+    K = torch.cat(parts_k, dim=1) if len(parts_k) > 1 or n_valid else k_own
+    V = torch.cat(parts_v, dim=1) if len(parts_v) > 1 or n_valid else v_own
+    if own_mask is None and own != "full":
+        own_mask = own_mask_matrix(q.shape[1], own, q.device)
+    simple = own_mask is None or (own == "causal" and extra_own is None)
+    if use_kernels(q) and simple:
+        causal = own_mask is not None
+        spec = (_fast_fwd, _fast_bwd, _ref_for_staged)
+        return staged(spec, (q, K, V), (scale, causal))
+    return ref.attend(q, K, V, None, scale, own_mask)
+
+
+# staged execution: library/hand-written forward + first-order backward, reference for the second order
+def _ref_for_staged(q, K, V, scale, causal):
+    om = own_mask_matrix(q.shape[1], "causal", q.device) if causal else None
+    return ref.attend(q, K, V, None, scale, om)
+
+
+def _fast_fwd(q, K, V, scale, causal):
+    from . import kernels
+    if kernels.available("attention"):
+        o, lse = kernels.attention_fwd(q, K, V, scale, causal)
+        return o, (o, lse)
+    with torch.no_grad():
+        o = _sdpa_fast(q, K, V, scale, causal)
+    return o, ()
+
+
+def _fast_bwd(g, tensors, saved, needs, scale, causal):
+    from . import kernels
+    q, K, V = tensors
+    if kernels.available("attention") and saved:
+        return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, causal)
+    with torch.enable_grad():
+        qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))
+        o = _sdpa_fast(qq, kk, vv, scale, causal)
+        return torch.autograd.grad(o, (qq, kk, vv), g)

@@ -1,0 +1,677 @@
+"""The training objective over a batch: chunk-parallel prefix, then a sequential pass over chunks for the
+suffix with the KV window and the per-sequence memory (fast weight or GDN state) carried along.
+
+Per chunk the suffix runs three forwards on the same chunk, key set and memory (reference
+``src/ttt/chunk_scan.py:6-23``):
+
+    A  outer-masked -> CART-weighted CE against the clean tokens          (the loss)
+    B  clean        -> this chunk's K/V, shifted into the window
+    C  inner        -> gradient w.r.t. W, one clipped step                 (the write)
+
+and the outer gradient flows through every write.  Memory scheduling is explicit: each prefix layer
+and each chunk step is a *recompute region* (``regions.region``): its inputs are kept, its forward runs
+without a graph, and its backward re-runs it with the graph (the inner step then with
+``create_graph``) — the reference's remat scan (``src/ttt/remat_scan.py``, ``model.py:588-592``,
+``chunk_scan.py:730-735``) as per-layer / per-chunk activation checkpointing.  Segments
+(``segment_chunks``) bound the prefix transients for long sequences and are where
+``truncate_fast_weight`` cuts the meta-gradient (``chunk_scan.py:39-49``).
+"""
+from __future__ import annotations
+
+import dataclasses as dc
+from typing import Dict, List, NamedTuple, Optional, Tuple
+
+import torch
+
+from ..models.blocks import CLEAN, INNER, OUTER, Net
+from ..ops import attention as A
+from ..ops import ce as CE
+from ..ops import functional as Fn
+from ..ops import reference as ref
+from ..utils import rng
+from . import inner as IN
+from . import objective as OBJ
+from .regions import region
+
+
+class Batch(NamedTuple):
+    input_ids: torch.Tensor                          # [B, T]
+    loss_mask: Optional[torch.Tensor] = None         # [B, T] bool
+    position_ids: Optional[torch.Tensor] = None      # [B, T]
+    inner_mask: Optional[torch.Tensor] = None        # [B, T] bool: host-chosen inner targets
+    inner_perm: Optional[torch.Tensor] = None        # [B, T] physical order of the inner stream (split task)
+    outer_t: Optional[torch.Tensor] = None           # [B] explicit noise level per sequence
+
+
+@dc.dataclass(frozen=True)
+class LossConfig:
+    """Everything ``loss_fn`` needs that is not in ``ModelConfig`` (reference chunk_scan.py:81-143)."""
+    time_reweighting: str = "cart"
+    cart_p: float = 0.1
+    cart_window: int = 512
+    outer_t: float = -1.0
+    outer_shift: bool = False
+    inner_lr: float = 1.0
+    inner_clip: float = 1.0
+    inner_lr_warmup_steps: int = 0
+    inner_mask_range: Tuple[float, float] = (0.5, 1.0)
+    inner_mask_ratio: float = -1.0
+    second_order: bool = True
+    remat_levels: int = 1
+    remat_prefix: bool = False
+    prefix_remat_levels: int = 1
+    segment_chunks: int = 0
+    truncate_fast_weight: bool = False
+    inner_views: int = 1
+    inner_view_mode: str = "complement"
+    inner_views_sequential: bool = False
+    inner_cart: bool = False
+    inner_mask_span: float = 0.0
+    inner_update: str = "sgd"
+    inner_task: str = "mask"
+    inner_from_outer: bool = False
+    inner_feat: str = "off"
+    inner_feat_weight: float = 1.0
+    inner_update_frac: float = 1.0
+    write: IN.WriteConfig = IN.WriteConfig()
+    write_plan: Tuple[int, ...] = ()
+    distill: bool = False
+    distill_t_range: Tuple[float, float] = (0.1, 0.3)
+    distill_weight: float = 1.0
+    distill_topk: int = 64
+    distill_meta: bool = True
+    distill_warmup_steps: int = 0
+    mtp: bool = False
+    mtp_weight: float = 0.3
+    inner_mtp_weight: float = 0.5
+    inner_context_frac: float = 0.5
+    no_write: bool = False
+    write_off: bool = False
+    aux_causal_weight: float = 0.0
+    per_sequence: bool = False
+    per_token: bool = False
+    score_from_chunk: int = 0
+    reread_chunks: int = 0
+    window_drop: float = 0.0
+    window_drop_until: int = 0
+    self_prior: float = 0.0
+    outer_views: int = 1
+    fused_ce_block: int = 8192
+    attn_chunk_batch: int = 2
+    compute_dtype: str = "bfloat16"
+    remat: bool = True                    # False: keep every activation (small models, tests)
+
+
+def _pad_left_shift(x: torch.Tensor, k: int) -> torch.Tensor:
+    """``y[:, i] = x[:, i + k]``, zero beyond the end (``jnp.pad(x[:, k:], ((0,0),(0,k)))``)."""
+    return torch.cat([x[:, k:], torch.zeros_like(x[:, :k])], dim=1)
+
+
+def shift_slots(x: torch.Tensor, k: int):
+    """``(y, valid)``: ``y[:, i] = x[:, i + k]`` along dim 1, the edge slot repeated where out of range."""
+    C = x.shape[1]
+    i = torch.arange(C, device=x.device)
+    if k == 0:
+        return x, torch.ones(C, dtype=torch.bool, device=x.device)
+    if k > 0:
+        return torch.cat([x[:, k:], x[:, -1:].expand(-1, k, *x.shape[2:])], 1), i <= C - 1 - k
+    return torch.cat([x[:, :1].expand(-1, -k, *x.shape[2:]), x[:, :k]], 1), i >= -k
+
+
+def make_feat_target(hc: torch.Tensor, tgt_idx: torch.Tensor) -> torch.Tensor:
+    t = torch.gather(hc.float(), 1, tgt_idx.long()[..., None].expand(-1, -1, hc.shape[-1]))
+    return (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-6)).detach()
+
+
+def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfig):
+    """Batch loss and diagnostics.  ``key``: ``[2]`` (training) or row-wise ``[B, 2]`` (evaluation)."""
+    mc = net.cfg
+    use_gdn = mc.memory == "gdn"
+    if use_gdn:
+        if cfg.inner_from_outer or cfg.write_off or cfg.distill or cfg.mtp or cfg.inner_feat != "off":
+            raise ValueError("memory gdn: no inner stream (inner_from_outer / write_off / distill / mtp / inner_feat do not apply)")
+        cfg = dc.replace(cfg, no_write=True)
+    ids = batch.input_ids.long()
+    dev = ids.device
+    B, T = ids.shape
+    C, Wn, S, F_ = mc.chunk_size, mc.window_chunks, mc.suffix_len, mc.fast_len
+    if T % C:
+        raise ValueError(f"seq_len {T} not a multiple of chunk_size {C}")
+    nc = T // C
+    pos = torch.arange(T, device=dev)[None].expand(B, T) if batch.position_ids is None else batch.position_ids.long()
+    key = key.to(dev)
+    train_graph = torch.is_grad_enabled()
+    use_regions = cfg.remat and train_graph
+
+    # ---- keys (the split order is a contract, reference chunk_scan.py:229-237)
+    if key.dim() == 2:
+        ks3 = rng.split(key, 3)
+        key_mask, key_inner = ks3[:, 1], ks3[:, 2]
+        inner_keys = rng.split(key_inner, nc).transpose(0, 1)                       # [nc, B, 2]
+    else:
+        ks3 = rng.split(key, 3)
+        key_mask, key_inner = ks3[1], ks3[2]
+        inner_keys = rng.split(key_inner, nc * B).reshape(nc, B, 2)
+    fold = lambda k, v: rng.fold_in(k, v)
+
+    # ---- outer objective
+    loss_mask = batch.loss_mask
+    if cfg.score_from_chunk:
+        scored = (torch.arange(T, device=dev) >= cfg.score_from_chunk * C)[None]
+        loss_mask = scored.expand(B, T) if loss_mask is None else (loss_mask.bool() & scored)
+    t_in = batch.outer_t
+    if cfg.outer_t >= 0:
+        t_in = torch.full((B,), cfg.outer_t, dtype=torch.float32, device=dev)
+    kernel = ref.cart_kernel(cfg.cart_p, cfg.cart_window, dev) if (cfg.time_reweighting == "cart" or cfg.inner_cart) else None
+
+    def noisy_view(k):
+        x_t, t, t_mask = OBJ.q_sample(k, ids, loss_mask, mc.mask_token_id, t=t_in)
+        w_raw = OBJ.time_weights(cfg.time_reweighting, t, t_mask, kernel)
+        if cfg.outer_shift:
+            m_outer = _pad_left_shift(t_mask, 1)
+            weight = _pad_left_shift(w_raw, 1) * m_outer.float()
+        else:
+            m_outer, weight = t_mask, w_raw * t_mask.float()
+        return x_t, t, t_mask, w_raw, m_outer, weight
+
+    x_t, t, t_mask, w_raw, m_outer, weight = noisy_view(key_mask)
+    tgt_outer = _pad_left_shift(ids, 1) if cfg.outer_shift else ids
+    VO = cfg.outer_views
+    if VO < 1:
+        raise ValueError("outer_views >= 1")
+    if VO > 1 and (cfg.distill or cfg.mtp or cfg.reread_chunks or cfg.inner_from_outer or cfg.per_sequence
+                   or cfg.per_token or mc.read_block):
+        raise ValueError("outer_views > 1 is a training option: not with distill / mtp / reread_chunks / inner_from_outer / "
+                         "per-sequence or per-token scores / read_block")
+    extra_views = [noisy_view(fold(key_mask, v)) for v in range(1, VO)]
+    if (cfg.mtp or cfg.distill) and (cfg.no_write or cfg.inner_from_outer or cfg.inner_task == "split" or cfg.inner_views != 1):
+        raise ValueError("distill / mtp need a single-view mask or causal write (not no_write / inner_from_outer / split)")
+    if cfg.write_off and (cfg.no_write or cfg.inner_from_outer or cfg.distill or cfg.mtp or cfg.inner_views != 1
+                          or cfg.inner_feat != "off"):
+        raise ValueError("write_off keeps one plain inner stream (not no_write / inner_from_outer / distill / mtp / views / feat)")
+    if cfg.aux_causal_weight > 0 and (cfg.no_write or cfg.inner_from_outer):
+        raise ValueError("aux_causal_weight needs an inner stream (not no_write / inner_from_outer)")
+    if cfg.write_plan and (not cfg.write.plain or cfg.inner_task != "causal" or cfg.inner_views != 1 or cfg.no_write
+                           or cfg.write_off or cfg.inner_from_outer or cfg.reread_chunks or min(cfg.write_plan) < 0):
+        raise ValueError("write_plan needs the plain causal write (one view, a write, no re-read) and steps >= 0")
+    if not cfg.write.plain:
+        cfg.write.check(C)
+        if (cfg.inner_task != "causal" or cfg.inner_views != 1 or cfg.no_write or cfg.inner_from_outer or cfg.write_off
+                or cfg.distill or cfg.mtp or cfg.inner_feat != "off" or cfg.inner_update_frac < 1.0):
+            raise ValueError("the write schemes need the plain causal write (inner_task causal, one view, a write; "
+                             "not with write_off / distill / mtp / inner_feat / inner_update_frac)")
+        if cfg.write.kvb_weight > 0 and not net.cw.has("inner_kvb_value.weight"):
+            raise ValueError("inner_kvb_weight needs a model with inner_kvb_head")
+    if cfg.self_prior > 0 and (use_gdn or cfg.no_write or cfg.write_off or cfg.inner_from_outer or cfg.write_plan
+                               or cfg.reread_chunks or cfg.inner_views != 1):
+        raise ValueError("self_prior reads a chunk after its own write: it needs a write (TTT, one view, no write plan / "
+                         "re-read)")
+    base_key = key if key.dim() == 1 else key[0]
+    reach = mc.reach
+    if cfg.window_drop > 0:
+        drop = bool(rng.uniform(fold(base_key, 7), ()) < cfg.window_drop) and step < cfg.window_drop_until
+        reach = 0 if drop else (Wn if mc.reach is None else mc.reach)
+    sp_flags = None
+    if cfg.self_prior > 0:
+        sp_flags = (rng.uniform(fold(key, 8), ()) if key.dim() == 2 else rng.uniform(fold(key, 8), (B,))) < cfg.self_prior
+    if cfg.mtp:
+        if not cfg.outer_shift or cfg.inner_task != "causal":
+            raise ValueError("mtp needs outer_shift and the causal write")
+        if not net.cw.has("mtp_head.weight"):
+            raise ValueError("mtp needs a model with mtp_head")
+        tgt_mtp = _pad_left_shift(ids, 2)
+        m_mtp = _pad_left_shift(t_mask, 2)
+        w_mtp = _pad_left_shift(w_raw, 2) * m_mtp.float()
+    else:
+        tgt_mtp = m_mtp = w_mtp = None
+
+    # ---- re-read layout (evaluation; reference chunk_scan.py:340-372)
+    T0, nc0, n_rr = T, nc, cfg.reread_chunks
+    host_mask, host_perm = batch.inner_mask, batch.inner_perm
+    if n_rr:
+        if cfg.segment_chunks <= 0 or n_rr % cfg.segment_chunks:
+            raise ValueError("reread_chunks needs segment_chunks > 0 dividing it (the window reset is a segment boundary)")
+        if cfg.distill:
+            raise ValueError("reread_chunks with distill is not supported")
+        nC = n_rr * C
+        dup = lambda a: torch.cat([a[:, :nC], a], dim=1)
+        zero = lambda a: torch.cat([torch.zeros_like(a[:, :nC]), a], dim=1)
+        x_t = torch.cat([ids[:, :nC], x_t], dim=1)
+        ids, pos, m_outer, weight, tgt_outer = dup(ids), dup(pos), zero(m_outer), zero(weight), dup(tgt_outer)
+        if cfg.mtp:
+            tgt_mtp, m_mtp, w_mtp = dup(tgt_mtp), zero(m_mtp), zero(w_mtp)
+        if host_mask is not None:
+            host_mask = dup(host_mask)
+        if host_perm is not None:
+            host_perm = torch.cat([host_perm[:, :nC], host_perm + nC], dim=1)
+        kf = fold(key_inner, 1)
+        rr_inner = rng.split(kf, n_rr).transpose(0, 1) if key_inner.dim() == 2 else rng.split(kf, n_rr * B).reshape(n_rr, B, 2)
+        inner_keys = torch.cat([rr_inner, inner_keys], dim=0)
+        T, nc = T + nC, nc + n_rr
+    eff = (lambda c: c - n_rr * (c >= n_rr)) if n_rr else (lambda c: c)
+    plan = (tuple(cfg.write_plan) + (1,) * nc)[:nc] if cfg.write_plan else None
+
+    # ---- the inner (write) task: what stream C sees and predicts (reference chunk_scan.py:375-427)
+    ids_c = OBJ.to_chunks(ids, C)                                                 # [nc, B, C]
+    pos_c = OBJ.to_chunks(pos, C)
+    own_inner = "full"
+    pos_in_c, pos_q_c, perm_c = pos_c, None, None
+    V = cfg.inner_views
+    if cfg.inner_task == "mask":
+        if host_mask is not None:
+            if V != 1:
+                raise ValueError("host-side inner masks support one view")
+            inner_mask_c = OBJ.to_chunks(host_mask.bool(), C)
+            x_inner_c = torch.where(inner_mask_c, torch.full_like(ids_c, mc.mask_token_id), ids_c)
+        else:
+            x_inner_c, inner_mask_c = OBJ.inner_masks(inner_keys, ids_c, cfg.inner_mask_ratio, cfg.inner_mask_range,
+                                                      mc.mask_token_id, mc.pad_token_id, V, cfg.inner_mask_span,
+                                                      cfg.inner_view_mode)             # [nc, B, (V,) C]
+        target_c = ids_c
+        if cfg.inner_cart:
+            shp = inner_mask_c.shape
+            flat_m = inner_mask_c.reshape(-1, C)
+            inner_mask_c = (OBJ.cart_weights(1.0 - flat_m.float(), kernel) * flat_m.float()).reshape(shp)
+    else:
+        if V != 1:
+            raise ValueError("causal / split inner tasks are single-view")
+        if cfg.inner_task == "split":
+            if host_perm is None:
+                raise ValueError("inner_task split needs Batch.inner_perm (host-side, data.masks.split_perm)")
+            perm_c = OBJ.to_chunks(host_perm.long(), C)
+            K = int(round(cfg.inner_context_frac * C))
+            own_inner = f"split:{K}"
+        else:
+            perm_c = torch.arange(T, device=dev).reshape(nc, 1, C).expand(nc, B, C)
+            K = 0
+            own_inner = "causal"
+        x_inner_c = torch.gather(ids[None].expand(nc, B, T), 2, perm_c)
+        pos_in_c = torch.gather(pos[None].expand(nc, B, T), 2, perm_c)
+        target_c = torch.cat([x_inner_c[:, :, 1:], x_inner_c[:, :, -1:]], dim=2)
+        pos_q_c = torch.cat([pos_in_c[:, :, 1:], pos_in_c[:, :, -1:]], dim=2)
+        slot = torch.arange(C, device=dev)
+        inner_mask_c = ((slot >= max(K - 1, 0)) & (slot <= C - 2))[None, None].expand(nc, B, C)
+    if cfg.inner_feat != "off":
+        if cfg.no_write or cfg.inner_from_outer:
+            raise ValueError("inner_feat needs the inner stream (not no_write / inner_from_outer)")
+        if not net.cw.has("inner_feat_head.weight"):
+            raise ValueError("inner_feat needs a model with inner_feat_head")
+        i = torch.arange(C, device=dev)
+        if cfg.inner_task == "mask":
+            tgt_idx_c = i[None, None].expand(nc, B, C)
+        elif cfg.inner_task == "causal":
+            tgt_idx_c = torch.clamp(i + 1, max=C - 1)[None, None].expand(nc, B, C)
+        else:
+            local = perm_c - (torch.arange(nc, device=dev) * C)[:, None, None]
+            tgt_idx_c = torch.cat([local[:, :, 1:], local[:, :, -1:]], dim=2)
+    else:
+        tgt_idx_c = None
+
+    # ---- the distillation teacher stream (reference chunk_scan.py:437-452)
+    if cfg.distill:
+        kT = fold(key_inner, 2)
+        keys_T = rng.split(kT, nc).transpose(0, 1) if key_inner.dim() == 2 else rng.split(kT, nc * B).reshape(nc, B, 2)
+        x_teacher_c, m_teacher_c = OBJ.inner_masks(keys_T, ids_c, -1.0, cfg.distill_t_range, mc.mask_token_id, mc.pad_token_id)
+    else:
+        x_teacher_c = m_teacher_c = None
+    s_S = 1 if cfg.inner_task == "causal" else 0
+    s_T = 1 if cfg.outer_shift else 0
+    if cfg.mtp:
+        slot = torch.arange(C, device=dev)
+        mtp_tgt_c = torch.cat([x_inner_c[:, :, 2:], x_inner_c[:, :, -2:]], dim=2)
+        mtp_mask_c = (slot <= C - 3)[None, None].expand(nc, B, C).float()
+    else:
+        mtp_tgt_c = mtp_mask_c = None
+
+    # ---- segments
+    n_seg_chunks = cfg.segment_chunks or nc
+    if nc % n_seg_chunks:
+        raise ValueError(f"{nc} chunks not a multiple of segment_chunks {n_seg_chunks}")
+    if n_seg_chunks < Wn and n_seg_chunks < nc:
+        raise ValueError(f"segment_chunks {n_seg_chunks} < window_chunks {Wn}: the carried window would be short")
+    n_seg = nc // n_seg_chunks
+    T_seg = n_seg_chunks * C
+    nkv, d = mc.num_key_value_heads, mc.head_dim
+    Lp = mc.prefix_len
+    cdt = net.dtype
+    lr_now = IN.inner_lr(step, cfg.inner_lr, cfg.inner_lr_warmup_steps)
+    distill_w = cfg.distill_weight
+    if cfg.distill and cfg.distill_warmup_steps > 0:
+        distill_w = cfg.distill_weight * min(1.0, step / cfg.distill_warmup_steps)
+    clean_prime = (not cfg.write.plain) and cfg.write.kvb_weight > 0 and cfg.write.kvb_value == "clean"
+    rb = mc.read_block
+    if rb and cfg.distill:
+        raise ValueError("read_block: no distillation teacher stream")
+    clean_own = "full" if not rb else f"block:{rb}"
+    read_own = None if not rb else A.read_mask_matrix(C, rb, dev)
+    lm_w_of = net.lm_weight
+    fb = cfg.fused_ce_block
+    create_graph = train_graph and cfg.second_order
+
+    # ---- streams of the prefix: [outer, clean, inner views..., teacher, extra outer views...]
+    has_inner = not (cfg.no_write or cfg.inner_from_outer)
+    x_inner = None
+    if has_inner:
+        x_inner = [OBJ.from_chunks(x_inner_c)] if V == 1 else [OBJ.from_chunks(x_inner_c[:, :, v]) for v in range(V)]
+    streams = [x_t, ids] + (x_inner or []) + ([OBJ.from_chunks(x_teacher_c)] if cfg.distill else []) + [v[0] for v in extra_views]
+    ids_streams = torch.stack(streams, dim=1)                                       # [B, NS, T]
+    NS = ids_streams.shape[1]
+    n_inner = V if has_inner else 0
+    n_teacher = 1 if cfg.distill else 0
+    owns = ["full", "full"] + [own_inner] * n_inner + ["full"] * (n_teacher + VO - 1)
+    p_q_outer_full = pos + 1 if cfg.outer_shift else pos
+    if not cfg.outer_shift and (cfg.inner_task == "mask" or not has_inner):
+        pos_k_streams = pos[:, None].expand(B, NS, T)
+        pos_q_streams = None
+    else:
+        p_in = OBJ.from_chunks(pos_in_c) if cfg.inner_task != "mask" else pos
+        p_q = OBJ.from_chunks(pos_q_c) if (pos_q_c is not None and cfg.inner_task != "mask") else pos
+        pk = [pos, pos] + [p_in] * n_inner + [pos] * (n_teacher + VO - 1)
+        pq = [p_q_outer_full, pos] + [p_q] * n_inner + [p_q_outer_full] * (n_teacher + VO - 1)
+        pos_k_streams, pos_q_streams = torch.stack(pk, 1), torch.stack(pq, 1)
+
+    # ---- carries at the sequence start
+    kvp = None                                                                      # per prefix layer (k, v) tails
+    kvs = [(torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev), torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev))
+           for _ in range(S)]
+    if use_gdn:
+        mem = torch.zeros(B, S, mc.gdn_heads, mc.gdn_head_dim, mc.gdn_head_dim, dtype=torch.float32, device=dev)
+        W0 = None
+    else:
+        W0 = net.template_fast(B)
+        if train_graph:
+            W0 = [tuple(t.clone() for t in w) for w in W0]          # differentiable views of the template, materialised
+        mem = None
+    W = W0
+
+    acc = dict(ce_sum=0.0, mask_count=0.0, ce2_sum=0.0, mask2_count=0.0, distill_mass=0.0, aux=0.0)
+    inner_stats = IN.zero_stats(dev)
+    plan_ce = torch.zeros(2, device=dev)
+    ce_chunk = [None] * nc
+    mask_chunk = [None] * nc
+    ce_seq = torch.zeros(B, device=dev)
+    mask_seq = torch.zeros(B, device=dev)
+    ce_tok, mask_tok = [None] * nc, [None] * nc
+
+    views_w_c = [OBJ.to_chunks(v[5], C) for v in extra_views]
+    views_m_c = [OBJ.to_chunks(v[4], C) for v in extra_views]
+    weight_c, m_outer_c, tgt_outer_c = OBJ.to_chunks(weight, C), OBJ.to_chunks(m_outer, C), OBJ.to_chunks(tgt_outer, C)
+    if cfg.mtp:
+        tok2_c, wgt2_c, tm2_c = OBJ.to_chunks(tgt_mtp, C), OBJ.to_chunks(w_mtp, C), OBJ.to_chunks(m_mtp, C)
+
+    for g in range(n_seg):
+        sl = slice(g * T_seg, (g + 1) * T_seg)
+        first = eff(g * n_seg_chunks)
+        if n_rr and g * n_seg_chunks == n_rr:
+            kvp = None                                                              # the second pass restarts the window
+        # ---- prefix: all chunks of the segment, all streams, layer by layer
+        h = net.embed_tokens(ids_streams[:, :, sl])                                 # [B, NS, T_seg, H]
+        pk_seg = pos_k_streams[:, :, sl]
+        pq_seg = None if pos_q_streams is None else pos_q_streams[:, :, sl]
+        kvp_next = []
+        for l in range(Lp):
+            win = None if kvp is None else kvp[l]
+
+            def layer_fn(h_in, *w, _l=l, _has=win is not None, _pk=pk_seg, _pq=pq_seg, _first=first):
+                hh, tail = net.prefix_layer(_l, h_in, _pk, _pq, _first, (w[0], w[1]) if _has else None, owns, reach, rb)
+                return hh, tail[0], tail[1]
+            ins = (h,) + (tuple(win) if win is not None else ())
+            h, tk, tv = region(layer_fn, ins, use_regions)
+            kvp_next.append((tk, tv))
+        kvp = kvp_next if n_seg > 1 else None
+        hch = h.unflatten(2, (n_seg_chunks, C))                                     # [B, NS, ncs, C, H]
+
+        # ---- suffix: chunk by chunk
+        for j in range(n_seg_chunks):
+            c = g * n_seg_chunks + j
+            nv = A.valid_window_chunks(eff(c), Wn, reach)
+            ho, hc = hch[:, OUTER, j], hch[:, CLEAN, j]
+            hi = None
+            if has_inner:
+                hi = hch[:, INNER, j] if V == 1 else hch[:, INNER:INNER + V, j]
+            ht = hch[:, INNER + n_inner, j] if cfg.distill else None
+            hv = [hch[:, NS - VO + 1 + k, j] for k in range(VO - 1)]
+            p = pos_c[c]
+            consts = dict(
+                c=c, nv=nv, p=p, tok=tgt_outer_c[c], wgt=weight_c[c], tm=m_outer_c[c], im=inner_mask_c[c] if has_inner or cfg.inner_from_outer else None,
+                tgt=target_c[c], p_in=pos_in_c[c], p_q=None if pos_q_c is None else pos_q_c[c],
+                ti=None if tgt_idx_c is None else tgt_idx_c[c], mt=None if m_teacher_c is None else m_teacher_c[c],
+                tok2=tok2_c[c] if cfg.mtp else None, wgt2=wgt2_c[c] if cfg.mtp else None, tm2=tm2_c[c] if cfg.mtp else None,
+                mtp_t=None if mtp_tgt_c is None else mtp_tgt_c[c], mtp_m=None if mtp_mask_c is None else mtp_mask_c[c],
+                wv=[w[c] for w in views_w_c], tmv=[m[c] for m in views_m_c], k_c=None if plan is None else plan[c])
+
+            n_kv = 2 * S
+            mem_flat = [mem] if use_gdn else ([] if cfg.no_write else IN.flat(W))
+            n_mem = len(mem_flat)
+            dyn = [t for pair in kvs for t in pair] + mem_flat + [ho, hc] + ([hi] if hi is not None else []) \
+                + ([ht] if ht is not None else []) + hv
+
+            def step_fn(*ts, _k=consts, _n_kv=n_kv, _n_mem=n_mem, _has_hi=hi is not None, _has_ht=ht is not None):
+                kv_l = [(ts[2 * i], ts[2 * i + 1]) for i in range(S)]
+                o = _n_kv
+                memv = ts[o:o + _n_mem]; o += _n_mem
+                ho_, hc_ = ts[o], ts[o + 1]; o += 2
+                hi_ = ts[o] if _has_hi else None; o += int(_has_hi)
+                ht_ = ts[o] if _has_ht else None; o += int(_has_ht)
+                hv_ = ts[o:]
+                return _suffix_step(net, cfg, kv_l, memv, ho_, hc_, hi_, ht_, hv_, _k, W0, sp_flags, lr_now, distill_w,
+                                    create_graph, own_inner, clean_own, read_own, clean_prime, s_S, s_T, B, C, S, use_gdn)
+            outs = region(step_fn, tuple(dyn), use_regions)
+            kvs = [(outs[2 * i], outs[2 * i + 1]) for i in range(S)]
+            o = n_kv
+            if use_gdn:
+                mem = outs[o]; o += 1
+            elif not cfg.no_write:
+                W = IN.unflat(outs[o:o + n_mem]); o += n_mem
+            ce_sum_c, mask_count_c, ce2_c, m2_c, dmass_c, st_c, plan_c, ce_seq_c, mask_seq_c, ce_tok_c, mask_tok_c, aux_c = outs[o:o + 12]
+            acc["aux"] = acc["aux"] + aux_c
+            acc["ce_sum"] = acc["ce_sum"] + ce_sum_c
+            acc["mask_count"] = acc["mask_count"] + mask_count_c
+            acc["ce2_sum"] = acc["ce2_sum"] + ce2_c
+            acc["mask2_count"] = acc["mask2_count"] + m2_c
+            acc["distill_mass"] = acc["distill_mass"] + dmass_c
+            inner_stats = inner_stats + st_c.detach()
+            plan_ce = plan_ce + plan_c.detach()
+            ce_chunk[c], mask_chunk[c] = ce_sum_c.detach(), mask_count_c.detach()
+            ce_seq, mask_seq = ce_seq + ce_seq_c.detach(), mask_seq + mask_seq_c.detach()
+            ce_tok[c], mask_tok[c] = ce_tok_c, mask_tok_c
+        if cfg.truncate_fast_weight and not use_gdn and not cfg.no_write:
+            W = [tuple(t.detach() for t in w) for w in W]
+
+    main_loss = acc["ce_sum"] / (acc["mask_count"] + 1e-6)
+    mtp_loss = acc["ce2_sum"] / (acc["mask2_count"] + 1e-6)
+    loss = main_loss + cfg.mtp_weight * mtp_loss if cfg.mtp and cfg.mtp_weight > 0 else main_loss
+    n_in = nc * B
+    n_plan = sum(1 for k in cfg.write_plan[:nc] if k > 1)
+    st = dict(zip(IN.STAT_NAMES, inner_stats.unbind(0)))
+    if cfg.aux_causal_weight > 0:
+        # the inner stream's mean CE (before any write) as an auxiliary objective of the shared weights
+        loss = loss + cfg.aux_causal_weight * acc["aux"] / n_in
+    if use_gdn:
+        rms = torch.sqrt(mem.detach().pow(2).mean())
+        drift = {"ttt_drift_rel": rms, "ttt_delta_norm": torch.sqrt(mem.detach().pow(2).sum()),
+                 "ttt_init_norm": torch.zeros((), device=dev)}
+    else:
+        with torch.no_grad():
+            drift = IN.drift_stats(W if not cfg.no_write else W0, W0)
+    ce_chunk_t, mask_chunk_t = torch.stack(ce_chunk), torch.stack(mask_chunk)
+    as_t = lambda x: x.detach() if torch.is_tensor(x) else torch.tensor(float(x), device=dev)
+    stats = {
+        **drift,
+        "inner_loss": st["loss"] / n_in,
+        **({"inner_plan_pre": plan_ce[0] / (B * n_plan), "inner_plan_post": plan_ce[1] / (B * n_plan)} if n_plan else {}),
+        "inner_grad_norm": st["grad_norm"] / n_in, "inner_clipped_frac": st["clipped"] / n_in,
+        "inner_feat": st["feat"] / n_in, "inner_distill": st["distill"] / n_in, "inner_mtp": st["mtp"] / n_in,
+        "inner_kvb": st["kvb"] / n_in,
+        "main_loss": as_t(main_loss), "mtp_loss": as_t(mtp_loss), "mtp_mask_count": as_t(acc["mask2_count"]),
+        "distill_mass": as_t(acc["distill_mass"]) / n_in,
+        "inner_lr": torch.tensor(lr_now, device=dev),
+        "masked_frac": as_t(acc["mask_count"]) / (B * T0 * VO), "mask_count": as_t(acc["mask_count"]),
+        "loss_by_chunk": (ce_chunk_t / (mask_chunk_t + 1e-6))[n_rr:], "mask_by_chunk": mask_chunk_t[n_rr:],
+    }
+    if cfg.per_sequence:
+        stats["loss_by_seq"] = ce_seq / (mask_seq + 1e-6)
+        stats["mask_by_seq"] = mask_seq
+    if cfg.per_token:
+        ce_flat = torch.stack(ce_tok, 1).reshape(B, T)[:, n_rr * C:]
+        mask_flat = torch.stack(mask_tok, 1).reshape(B, T)[:, n_rr * C:]
+        if cfg.outer_shift:
+            ce_flat = torch.cat([torch.zeros_like(ce_flat[:, :1]), ce_flat[:, :-1]], 1)
+            mask_flat = torch.cat([torch.zeros_like(mask_flat[:, :1]), mask_flat[:, :-1]], 1)
+        stats["ce_by_token"], stats["mask_by_token"] = ce_flat, mask_flat
+    return loss, stats
+
+
+def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0, sp_flags, lr_now, distill_w, create_graph,
+                 own_inner, clean_own, read_own, clean_prime, s_S, s_T, B, C, S, use_gdn):
+    """One chunk: streams B, C, A (reference chunk_scan.py:516-677).  Returns the flat tuple
+    ``(kv_next..., memory..., ce_sum, mask_count, ce2_sum, mask2_count, distill_mass, inner stats [7], plan_ce [2],
+    ce_seq [B], mask_seq [B], ce_tok, mask_tok, aux)``."""
+    dev = ho.device
+    nv, p = k["nv"], k["p"]
+    fb = cfg.fused_ce_block
+    lm_w = net.lm_weight()
+    zero = torch.zeros((), dtype=torch.float32, device=dev)
+    W = None if (use_gdn or not memv) else IN.unflat(list(memv))
+    if W is None and not use_gdn:
+        W = W0                                                                       # no_write: the constant template
+    mem = memv[0] if use_gdn else None
+    Wc = None if use_gdn else IN.cast_fast(W, net.dtype)
+    p_q_outer = (p + 1) if cfg.outer_shift else None
+    rb = net.cfg.read_block
+
+    def sf(h, Wm, pq=None, update=False, prime=False, own="full", own_mask=None, own_kv=None):
+        if use_gdn:
+            return net.suffix_forward(h, p, kv, None, nv, pos_q=pq, memory_state=Wm, update_memory=update, own=own,
+                                      own_mask=own_mask, own_kv=own_kv)
+        return net.suffix_forward(h, p, kv, Wm, nv, pos_q=pq, return_prime=prime, own=own, own_mask=own_mask, own_kv=own_kv)
+
+    # T. distillation teacher (forward only) -> the write's soft targets
+    extras = None
+    distill_mass = zero
+    if cfg.distill or cfg.mtp:
+        soft_ids = soft_q = soft_mask = None
+        if cfg.distill:
+            with torch.no_grad():
+                hT = sf(ht, Wc, p_q_outer)[0]
+                ids_k, logp = CE.topk_logprobs(hT.reshape(B * C, -1), lm_w, cfg.distill_topk, fb or 8192)
+                q_k = torch.exp(logp)
+                mass = q_k.sum(-1).view(B, C).mean(1)
+                distill_mass = mass.sum()
+                ids_k, q_k = ids_k.view(B, C, -1), q_k.view(B, C, -1)
+                soft_ids, ok_a = shift_slots(ids_k, s_S - s_T)
+                soft_q, _ = shift_slots(q_k, s_S - s_T)
+                masked_t, ok_b = shift_slots(k["mt"], s_S)
+                first = k["im"].reshape(B, -1, C)[:, 0]
+                soft_mask = (masked_t & (first > 0) & (ok_a & ok_b)[None]).float()
+        extras = IN.InnerExtras(soft_ids, soft_q, soft_mask, k["mtp_t"], k["mtp_m"])
+
+    # B. clean -> next KV window; with memory gdn also the state written from this chunk
+    resB = sf(hc, mem if use_gdn else Wc, update=use_gdn, prime=clean_prime, own=clean_own)
+    own_kv = resB[1]
+    kv_next = [(torch.cat([ck[:, C:], ok], dim=1), torch.cat([cv[:, C:], ov], dim=1)) if ck.shape[1] else (ck, cv)
+               for (ck, cv), (ok, ov) in zip(kv, own_kv)]
+    mem_next = None
+    if use_gdn:
+        mem_next = resB[2] if lr_now > 0 else mem
+
+    # C. the write
+    plan_ce = torch.zeros(2, device=dev)
+    st = IN.zero_stats(dev)
+    aux_term = None
+    if cfg.no_write:
+        W_next = W
+    elif cfg.write_off:
+        pq = None if cfg.inner_task == "mask" else k["p_q"]
+        obj, terms = IN.inner_objective(W, net, hi, k["tgt"], k["im"], kv, k["p_in"], nv, fb, pos_q=pq, own=own_inner)
+        W_next = W
+        st = st.clone(); st[0] = terms[0]
+        aux_term = obj
+    else:
+        feat_tgt = make_feat_target(hc, k["ti"]) if cfg.inner_feat != "off" else None
+        V = cfg.inner_views
+        if cfg.inner_from_outer:
+            W_next, st = IN.inner_update(W, net, ho, k["tok"], k["wgt"].float(), kv, p, nv, lr_now, cfg.inner_clip, fb,
+                                         cfg.inner_update, create_graph=create_graph, h_clean=hc, pos_q=p_q_outer,
+                                         frac=cfg.inner_update_frac)
+        elif V > 1 and cfg.inner_views_sequential:
+            W_next, sts = W, []
+            for v in range(V):
+                W_next, st_v = IN.inner_update(W_next, net, hi[:, v], k["tgt"], k["im"][:, v], kv, k["p_in"], nv, lr_now / V,
+                                               cfg.inner_clip / V, fb, cfg.inner_update, create_graph=create_graph,
+                                               h_clean=hc, feat_tgt=feat_tgt, feat_mode=cfg.inner_feat,
+                                               feat_weight=cfg.inner_feat_weight, frac=cfg.inner_update_frac)
+                sts.append(st_v)
+            st = torch.stack(sts).mean(0)
+        elif not cfg.write.plain:
+            W_next, st = IN.write_chunk(W, net, hi, k["tgt"], k["im"], kv, k["p_in"], nv, lr_now, cfg.inner_clip, fb,
+                                        cfg.inner_update, hc, k["p_q"], own_inner, cfg.write, create_graph=create_graph,
+                                        W0=W0, kvb_src=resB[2][0] if clean_prime else None)
+        else:
+            def plain_step(w, cg=create_graph):
+                return IN.inner_update(w, net, hi, k["tgt"], k["im"], kv, k["p_in"], nv, lr_now, cfg.inner_clip, fb,
+                                       cfg.inner_update, create_graph=cg, h_clean=hc,
+                                       pos_q=None if cfg.inner_task == "mask" else k["p_q"], own=own_inner,
+                                       feat_tgt=feat_tgt, feat_mode=cfg.inner_feat, feat_weight=cfg.inner_feat_weight,
+                                       frac=cfg.inner_update_frac, extras=extras, distill_weight=distill_w,
+                                       mtp_weight=cfg.inner_mtp_weight, distill_meta=cfg.distill_meta)
+            if cfg.write_plan:
+                k_c = k["k_c"]
+                W1, st = plain_step(W)
+                Wk = W1
+                for _ in range(1, max(k_c, 1)):
+                    Wk = plain_step(Wk)[0]
+                W_next = Wk if k_c > 0 else W
+                if k_c > 1:
+                    post = plain_step(Wk, False)[1][0]
+                    plan_ce = torch.stack([st[0], post])
+            else:
+                W_next, st = plain_step(W)
+        if not cfg.second_order:
+            W_next = [tuple(t.detach() for t in w) for w in W_next]
+    if cfg.aux_causal_weight > 0 and not cfg.no_write and aux_term is None:
+        pq = None if cfg.inner_task == "mask" else k["p_q"]
+        aux_term, _ = IN.inner_objective(W, net, hi, k["tgt"], k["im"], kv, k["p_in"], nv, fb, pos_q=pq, own=own_inner)
+
+    # A. the read: the memory as it was before this chunk's write, or (self-prior rows) after it
+    if use_gdn:
+        W_read = mem
+    elif sp_flags is None:
+        W_read = Wc
+    else:
+        sel = [tuple(torch.where(sp_flags.view(B, 1, 1), b_, a_) for a_, b_ in zip(wa, wb)) for wa, wb in zip(W, W_next)]
+        W_read = IN.cast_fast(sel, net.dtype)
+    read_kv = own_kv if rb else None
+    hA = sf(ho, W_read, p_q_outer, own="full", own_mask=read_own, own_kv=read_kv)[0]
+    tok, wgt, tm = k["tok"], k["wgt"], k["tm"]
+    ce_seq = mask_seq = torch.zeros(B, device=dev)
+    if cfg.per_sequence:
+        ce_seq = torch.stack([CE.weighted_ce(hA[b], lm_w, tok[b], wgt[b].float(), fb) for b in range(B)])
+        ce_sum = ce_seq.sum()
+        mask_seq = tm.float().sum(1)
+    else:
+        ce_sum = CE.weighted_ce(hA.reshape(B * C, -1), lm_w, tok.reshape(-1), wgt.reshape(-1).float(), fb)
+    ce2_sum = mask2 = zero
+    if cfg.mtp and cfg.mtp_weight > 0:
+        h2 = Fn.linear(hA, net.p("mtp_head.weight"))
+        ce2_sum = CE.weighted_ce(h2.reshape(B * C, -1), lm_w, k["tok2"].reshape(-1), k["wgt2"].reshape(-1).float(), fb)
+        mask2 = k["tm2"].float().sum()
+    mask_count = tm.float().sum()
+    for i, hvi in enumerate(hv):
+        hV = sf(hvi, W_read, p_q_outer)[0]
+        ce_sum = ce_sum + CE.weighted_ce(hV.reshape(B * C, -1), lm_w, tok.reshape(-1), k["wv"][i].reshape(-1).float(), fb)
+        mask_count = mask_count + k["tmv"][i].float().sum()
+    if cfg.per_token:
+        ce_tok = CE.per_token_ce(hA.reshape(B * C, -1).detach(), lm_w.detach(), tok.reshape(-1), fb or 8192).view(B, C)
+        mask_tok = tm.float()
+    else:
+        ce_tok = mask_tok = torch.zeros(1, device=dev)
+    aux_out = aux_term if (aux_term is not None and cfg.aux_causal_weight > 0) else zero
+    outs = [t for pair in kv_next for t in pair]
+    if use_gdn:
+        outs.append(mem_next)
+    elif not cfg.no_write:
+        outs += IN.flat(W_next)
+    outs += [ce_sum.float(), mask_count, ce2_sum.float() if torch.is_tensor(ce2_sum) else zero, mask2, distill_mass,
+             st, plan_ce, ce_seq, mask_seq, ce_tok, mask_tok, aux_out.float()]
+    return tuple(outs)

@@ -69,19 +69,31 @@ def fold_in(k: torch.Tensor, data) -> torch.Tensor:
     return torch.stack([y0, y1], dim=-1)
 
 
-def bits(k: torch.Tensor, shape: Sequence[int]) -> torch.Tensor:
-    """32 random bits per element: ``k [..., 2]`` -> int64 ``[..., *shape]``."""
+_CHUNK = 1 << 24       # elements generated at a time (bounds the int64 temporaries)
+
+
+def bits(k: torch.Tensor, shape: Sequence[int], start: int = 0, count: int = -1) -> torch.Tensor:
+    """32 random bits per element: ``k [..., 2]`` -> int64 ``[..., *shape]`` (or the flat slice
+    ``[start, start+count)`` of it when ``count >= 0``)."""
     n = int(math.prod(shape)) if len(shape) else 1
-    hi, lo = _iota(n, k.device)
-    y0, y1 = threefry2x32(k[..., 0:1], k[..., 1:2], hi, lo)
-    return (y0 ^ y1).reshape(*k.shape[:-1], *shape)
+    lo_i, hi_i = (0, n) if count < 0 else (start, start + count)
+    i = torch.arange(lo_i, hi_i, dtype=torch.int64, device=k.device)
+    y0, y1 = threefry2x32(k[..., 0:1], k[..., 1:2], (i >> 32) & M32, i & M32)
+    out = y0 ^ y1
+    return out.reshape(*k.shape[:-1], *shape) if count < 0 else out
+
+
+def _to_unit(b: torch.Tensor) -> torch.Tensor:
+    return ((b >> 9) | 0x3F800000).to(torch.int32).view(torch.float32) - 1.0
 
 
 def uniform(k: torch.Tensor, shape: Sequence[int] = (), lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
     """float32 uniform on ``[lo, hi)``; ``k [..., 2]`` -> ``[..., *shape]``."""
-    b = bits(k, shape)
-    mant = ((b >> 9) | 0x3F800000).to(torch.int32)
-    u = mant.view(torch.float32) - 1.0
+    n = int(math.prod(shape)) if len(shape) else 1
+    if n <= _CHUNK or k.dim() > 1:
+        u = _to_unit(bits(k, shape))
+    else:
+        u = torch.cat([_to_unit(bits(k, shape, s, min(_CHUNK, n - s))) for s in range(0, n, _CHUNK)]).reshape(*shape)
     if lo != 0.0 or hi != 1.0:
         u = torch.clamp_min(u * (hi - lo) + lo, lo)
     return u
