@@ -1,0 +1,214 @@
+"""Headline benchmark: training tokens/s of the 1B TTT model (whole job, all GPUs).
+
+    python bench.py --gpus 1 --steps K --warmup W                      (single GPU)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W                          (one rank per GPU)
+
+Config ``8k`` (default) is the 1B trunk at 8192 tokens: 16 layers, d_model 2048, 32 query / 8 KV heads of
+64, SwiGLU 8192, RoPE theta 5e5, vocab 128256, tied embeddings, chunks of 1024 with a window of 8 chunks,
+fast-weight MLPs in the last 4 layers written by one clipped inner step per chunk with the outer
+gradient through every write, bf16 compute with f32 masters and AdamW; 32 sequences per GPU per step
+(global batch 256 x 8192 on 8 GPUs, weak scaling).  Data: synthetic Zipf(1.1) tokens with EOS at
+geometric document boundaries, random-init weights.
+
+Two timed regions of K optimiser steps each, both bracketed by a barrier and a device synchronise and
+timed with CUDA events (max over ranks): ``value`` with the step's tokens already on the device, and
+``e2e`` through the public ``Engine.train_step`` with the tokens copied from pinned host memory every
+step and the loss read back to the host.  The working set of a step (3 GB of bf16 weights, GBs of
+activations) is far larger than the 126 MB L2, so no explicit flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+BASELINE_TOK_S_PER_DEVICE = 4500.0        # reference, GH200, 2 sequences/device (docs/launch.md:73)
+
+CONFIGS = {
+    "8k": dict(model="configs/b200_1b_8k", seq_len=8192, mean_doc=2048, seqs_per_gpu=32, micro=4, extra={}),
+    "32k": dict(model="configs/b200_1b_32k", seq_len=32768, mean_doc=8192, seqs_per_gpu=4, micro=1,
+                extra=dict(segment_chunks=8, inner_norm_alpha=1.0, inner_norm_cap=128.0, inner_lr=0.82, self_prior=0.1)),
+    "128k": dict(model="configs/b200_1b_128k", seq_len=131072, mean_doc=32768, seqs_per_gpu=1, micro=1,
+                 extra=dict(segment_chunks=8, truncate_fast_weight=True, inner_norm_alpha=1.0, inner_norm_cap=128.0,
+                            inner_lr=0.82, self_prior=0.1)),
+    "gdn": dict(model="configs/b200_1b_gdn", seq_len=32768, mean_doc=8192, seqs_per_gpu=4, micro=1, extra=dict(segment_chunks=8)),
+    "tiny": dict(model="configs/tiny_baseline", seq_len=512, mean_doc=200, seqs_per_gpu=2, micro=2, extra=dict(cart_window=64)),
+}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        busy = [x for x in sm if x > 0.5 * mx] or sm
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args) -> int:
+    """The reference is a JAX / Equinox / Optax program; none of the three is installed in this image and no
+    index is reachable, so the reference arm cannot run."""
+    why = "reference needs jax 0.11 + equinox + optax (not in the image or the offline wheelhouse); import jax fails"
+    try:
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
+        import jax  # noqa: F401
+        import equinox  # noqa: F401
+        import optax  # noqa: F401
+        why = "jax present but the reference arm is not wired for this image"
+    except Exception:
+        pass
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", default="8k", choices=sorted(CONFIGS))
+    ap.add_argument("--seqs-per-gpu", type=int, default=0)
+    ap.add_argument("--micro", type=int, default=0)
+    ap.add_argument("--fsdp", type=int, default=0)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, here)
+    from dttt_b200.data.synth import zipf_tokens
+    from dttt_b200.engine import Engine
+    from dttt_b200.ops import gemm, kernels
+    from dttt_b200.parallel.mesh import init_distributed, make_mesh
+    from dttt_b200.schema import ModelConfig, TrainConfig
+
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+    rank, world, local = init_distributed()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    spec = CONFIGS[args.config]
+    mesh = make_mesh(args.fsdp, args.tp, dev)
+    mc = ModelConfig.load(os.path.join(here, spec["model"]))
+    per_gpu = args.seqs_per_gpu or spec["seqs_per_gpu"]
+    micro = min(args.micro or spec["micro"], per_gpu)
+    accum = per_gpu // micro
+    T = spec["seq_len"]
+    tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
+                     seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
+                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **spec["extra"])
+    eng = Engine(mc, tc, mesh, dev)
+
+    # synthetic data: distinct tokens for every step, on pinned host memory
+    n_steps = W + 2 * K
+    toks = zipf_tokens(n_steps * per_gpu * T, mc.vocab_size, seed=1234 + mesh.batch_index, eos=mc.eos_token_id,
+                       mean_doc=spec["mean_doc"], exclude=(mc.mask_token_id, mc.pad_token_id, mc.bos_token_id or -1))
+    host = torch.from_numpy(toks.astype(np.int32)).view(n_steps, accum, micro, T).pin_memory()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for s in range(W):
+        m = eng.train_step(host[s].to(dev, non_blocking=True), s)
+    launches0 = gemm.LAUNCHES + kernels.LAUNCHES
+
+    def timed(first_step: int, e2e: bool):
+        staged = None if e2e else [host[first_step + i].to(dev) for i in range(K)]
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        last = None
+        for i in range(K):
+            x = host[first_step + i].to(dev, non_blocking=True) if e2e else staged[i]
+            last = eng.train_step(x, first_step + i)          # returns host floats: the loss is read back every step
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), last
+
+    clocks = ClockSampler(local)
+    clocks.start()
+    ms_dev, last = timed(W, e2e=False)
+    launches = gemm.LAUNCHES + kernels.LAUNCHES - launches0
+    ck = clocks.stop()
+    ms_e2e = None
+    if not args.no_e2e:
+        ms_e2e, last = timed(W + K, e2e=True)
+    tokens_per_step = per_gpu * mesh.batch_ranks * T
+    value = tokens_per_step * K / (ms_dev / 1e3)
+    out = {
+        "metric": "train tokens/s (whole job)", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": ms_dev / K, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / (BASELINE_TOK_S_PER_DEVICE * world), "dtype": "bf16",
+        "data": "synthetic Zipf(1.1) tokens with EOS at geometric document boundaries; random-init weights",
+        "config": {"model": f"1B TTT ({args.config}): " + spec["model"], "global_batch": per_gpu * mesh.batch_ranks, "seq_len": T,
+                   "parallelism": f"dp{mesh.dp}xfsdp{mesh.fsdp}xtp{mesh.tp}", "micro_batch_per_gpu": micro, "grad_accum": accum,
+                   "l2": "per-step working set (3 GB bf16 weights + activations) >> 126 MB L2; no explicit flush",
+                   "params": eng.n_params},
+        "clocks": ck, "gpu_launches": launches, "final_loss": last.get("main_loss") if last else None,
+    }
+    if ms_e2e is not None:
+        out["e2e"] = {"value": tokens_per_step * K / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,
+                      "h2d_bytes_per_step": per_gpu * T * 4, "d2h_bytes_per_step": 8}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

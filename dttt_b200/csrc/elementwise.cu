@@ -1,0 +1,321 @@
+// Bandwidth-bound kernels: RMSNorm (forward / backward), rotary embedding (forward / backward),
+// SwiGLU (forward / backward), AdamW on flat f32 shards, and the per-sequence pieces of the inner
+// step (sum of squares, scaled update).  bf16 activations, f32 math, 16-byte vector accesses.
+// Each launcher is extern "C", takes raw device pointers and a stream, allocates nothing.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(p[i]);
+    f[2 * i] = t.x; f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One warp per row; D a multiple of 8.  y = w * x * rsqrt(mean(x^2) + eps), f32 math (reference
+// src/ttt/model.py:123-134).
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, long long rows, int D,
+                                   float eps) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    float ss = 0.f;
+    for (int c = lane; c < D / 8; c += 32) {
+      float f[8];
+      unpack8(xr[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd) rstd[row] = r;
+    uint4* yr = reinterpret_cast<uint4*>(y + row * D);
+    for (int c = lane; c < D / 8; c += 32) {
+      float f[8];
+      unpack8(xr[c], f);
+      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+      f[0] *= r * w0.x; f[1] *= r * w0.y; f[2] *= r * w0.z; f[3] *= r * w0.w;
+      f[4] *= r * w1.x; f[5] *= r * w1.y; f[6] *= r * w1.z; f[7] *= r * w1.w;
+      yr[c] = pack8(f);
+    }
+  }
+}
+
+// dx = r * (w*dy - xhat * mean(w*dy*xhat)),  dw += sum_rows dy * xhat,  xhat = x * r.
+// Each warp walks rows; its lane-local dw partials (for the columns it owns) are reduced through shared
+// memory per block and added to the f32 dw with one atomic per column per block.
+template <int MAXC>
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                   const __nv_bfloat16* __restrict__ dy, const float* __restrict__ rstd,
+                                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, long long rows, int D) {
+  extern __shared__ float sdw[];
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  float acc[MAXC][8];
+#pragma unroll
+  for (int j = 0; j < MAXC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+  const int nchunk = D / 8;
+  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+        float fx[8], fg[8];
+        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xh = fx[i] * r;
+          dot += ww[i] * fg[i] * xh;
+          acc[j][i] += fg[i] * xh;
+        }
+      }
+    }
+    dot = warp_sum(dot) / D;
+    uint4* dr = reinterpret_cast<uint4*>(dx + row * D);
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+        float fx[8], fg[8], o[8];
+        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = r * (ww[i] * fg[i] - fx[i] * r * dot);
+        dr[c] = pack8(o);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(&sdw[c * 8 + i], acc[j][i]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], sdw[i]);
+  }
+}
+
+// ------------------------------------------------------------------ rotary embedding
+// x [rows, heads, d] -> out; angle = pos[row] * inv_freq[i]; out = x*cos + rot(x)*sin with
+// rot(x) = [-x2, x1] (half rotation, reference model.py:111-117).  sign = -1 gives the backward.
+// One thread per (row, head, 8-element slice of the first half).
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                            const long long* __restrict__ pos, const float* __restrict__ inv_freq, long long rows,
+                            int heads, int d, float sign) {
+  const int slices = d / 16;                       // 8-element slices in one half
+  const long long total = rows * heads * slices;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int sl = (int)(t % slices);
+    const long long rh = t / slices;
+    const long long row = rh / heads;
+    const __nv_bfloat16* base = x + rh * d;
+    float a[8], b[8], oa[8], ob[8];
+    unpack8(*reinterpret_cast<const uint4*>(base + sl * 8), a);
+    unpack8(*reinterpret_cast<const uint4*>(base + d / 2 + sl * 8), b);
+    const float p = (float)pos[row];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float s, c;
+      sincosf(p * inv_freq[sl * 8 + i], &s, &c);
+      s *= sign;
+      oa[i] = a[i] * c - b[i] * s;
+      ob[i] = b[i] * c + a[i] * s;
+    }
+    __nv_bfloat16* ob_ = out + rh * d;
+    *reinterpret_cast<uint4*>(ob_ + sl * 8) = pack8(oa);
+    *reinterpret_cast<uint4*>(ob_ + d / 2 + sl * 8) = pack8(ob);
+  }
+}
+
+// ------------------------------------------------------------------ SwiGLU
+__global__ void swiglu_fwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, uint4* __restrict__ y,
+                                  long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float fg[8], fu[8], o[8];
+    unpack8(g[i], fg); unpack8(u[i], fu);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = fg[k] / (1.f + __expf(-fg[k])) * fu[k];
+    y[i] = pack8(o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ u, const uint4* __restrict__ dy,
+                                  uint4* __restrict__ dg, uint4* __restrict__ du, long long n8) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float fg[8], fu[8], fd[8], og[8], ou[8];
+    unpack8(g[i], fg); unpack8(u[i], fu); unpack8(dy[i], fd);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float s = 1.f / (1.f + __expf(-fg[k]));
+      const float silu = fg[k] * s;
+      ou[k] = fd[k] * silu;
+      og[k] = fd[k] * fu[k] * (s + silu * (1.f - s));
+    }
+    dg[i] = pack8(og); du[i] = pack8(ou);
+  }
+}
+
+// ------------------------------------------------------------------ AdamW on a flat f32 range
+// g is pre-multiplied by gscale (the clip factor); optax semantics (see optim.py).
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const float* __restrict__ g, long long n, float lr, float b1, float b2, float eps, float wd,
+                             float bc1, float bc2, float gscale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float gg = g[i] * gscale;
+    const float mm = b1 * m[i] + (1.f - b1) * gg;
+    const float vv = b2 * v[i] + (1.f - b2) * gg * gg;
+    m[i] = mm; v[i] = vv;
+    const float pp = p[i];
+    const float upd = (mm / bc1) / (sqrtf(vv / bc2) + eps) + wd * pp;
+    p[i] = pp - lr * upd;
+  }
+}
+
+// ------------------------------------------------------------------ inner step pieces (per sequence)
+// out[b] += sum over the n elements of sequence b of x^2   (x: [B, n] f32 or bf16)
+template <typename T>
+__global__ void seq_sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const T* xb = x + (long long)b * n;
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float f = (float)xb[i];
+    s += f * f;
+  }
+  s = warp_sum(s);
+  __shared__ float red[32];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(&out[b], s);
+  }
+}
+// w_new[b, i] = w[b, i] - coef[b] * g[b, i]   (f32 master carry; g f32 or bf16); optional bf16 copy of w_new
+template <typename T>
+__global__ void seq_axpy_kernel(const float* __restrict__ w, const T* __restrict__ g, const float* __restrict__ coef,
+                                float* __restrict__ w_new, __nv_bfloat16* __restrict__ w_lo, long long n) {
+  const int b = blockIdx.y;
+  const float c = coef[b];
+  const long long off = (long long)b * n;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float r = w[off + i] - c * (float)g[off + i];
+    w_new[off + i] = r;
+    if (w_lo) w_lo[off + i] = __float2bfloat16(r);
+  }
+}
+
+inline int grid_for(long long n, int block, int cap = 148 * 16) {
+  long long g = (n + block - 1) / block;
+  return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+extern "C" int dttt_rmsnorm_fwd(const void* x, const float* w, void* y, float* rstd, long long rows, int D, float eps,
+                                cudaStream_t s) {
+  if (D % 8) return -2;
+  const int wpb = 8;
+  long long blocks = (rows + wpb - 1) / wpb;
+  int grid = (int)(blocks > 148 * 32 ? 148 * 32 : (blocks < 1 ? 1 : blocks));
+  rmsnorm_fwd_kernel<<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rstd, rows, D, eps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd, void* dx, float* dw,
+                                long long rows, int D, cudaStream_t s) {
+  if (D % 8 || D > 8192) return -2;
+  const int wpb = 8;
+  long long blocks = (rows + wpb - 1) / wpb;
+  int grid = (int)(blocks > 148 * 4 ? 148 * 4 : (blocks < 1 ? 1 : blocks));
+  const int chunks = (D / 8 + 31) / 32;
+  size_t smem = (size_t)D * sizeof(float);
+#define LAUNCH(MC) rmsnorm_bwd_kernel<MC><<<grid, wpb * 32, smem, s>>>((const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, \
+                                                                      rstd, (__nv_bfloat16*)dx, dw, rows, D)
+  if (chunks <= 1) LAUNCH(1);
+  else if (chunks <= 2) LAUNCH(2);
+  else if (chunks <= 4) LAUNCH(4);
+  else if (chunks <= 8) LAUNCH(8);
+  else if (chunks <= 16) LAUNCH(16);
+  else LAUNCH(32);
+#undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_rope(const void* x, void* out, const long long* pos, const float* inv_freq, long long rows, int heads,
+                         int d, float sign, cudaStream_t s) {
+  if (d % 16) return -2;
+  long long total = rows * heads * (d / 16);
+  rope_kernel<<<grid_for(total, 256, 148 * 32), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, pos, inv_freq, rows,
+                                                            heads, d, sign);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_swiglu_fwd(const void* g, const void* u, void* y, long long n, cudaStream_t s) {
+  if (n % 8) return -2;
+  swiglu_fwd_kernel<<<grid_for(n / 8, 256, 148 * 32), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (uint4*)y, n / 8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_swiglu_bwd(const void* g, const void* u, const void* dy, void* dg, void* du, long long n, cudaStream_t s) {
+  if (n % 8) return -2;
+  swiglu_bwd_kernel<<<grid_for(n / 8, 256, 148 * 32), 256, 0, s>>>((const uint4*)g, (const uint4*)u, (const uint4*)dy,
+                                                                  (uint4*)dg, (uint4*)du, n / 8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_adamw(float* p, float* m, float* v, const float* g, long long n, float lr, float b1, float b2, float eps,
+                          float wd, float bc1, float bc2, float gscale, cudaStream_t s) {
+  adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(p, m, v, g, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_seq_sumsq(const void* x, float* out, int B, long long n, int is_bf16, cudaStream_t s) {
+  dim3 grid(grid_for(n, 256, 148 * 2), B);
+  if (is_bf16) seq_sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, out, n);
+  else seq_sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)x, out, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_seq_axpy(const float* w, const void* g, const float* coef, float* w_new, void* w_lo, int B, long long n,
+                             int g_is_bf16, cudaStream_t s) {
+  dim3 grid(grid_for(n, 256, 148 * 4), B);
+  if (g_is_bf16) seq_axpy_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(w, (const __nv_bfloat16*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
+  else seq_axpy_kernel<float><<<grid, 256, 0, s>>>(w, (const float*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
+  return (int)cudaGetLastError();
+}

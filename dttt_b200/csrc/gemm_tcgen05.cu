@@ -328,6 +328,17 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (a_batch % 8) || (b_batch % 8))
     return -2;
+  // The tensor-map encoder is a driver call and needs a current context in the calling thread.  Autograd
+  // runs backward passes on its own threads, where no runtime call may have bound the primary context yet:
+  // bind it once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaSetDevice(dev);
+    cudaFree(0);
+    ctx_bound = true;
+  }
   if (g_num_sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);

@@ -22,7 +22,6 @@ import torch
 from ..ops import functional as Fn
 from ..ops import attention as A
 from ..schema import ModelConfig
-from .params import ComputeWeights
 
 OUTER, CLEAN, INNER = 0, 1, 2      # stream indices of the prefix (inner views occupy INNER, INNER+1, ...)
 
@@ -34,7 +33,7 @@ def cast_like(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 class Net:
     """Stateless forward functions over a ``ComputeWeights`` view."""
 
-    def __init__(self, cfg: ModelConfig, cw: ComputeWeights):
+    def __init__(self, cfg: ModelConfig, cw):
         self.cfg, self.cw = cfg, cw
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.dtype = cw.dtype
@@ -48,9 +47,9 @@ class Net:
 
     # ---- pieces
     def embed_tokens(self, ids: torch.Tensor) -> torch.Tensor:
-        """Lookup from the f32 master (its gradient is a f32 scatter-add; reference model.py:534-542)."""
+        """Embedding lookup whose gradient is a f32 scatter-add (reference model.py:534-542)."""
         from ..ops import embed as E
-        return E.embedding(self.cw.master["embed"], ids, self.dtype)
+        return E.embedding(self.p("embed"), ids, self.dtype, self.cw.grad_buffer("embed") if self.cw.train else None)
 
     def logits(self, h: torch.Tensor) -> torch.Tensor:
         w = self.lm_weight()
@@ -72,11 +71,8 @@ class Net:
         if cfg.qk_norm:
             q = Fn.rms_norm(q, self.p(f"{stack}.attn.q_norm.weight", l), cfg.rms_norm_eps)
             k = Fn.rms_norm(k, self.p(f"{stack}.attn.k_norm.weight", l), cfg.rms_norm_eps)
-        cos, sin = Fn.rope_cos_sin(pos, d, cfg.rope_theta, cfg.rope_scaling)
-        if pos_q is None:
-            return Fn.apply_rope(q, cos, sin), Fn.apply_rope(k, cos, sin), v
-        cq, sq = Fn.rope_cos_sin(pos_q, d, cfg.rope_theta, cfg.rope_scaling)
-        return Fn.apply_rope(q, cq, sq), Fn.apply_rope(k, cos, sin), v
+        rope = lambda t, p_: Fn.rope(t, p_, d, cfg.rope_theta, cfg.rope_scaling)
+        return rope(q, pos if pos_q is None else pos_q), rope(k, pos), v
 
     def mlp(self, stack: str, l: int, x: torch.Tensor) -> torch.Tensor:
         g = Fn.linear(x, self.p(f"{stack}.mlp.gate.weight", l))
@@ -159,8 +155,7 @@ class Net:
                 own = f"block:{read_block}"
             a_s = [None] * nc
             for nv, cs in groups.items():
-                idx = torch.as_tensor(cs, device=q.device)
-                sel = (lambda t: t[:, cs[0]:cs[-1] + 1] if cs == list(range(cs[0], cs[-1] + 1)) else t[:, idx])
+                sel = (lambda t, _a=cs[0], _b=cs[-1] + 1: t[:, _a:_b])        # chunks sharing a valid length are contiguous
                 fl = lambda t: t.flatten(0, 1)
                 if read_block and s == OUTER:
                     extra = (fl(sel(kc.unflatten(1, (nc, C)))), fl(sel(vc.unflatten(1, (nc, C)))))
@@ -279,7 +274,7 @@ class Net:
         """The ``W_0`` template broadcast to the batch, f32: the fast weight at the sequence start."""
         out = []
         for f in range(self.cfg.fast_len):
-            out.append(tuple(self.cw.master[f"fast_weight.{n}.weight"][f].float().unsqueeze(0).expand(B, -1, -1)
+            out.append(tuple(self.p(f"fast_weight.{n}.weight", f).float().unsqueeze(0).expand(B, -1, -1)
                              for n in ("gate", "up", "down")))
         return out
 

@@ -7,12 +7,9 @@ MLP, ``src/ttt/gdn.py:57-66`` GDN).  ``param_spec`` reproduces that order and th
 what makes checkpoints interchangeable (``dttt_b200.ckpt``).  Names are the pytree paths joined by
 dots, e.g. ``prefix.attn.q.weight [L-S, H, nh*d]``.
 
-In memory the f32 master copy keeps the stacked form.  Each step builds a *compute view*
-(``ComputeWeights``): bf16 leaf copies of the matrices, split per layer (views of the stacked copy),
-with the f32 master leaves of the small parameters (norm weights, gates, scalars) used directly.
-First-order weight gradients are accumulated by the GEMM epilogue straight into the f32 gradient
-buffers of the masters (``ops.linear.linear_w``); what reaches a bf16 leaf through ordinary autograd
-(second-order terms) is folded into the same buffers by ``ComputeWeights.fold_grads``.
+In memory the parameters live in ``parallel.store.ParamStore`` (sharded f32 masters, full compute
+copies, full f32 gradient buffers); ``is_small`` says which parameters are used in f32 (norm weights,
+biases, gates, scalars) rather than through a compute-dtype copy.
 """
 from __future__ import annotations
 
@@ -99,13 +96,17 @@ def count_params(cfg: ModelConfig) -> int:
 
 
 def init_params(cfg: ModelConfig, seed: int, device="cpu") -> "OrderedDict[str, torch.Tensor]":
-    """f32 master parameters.  Every leaf draws from its own counter-based key (the seed folded with
+    """All parameters at once (small models, tests); see ``iter_init``."""
+    return OrderedDict(iter_init(cfg, seed, device))
+
+
+def iter_init(cfg: ModelConfig, seed: int, device="cpu"):
+    """Yield ``(name, f32 tensor)`` in checkpoint order, one parameter at a time.  Every leaf draws from its own counter-based key (the seed folded with
     the leaf's index, then with the layer index for stacked leaves), so the values do not depend on the
     device, the process count or how the tree is later sharded.  Normal leaves have std
     ``initializer_range`` (reference model.py:137-148), norm weights are 1, gates / biases 0, the GDN
     decay is initialised long (reference gdn.py:74-88)."""
     base = trng.key(seed, device)
-    out: "OrderedDict[str, torch.Tensor]" = OrderedDict()
     for idx, (name, (shape, kind)) in enumerate(param_spec(cfg).items()):
         k = trng.fold_in(base, idx + 1)
         if kind == "ones":
@@ -131,8 +132,7 @@ def init_params(cfg: ModelConfig, seed: int, device="cpu") -> "OrderedDict[str, 
             t[..., -1] = 1.0                                     # identity filter: the option starts as "no conv"
         else:
             raise ValueError(kind)
-        out[name] = t.to(device=device, dtype=torch.float32).contiguous()
-    return out
+        yield name, t.to(device=device, dtype=torch.float32).contiguous()
 
 
 # parameters that stay f32 leaves in the compute view (everything that is not a matrix operand of a GEMM)
@@ -142,54 +142,3 @@ _SMALL = re.compile(r"norm|bias|inner_gate|inner_token_gate|inner_decay_logit|in
 
 def is_small(name: str) -> bool:
     return bool(_SMALL.search(name))
-
-
-class ComputeWeights:
-    """The per-step compute view of the parameters.
-
-    ``master``: name -> f32 leaf (``requires_grad``; its ``.grad`` is the f32 accumulation buffer).
-    ``lo``: name -> compute-dtype leaf copy of every matrix (``requires_grad`` when training).
-    ``get(name, layer)`` returns the tensor a forward should use for that layer; matrices carry
-    ``.grad_target = (f32 grad buffer, layer)`` for the GEMM epilogue's direct accumulation.
-    """
-
-    def __init__(self, master: Dict[str, torch.Tensor], dtype: torch.dtype, train: bool = True):
-        self.master = master
-        self.dtype = dtype
-        self.train = train
-        self.lo: Dict[str, torch.Tensor] = {}          # stacked compute-dtype copies (no autograd)
-        self._leaves: Dict[Tuple[str, int], torch.Tensor] = {}
-        self.direct = all(p.dtype == dtype for p in master.values())   # f32 checks: use the masters themselves
-        if not self.direct:
-            for name, p in master.items():
-                if not is_small(name):
-                    self.lo[name] = p.detach().to(dtype)
-
-    def get(self, name: str, layer: Optional[int] = None) -> torch.Tensor:
-        if self.direct or is_small(name):
-            src = self.master[name]
-            return src if layer is None else src[layer]
-        key = (name, -1 if layer is None else layer)
-        t = self._leaves.get(key)
-        if t is None:
-            base = self.lo[name]
-            t = (base if layer is None else base[layer]).detach()
-            if self.train and self.master[name].requires_grad:
-                t.requires_grad_(True)
-                t.grad_target = (self.master[name], layer)
-            self._leaves[key] = t
-        return t
-
-    def has(self, name: str) -> bool:
-        return name in self.master
-
-    def fold_grads(self) -> None:
-        """Add what autograd left on the compute-dtype leaves into the f32 gradient buffers."""
-        for (name, layer), t in self._leaves.items():
-            if t.grad is None:
-                continue
-            p = self.master[name]
-            if p.grad is None:
-                p.grad = torch.zeros_like(p)
-            (p.grad if layer < 0 else p.grad[layer]).add_(t.grad)
-            t.grad = None

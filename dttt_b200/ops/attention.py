@@ -73,10 +73,19 @@ def _own_mask_cpu(chunk: int, own: str) -> Optional[torch.Tensor]:
     raise ValueError(f"own-chunk mode {own!r}")
 
 
+_DEV_MASKS = {}
+
+
 def own_mask_matrix(chunk: int, own: str, device=None) -> Optional[torch.Tensor]:
-    """``[C, C]`` bool own-chunk pattern (None for ``full``); reference attention.py:132-150."""
+    """``[C, C]`` bool own-chunk pattern (None for ``full``); reference attention.py:132-150.  Cached per device."""
     m = _own_mask_cpu(chunk, own)
-    return None if m is None else m.to(device)
+    if m is None or device is None or torch.device(device).type == "cpu":
+        return m
+    key = (chunk, own, str(device))
+    d = _DEV_MASKS.get(key)
+    if d is None:
+        d = _DEV_MASKS[key] = m.to(device)
+    return d
 
 
 def read_mask_matrix(chunk: int, block: int, device=None) -> torch.Tensor:
@@ -134,9 +143,42 @@ def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_w
 
 
 # staged execution: library/hand-written forward + first-order backward, reference for the second order
+_BIAS = {}
+
+
+def _causal_bias(C: int, Kn: int, device) -> torch.Tensor:
+    """``[C, Kn]`` f32 additive mask, causal aligned to the end of the key axis."""
+    key = (C, Kn, str(device))
+    b = _BIAS.get(key)
+    if b is None:
+        i = torch.arange(C, device=device)[:, None]
+        j = torch.arange(Kn, device=device)[None, :]
+        b = _BIAS[key] = torch.where(j <= i + (Kn - C), 0.0, ref.NEG).float()
+        if len(_BIAS) > 32:
+            _BIAS.pop(next(iter(_BIAS)))
+    return b
+
+
 def _ref_for_staged(q, K, V, scale, causal):
-    om = own_mask_matrix(q.shape[1], "causal", q.device) if causal else None
-    return ref.attend(q, K, V, None, scale, om)
+    """The differentiable-to-any-order statement used when a backward is recorded.  On the GPU the two
+    products run on the tensor-core GEMM (batched over sequence x KV head, the query heads of a group folded
+    into the rows), scores and softmax in f32 as in the reference (attention.py:181-201)."""
+    if not use_kernels(q):
+        om = own_mask_matrix(q.shape[1], "causal", q.device) if causal else None
+        return ref.attend(q, K, V, None, scale, om)
+    from .gemm import mm
+    n, C, nh, d = q.shape
+    Kn, nkv = K.shape[1], K.shape[2]
+    rep = nh // nkv
+    qg = q.reshape(n, C, nkv, rep, d).permute(0, 2, 3, 1, 4).reshape(n * nkv, rep * C, d)
+    kg = K.permute(0, 2, 1, 3).reshape(n * nkv, Kn, d)
+    vg = V.permute(0, 2, 1, 3).reshape(n * nkv, Kn, d)
+    s = mm(qg, kg, False, True, out_dtype=torch.float32) * scale
+    if causal:
+        s = (s.view(n * nkv, rep, C, Kn) + _causal_bias(C, Kn, q.device)).view(n * nkv, rep * C, Kn)
+    p = torch.softmax(s, dim=-1).to(q.dtype)
+    o = mm(p, vg)
+    return o.view(n, nkv, rep, C, d).permute(0, 3, 1, 2, 4).reshape(n, C, nh, d)
 
 
 def _fast_fwd(q, K, V, scale, causal):

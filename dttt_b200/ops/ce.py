@@ -81,10 +81,8 @@ def _ce_bwd(g, tensors, saved, needs, block, target=None):
     if need_E and not (kern and target is not None):
         g_E = torch.zeros(E.shape, dtype=torch.float32, device=E.device)
     if need_E and kern and target is not None:
-        master, layer = target
-        if master.grad is None:
-            master.grad = torch.zeros_like(master)
-        gbuf = master.grad if layer is None else master.grad[layer]
+        gfull, layer = target
+        gbuf = gfull if layer is None else gfull[layer]
     tl = targets.long()
     for s, e in _blocks(E.shape[0], block):
         logits = _block_logits(h, E[s:e])

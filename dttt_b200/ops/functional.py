@@ -71,7 +71,7 @@ def staged(spec, tensors: Sequence[torch.Tensor], consts: Sequence = ()):
 
 # ------------------------------------------------------------------ linear with direct f32 grad accumulation
 class _LinearW(torch.autograd.Function):
-    """``x @ w`` for a weight leaf that carries ``grad_target = (f32 master, layer)``: the first-order
+    """``x @ w`` for a weight leaf that carries ``grad_target = (f32 gradient buffer, layer)``: the first-order
     weight gradient ``x^T g`` is added by the GEMM epilogue into the master's f32 gradient buffer
     (no bf16 round trip, no separate accumulation pass); the weight then receives no autograd gradient.
     When the backward is being recorded (meta-gradient) both gradients are ordinary differentiable
@@ -98,10 +98,8 @@ class _LinearW(torch.autograd.Function):
             gx = _gemm.gemm_raw(g, w, False, True)
         if ctx.needs_input_grad[1] and not _INNER_BACKWARD[0]:
             if ctx.target is not None:
-                master, layer = ctx.target
-                if master.grad is None:
-                    master.grad = torch.zeros_like(master)
-                buf = master.grad if layer is None else master.grad[layer]
+                gbuf, layer = ctx.target
+                buf = gbuf if layer is None else gbuf[layer]
                 _gemm.gemm_raw(x, g, True, False, torch.float32, out=buf, accumulate=True)
             else:
                 gw = _gemm.gemm_raw(x, g, True, False)
@@ -157,10 +155,30 @@ def glu(gate: torch.Tensor, up: torch.Tensor, act: str = "silu") -> torch.Tensor
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    from . import kernels
-    if use_kernels(x) and kernels.available("rope"):
-        return kernels.rope(x, cos, sin)
     return ref.apply_rope(x, cos, sin)
+
+
+_INV_FREQ = {}
+
+
+def inv_freq(head_dim: int, theta: float, scaling, device) -> torch.Tensor:
+    key = (head_dim, theta, scaling, str(device))
+    t = _INV_FREQ.get(key)
+    if t is None:
+        t = _INV_FREQ[key] = ref.rope_inv_freq(head_dim, theta, scaling, "cpu").to(device)
+    return t
+
+
+def rope(x: torch.Tensor, pos: torch.Tensor, head_dim: int, theta: float, scaling=None) -> torch.Tensor:
+    """Rotary embedding of ``x [..., T, heads, d]`` at positions ``pos [..., T]`` (f32 angles, half-rotation
+    layout, optional llama3 frequency scaling; reference model.py:82-117)."""
+    from . import kernels
+    inv = inv_freq(head_dim, theta, scaling, x.device)
+    if use_kernels(x) and kernels.available("rope"):
+        return kernels.rope(x, pos.long(), inv)
+    ang = pos.float().unsqueeze(-1) * inv
+    emb = torch.cat([ang, ang], dim=-1)
+    return ref.apply_rope(x, emb.cos(), emb.sin())
 
 
 rope_cos_sin = ref.rope_cos_sin

@@ -39,3 +39,163 @@ def enable(name: str) -> None:
 
 # family -> a symbol whose presence means the family is built
 _SYMBOL: Dict[str, str] = {}
+
+# =============================================================================== elementwise family
+import ctypes as _ct
+
+from . import reference as _ref
+
+_vp, _ll, _i, _f = _ct.c_void_p, _ct.c_longlong, _ct.c_int, _ct.c_float
+_lib.register("dttt_rmsnorm_fwd", _i, [_vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
+_lib.register("dttt_rmsnorm_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
+_lib.register("dttt_rope", _i, [_vp, _vp, _vp, _vp, _ll, _i, _i, _f, _vp])
+_lib.register("dttt_swiglu_fwd", _i, [_vp, _vp, _vp, _ll, _vp])
+_lib.register("dttt_swiglu_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _ll, _vp])
+_lib.register("dttt_adamw", _i, [_vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _vp])
+_lib.register("dttt_seq_sumsq", _i, [_vp, _vp, _i, _ll, _i, _vp])
+_lib.register("dttt_seq_axpy", _i, [_vp, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp])
+_SYMBOL.update(rmsnorm="dttt_rmsnorm_fwd", rope="dttt_rope", swiglu="dttt_swiglu_fwd", adamw="dttt_adamw",
+               seq="dttt_seq_sumsq")
+
+
+def _p(t):
+    return _ct.c_void_p(t.data_ptr()) if t is not None else _ct.c_void_p(0)
+
+
+def _stream():
+    return _ct.c_void_p(_lib.stream_ptr())
+
+
+def _check(rc, what):
+    global LAUNCHES
+    if rc != 0:
+        raise _lib.KernelError(f"{what} launch failed rc={rc}")
+    LAUNCHES += 1
+
+
+# ---- RMSNorm
+def _rms_fwd(x, w, eps):
+    xc = x.contiguous()
+    D = xc.shape[-1]
+    rows = xc.numel() // D
+    y = torch.empty_like(xc)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    wf = w.detach().float().contiguous()
+    _check(_lib.lib().dttt_rmsnorm_fwd(_p(xc), _p(wf), _p(y), _p(rstd), rows, D, float(eps), _stream()), "rmsnorm_fwd")
+    return y, (rstd,)
+
+
+def _rms_bwd(g, tensors, saved, needs, eps):
+    x, w = tensors
+    (rstd,) = saved
+    xc, gc = x.contiguous(), g.contiguous()
+    D = xc.shape[-1]
+    rows = xc.numel() // D
+    dx = torch.empty_like(xc)
+    dw = torch.zeros(D, dtype=torch.float32, device=x.device) if needs[1] else None
+    wf = w.detach().float().contiguous()
+    _check(_lib.lib().dttt_rmsnorm_bwd(_p(xc), _p(wf), _p(gc), _p(rstd), _p(dx), _p(dw), rows, D, _stream()), "rmsnorm_bwd")
+    return dx, (dw.to(w.dtype) if dw is not None else None)
+
+
+_RMS_SPEC = (_rms_fwd, _rms_bwd, _ref.rms_norm)
+
+
+def rms_norm(x, w, eps):
+    from .functional import staged
+    if x.shape[-1] % 8:
+        return _ref.rms_norm(x, w, eps)
+    if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad):
+        return staged(_RMS_SPEC, (x, w), (eps,))
+    return _rms_fwd(x, w, eps)[0]
+
+
+# ---- rotary embedding
+def _rope_run(x, pos, inv_freq, sign):
+    xc = x.contiguous()
+    heads, d = xc.shape[-2], xc.shape[-1]
+    rows = xc.numel() // (heads * d)
+    out = torch.empty_like(xc)
+    pc = pos.contiguous()
+    assert pc.numel() == rows and pc.dtype == torch.int64, (pc.shape, rows, pc.dtype)
+    _check(_lib.lib().dttt_rope(_p(xc), _p(out), _p(pc), _p(inv_freq), rows, heads, d, float(sign), _stream()), "rope")
+    return out
+
+
+def _rope_ref(x, pos, inv_freq):
+    ang = pos.float().unsqueeze(-1) * inv_freq
+    emb = torch.cat([ang, ang], dim=-1)
+    return _ref.apply_rope(x, emb.cos(), emb.sin())
+
+
+_ROPE_SPEC = (lambda x, pos, inv: (_rope_run(x, pos, inv, 1.0), ()),
+              lambda g, tensors, saved, needs, pos, inv: (_rope_run(g, pos, inv, -1.0),),
+              _rope_ref)
+
+
+def rope(x, pos, inv_freq):
+    """``x [..., T, heads, d]`` rotated by the angles ``pos [..., T] * inv_freq [d/2]``."""
+    from .functional import staged
+    if x.shape[-1] % 16:
+        return _rope_ref(x, pos, inv_freq)
+    if torch.is_grad_enabled() and x.requires_grad:
+        return staged(_ROPE_SPEC, (x,), (pos, inv_freq))
+    return _rope_run(x, pos, inv_freq, 1.0)
+
+
+# ---- SwiGLU
+def _swiglu_fwd(g, u):
+    gc, uc = g.contiguous(), u.contiguous()
+    y = torch.empty_like(gc)
+    _check(_lib.lib().dttt_swiglu_fwd(_p(gc), _p(uc), _p(y), gc.numel(), _stream()), "swiglu_fwd")
+    return y, ()
+
+
+def _swiglu_bwd(dy, tensors, saved, needs):
+    g, u = tensors
+    gc, uc, dc = g.contiguous(), u.contiguous(), dy.contiguous()
+    dg, du = torch.empty_like(gc), torch.empty_like(uc)
+    _check(_lib.lib().dttt_swiglu_bwd(_p(gc), _p(uc), _p(dc), _p(dg), _p(du), gc.numel(), _stream()), "swiglu_bwd")
+    return dg, du
+
+
+_SWIGLU_SPEC = (_swiglu_fwd, _swiglu_bwd, lambda g, u: _ref.glu(g, u, "silu"))
+
+
+def swiglu(g, u):
+    from .functional import staged
+    if g.numel() % 8:
+        return _ref.glu(g, u, "silu")
+    if torch.is_grad_enabled() and (g.requires_grad or u.requires_grad):
+        return staged(_SWIGLU_SPEC, (g, u), ())
+    return _swiglu_fwd(g, u)[0]
+
+
+# ---- AdamW on a flat f32 range (in place)
+def adamw(p, m, v, g, lr, b1, b2, eps, wd, bc1, bc2, gscale):
+    _check(_lib.lib().dttt_adamw(_p(p), _p(m), _p(v), _p(g), p.numel(), float(lr), float(b1), float(b2), float(eps), float(wd),
+                                 float(bc1), float(bc2), float(gscale), _stream()), "adamw")
+
+
+# ---- per-sequence pieces of the inner step
+def seq_sumsq(ts):
+    """``[B]`` f32: sum over a list of ``[B, ...]`` tensors (f32 or bf16) of the squared entries per sequence."""
+    B = ts[0].shape[0]
+    out = torch.zeros(B, dtype=torch.float32, device=ts[0].device)
+    for t in ts:
+        tc = t.contiguous()
+        _check(_lib.lib().dttt_seq_sumsq(_p(tc), _p(out), B, tc.numel() // B, 1 if tc.dtype == torch.bfloat16 else 0, _stream()),
+               "seq_sumsq")
+    return out
+
+
+def seq_axpy(w, g, coef, want_lo=False):
+    """``w - coef[b] * g`` per sequence: ``w [B, ...]`` f32, ``g`` f32 or bf16, ``coef [B]`` f32.  Returns the f32
+    result and, with ``want_lo``, its bf16 copy produced in the same pass."""
+    B = w.shape[0]
+    wc, gc = w.contiguous(), g.contiguous()
+    out = torch.empty_like(wc)
+    lo = torch.empty(wc.shape, dtype=torch.bfloat16, device=w.device) if want_lo else None
+    _check(_lib.lib().dttt_seq_axpy(_p(wc), _p(gc), _p(coef.float().contiguous()), _p(out), _p(lo), B, wc.numel() // B,
+                                    1 if gc.dtype == torch.bfloat16 else 0, _stream()), "seq_axpy")
+    return (out, lo) if want_lo else out

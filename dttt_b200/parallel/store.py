@@ -1,0 +1,189 @@
+"""Sharded parameter storage: f32 masters and optimiser moments split over the FSDP group, full
+compute copies and full f32 gradient buffers on every rank.
+
+The reference keeps f32 masters and Adam moments sharded on the last divisible axis of every array
+and lets XLA all-gather bf16 copies per use (``src/ttt/sharding.py:39-52``, ``train.py:678-707``).  On a
+180 GB part the full bf16 copy of a 1.4 B model is 3 GB, so this store gathers every compute copy once
+per step and keeps it resident; what is sharded is what is large and persistent: the f32 master, the
+two Adam moments (``1/fsdp`` of ``12 bytes x params`` per rank).
+
+Layout: parameters are laid out back to back in two flat index spaces, *big* (matrices: compute dtype
+copies) and *small* (norm weights, biases, gates, scalars: used in f32).  Every parameter is a shaped
+view into the flat buffers.  Rank ``r`` of the FSDP group owns the flat slice
+``[r * n / fsdp, (r + 1) * n / fsdp)`` of each space, regardless of parameter boundaries.
+
+A step is: ``zero_grad`` -> forward/backward (gradients land in ``grad_*`` by GEMM-epilogue
+accumulation or ``fold_grads``) -> ``reduce_grads`` (reduce-scatter over fsdp, all-reduce over dp) ->
+optimiser on the shards (``optim.ShardedAdamW``) -> ``sync_compute`` (cast + all-gather).
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..models.params import is_small
+from .mesh import Mesh
+
+ALIGN = 64          # elements; keeps every parameter view 128-byte aligned in bf16
+
+
+class ParamStore:
+    def __init__(self, spec: "OrderedDict[str, Tuple[Tuple[int, ...], str]]", mesh: Mesh, compute_dtype: torch.dtype,
+                 device: torch.device, trainable: bool = True):
+        self.spec, self.mesh, self.dtype, self.device = spec, mesh, compute_dtype, device
+        self.trainable = trainable
+        self.fs = mesh.fsdp
+        self.slots: Dict[str, Tuple[str, int, int, Tuple[int, ...]]] = {}      # name -> (space, offset, numel, shape)
+        offs = {"big": 0, "small": 0}
+        for name, (shape, _) in spec.items():
+            space = "small" if is_small(name) else "big"
+            n = math.prod(shape) if shape else 1
+            self.slots[name] = (space, offs[space], n, tuple(shape))
+            offs[space] += -(-n // ALIGN) * ALIGN
+        pad = ALIGN * self.fs
+        self.n = {k: max(pad, -(-v // pad) * pad) for k, v in offs.items()}
+        self.shard_n = {k: v // self.fs for k, v in self.n.items()}
+        f32 = torch.float32
+        self.lo = {"big": torch.zeros(self.n["big"], dtype=compute_dtype, device=device),
+                   "small": torch.zeros(self.n["small"], dtype=f32, device=device)}
+        self.grad = {k: torch.zeros(self.n[k], dtype=f32, device=device) for k in ("big", "small")} if trainable else None
+        ns = self.shard_n["big"] + self.shard_n["small"]
+        self.master = torch.zeros(ns, dtype=f32, device=device)                   # [big shard | small shard]
+        self.grad_shard = torch.zeros(ns, dtype=f32, device=device) if trainable else None
+
+    # ---- geometry
+    def shard_range(self, space: str) -> Tuple[int, int]:
+        r = self.mesh.fsdp_index
+        return r * self.shard_n[space], (r + 1) * self.shard_n[space]
+
+    def master_part(self, space: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        buf = self.master if buf is None else buf
+        nb = self.shard_n["big"]
+        return buf[:nb] if space == "big" else buf[nb:]
+
+    def segments(self) -> List[Tuple[str, int, int]]:
+        """``(name, start, end)`` ranges of this rank's master shard (indices into ``self.master``)."""
+        out = []
+        for name, (space, off, n, _) in self.slots.items():
+            lo, hi = self.shard_range(space)
+            a, b = max(off, lo), min(off + n, hi)
+            if a < b:
+                base = 0 if space == "big" else self.shard_n["big"]
+                out.append((name, base + a - lo, base + b - lo))
+        return out
+
+    # ---- views
+    def lo_view(self, name: str) -> torch.Tensor:
+        space, off, n, shape = self.slots[name]
+        return self.lo[space][off:off + n].view(shape)
+
+    def grad_view(self, name: str) -> torch.Tensor:
+        space, off, n, shape = self.slots[name]
+        return self.grad[space][off:off + n].view(shape)
+
+    def names(self):
+        return self.slots.keys()
+
+    # ---- filling
+    def load_full(self, name: str, value: torch.Tensor) -> None:
+        """Set parameter ``name`` from a full f32 tensor (every rank passes the same values)."""
+        space, off, n, shape = self.slots[name]
+        v = value.to(device=self.device, dtype=torch.float32).reshape(-1)
+        assert v.numel() == n, (name, tuple(value.shape), shape)
+        self.lo[space][off:off + n].copy_(v)
+        lo, hi = self.shard_range(space)
+        a, b = max(off, lo), min(off + n, hi)
+        if a < b:
+            self.master_part(space)[a - lo:b - lo].copy_(v[a - off:b - off])
+
+    def gather_full(self, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The full f32 value of ``name`` assembled from the master shards (collective over the FSDP group).
+        ``buf``: another sharded buffer laid out like the master (an Adam moment)."""
+        space, off, n, shape = self.slots[name]
+        part = self.master_part(space, buf)
+        if self.fs == 1:
+            return part[off:off + n].view(shape).clone()
+        full = torch.empty(self.n[space], dtype=torch.float32, device=self.device)
+        dist.all_gather_into_tensor(full, part.contiguous(), group=self.mesh.fsdp_group)
+        return full[off:off + n].view(shape).clone()
+
+    # ---- the step's collectives
+    def zero_grad(self) -> None:
+        for g in self.grad.values():
+            g.zero_()
+
+    def reduce_grads(self) -> None:
+        """Sum the full gradient buffers over every data rank and leave this rank's slice in ``grad_shard``."""
+        m = self.mesh
+        for space in ("big", "small"):
+            out = self.master_part(space, self.grad_shard)
+            g = self.grad[space]
+            if self.fs > 1:
+                dist.reduce_scatter_tensor(out, g, op=dist.ReduceOp.SUM, group=m.fsdp_group)
+            else:
+                out.copy_(g)
+            if m.dp > 1:
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=m.dp_group)
+
+    def sync_compute(self) -> None:
+        """Refresh the compute copies from the (updated) master shards: cast, then all-gather."""
+        m = self.mesh
+        for space in ("big", "small"):
+            lo, hi = self.shard_range(space)
+            src = self.master_part(space)
+            self.lo[space][lo:hi].copy_(src)
+            if self.fs > 1:
+                dist.all_gather_into_tensor(self.lo[space], self.lo[space][lo:hi].clone(), group=m.fsdp_group)
+
+    def all_reduce_scalar(self, x: torch.Tensor, groups=("fsdp", "dp")) -> torch.Tensor:
+        m = self.mesh
+        if "fsdp" in groups and m.fsdp > 1:
+            dist.all_reduce(x, group=m.fsdp_group)
+        if "dp" in groups and m.dp > 1:
+            dist.all_reduce(x, group=m.dp_group)
+        return x
+
+
+class ComputeWeights:
+    """The compute view the model is run with: per-layer leaf tensors over a ``ParamStore``.
+
+    ``get(name, layer)`` returns a detached view of the store's compute copy, marked ``requires_grad``
+    when training.  Matrices carry ``grad_target = (f32 gradient view, layer)`` so the GEMM epilogue can
+    accumulate first-order weight gradients in place; whatever reaches a leaf through ordinary autograd is
+    added to the same buffers by ``fold_grads``."""
+
+    def __init__(self, store: ParamStore, train: bool = True):
+        self.store, self.train = store, train and store.trainable
+        self.dtype = store.dtype
+        self._leaves: Dict[Tuple[str, int], torch.Tensor] = {}
+
+    def has(self, name: str) -> bool:
+        return name in self.store.slots
+
+    def get(self, name: str, layer: Optional[int] = None) -> torch.Tensor:
+        key = (name, -1 if layer is None else layer)
+        t = self._leaves.get(key)
+        if t is None:
+            base = self.store.lo_view(name)
+            t = (base if layer is None else base[layer]).detach()
+            if self.train:
+                t.requires_grad_(True)
+                if not is_small(name):
+                    t.grad_target = (self.store.grad_view(name), layer)
+            self._leaves[key] = t
+        return t
+
+    def grad_buffer(self, name: str) -> torch.Tensor:
+        return self.store.grad_view(name)
+
+    def fold_grads(self) -> None:
+        for (name, layer), t in self._leaves.items():
+            if t.grad is None:
+                continue
+            g = self.store.grad_view(name)
+            (g if layer < 0 else g[layer]).add_(t.grad)
+            t.grad = None

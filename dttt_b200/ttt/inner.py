@@ -105,7 +105,10 @@ def unflat(ts: Sequence[torch.Tensor]) -> FastW:
 
 def seq_norm(ts: Sequence[torch.Tensor]) -> torch.Tensor:
     """Per-sequence global norm ``[B]`` over a list of ``[B, ...]`` tensors: ``sqrt(sum sq + 1e-8)``."""
-    sq = sum(t.float().pow(2).flatten(1).sum(1) for t in ts)
+    from ..ops import kernels
+    if ts[0].is_cuda and not torch.is_grad_enabled() and kernels.available("seq"):
+        return torch.sqrt(kernels.seq_sumsq(list(ts)) + 1e-8)
+    sq = sum(torch.linalg.vector_norm(t.flatten(1), dim=1, dtype=torch.float32).pow(2) for t in ts)
     return torch.sqrt(sq + 1e-8)
 
 
@@ -342,6 +345,29 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
     net = model
     Wl = flat(W)
     g = [x.float() for x in g]
+    plain = (rule == "sgd" and unit_mask is None and frac >= 1.0 and scale is None
+             and not net.cw.has("inner_precond.0.gate.weight") and not net.cw.has("inner_gate.weight")
+             and not net.cw.has("inner_decay_logit"))
+    if plain:
+        # the main line: one norm, one fused multiply-add per matrix
+        norm = seq_norm(g)
+        s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
+        B = Wl[0].shape[0]
+        eta = torch.full((len(W),), float(lr), dtype=torch.float32, device=Wl[0].device)
+        if net.cw.has("inner_step_log"):
+            eta = eta * torch.exp(net.p("inner_step_log").float())
+        coef = s[:, None] * eta[None, :]                                    # [B, F]
+        from ..ops import kernels
+        fused = Wl[0].is_cuda and not torch.is_grad_enabled() and kernels.available("seq")
+        new = []
+        for f in range(len(W)):
+            for j in range(3):
+                p, d = Wl[3 * f + j], g[3 * f + j]
+                if fused:
+                    new.append(kernels.seq_axpy(p, d, coef[:, f]))
+                else:
+                    new.append(torch.addcmul(p, coef[:, f].view(B, 1, 1), d, value=-1.0))
+        return unflat(new), norm
     if unit_mask is not None:
         g = mask_units(g, unit_mask)
     u = direction(g, rule)

@@ -15,11 +15,13 @@ from typing import Callable, Sequence, Tuple
 
 import torch
 
+from ..utils import prof
+
 
 class _Region(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, fn, *inputs):
-        ctx.fn = fn
+    def forward(ctx, fn, label, *inputs):
+        ctx.fn, ctx.label = fn, label
         ctx.save_for_backward(*inputs)
         with torch.no_grad():
             outs = fn(*inputs)
@@ -31,17 +33,18 @@ class _Region(torch.autograd.Function):
     def backward(ctx, *gouts):
         inputs = ctx.saved_tensors
         det = [t.detach().requires_grad_(t.is_floating_point() and need)
-               for t, need in zip(inputs, ctx.needs_input_grad[1:])]
-        with torch.enable_grad():
-            outs = tuple(ctx.fn(*det))
-        sel = [(o, g) for o, g in zip(outs, gouts) if g is not None and o.requires_grad]
-        if sel:
-            torch.autograd.backward([o for o, _ in sel], [g for _, g in sel])
-        return (None, *[d.grad if d.requires_grad else None for d in det])
+               for t, need in zip(inputs, ctx.needs_input_grad[2:])]
+        with prof.range(ctx.label or "region.bwd"):
+            with torch.enable_grad():
+                outs = tuple(ctx.fn(*det))
+            sel = [(o, g) for o, g in zip(outs, gouts) if g is not None and o.requires_grad]
+            if sel:
+                torch.autograd.backward([o for o, _ in sel], [g for _, g in sel])
+        return (None, None, *[d.grad if d.requires_grad else None for d in det])
 
 
-def region(fn: Callable, inputs: Sequence[torch.Tensor], enabled: bool = True) -> Tuple[torch.Tensor, ...]:
-    """``fn(*inputs)`` as a recompute region (``enabled``) or directly."""
+def region(fn: Callable, inputs: Sequence[torch.Tensor], enabled: bool = True, label: str = "") -> Tuple[torch.Tensor, ...]:
+    """``fn(*inputs)`` as a recompute region (``enabled``) or directly; ``label`` names its backward in ``utils.prof``."""
     if not enabled or not torch.is_grad_enabled():
         return tuple(fn(*inputs))
-    return _Region.apply(fn, *inputs)
+    return _Region.apply(fn, label, *inputs)

@@ -28,7 +28,7 @@ from ..ops import attention as A
 from ..ops import ce as CE
 from ..ops import functional as Fn
 from ..ops import reference as ref
-from ..utils import rng
+from ..utils import prof, rng
 from . import inner as IN
 from . import objective as OBJ
 from .regions import region
@@ -131,8 +131,14 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         if cfg.inner_from_outer or cfg.write_off or cfg.distill or cfg.mtp or cfg.inner_feat != "off":
             raise ValueError("memory gdn: no inner stream (inner_from_outer / write_off / distill / mtp / inner_feat do not apply)")
         cfg = dc.replace(cfg, no_write=True)
+    # Everything up to the first model call (noising, weights, inner masks, positions) is integer / small-float
+    # work on [B, T] arrays: it runs on the host, where the token ids come from, and is moved to the device in
+    # one go; the device queue never waits on it.
+    run_dev = net.p("final_norm.weight").device
+    host = torch.device("cpu")
+    batch = Batch(*[None if x is None else x.to(host) for x in batch])
     ids = batch.input_ids.long()
-    dev = ids.device
+    dev = host
     B, T = ids.shape
     C, Wn, S, F_ = mc.chunk_size, mc.window_chunks, mc.suffix_len, mc.fast_len
     if T % C:
@@ -370,6 +376,17 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         pq = [p_q_outer_full, pos] + [p_q] * n_inner + [p_q_outer_full] * (n_teacher + VO - 1)
         pos_k_streams, pos_q_streams = torch.stack(pk, 1), torch.stack(pq, 1)
 
+    # ---- host -> device, once
+    dev = run_dev
+    D = lambda x: None if x is None else x.to(dev, non_blocking=True)
+    ids_streams, pos_k_streams, pos_q_streams, pos_c = D(ids_streams), D(pos_k_streams), D(pos_q_streams), D(pos_c)
+    inner_mask_c, target_c, pos_in_c, pos_q_c, tgt_idx_c = D(inner_mask_c), D(target_c), D(pos_in_c), D(pos_q_c), D(tgt_idx_c)
+    m_teacher_c, mtp_tgt_c, mtp_mask_c, sp_flags, read_own = D(m_teacher_c), D(mtp_tgt_c), D(mtp_mask_c), D(sp_flags), D(read_own)
+    weight, m_outer, tgt_outer = D(weight), D(m_outer), D(tgt_outer)
+    extra_views = [tuple(D(x) for x in v) for v in extra_views]
+    if cfg.mtp:
+        tgt_mtp, w_mtp, m_mtp = D(tgt_mtp), D(w_mtp), D(m_mtp)
+
     # ---- carries at the sequence start
     kvp = None                                                                      # per prefix layer (k, v) tails
     kvs = [(torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev), torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev))
@@ -416,7 +433,8 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
                 hh, tail = net.prefix_layer(_l, h_in, _pk, _pq, _first, (w[0], w[1]) if _has else None, owns, reach, rb)
                 return hh, tail[0], tail[1]
             ins = (h,) + (tuple(win) if win is not None else ())
-            h, tk, tv = region(layer_fn, ins, use_regions)
+            with prof.range("prefix_layer.fwd"):
+                h, tk, tv = region(layer_fn, ins, use_regions, "prefix_layer.bwd")
             kvp_next.append((tk, tv))
         kvp = kvp_next if n_seg > 1 else None
         hch = h.unflatten(2, (n_seg_chunks, C))                                     # [B, NS, ncs, C, H]
@@ -456,7 +474,8 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
                 hv_ = ts[o:]
                 return _suffix_step(net, cfg, kv_l, memv, ho_, hc_, hi_, ht_, hv_, _k, W0, sp_flags, lr_now, distill_w,
                                     create_graph, own_inner, clean_own, read_own, clean_prime, s_S, s_T, B, C, S, use_gdn)
-            outs = region(step_fn, tuple(dyn), use_regions)
+            with prof.range("suffix_step.fwd"):
+                outs = region(step_fn, tuple(dyn), use_regions, "suffix_step.bwd")
             kvs = [(outs[2 * i], outs[2 * i + 1]) for i in range(S)]
             o = n_kv
             if use_gdn:
@@ -567,7 +586,8 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
         extras = IN.InnerExtras(soft_ids, soft_q, soft_mask, k["mtp_t"], k["mtp_m"])
 
     # B. clean -> next KV window; with memory gdn also the state written from this chunk
-    resB = sf(hc, mem if use_gdn else Wc, update=use_gdn, prime=clean_prime, own=clean_own)
+    with prof.range("step.B_clean"):
+        resB = sf(hc, mem if use_gdn else Wc, update=use_gdn, prime=clean_prime, own=clean_own)
     own_kv = resB[1]
     kv_next = [(torch.cat([ck[:, C:], ok], dim=1), torch.cat([cv[:, C:], ov], dim=1)) if ck.shape[1] else (ck, cv)
                for (ck, cv), (ok, ov) in zip(kv, own_kv)]
@@ -626,7 +646,8 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
                     post = plain_step(Wk, False)[1][0]
                     plan_ce = torch.stack([st[0], post])
             else:
-                W_next, st = plain_step(W)
+                with prof.range("step.C_write"):
+                    W_next, st = plain_step(W)
         if not cfg.second_order:
             W_next = [tuple(t.detach() for t in w) for w in W_next]
     if cfg.aux_causal_weight > 0 and not cfg.no_write and aux_term is None:
@@ -642,7 +663,8 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
         sel = [tuple(torch.where(sp_flags.view(B, 1, 1), b_, a_) for a_, b_ in zip(wa, wb)) for wa, wb in zip(W, W_next)]
         W_read = IN.cast_fast(sel, net.dtype)
     read_kv = own_kv if rb else None
-    hA = sf(ho, W_read, p_q_outer, own="full", own_mask=read_own, own_kv=read_kv)[0]
+    with prof.range("step.A_read"):
+        hA = sf(ho, W_read, p_q_outer, own="full", own_mask=read_own, own_kv=read_kv)[0]
     tok, wgt, tm = k["tok"], k["wgt"], k["tm"]
     ce_seq = mask_seq = torch.zeros(B, device=dev)
     if cfg.per_sequence:
@@ -650,7 +672,8 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
         ce_sum = ce_seq.sum()
         mask_seq = tm.float().sum(1)
     else:
-        ce_sum = CE.weighted_ce(hA.reshape(B * C, -1), lm_w, tok.reshape(-1), wgt.reshape(-1).float(), fb)
+        with prof.range("step.A_ce"):
+            ce_sum = CE.weighted_ce(hA.reshape(B * C, -1), lm_w, tok.reshape(-1), wgt.reshape(-1).float(), fb)
     ce2_sum = mask2 = zero
     if cfg.mtp and cfg.mtp_weight > 0:
         h2 = Fn.linear(hA, net.p("mtp_head.weight"))

@@ -1,0 +1,202 @@
+"""Numerics of every hand-written kernel against a plain PyTorch f32 statement of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    yield
+    from dttt_b200.ops import _lib
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-12)
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb,batch", [(256, 256, 128, 0, 0, 1), (300, 520, 200, 0, 1, 1), (384, 512, 256, 1, 0, 3),
+                                              (512, 128, 512, 1, 1, 1), (2048, 2048, 1024, 0, 0, 2), (130, 72, 1032, 0, 1, 1)])
+def test_gemm_layouts(M, N, K, ta, tb, batch):
+    from dttt_b200.ops import gemm
+    torch.manual_seed(0)
+    lead = (batch,) if batch > 1 else ()
+    a = torch.randn(*lead, *((K, M) if ta else (M, K)), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(*lead, *((N, K) if tb else (K, N)), device="cuda", dtype=torch.bfloat16)
+    c = gemm.gemm_raw(a, b, bool(ta), bool(tb))
+    ref = (a.transpose(-1, -2) if ta else a).float() @ (b.transpose(-1, -2) if tb else b).float()
+    assert _rel(c, ref) < 1e-2
+
+
+def test_gemm_f32_accumulate_and_views():
+    from dttt_b200.ops import gemm
+    torch.manual_seed(1)
+    a = torch.randn(512, 640, device="cuda", dtype=torch.bfloat16)[:, :256]          # row stride 640
+    b = torch.randn(256, 384, device="cuda", dtype=torch.bfloat16)
+    out = torch.ones(512, 384, device="cuda")
+    gemm.gemm_raw(a, b, False, False, torch.float32, out=out, accumulate=True, alpha=0.5)
+    assert _rel(out, 1.0 + 0.5 * (a.float() @ b.float())) < 1e-5
+
+
+def test_mm_autograd_double_backward():
+    from dttt_b200.ops import gemm
+    torch.manual_seed(2)
+    a = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = gemm.mm(a, b)
+    (ga,) = torch.autograd.grad((y.float() ** 2).sum(), a, create_graph=True)
+    (gb2,) = torch.autograd.grad(ga.float().pow(2).sum(), b)
+    a32, b32 = a.detach().float().requires_grad_(), b.detach().float().requires_grad_()
+    (ga_r,) = torch.autograd.grad(((a32 @ b32) ** 2).sum(), a32, create_graph=True)
+    (gb2_r,) = torch.autograd.grad(ga_r.pow(2).sum(), b32)
+    assert _rel(ga, ga_r) < 3e-2 and _rel(gb2, gb2_r) < 5e-2
+
+
+@pytest.mark.parametrize("rows,D", [(1000, 2048), (77, 64), (4096, 128), (33, 8192)])
+def test_rmsnorm(rows, D):
+    from dttt_b200.ops import kernels, reference as ref
+    torch.manual_seed(3)
+    x = torch.randn(rows, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).requires_grad_()
+    y = kernels.rms_norm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    dx, dw = torch.autograd.grad(y, (x, w), g)
+    x32, w32 = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = ref.rms_norm(x32, w32, 1e-6)
+    dxr, dwr = torch.autograd.grad(yr, (x32, w32), g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(dx, dxr) < 2e-2 and _rel(dw, dwr) < 2e-2
+
+
+def test_rmsnorm_second_order_matches_reference():
+    from dttt_b200.ops import kernels, reference as ref
+    torch.manual_seed(4)
+    x = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.ones(128, device="cuda", requires_grad=True)
+    y = kernels.rms_norm(x, w, 1e-6)
+    (dx,) = torch.autograd.grad(y.float().pow(2).sum(), x, create_graph=True)
+    (ddx,) = torch.autograd.grad(dx.float().pow(2).sum(), x)
+    x32 = x.detach().float().requires_grad_()
+    (dxr,) = torch.autograd.grad(ref.rms_norm(x32, w.detach(), 1e-6).pow(2).sum(), x32, create_graph=True)
+    (ddxr,) = torch.autograd.grad(dxr.pow(2).sum(), x32)
+    assert _rel(ddx, ddxr) < 0.1
+
+
+@pytest.mark.parametrize("d,heads", [(64, 8), (128, 4), (32, 3)])
+def test_rope(d, heads):
+    from dttt_b200.ops import functional as Fn, reference as ref
+    torch.manual_seed(5)
+    x = torch.randn(2, 300, heads, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    pos = torch.randint(0, 131072, (2, 300), device="cuda")
+    scaling = (("factor", 16.0), ("high_freq_factor", 4.0), ("low_freq_factor", 1.0),
+               ("original_max_position_embeddings", 8192), ("rope_type", "llama3"))
+    y = Fn.rope(x, pos, d, 500000.0, scaling)
+    g = torch.randn_like(y)
+    (dx,) = torch.autograd.grad(y, x, g)
+    x32 = x.detach().float().requires_grad_()
+    cos, sin = ref.rope_cos_sin(pos, d, 500000.0, scaling)
+    yr = ref.apply_rope(x32, cos, sin)
+    (dxr,) = torch.autograd.grad(yr, x32, g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(dx, dxr) < 1e-2
+
+
+def test_swiglu():
+    from dttt_b200.ops import kernels, reference as ref
+    torch.manual_seed(6)
+    g = torch.randn(513, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    u = torch.randn(513, 1024, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = kernels.swiglu(g, u)
+    dy = torch.randn_like(y)
+    dg, du = torch.autograd.grad(y, (g, u), dy)
+    g32, u32 = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    yr = ref.glu(g32, u32)
+    dgr, dur = torch.autograd.grad(yr, (g32, u32), dy.float())
+    assert _rel(y, yr) < 1e-2 and _rel(dg, dgr) < 2e-2 and _rel(du, dur) < 2e-2
+
+
+def test_adamw_and_seq_ops():
+    from dttt_b200.ops import kernels
+    torch.manual_seed(7)
+    n = 100_003
+    p, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v = v.abs()
+    p0, m0, v0 = p.clone(), m.clone(), v.clone()
+    kernels.adamw(p, m, v, g, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 0.5)
+    gg = g * 0.5
+    mr = 0.9 * m0 + 0.1 * gg
+    vr = 0.95 * v0 + 0.05 * gg * gg
+    pr = p0 - 1e-3 * ((mr / 0.1) / ((vr / 0.05).sqrt() + 1e-8) + 0.1 * p0)
+    assert _rel(p, pr) < 1e-5 and _rel(m, mr) < 1e-6 and _rel(v, vr) < 1e-6
+    w = torch.randn(3, 700, 33, device="cuda")
+    gb = torch.randn(3, 700, 33, device="cuda", dtype=torch.bfloat16)
+    ss = kernels.seq_sumsq([w, gb])
+    assert _rel(ss, w.pow(2).flatten(1).sum(1) + gb.float().pow(2).flatten(1).sum(1)) < 1e-4
+    coef = torch.tensor([0.5, 1.0, 2.0], device="cuda")
+    out, lo = kernels.seq_axpy(w, gb, coef, want_lo=True)
+    refv = w - coef.view(3, 1, 1) * gb.float()
+    assert _rel(out, refv) < 1e-6 and _rel(lo, refv) < 1e-2
+
+
+def test_weighted_ce_matches_dense_with_grads():
+    from dttt_b200.ops import ce as CE, reference as ref
+    torch.manual_seed(8)
+    N, H, V = 512, 256, 5000
+    h = (0.5 * torch.randn(N, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    E = (0.1 * torch.randn(V, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    y = torch.randint(0, V, (N,), device="cuda")
+    w = torch.rand(N, device="cuda")
+    loss = CE.weighted_ce(h, E, y, w, 2048)
+    gh, gE = torch.autograd.grad(loss, (h, E))
+    h32, E32 = h.detach().float().requires_grad_(), E.detach().float().requires_grad_()
+    lr = ref.weighted_ce_dense(h32, E32, y, w)
+    ghr, gEr = torch.autograd.grad(lr, (h32, E32))
+    assert abs(loss.item() - lr.item()) / lr.item() < 5e-3
+    assert _rel(gh, ghr) < 3e-2 and _rel(gE, gEr) < 3e-2
+    pt = CE.per_token_ce(h.detach(), E.detach(), y, 2048)
+    assert _rel(pt, ref.per_token_ce_dense(h32.detach(), E32.detach(), y)) < 1e-2
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_window_staged(causal):
+    from dttt_b200.ops import attention as A, reference as ref
+    torch.manual_seed(9)
+    n, C, nh, nkv, d, W = 2, 128, 8, 2, 64, 3
+    q = torch.randn(n, C, nh, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(n, C, nkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(n, C, nkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    kw = torch.randn(n, W * C, nkv, d, device="cuda", dtype=torch.bfloat16)
+    vw = torch.randn(n, W * C, nkv, d, device="cuda", dtype=torch.bfloat16)
+    o = A.attend_window(q, k, v, kw, vw, 2, C, d ** -0.5, own="causal" if causal else "full")
+    g = torch.randn_like(o)
+    dq, dk, dv = torch.autograd.grad(o, (q, k, v), g)
+    q32, k32, v32 = (t.detach().float().requires_grad_() for t in (q, k, v))
+    K = torch.cat([kw[:, C:].float(), k32], 1)
+    V = torch.cat([vw[:, C:].float(), v32], 1)
+    om = A.own_mask_matrix(C, "causal", "cuda") if causal else None
+    orf = ref.attend(q32, K, V, None, d ** -0.5, om)
+    dqr, dkr, dvr = torch.autograd.grad(orf, (q32, k32, v32), g.float())
+    assert _rel(o, orf) < 2e-2 and _rel(dq, dqr) < 3e-2 and _rel(dk, dkr) < 3e-2 and _rel(dv, dvr) < 3e-2
+    # recorded backward (second order path) agrees with the first-order kernels
+    o2 = A.attend_window(q, k, v, kw, vw, 2, C, d ** -0.5, own="causal" if causal else "full")
+    (dq2,) = torch.autograd.grad(o2, q, g, create_graph=True)
+    assert _rel(dq2, dqr) < 3e-2
+
+
+def test_train_step_bf16_close_to_f32_cpu():
+    """One training step of a small model: bf16 kernels on the GPU against the f32 CPU path."""
+    from dttt_b200.engine import Engine
+    from dttt_b200.schema import ModelConfig, TrainConfig
+    mc = ModelConfig(vocab_size=2048, hidden_size=128, intermediate_size=256, num_hidden_layers=3, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=32, suffix_len=2, chunk_size=64, window_chunks=2, qk_norm=True,
+                     mask_token_id=2047, pad_token_id=2046, eos_token_id=2046)
+    kw = dict(seq_len=256, batch_size=2, steps=10, warmup_steps=2, inner_lr_warmup_steps=0, inner_task="causal", outer_shift=True,
+              cart_window=32, fused_ce_block=512)
+    ids = torch.randint(0, 2000, (2, 256))
+    out = {}
+    for name, dev, dt in (("gpu", "cuda", "bfloat16"), ("cpu", "cpu", "float32")):
+        eng = Engine(mc, TrainConfig(compute_dtype=dt, **kw), device=torch.device(dev))
+        out[name] = eng.train_step(ids, 0)
+    for k in ("main_loss", "inner_loss", "grad_norm", "inner_grad_norm"):
+        a, b = out["gpu"][k], out["cpu"][k]
+        assert abs(a - b) / (abs(b) + 1e-6) < 0.05, (k, a, b)
