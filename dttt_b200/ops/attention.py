@@ -187,7 +187,7 @@ def _fast_fwd(q, K, V, scale, causal):
         o, lse = kernels.attention_fwd(q, K, V, scale, causal)
         return o, (o, lse)
     with torch.no_grad():
-        o = _sdpa_fast(q, K, V, scale, causal)
+        o = _sdpa_fast(q, K, V, scale, causal) if q.is_cuda else _ref_for_staged(q, K, V, scale, causal)
     return o, ()
 
 
@@ -198,5 +198,5 @@ def _fast_bwd(g, tensors, saved, needs, scale, causal):
         return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, causal)
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))
-        o = _sdpa_fast(qq, kk, vv, scale, causal)
+        o = _sdpa_fast(qq, kk, vv, scale, causal) if q.is_cuda else _ref_for_staged(qq, kk, vv, scale, causal)
         return torch.autograd.grad(o, (qq, kk, vv), g)

@@ -112,9 +112,9 @@ _SPEC = (_ce_fwd, _ce_bwd, _ce_ref)
 
 def weighted_ce(h: torch.Tensor, E: torch.Tensor, targets: torch.Tensor, weights: torch.Tensor, block: int = 8192) -> torch.Tensor:
     """``sum_i w_i CE_i`` (f32 scalar).  ``block == 0``: the dense reference (tests)."""
-    if block <= 0 or not (h.is_cuda or h.requires_grad or E.requires_grad):
+    if block <= 0:
         return ref.weighted_ce_dense(h, E, targets, weights)
-    if not h.is_cuda:
+    if not h.is_cuda and not _gemm.EMULATE:
         # CPU: the streamed forward is only a memory device; autograd through the dense statement is exact
         return ref.weighted_ce_dense(h, E, targets, weights)
     return staged(_SPEC, (h, E, targets, weights), (block, getattr(E, "grad_target", None)))

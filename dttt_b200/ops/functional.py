@@ -29,7 +29,7 @@ mm = _gemm.mm
 def use_kernels(*tensors: torch.Tensor) -> bool:
     """Kernels run for CUDA bf16 activations; anything else takes the reference path."""
     t = tensors[0]
-    return t.is_cuda and t.dtype == torch.bfloat16 and not _gemm._FORCE_TORCH
+    return (t.is_cuda or _gemm.EMULATE) and t.dtype == torch.bfloat16 and not _gemm._FORCE_TORCH
 
 
 class _Staged(torch.autograd.Function):

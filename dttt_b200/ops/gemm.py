@@ -20,12 +20,31 @@ import torch
 
 from . import _lib
 
+import os
+
 _FORCE_TORCH = False          # tests flip this to compare the kernel against torch.matmul
 LAUNCHES = 0                  # kernel launches issued by this module (bench accounting)
+# DTTT_EMULATE=1: run the kernel code paths (custom autograd functions, in-place f32 gradient accumulation,
+# staged backward) on CPU bf16 tensors with every device kernel replaced by its PyTorch statement.  It lets the
+# CPU test-suite exercise exactly the control flow a GPU run takes.
+EMULATE = os.environ.get("DTTT_EMULATE", "0") == "1"
 
 
 def _kernel_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and not _FORCE_TORCH
+    return (x.is_cuda or EMULATE) and x.dtype == torch.bfloat16 and not _FORCE_TORCH
+
+
+def _emulated_gemm(a, b, ta, tb, out_dtype, out, accumulate, alpha):
+    x = a.transpose(-1, -2) if ta else a
+    y = b.transpose(-1, -2) if tb else b
+    r = torch.matmul(x.float(), y.float()) * alpha
+    if out is None:
+        return r.to(out_dtype)
+    if accumulate:
+        out.copy_((out.float() + r).to(out.dtype))
+    else:
+        out.copy_(r.to(out.dtype))
+    return out
 
 
 def _as_rows(x: torch.Tensor) -> torch.Tensor:
@@ -47,6 +66,9 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
     every batch entry of a 3-D one.  ``out`` (+ ``accumulate``) writes / adds into an existing tensor."""
     global LAUNCHES
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, (a.dtype, b.dtype)
+    if not a.is_cuda:
+        LAUNCHES += 1
+        return _emulated_gemm(a, b, ta, tb, out_dtype, out, accumulate, alpha)
     a, b = _as_rows(a), _as_rows(b)
     M, K = (a.shape[-1], a.shape[-2]) if ta else (a.shape[-2], a.shape[-1])
     Kb, N = (b.shape[-1], b.shape[-2]) if tb else (b.shape[-2], b.shape[-1])
@@ -56,8 +78,6 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
         batch = a.shape[0] if a.dim() == 3 else b.shape[0]
         if a.dim() == 3 and b.dim() == 3:
             assert a.shape[0] == b.shape[0]
-    if a.dim() == 2 and b.dim() == 3 and not ta and not tb and False:
-        pass
     a_batch = a.stride(0) if a.dim() == 3 else 0
     b_batch = b.stride(0) if b.dim() == 3 else 0
     if batch > 1 and a.dim() == 3 and b.dim() == 2 and not ta and a.is_contiguous():

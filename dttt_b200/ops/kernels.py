@@ -19,7 +19,12 @@ LAUNCHES = 0
 
 
 def available(name: str) -> bool:
-    if name in _DISABLED or not torch.cuda.is_available():
+    from . import gemm as _g
+    if name in _DISABLED:
+        return False
+    if _g.EMULATE and not torch.cuda.is_available():
+        return name in _EMULATED
+    if not torch.cuda.is_available():
         return False
     ok = _FAMILIES.get(name)
     if ok is None:
@@ -39,6 +44,8 @@ def enable(name: str) -> None:
 
 # family -> a symbol whose presence means the family is built
 _SYMBOL: Dict[str, str] = {}
+# families whose launchers have a PyTorch stand-in for CPU tensors (DTTT_EMULATE=1, see ops.gemm)
+_EMULATED = {"rmsnorm", "rope", "swiglu"}
 
 # =============================================================================== elementwise family
 import ctypes as _ct
@@ -81,6 +88,10 @@ def _rms_fwd(x, w, eps):
     y = torch.empty_like(xc)
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     wf = w.detach().float().contiguous()
+    if not x.is_cuda:
+        x32 = xc.float()
+        r = torch.rsqrt(x32.pow(2).mean(-1) + eps)
+        return (wf * x32 * r[..., None]).to(x.dtype), (r.reshape(-1),)
     _check(_lib.lib().dttt_rmsnorm_fwd(_p(xc), _p(wf), _p(y), _p(rstd), rows, D, float(eps), _stream()), "rmsnorm_fwd")
     return y, (rstd,)
 
@@ -94,6 +105,11 @@ def _rms_bwd(g, tensors, saved, needs, eps):
     dx = torch.empty_like(xc)
     dw = torch.zeros(D, dtype=torch.float32, device=x.device) if needs[1] else None
     wf = w.detach().float().contiguous()
+    if not x.is_cuda:
+        x32, g32, r = xc.float().reshape(rows, D), gc.float().reshape(rows, D), rstd[:, None]
+        xh = x32 * r
+        dxv = r * (wf * g32 - xh * (wf * g32 * xh).mean(-1, keepdim=True))
+        return dxv.to(x.dtype).view(x.shape), ((g32 * xh).sum(0).to(w.dtype) if needs[1] else None)
     _check(_lib.lib().dttt_rmsnorm_bwd(_p(xc), _p(wf), _p(gc), _p(rstd), _p(dx), _p(dw), rows, D, _stream()), "rmsnorm_bwd")
     return dx, (dw.to(w.dtype) if dw is not None else None)
 
@@ -118,6 +134,10 @@ def _rope_run(x, pos, inv_freq, sign):
     out = torch.empty_like(xc)
     pc = pos.contiguous()
     assert pc.numel() == rows and pc.dtype == torch.int64, (pc.shape, rows, pc.dtype)
+    if not x.is_cuda:
+        ang = pc.float().unsqueeze(-1) * inv_freq
+        emb = torch.cat([ang, ang], dim=-1)
+        return _ref.apply_rope(xc, emb.cos(), sign * emb.sin())
     _check(_lib.lib().dttt_rope(_p(xc), _p(out), _p(pc), _p(inv_freq), rows, heads, d, float(sign), _stream()), "rope")
     return out
 
@@ -146,6 +166,8 @@ def rope(x, pos, inv_freq):
 # ---- SwiGLU
 def _swiglu_fwd(g, u):
     gc, uc = g.contiguous(), u.contiguous()
+    if not g.is_cuda:
+        return _ref.glu(gc.float(), uc.float()).to(g.dtype), ()
     y = torch.empty_like(gc)
     _check(_lib.lib().dttt_swiglu_fwd(_p(gc), _p(uc), _p(y), gc.numel(), _stream()), "swiglu_fwd")
     return y, ()
@@ -154,6 +176,10 @@ def _swiglu_fwd(g, u):
 def _swiglu_bwd(dy, tensors, saved, needs):
     g, u = tensors
     gc, uc, dc = g.contiguous(), u.contiguous(), dy.contiguous()
+    if not g.is_cuda:
+        sg = torch.sigmoid(gc.float())
+        silu = gc.float() * sg
+        return (dc.float() * uc.float() * (sg + silu * (1 - sg))).to(g.dtype), (dc.float() * silu).to(u.dtype)
     dg, du = torch.empty_like(gc), torch.empty_like(uc)
     _check(_lib.lib().dttt_swiglu_bwd(_p(gc), _p(uc), _p(dc), _p(dg), _p(du), gc.numel(), _stream()), "swiglu_bwd")
     return dg, du

@@ -313,6 +313,12 @@ def inner_grad(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid, f
     extras = kw.get("extras")
     soft_first_order = extras is not None and extras.soft_ids is not None and not distill_meta
     Wl = flat(W)
+    if not create_graph:
+        # a first-order write: nothing outside this call may see the graph built here
+        h_inner = h_inner.detach()
+        kv = [(a.detach(), b.detach()) for a, b in kv]
+        h_clean = None if h_clean is None else h_clean.detach()
+        tok_w = None if tok_w is None else tok_w.detach()
     with torch.enable_grad():
         if not create_graph:
             Wl = [w.detach().requires_grad_(True) for w in Wl]

@@ -547,6 +547,9 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
     ``(kv_next..., memory..., ce_sum, mask_count, ce2_sum, mask2_count, distill_mass, inner stats [7], plan_ce [2],
     ce_seq [B], mask_seq [B], ce_tok, mask_tok, aux)``."""
     dev = ho.device
+    # the outer gradient flows through the write only in a recorded pass; a region's first (unrecorded) run
+    # takes the inner gradient at first order
+    create_graph = create_graph and torch.is_grad_enabled()
     nv, p = k["nv"], k["p"]
     fb = cfg.fused_ce_block
     lm_w = net.lm_weight()

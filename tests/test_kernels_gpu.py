@@ -74,11 +74,12 @@ def test_rmsnorm_second_order_matches_reference():
     torch.manual_seed(4)
     x = torch.randn(64, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     w = torch.ones(128, device="cuda", requires_grad=True)
+    r = torch.randn(64, 128, device="cuda")
     y = kernels.rms_norm(x, w, 1e-6)
-    (dx,) = torch.autograd.grad(y.float().pow(2).sum(), x, create_graph=True)
+    (dx,) = torch.autograd.grad((y.float() * r).sum(), x, create_graph=True)
     (ddx,) = torch.autograd.grad(dx.float().pow(2).sum(), x)
     x32 = x.detach().float().requires_grad_()
-    (dxr,) = torch.autograd.grad(ref.rms_norm(x32, w.detach(), 1e-6).pow(2).sum(), x32, create_graph=True)
+    (dxr,) = torch.autograd.grad((ref.rms_norm(x32, w.detach(), 1e-6) * r).sum(), x32, create_graph=True)
     (ddxr,) = torch.autograd.grad(dxr.pow(2).sum(), x32)
     assert _rel(ddx, ddxr) < 0.1
 
