@@ -41,11 +41,14 @@ def zipf_tokens(n: int, vocab: int, seed: int, s: float = 1.1, eos: Optional[int
     return toks
 
 
-def write_stream(path: str, tokens: np.ndarray, eos: int, name: str = "synthetic", tokenizer: str = "synthetic-zipf") -> str:
+def write_stream(path: str, tokens: np.ndarray, eos: int, name: str = "synthetic", vocab: int = 0) -> str:
     os.makedirs(path, exist_ok=True)
     tokens.astype("<u4").tofile(os.path.join(path, "tokens.u32"))
-    meta = {"name": name, "num_tokens": int(tokens.size), "num_docs": int((tokens == eos).sum()), "eos_token_id": int(eos),
-            "tokenizer": tokenizer, "dtype": "uint32", "max_token_id": int(tokens.max())}
+    vocab = int(vocab or int(tokens.max()) + 1)
+    meta = {"name": name, "files": [], "min_doc_tokens": 0, "bos": False, "sep": "eos", "clean": "",
+            "tokenizer": {"class": "synthetic-zipf", "len": vocab, "vocab_size": vocab, "eos_token_id": int(eos),
+                          "bos_token_id": None},
+            "num_docs": int((tokens == eos).sum()), "dropped_docs": 0, "num_tokens": int(tokens.size)}
     with open(os.path.join(path, "meta.json"), "w") as fh:
         json.dump(meta, fh, indent=2)
     return path
