@@ -80,7 +80,7 @@ def bits(k: torch.Tensor, shape: Sequence[int], start: int = 0, count: int = -1)
     i = torch.arange(lo_i, hi_i, dtype=torch.int64, device=k.device)
     y0, y1 = threefry2x32(k[..., 0:1], k[..., 1:2], (i >> 32) & M32, i & M32)
     out = y0 ^ y1
-    return out.reshape(*k.shape[:-1], *shape) if count < 0 else out
+    return out.reshape(tuple(k.shape[:-1]) + tuple(shape)) if count < 0 else out
 
 
 def _to_unit(b: torch.Tensor) -> torch.Tensor:
