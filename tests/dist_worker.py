@@ -1,0 +1,52 @@
+"""Worker for the multi-process CPU tests (gloo): ``python dist_worker.py <case> <out_dir>`` under torchrun-style env."""
+import json
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from util import tiny_model, tiny_train  # noqa: E402
+from dttt_b200.engine import Engine  # noqa: E402
+from dttt_b200.parallel.mesh import init_distributed, make_mesh  # noqa: E402
+from dttt_b200.ckpt import store as CK  # noqa: E402
+
+
+def main():
+    case, out = sys.argv[1], sys.argv[2]
+    rank, world, _ = init_distributed("gloo", timeout_s=int(os.environ.get("TEST_TIMEOUT_S", "60")))
+    fsdp = int(os.environ.get("TEST_FSDP", "0"))
+    mesh = make_mesh(fsdp, 1, torch.device("cpu"))
+    eng = Engine(tiny_model(), tiny_train(batch_size=4, fsdp_size=fsdp), mesh, torch.device("cpu"))
+    ids = torch.randint(0, 120, (4, 32), generator=torch.Generator().manual_seed(0))
+    n = 4 // mesh.batch_ranks
+    mine = ids[mesh.batch_index * n:(mesh.batch_index + 1) * n]
+    if case == "train":
+        ms = [eng.train_step(mine, s) for s in range(3)]
+        full = {k: eng.store.gather_full(k) for k in eng.store.names()}
+        d = CK.save(os.path.join(out, "ck"), 2, eng, "h")
+        if rank == 0:
+            torch.save({"metrics": ms, "params": full, "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
+    elif case == "rank_exits":
+        # rank 1 leaves between steps (no collective in flight); the others must get an error, not hang
+        eng.train_step(mine, 0)
+        if rank == 1:
+            os._exit(7)
+        t0 = time.time()
+        try:
+            eng.train_step(mine, 1)
+            outcome = "no error"
+        except Exception as e:                                    # noqa: BLE001
+            outcome = type(e).__name__
+        with open(os.path.join(out, f"rank{rank}.json"), "w") as fh:
+            json.dump({"outcome": outcome, "seconds": time.time() - t0}, fh)
+        os._exit(0)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
