@@ -1,0 +1,343 @@
+// Chunk-window flash attention, forward, on tcgen05 tensor cores with the score and output accumulators
+// in tensor memory.
+//
+//   O[b, i, h, :] = softmax_j( scale * Q[b, i, h, :] . K[b, j, h / rep, :] + mask(i, j) ) V[b, j, h / rep, :]
+//
+// Q [n, Cq, nh, d], K / V [n, Kn, nkv, d] (bf16, d contiguous), O like Q, LSE [n, nh, Cq] (f32, natural log).
+// Every key is valid (the caller slices the valid suffix of the KV window, reference src/ttt/attention.py:109-120);
+// `causal` aligns a causal pattern to the END of the key axis: query i sees keys j <= i + (Kn - Cq), which is the
+// inner stream's own-chunk pattern with the whole window visible (reference attention.py:132-150).  GQA shares a
+// K/V head among rep = nh / nkv query heads.
+//
+// One CTA = 128 query rows of one (sequence, head).  Per block of 128 keys:
+//   warp 0     TMA: K and V tiles into a ring of shared-memory stages (128B swizzle)
+//   warp 1     tcgen05.mma: S = Q K^T into one of two TMEM score buffers, then O += P V
+//   warps 2-5  softmax: one thread per query row reads its score row from TMEM (tcgen05.ld), keeps the running max
+//              and sum, rescales the O row in TMEM, writes P (bf16) into shared memory as the A operand of P V
+// S(j+1) is issued before the softmax of block j finishes, so the tensor pipe and the exponentials overlap.
+// Every wait is bounded (ptx_sm100.cuh): on a timeout the roles leave through the common exit and TMEM is freed.
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace dttt {
+
+constexpr int AQ = 128;   // query rows per CTA
+constexpr int AK = 128;   // keys per block
+
+struct AttnParams {
+  int n, Cq, Kn, nh, nkv, causal;
+  float scale;
+  __nv_bfloat16* O;
+  float* lse;
+  int* status;
+};
+
+template <int D>
+struct AttnSmem {
+  static constexpr int Q_BYTES = AQ * D * 2;
+  static constexpr int P_BYTES = AQ * AK * 2;
+  static constexpr int KV_BYTES = 2 * AK * D * 2;          // K tile + V tile
+  static constexpr int STAGES = (D == 64) ? 4 : 2;
+  static constexpr int TOTAL = Q_BYTES + P_BYTES + STAGES * KV_BYTES + 1024 + 1024;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV, const AttnParams p) {
+  using L = AttnSmem<D>;
+  constexpr int DB = D / 64;                                // 64-wide d blocks (one 128-byte row each)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sP = sQ + L::Q_BYTES;
+  uint8_t* sKV = sP + L::P_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + L::STAGES * L::KV_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + L::STAGES;
+  uint64_t* s_full = kv_empty + L::STAGES;     // [2]
+  uint64_t* p_ready = s_full + 2;
+  uint64_t* o_done = p_ready + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 1);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.nh / p.nkv);
+  const int q0 = qt * AQ;
+  const int off = p.Kn - p.Cq;                              // causal alignment to the end of the key axis
+  int last_key = p.Kn - 1;
+  if (p.causal) last_key = min(last_key, q0 + AQ - 1 + off);
+  const int nb = last_key / AK + 1;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < L::STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&s_full[0], 1); mbar_init(&s_full[1], 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) tma_load_4d(sQ + db * (AQ * 128), &mapQ, q_full, db * 64, h, q0, b);
+      for (int j = 0; j < nb; ++j) {
+        const int s = j % L::STAGES;
+        const uint32_t ph = (j / L::STAGES) & 1;
+        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
+        uint8_t* sK = sKV + s * L::KV_BYTES;
+        uint8_t* sV = sK + AK * D * 2;
+        mbar_expect_tx(&kv_full[s], L::KV_BYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_4d(sK + db * (AK * 128), &mapK, &kv_full[s], db * 64, hk, j * AK, b);
+          tma_load_4d(sV + db * (AK * 128), &mapV, &kv_full[s], db * 64, hk, j * AK, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_s = make_idesc_bf16(AQ, AK, 0, 0);          // S = Q K^T: both K-major
+      const uint32_t idesc_o = make_idesc_bf16(AQ, D, 0, 1);           // O += P V: P K-major, V N-major
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_word, p.status, ERR_WAIT_FULL);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % L::STAGES;
+        if (!mbar_wait_bounded(&kv_full[s], (j / L::STAGES) & 1, abort_word, p.status, ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sKV + s * L::KV_BYTES);
+        const uint32_t d_s = tmem + ((j & 1) ? S_COL1 : S_COL0);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t koff = (k / 4) * (AQ * 128) + (k % 4) * 32;   // 64-wide d block, then 32 bytes per UMMA_K
+          umma_f16(d_s, make_smem_desc(aQ + koff, 16, 1024), make_smem_desc(aK + koff, 16, 1024), idesc_s, k ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < nb && ok; ++j) {
+        if (j + 1 < nb) { ok = issue_s(j + 1); if (!ok) break; }
+        if (!mbar_wait_bounded(p_ready, j & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const int s = j % L::STAGES;
+        const uint32_t aV = smem_u32(sKV + s * L::KV_BYTES + AK * D * 2);
+#pragma unroll
+        for (int k = 0; k < AK / 16; ++k) {
+          const uint32_t pa = aP + (k / 4) * (AQ * 128) + (k % 4) * 32;  // P: 64-key halves, K-major
+          const uint32_t va = aV + k * (16 * 128);                        // V: 16 key rows per UMMA_K
+          umma_f16(tmem + O_COL, make_smem_desc(pa, 16, 1024), make_smem_desc(va, AK * 128, 1024), idesc_o, (j | k) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(o_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue (one thread per row)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                    // row within the tile == TMEM lane
+    const int qi = q0 + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int limit = p.causal ? (qi + off) : (p.Kn - 1);   // last visible key of this row
+    float m = -1e30f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(&s_full[j & 1], (j >> 1) & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_addr = tmem + ((j & 1) ? S_COL1 : S_COL0) + lane_addr;
+      const int kbase = j * AK;
+      const bool edge = (kbase + AK - 1 > limit) || (kbase + AK > p.Kn);
+      // pass 1: row maximum
+      float mx = m;
+#pragma unroll 1
+      for (int c = 0; c < AK; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]);
+          if (edge && (kbase + c + i > limit || kbase + c + i >= p.Kn)) v = -1e30f;
+          mx = fmaxf(mx, v);
+        }
+      }
+      const float alpha = exp2f((m - mx) * sl2);
+      m = mx;
+      if (j > 0) {
+        // P and O are free once the previous P V product has completed; then rescale this row of O
+        if (lane == 0) got = mbar_wait_bounded(o_done, (j - 1) & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!got) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < D; c += 16) {
+          uint32_t r[16];
+          tmem_ld_32x16(tmem + O_COL + lane_addr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x16(tmem + O_COL + lane_addr + c, r);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: probabilities -> shared memory (bf16, the swizzled K-major A operand), running sum
+      float sum = 0.f;
+      const float mneg = -m * sl2;
+#pragma unroll 1
+      for (int c = 0; c < AK; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float v0 = __uint_as_float(r[i]), v1 = __uint_as_float(r[i + 1]);
+          if (edge) {
+            if (kbase + c + i > limit || kbase + c + i >= p.Kn) v0 = -1e30f;
+            if (kbase + c + i + 1 > limit || kbase + c + i + 1 >= p.Kn) v1 = -1e30f;
+          }
+          const float p0 = exp2f(fmaf(v0, sl2, mneg)), p1 = exp2f(fmaf(v1, sl2, mneg));
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          // the sum runs over the rounded values the tensor core will see
+          sum += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+          packed[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
+        }
+        // 32 keys = 64 bytes = four 16-byte chunks of this row inside the 64-key half (c / 64)
+        uint8_t* base = sP + (c / 64) * (AQ * 128) + (row / 8) * 1024 + (row % 8) * 128;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (c % 64) / 8 + q;                // logical 16-byte chunk within the 128-byte row
+          *reinterpret_cast<uint4*>(base + ((chunk ^ (row % 8)) * 16)) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      fence_async_proxy();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok) {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(o_done, (nb - 1) & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got) {
+        tc_fence_after();
+        const float inv = 1.f / l;
+        __nv_bfloat16* out = p.O + (((long long)b * p.Cq + qi) * p.nh + h) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem + O_COL + lane_addr + c, r);
+          tmem_ld_wait();
+          if (qi < p.Cq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                vb[q] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * q]) * inv, __uint_as_float(r[i + 2 * q + 1]) * inv);
+              *reinterpret_cast<uint4*>(out + c + i) = v;
+            }
+          }
+        }
+        if (qi < p.Cq && p.lse) p.lse[((long long)b * p.nh + h) * p.Cq + qi] = m * p.scale + logf(l);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn4 attn_encode_fn() {
+  static EncodeTiledFn4 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn4>(ptr);
+  });
+  return fn;
+}
+
+// [n, rows, heads, d] bf16 with d contiguous; box = 64 d x 1 head x 128 rows x 1
+static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int heads, int d) {
+  EncodeTiledFn4 enc = attn_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)rows * heads * d * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+}  // namespace dttt
+
+using namespace dttt;
+
+// Q [n, Cq, nh, d], K / V [n, Kn, nkv, d], O [n, Cq, nh, d] (bf16, contiguous), lse [n, nh, Cq] f32 or null.  d in {64, 128}.
+extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, void* O, float* lse, int n, int Cq, int Kn, int nh,
+                             int nkv, int d, float scale, int causal, int* status, cudaStream_t stream) {
+  if ((d != 64 && d != 128) || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
+  if (causal && Kn < Cq) return -3;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
+  CUtensorMap mq, mk, mv;
+  int r;
+  if ((r = make_map4(&mq, Q, n, Cq, nh, d))) return 100 + r;
+  if ((r = make_map4(&mk, K, n, Kn, nkv, d))) return 200 + r;
+  if ((r = make_map4(&mv, V, n, Kn, nkv, d))) return 300 + r;
+  AttnParams p;
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
+  p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
+  dim3 grid((Cq + AQ - 1) / AQ, nh, n);
+  static bool attr64 = false, attr128 = false;
+  if (d == 64) {
+    if (!attr64) { cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<64>::TOTAL); attr64 = true; }
+    attn_fwd_kernel<64><<<grid, 192, AttnSmem<64>::TOTAL, stream>>>(mq, mk, mv, p);
+  } else {
+    if (!attr128) { cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<128>::TOTAL); attr128 = true; }
+    attn_fwd_kernel<128><<<grid, 192, AttnSmem<128>::TOTAL, stream>>>(mq, mk, mv, p);
+  }
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

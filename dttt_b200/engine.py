@@ -75,7 +75,8 @@ class Engine:
         self.device = device or self.mesh.device
         self.dtype = torch_dtype(train_cfg.compute_dtype)
         self.spec = param_spec(model_cfg)
-        self.store = ParamStore(self.spec, self.mesh, self.dtype, self.device, trainable=trainable)
+        self.store = ParamStore(self.spec, self.mesh, self.dtype, self.device, trainable=trainable,
+                                fused_comm=train_cfg.fused_comm)
         self.n_params = count_params(model_cfg)
         if init:
             self.init_weights(train_cfg.seed)
@@ -155,7 +156,8 @@ class Engine:
         with prof.range("optimizer"):
             om = self.opt.step(grad_scale=wsum_g)
         with prof.range("sync_compute"):
-            st.sync_compute()
+            if not self.opt.wrote_compute:
+                st.sync_compute()
         from .ops import _lib
         if self.device.type == "cuda":
             _lib.check_status(self.device)

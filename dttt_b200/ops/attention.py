@@ -183,7 +183,7 @@ def _ref_for_staged(q, K, V, scale, causal):
 
 def _fast_fwd(q, K, V, scale, causal):
     from . import kernels
-    if kernels.available("attention"):
+    if kernels.available("attention") and kernels.attention_supported(q, K):
         o, lse = kernels.attention_fwd(q, K, V, scale, causal)
         return o, (o, lse)
     with torch.no_grad():
@@ -194,7 +194,7 @@ def _fast_fwd(q, K, V, scale, causal):
 def _fast_bwd(g, tensors, saved, needs, scale, causal):
     from . import kernels
     q, K, V = tensors
-    if kernels.available("attention") and saved:
+    if kernels.available("attention_bwd") and saved:
         return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, causal)
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))

@@ -225,3 +225,27 @@ def seq_axpy(w, g, coef, want_lo=False):
     _check(_lib.lib().dttt_seq_axpy(_p(wc), _p(gc), _p(coef.float().contiguous()), _p(out), _p(lo), B, wc.numel() // B,
                                     1 if gc.dtype == torch.bfloat16 else 0, _stream()), "seq_axpy")
     return (out, lo) if want_lo else out
+
+
+# =============================================================================== attention family
+_lib.register("dttt_attn_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp])
+_SYMBOL.update(attention="dttt_attn_fwd")
+
+
+def attention_fwd(q, k, v, scale, causal):
+    """Flash attention forward on the tcgen05 kernel.  ``q [n, Cq, nh, d]``, ``k / v [n, Kn, nkv, d]`` bf16, every key
+    valid, ``causal`` aligned to the end of the key axis.  Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
+    n, Cq, nh, d = q.shape
+    Kn, nkv = k.shape[1], k.shape[2]
+    assert q.dtype == torch.bfloat16 and d in (64, 128), (q.dtype, d)
+    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(qc)
+    lse = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
+    st = _lib.status_tensor(q.device)
+    _check(_lib.lib().dttt_attn_fwd(_p(qc), _p(kc), _p(vc), _p(o), _p(lse), n, Cq, Kn, nh, nkv, d, float(scale), 1 if causal else 0,
+                                    _p(st), _stream()), "attn_fwd")
+    return o, lse
+
+
+def attention_supported(q, k) -> bool:
+    return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and (q.shape[2] % k.shape[2] == 0)

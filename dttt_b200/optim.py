@@ -59,6 +59,7 @@ class ShardedAdamW:
         self.m = torch.zeros_like(store.master)
         self.v = torch.zeros_like(store.master)
         self.count = 0                                   # optimiser steps taken (optax's ``count``)
+        self.wrote_compute = False                       # the fused step also refreshed every rank's compute copies
         nd = re.compile(no_decay_pattern) if no_decay_pattern else None
         fast = re.compile(r"(^|\.)fast_weight(\.|$)")
         self.segs: List[Tuple[str, int, int, float, float]] = []
@@ -94,7 +95,18 @@ class ShardedAdamW:
         bc1, bc2 = 1.0 - self.b1 ** t, 1.0 - self.b2 ** t
         from .ops import kernels
         fused = g.is_cuda and kernels.available("adamw")
-        for name, a, b, decay, scale in self.segs:
+        if st.fused:
+            # AdamW on the shard and the all-gather of the updated compute copies in one kernel per segment: the new
+            # value of every element is stored into every FSDP rank's compute buffer over NVLink as it is produced.
+            from .parallel import symm
+            me = st.mesh.fsdp_index
+            for name, a, b, decay, scale in self.segs:
+                space, off = st.space_of_master_index(a)
+                symm.adamw_allgather(st.master[a:b], self.m[a:b], self.v[a:b], g[a:b], lr * scale, self.b1, self.b2, self.eps,
+                                     decay, bc1, bc2, factor, st._lo_tables[space], st.fs, me, off, space == "big" and st.dtype == torch.bfloat16)
+            st.barrier()                                     # every rank's stores have landed before anyone reads
+            self.wrote_compute = True
+        for name, a, b, decay, scale in ([] if st.fused else self.segs):
             p, m, v, gg = st.master[a:b], self.m[a:b], self.v[a:b], g[a:b]
             if fused:
                 kernels.adamw(p, m, v, gg, lr * scale, self.b1, self.b2, self.eps, decay, bc1, bc2, factor)

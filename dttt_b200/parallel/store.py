@@ -33,7 +33,7 @@ ALIGN = 64          # elements; keeps every parameter view 128-byte aligned in b
 
 class ParamStore:
     def __init__(self, spec: "OrderedDict[str, Tuple[Tuple[int, ...], str]]", mesh: Mesh, compute_dtype: torch.dtype,
-                 device: torch.device, trainable: bool = True):
+                 device: torch.device, trainable: bool = True, fused_comm: bool = True):
         self.spec, self.mesh, self.dtype, self.device = spec, mesh, compute_dtype, device
         self.trainable = trainable
         self.fs = mesh.fsdp
@@ -48,9 +48,30 @@ class ParamStore:
         self.n = {k: max(pad, -(-v // pad) * pad) for k, v in offs.items()}
         self.shard_n = {k: v // self.fs for k, v in self.n.items()}
         f32 = torch.float32
-        self.lo = {"big": torch.zeros(self.n["big"], dtype=compute_dtype, device=device),
-                   "small": torch.zeros(self.n["small"], dtype=f32, device=device)}
-        self.grad = {k: torch.zeros(self.n[k], dtype=f32, device=device) for k in ("big", "small")} if trainable else None
+        # With more than one FSDP rank on GPUs the compute copies and the gradient buffers live in peer-accessible
+        # memory (parallel.symm): the fused reduce-scatter / optimiser / all-gather kernels read and write the other
+        # ranks' copies directly over NVLink.  Otherwise they are ordinary tensors and the collectives are NCCL / gloo.
+        self.peer = None
+        self.fused = bool(fused_comm and trainable and self.fs > 1 and device.type == "cuda")
+        if self.fused:
+            from .symm import PeerBuffer
+            lo_big = self.n["big"] * torch.empty(0, dtype=compute_dtype).element_size()
+            self._off = {"lo_big": 0, "lo_small": lo_big}
+            self._off["grad_big"] = self._off["lo_small"] + self.n["small"] * 4
+            self._off["grad_small"] = self._off["grad_big"] + self.n["big"] * 4
+            total = self._off["grad_small"] + self.n["small"] * 4
+            self.peer = PeerBuffer(total, mesh.fsdp_group, device)
+            self.lo = {"big": self.peer.tensor(self._off["lo_big"], self.n["big"], compute_dtype),
+                       "small": self.peer.tensor(self._off["lo_small"], self.n["small"], f32)}
+            self.grad = {k: self.peer.tensor(self._off["grad_" + k], self.n[k], f32) for k in ("big", "small")}
+            self._grad_tables = {k: self.peer.ptr_table(self._off["grad_" + k]) for k in ("big", "small")}
+            self._lo_tables = {k: self.peer.ptr_table(self._off["lo_" + k]) for k in ("big", "small")}
+            self.sumsq = torch.zeros(2, dtype=f32, device=device)
+            self._bar = torch.zeros(1, dtype=f32, device=device)
+        else:
+            self.lo = {"big": torch.zeros(self.n["big"], dtype=compute_dtype, device=device),
+                       "small": torch.zeros(self.n["small"], dtype=f32, device=device)}
+            self.grad = {k: torch.zeros(self.n[k], dtype=f32, device=device) for k in ("big", "small")} if trainable else None
         ns = self.shard_n["big"] + self.shard_n["small"]
         self.master = torch.zeros(ns, dtype=f32, device=device)                   # [big shard | small shard]
         self.grad_shard = torch.zeros(ns, dtype=f32, device=device) if trainable else None
@@ -66,15 +87,29 @@ class ParamStore:
         return buf[:nb] if space == "big" else buf[nb:]
 
     def segments(self) -> List[Tuple[str, int, int]]:
-        """``(name, start, end)`` ranges of this rank's master shard (indices into ``self.master``)."""
+        """``(name, start, end)`` ranges of this rank's master shard (indices into ``self.master``).  Ends are rounded
+        up to the slot alignment (the padding holds zeros and stays zero under AdamW), so every range is a whole
+        number of 16-byte vectors."""
         out = []
         for name, (space, off, n, _) in self.slots.items():
             lo, hi = self.shard_range(space)
-            a, b = max(off, lo), min(off + n, hi)
+            a, b = max(off, lo), min(-(-(off + n) // ALIGN) * ALIGN, hi)
             if a < b:
                 base = 0 if space == "big" else self.shard_n["big"]
                 out.append((name, base + a - lo, base + b - lo))
         return out
+
+    def space_of_master_index(self, idx: int) -> Tuple[str, int]:
+        """``(space, flat offset in that space)`` of an index into this rank's master shard."""
+        nb = self.shard_n["big"]
+        if idx < nb:
+            return "big", self.shard_range("big")[0] + idx
+        return "small", self.shard_range("small")[0] + idx - nb
+
+    def barrier(self) -> None:
+        """Stream-ordered barrier over the FSDP group (a one-element all-reduce)."""
+        if self.fs > 1:
+            dist.all_reduce(self._bar, group=self.mesh.fsdp_group)
 
     # ---- views
     def lo_view(self, name: str) -> torch.Tensor:
@@ -119,6 +154,19 @@ class ParamStore:
     def reduce_grads(self) -> None:
         """Sum the full gradient buffers over every data rank and leave this rank's slice in ``grad_shard``."""
         m = self.mesh
+        if self.fused:
+            # one kernel per space: every rank pulls its slice of every peer's gradient buffer over NVLink, sums,
+            # and accumulates the slice's squared norm; no library collective.
+            from . import symm
+            self.barrier()                                   # every rank's backward has finished writing its buffer
+            self.sumsq.zero_()
+            for i, space in enumerate(("big", "small")):
+                lo, hi = self.shard_range(space)
+                symm.reduce_scatter_sumsq(self._grad_tables[space], self.fs, m.fsdp_index, lo, hi - lo, 1.0,
+                                          self.master_part(space, self.grad_shard), self.sumsq[i:i + 1])
+                if m.dp > 1:
+                    dist.all_reduce(self.master_part(space, self.grad_shard), op=dist.ReduceOp.SUM, group=m.dp_group)
+            return
         for space in ("big", "small"):
             out = self.master_part(space, self.grad_shard)
             g = self.grad[space]

@@ -1,0 +1,180 @@
+"""Time the hand-written kernels in isolation and report them against the measured peaks.
+
+    python -m dttt_b200.tools.kernel_bench gemm --m 8192 --n 8192 --k 8192 [--ta] [--tb] [--batch B] [--f32acc]
+    python -m dttt_b200.tools.kernel_bench rmsnorm|rope|swiglu|adamw --rows R --dim D
+    python -m dttt_b200.tools.kernel_bench attn --seqs 8 --cq 1024 --kn 9216 --heads 32 --kv-heads 8 --head-dim 64 [--causal]
+    python -m dttt_b200.tools.kernel_bench suite            (the shapes of the 1B model)
+
+Timing: CUDA events on the launching stream, 3 warm-up launches, best of ``--iters``; between timed launches a
+buffer larger than L2 (256 MiB) is written so no operand is L2-resident from the previous launch.  The roofline
+denominators are the measured copy bandwidth and cuBLAS bf16 burst throughput in ``MEASURED_PEAKS.json`` at the
+repository root (fallback 6.65 TB/s, 1.59 PFLOP/s).  One JSON line per case; ``--once`` runs each kernel a single
+time after one warm-up (the form to capture under a profiler).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+_FLUSH = None
+
+
+def flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.fill_(1)
+
+
+def timeit(fn, iters=10, once=False):
+    fn()
+    if once:
+        torch.cuda.synchronize()
+        fn()
+        torch.cuda.synchronize()
+        return float("nan")
+    for _ in range(2):
+        fn()
+    best = 1e30
+    for _ in range(iters):
+        flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); fn(); e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    return best
+
+
+def bench_gemm(a, out):
+    from dttt_b200.ops import gemm
+    M, N, K, B = a.m, a.n, a.k, a.batch
+    lead = (B,) if B > 1 else ()
+    A = torch.randn(*lead, *((K, M) if a.ta else (M, K)), device="cuda", dtype=torch.bfloat16)
+    Bm = torch.randn(*lead, *((N, K) if a.tb else (K, N)), device="cuda", dtype=torch.bfloat16)
+    C = torch.zeros(*lead, M, N, device="cuda", dtype=torch.float32) if a.f32acc else None
+    fn = lambda: gemm.gemm_raw(A, Bm, a.ta, a.tb, torch.float32 if a.f32acc else torch.bfloat16, out=C, accumulate=a.f32acc)
+    ms = timeit(fn, a.iters, a.once)
+    hbm, flops, src = peaks()
+    fl = 2.0 * M * N * K * B
+    res = {"kernel": "gemm_bf16_tcgen05", "M": M, "N": N, "K": K, "batch": B, "ta": a.ta, "tb": a.tb, "f32_accumulate": a.f32acc,
+           "ms": ms, "tflops": fl / ms / 1e9, "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src}
+    if a.compare and not a.once:
+        X = A.transpose(-1, -2) if a.ta else A
+        Y = Bm.transpose(-1, -2) if a.tb else Bm
+        mt = timeit(lambda: torch.matmul(X, Y), a.iters)
+        res.update(ms_cublas=mt, tflops_cublas=fl / mt / 1e9, vs_cublas=mt / ms)
+    out(res)
+
+
+def bench_elementwise(a, out):
+    from dttt_b200.ops import kernels
+    R, D = a.rows, a.dim
+    hbm, _, src = peaks()
+    x = torch.randn(R, D, device="cuda", dtype=torch.bfloat16)
+    if a.cmd == "rmsnorm":
+        w = torch.ones(D, device="cuda")
+        y, (rstd,) = kernels._rms_fwd(x, w, 1e-6)
+        g = torch.randn_like(x)
+        cases = [("rmsnorm_fwd", lambda: kernels._rms_fwd(x, w, 1e-6), 2 * R * D * 2),
+                 ("rmsnorm_bwd", lambda: kernels._rms_bwd(g, (x, w), (rstd,), (True, True), 1e-6), 3 * R * D * 2)]
+    elif a.cmd == "swiglu":
+        u, g = torch.randn_like(x), torch.randn_like(x)
+        cases = [("swiglu_fwd", lambda: kernels._swiglu_fwd(x, u), 3 * R * D * 2),
+                 ("swiglu_bwd", lambda: kernels._swiglu_bwd(g, (x, u), (), (True, True)), 5 * R * D * 2)]
+    elif a.cmd == "rope":
+        heads, d = D // 64, 64
+        xx = x.view(R, heads, d)
+        pos = torch.arange(R, device="cuda")
+        from dttt_b200.ops import functional as Fn
+        inv = Fn.inv_freq(d, 5e5, None, xx.device)
+        cases = [("rope", lambda: kernels._rope_run(xx, pos, inv, 1.0), 2 * R * D * 2)]
+    else:
+        n = R * D
+        p, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+        cases = [("adamw", lambda: kernels.adamw(p, m, v, g, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0), 7 * n * 4)]
+    for name, fn, nbytes in cases:
+        ms = timeit(fn, a.iters, a.once)
+        out({"kernel": name, "rows": R, "dim": D, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_copy_bw": nbytes / (ms * 1e-3) / hbm, "peaks": src})
+
+
+def bench_attn(a, out):
+    from dttt_b200.ops import kernels
+    from dttt_b200.ops.attention import _sdpa_fast
+    n, Cq, Kn, nh, nkv, d = a.seqs, a.cq, a.kn, a.heads, a.kv_heads, a.head_dim
+    q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    ms = timeit(lambda: kernels.attention_fwd(q, k, v, d ** -0.5, a.causal), a.iters, a.once)
+    _, flops, src = peaks()
+    pairs = Cq * Kn - (Cq * (Cq - 1) // 2 if a.causal else 0)             # visible (query, key) pairs
+    fl = 4.0 * n * nh * d * pairs
+    res = {"kernel": "attn_fwd_tcgen05", "seqs": n, "Cq": Cq, "Kn": Kn, "heads": nh, "kv_heads": nkv, "head_dim": d,
+           "causal": a.causal, "ms": ms, "tflops": fl / ms / 1e9, "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src}
+    if a.compare and not a.once:
+        with torch.no_grad():
+            mt = timeit(lambda: _sdpa_fast(q, k, v, d ** -0.5, a.causal), a.iters)
+        res.update(ms_library=mt, tflops_library=fl / mt / 1e9, vs_library=mt / ms)
+    out(res)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.kernel_bench")
+    ap.add_argument("cmd", choices=["gemm", "attn", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
+    ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
+    ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1); ap.add_argument("--ta", action="store_true"); ap.add_argument("--tb", action="store_true")
+    ap.add_argument("--f32acc", action="store_true"); ap.add_argument("--compare", action="store_true")
+    ap.add_argument("--rows", type=int, default=49152); ap.add_argument("--dim", type=int, default=2048)
+    ap.add_argument("--iters", type=int, default=10); ap.add_argument("--once", action="store_true")
+    ap.add_argument("--out", default="")
+    a = ap.parse_args(argv)
+    sys.path.insert(0, ROOT)
+    lines = []
+
+    def out(d):
+        lines.append(json.dumps(d))
+        print(lines[-1], flush=True)
+    if a.cmd == "gemm":
+        bench_gemm(a, out)
+    elif a.cmd == "attn":
+        bench_attn(a, out)
+    elif a.cmd == "suite":
+        a.compare = True
+        shapes = [(8192, 8192, 8192, 1, 0, 0, 0), (49152, 2048, 2048, 1, 0, 0, 0), (49152, 8192, 2048, 1, 0, 0, 0), (49152, 2048, 8192, 1, 0, 0, 0),
+                  (2048, 8192, 2048, 1, 0, 0, 0), (2048, 2048, 8192, 1, 0, 0, 0), (1024, 8192, 2048, 4, 0, 0, 0), (2048, 8192, 1024, 4, 1, 0, 0),
+                  (2048, 8192, 49152, 1, 1, 0, 1), (49152, 2048, 8192, 1, 0, 1, 0), (2048, 8192, 2048, 1, 0, 1, 0), (8192, 2048, 2048, 1, 1, 0, 1)]
+        for M, N, K, B, ta, tb, acc in shapes:
+            a.m, a.n, a.k, a.batch, a.ta, a.tb, a.f32acc = M, N, K, B, bool(ta), bool(tb), bool(acc)
+            bench_gemm(a, out)
+        for n, Cq, Kn, causal in ((8, 1024, 9216, True), (8, 1024, 9216, False), (16, 1024, 1024, True), (8, 1024, 4096, True)):
+            a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim = n, Cq, Kn, causal, 32, 8, 64
+            bench_attn(a, out)
+        for cmd, R, D in (("rmsnorm", 49152, 2048), ("swiglu", 49152, 8192), ("rope", 49152, 2048), ("adamw", 16384, 8192)):
+            a.cmd, a.rows, a.dim = cmd, R, D
+            bench_elementwise(a, out)
+    else:
+        bench_elementwise(a, out)
+    if a.out:
+        with open(a.out, "w") as fh:
+            fh.write("\n".join(lines) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,63 @@
+"""The tcgen05 flash-attention forward kernel against an f32 softmax(QK^T)V."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(q, k, v, scale, causal):
+    n, Cq, nh, d = q.shape
+    Kn, nkv = k.shape[1], k.shape[2]
+    rep = nh // nkv
+    q32 = q.float().permute(0, 2, 1, 3)                                   # [n, nh, Cq, d]
+    k32 = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    v32 = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = q32 @ k32.transpose(-1, -2) * scale
+    if causal:
+        i = torch.arange(Cq, device=q.device)[:, None]
+        j = torch.arange(Kn, device=q.device)[None, :]
+        s = s.masked_fill(j > i + (Kn - Cq), float("-inf"))
+    lse = torch.logsumexp(s, -1)
+    o = torch.softmax(s, -1) @ v32
+    return o.permute(0, 2, 1, 3), lse
+
+
+@pytest.mark.parametrize("n,Cq,Kn,nh,nkv,d,causal", [
+    (2, 128, 128, 4, 2, 64, True),
+    (2, 128, 128, 4, 2, 64, False),
+    (1, 256, 1280, 8, 2, 64, True),
+    (1, 256, 1280, 8, 2, 64, False),
+    (2, 200, 333, 4, 4, 128, False),
+    (1, 100, 100, 2, 1, 64, True),
+    (1, 384, 640, 4, 1, 128, True),
+    (1, 1024, 9216, 8, 2, 64, True),
+])
+def test_attn_fwd(n, Cq, Kn, nh, nkv, d, causal):
+    from dttt_b200.ops import _lib, kernels
+    assert kernels.available("attention"), "the attention kernel is not in the loaded library"
+    torch.manual_seed(3)
+    q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    o, lse = kernels.attention_fwd(q, k, v, scale, causal)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    oref, lref = _ref(q, k, v, scale, causal)
+    err = (o.float() - oref).abs().max().item()
+    assert err < 2e-2, err
+    assert (lse - lref).abs().max().item() < 2e-3
+
+
+def test_attn_fwd_large_magnitude():
+    """Scores far from zero: the running-max rescale has to carry the sum across key blocks."""
+    from dttt_b200.ops import kernels
+    torch.manual_seed(4)
+    n, Cq, Kn, nh, nkv, d = 1, 128, 512, 2, 2, 64
+    q = 4.0 * torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    k = 4.0 * torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    o, lse = kernels.attention_fwd(q, k, v, d ** -0.5, False)
+    oref, lref = _ref(q, k, v, d ** -0.5, False)
+    assert (o.float() - oref).abs().max().item() < 3e-2
+    assert ((lse - lref).abs() / lref.abs().clamp_min(1.0)).max().item() < 2e-3
