@@ -41,7 +41,23 @@ struct GemmParams {
   void* C;
   int* status;
   int tiles_m, tiles_n;
+  // cross-entropy epilogues (MODE 1 / 2)
+  const int* targets;       // [M] class index of every row (columns are classes, offset by col0)
+  const float* row_coef;    // [M] MODE 2: g * w_row
+  const float* row_lse;     // [M] MODE 2: log-partition of the row
+  float2* part;             // MODE 1: [tiles_n][part_stride] per-tile (max, sum exp(x - max))
+  float* tgt_logit;         // MODE 1: [M] logit of the target class
+  long long part_stride;
+  int col0;                 // class index of column 0
 };
+
+// Epilogue modes of the kernel below.
+//   0  C (+)= alpha * acc                                           (the GEMM)
+//   1  no C: per row and column tile, (max, sum exp) of the tile's logits and the target's logit
+//      (the forward of linear + cross-entropy, reference src/ttt/fused_ce.py:42-73)
+//   2  C = coef[row] * (exp(acc - lse[row]) - [col == target[row]])  in bf16
+//      (d loss / d logits, reference fused_ce.py:93-104), consumed by the two gradient GEMMs
+constexpr int EPI_STORE = 0, EPI_CE_PARTIAL = 1, EPI_CE_DLOGITS = 2;
 
 template <int BN>
 struct SmemLayout {
@@ -67,7 +83,7 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   tn = r / rows;
 }
 
-template <int BN>
+template <int BN, int MODE>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const GemmParams p) {
@@ -200,6 +216,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.M;
       const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+      if constexpr (MODE == EPI_CE_PARTIAL) {
+        constexpr float LOG2E = 1.4426950408889634f;
+        float mx = -3.0e38f;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (n0 + c + j < p.N) mx = fmaxf(mx, __uint_as_float(r[j]));
+        }
+        const int y = row_ok ? (p.targets[row] - p.col0) : -1;
+        float sum = 0.f, tgt = 0.f;
+        const float mneg = -mx * LOG2E;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]);
+            if (n0 + c + j < p.N) sum += exp2f(fmaf(v, LOG2E, mneg));
+            if (n0 + c + j == y) tgt = v;
+          }
+        }
+        if (row_ok) {
+          p.part[(long long)tn * p.part_stride + row] = make_float2(mx, sum);
+          if (y >= n0 && y < n0 + BN && y < p.N) p.tgt_logit[row] = tgt;
+        }
+      } else {
+      float coef = 0.f, lse = 0.f;
+      int y = -1;
+      if constexpr (MODE == EPI_CE_DLOGITS) {
+        if (row_ok) { coef = p.row_coef[row]; lse = p.row_lse[row]; y = p.targets[row] - p.col0; }
+      }
+      auto xform = [&](float acc_v, int colj) -> float {
+        if constexpr (MODE == EPI_CE_DLOGITS) return coef * (__expf(acc_v - lse) - (colj == y ? 1.f : 0.f));
+        else return acc_v * p.alpha;
+      };
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -213,8 +270,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
-                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4 v = make_float4(xform(__uint_as_float(r[j]), col + j), xform(__uint_as_float(r[j + 1]), col + j + 1),
+                                       xform(__uint_as_float(r[j + 2]), col + j + 2), xform(__uint_as_float(r[j + 3]), col + j + 3));
                 if (p.accumulate) {
                   float4 o = *reinterpret_cast<float4*>(out + j);
                   v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -223,7 +280,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               }
             } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
+                float v = xform(__uint_as_float(r[j]), col + j);
                 if (p.accumulate) v += out[j];
                 out[j] = v;
               }
@@ -235,7 +292,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               for (int j = 0; j < 32; j += 8) {
                 float f[8];
 #pragma unroll
-                for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[j + q]) * p.alpha;
+                for (int q = 0; q < 8; ++q) f[q] = xform(__uint_as_float(r[j + q]), col + j + q);
                 if (p.accumulate) {
                   uint4 o = *reinterpret_cast<uint4*>(out + j);
                   const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
@@ -253,13 +310,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               }
             } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]) * p.alpha;
+                float v = xform(__uint_as_float(r[j]), col + j);
                 if (p.accumulate) v += __bfloat162float(out[j]);
                 out[j] = __float2bfloat16(v);
               }
             }
           }
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
@@ -309,7 +367,70 @@ static int make_map(CUtensorMap* map, const void* ptr, long long inner, long lon
 }
 
 static int g_num_sms = 0;
-static bool g_attr_set[2] = {false, false};
+
+static int bind_thread_context() {
+  // The tensor-map encoder is a driver call and needs a current context in the calling thread.  Autograd
+  // runs backward passes on its own threads, where no runtime call may have bound the primary context yet:
+  // bind it once per thread.
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaSetDevice(dev);
+    cudaFree(0);
+    ctx_bound = true;
+  }
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return 0;
+}
+
+template <int BN, int MODE>
+static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, int max_ctas, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL);
+    attr_set = true;
+  }
+  long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
+  int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
+  int grid = (int)(tiles < cap ? tiles : cap);
+  gemm_bf16_kernel<BN, MODE><<<grid, 192, SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+// Combine the per-tile (max, sum exp) partials of EPI_CE_PARTIAL into lse[row] and nll[row] = lse - target logit.
+__global__ void ce_combine_kernel(const float2* __restrict__ part, long long part_stride, int tiles_n, int M,
+                                  const float* __restrict__ tgt_logit, float* __restrict__ lse, float* __restrict__ nll) {
+  // block = 32 rows x 8 tile-lanes; lane x owns a row, the 8 y-lanes split the column tiles
+  __shared__ float sm[8][32], ss[8][32];
+  const int row = blockIdx.x * 32 + threadIdx.x;
+  float m = -3.0e38f, s = 0.f;
+  if (row < M) {
+    for (int t = threadIdx.y; t < tiles_n; t += 8) {
+      const float2 v = part[(long long)t * part_stride + row];
+      const float nm = fmaxf(m, v.x);
+      s = s * __expf(m - nm) + v.y * __expf(v.x - nm);
+      m = nm;
+    }
+  }
+  sm[threadIdx.y][threadIdx.x] = m;
+  ss[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && row < M) {
+    float M2 = sm[0][threadIdx.x];
+    for (int k = 1; k < 8; ++k) M2 = fmaxf(M2, sm[k][threadIdx.x]);
+    float S2 = 0.f;
+    for (int k = 0; k < 8; ++k) S2 += ss[k][threadIdx.x] * __expf(sm[k][threadIdx.x] - M2);
+    const float l = M2 + logf(S2);
+    lse[row] = l;
+    if (nll) nll[row] = l - tgt_logit[row];
+  }
+}
 
 }  // namespace dttt
 
@@ -328,22 +449,7 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (a_batch % 8) || (b_batch % 8))
     return -2;
-  // The tensor-map encoder is a driver call and needs a current context in the calling thread.  Autograd
-  // runs backward passes on its own threads, where no runtime call may have bound the primary context yet:
-  // bind it once per thread.
-  static thread_local bool ctx_bound = false;
-  if (!ctx_bound) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaSetDevice(dev);
-    cudaFree(0);
-    ctx_bound = true;
-  }
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-  }
+  bind_thread_context();
   const int bn = (N > 128) ? 256 : 128;
   CUtensorMap mapA, mapB;
   int r;
@@ -355,28 +461,76 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   if (r) return 200 + r;
 
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.ldc = ldc; p.c_batch = c_batch; p.c_is_f32 = c_is_f32; p.accumulate = accumulate; p.alpha = alpha;
   p.C = C; p.status = status;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + bn - 1) / bn;
-  long long tiles = (long long)batch * p.tiles_m * p.tiles_n;
-  int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
-  int grid = (int)(tiles < cap ? tiles : cap);
-  if (bn == 256) {
-    if (!g_attr_set[0]) {
-      cudaFuncSetAttribute(gemm_bf16_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<256>::TOTAL);
-      g_attr_set[0] = true;
-    }
-    gemm_bf16_kernel<256><<<grid, 192, SmemLayout<256>::TOTAL, stream>>>(mapA, mapB, p);
-  } else {
-    if (!g_attr_set[1]) {
-      cudaFuncSetAttribute(gemm_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<128>::TOTAL);
-      g_attr_set[1] = true;
-    }
-    gemm_bf16_kernel<128><<<grid, 192, SmemLayout<128>::TOTAL, stream>>>(mapA, mapB, p);
-  }
+  if (bn == 256) return launch_gemm<256, EPI_STORE>(mapA, mapB, p, max_ctas, stream);
+  return launch_gemm<128, EPI_STORE>(mapA, mapB, p, max_ctas, stream);
+}
+
+// Number of float2 scratch entries dttt_linear_ce_fwd needs for `rows` rows and `classes` classes.
+extern "C" long long dttt_linear_ce_scratch_elems(int rows, int classes) {
+  const long long stride = ((long long)rows + 127) / 128 * 128;
+  return stride * ((classes + 255) / 256);
+}
+
+// Shared by the entry points that differ only in where the scratch comes from.
+int dttt_linear_ce_fwd_impl(const void* h, const void* E, const int* targets, int rows, int classes, int K, long long ldh,
+                            long long ldE, void* scratch, float* tgt_logit, float* lse, float* nll, int* status,
+                            cudaStream_t stream) {
+  if (rows <= 0 || classes <= 0 || K <= 0) return 0;
+  if ((ldh % 8) || (ldE % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(E) & 15)) return -2;
+  bind_thread_context();
+  CUtensorMap mapA, mapB;
+  int r;
+  if ((r = make_map(&mapA, h, K, rows, 1, ldh, 0, BM))) return 100 + r;
+  if ((r = make_map(&mapB, E, K, classes, 1, ldE, 0, 256))) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = rows; p.N = classes; p.K = K; p.batch = 1; p.alpha = 1.f; p.status = status;
+  p.tiles_m = (rows + BM - 1) / BM;
+  p.tiles_n = (classes + 255) / 256;
+  p.targets = targets; p.part = reinterpret_cast<float2*>(scratch); p.tgt_logit = tgt_logit;
+  p.part_stride = (long long)p.tiles_m * BM;
+  r = launch_gemm<256, EPI_CE_PARTIAL>(mapA, mapB, p, 0, stream);
+  if (r) return r;
+  ce_combine_kernel<<<(rows + 31) / 32, dim3(32, 8), 0, stream>>>(p.part, p.part_stride, p.tiles_n, rows, tgt_logit, lse, nll);
   cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : 1000 + (int)e;
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}
+
+// Forward of linear + cross-entropy: lse[r] = logsumexp_v(h_r . E_v), nll[r] = lse[r] - h_r . E_{target_r}.
+//   h [rows, K] bf16 (row stride ldh), E [classes, K] bf16 (row stride ldE), targets [rows] int32.
+//   scratch: dttt_linear_ce_scratch_elems(rows, classes) float2 entries of device memory (contents ignored);
+//   tgt_logit, lse, nll: [rows] f32 outputs (nll may be null).  Targets outside [0, classes) leave tgt_logit untouched.
+extern "C" int dttt_linear_ce_fwd(const void* h, const void* E, const int* targets, int rows, int classes, int K, long long ldh,
+                                  long long ldE, void* scratch, float* tgt_logit, float* lse, float* nll, int* status,
+                                  cudaStream_t stream) {
+  return dttt_linear_ce_fwd_impl(h, E, targets, rows, classes, K, ldh, ldE, scratch, tgt_logit, lse, nll, status, stream);
+}
+
+// d loss / d logits for the classes [col0, col0 + ncols): D[r, c] = coef[r] * (exp(h_r . E_{col0 + c} - lse[r]) - [col0 + c == target_r])
+// in bf16, row stride ldd.  Eb points at row col0 of E.
+extern "C" int dttt_linear_ce_dlogits(const void* h, const void* Eb, const int* targets, const float* coef, const float* lse,
+                                      void* D, int rows, int ncols, int K, long long ldh, long long ldE, long long ldd, int col0,
+                                      int* status, cudaStream_t stream) {
+  if (rows <= 0 || ncols <= 0 || K <= 0) return 0;
+  if ((ldh % 8) || (ldE % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(Eb) & 15)) return -2;
+  bind_thread_context();
+  CUtensorMap mapA, mapB;
+  int r;
+  if ((r = make_map(&mapA, h, K, rows, 1, ldh, 0, BM))) return 100 + r;
+  if ((r = make_map(&mapB, Eb, K, ncols, 1, ldE, 0, 256))) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = rows; p.N = ncols; p.K = K; p.batch = 1; p.alpha = 1.f; p.status = status;
+  p.ldc = ldd; p.C = D; p.c_is_f32 = 0;
+  p.tiles_m = (rows + BM - 1) / BM;
+  p.tiles_n = (ncols + 255) / 256;
+  p.targets = targets; p.row_coef = coef; p.row_lse = lse; p.col0 = col0;
+  return launch_gemm<256, EPI_CE_DLOGITS>(mapA, mapB, p, 0, stream);
 }

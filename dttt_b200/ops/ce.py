@@ -32,6 +32,9 @@ def _blocks(V: int, block: int):
 def _stream_lse(h: torch.Tensor, E: torch.Tensor, block: int) -> torch.Tensor:
     """``logZ [N]`` (f32) of ``h @ E^T``, one vocabulary block at a time."""
     N = h.shape[0]
+    if _fused(h, E):
+        from . import kernels
+        return kernels.linear_ce_fwd(h, E, torch.zeros(N, dtype=torch.int32, device=h.device))[0]
     run_max = torch.full((N,), float("-inf"), dtype=torch.float32, device=h.device)
     run_sum = torch.zeros(N, dtype=torch.float32, device=h.device)
     for s, e in _blocks(E.shape[0], block):
@@ -41,6 +44,14 @@ def _stream_lse(h: torch.Tensor, E: torch.Tensor, block: int) -> torch.Tensor:
         run_sum = run_sum * torch.exp(run_max - new_max) + torch.exp(logits - new_max[:, None]).sum(-1)
         run_max = new_max
     return run_max + torch.log(run_sum)
+
+
+def _fused(h: torch.Tensor, E: torch.Tensor) -> bool:
+    """Whether the GEMM-epilogue kernels (``csrc/gemm_tcgen05.cu``, the cross-entropy epilogues) take this call."""
+    if not (use_kernels(h) and h.is_cuda):
+        return False
+    from . import kernels
+    return kernels.available("linear_ce") and kernels.linear_ce_supported(h, E)
 
 
 def _block_logits(h: torch.Tensor, Eb: torch.Tensor) -> torch.Tensor:
@@ -65,6 +76,10 @@ def _ce_ref(h, E, targets, weights, block, target=None):
 
 def _ce_fwd(h, E, targets, weights, block, target=None):
     with torch.no_grad():
+        if _fused(h, E):
+            from . import kernels
+            logZ, nll = kernels.linear_ce_fwd(h, E, targets)
+            return (weights.float() * nll).sum(), (logZ,)
         logZ = _stream_lse(h, E, block)
         loss = (weights.float() * (logZ - _target_logit(h, E, targets))).sum()
     return loss, (logZ,)
@@ -84,14 +99,22 @@ def _ce_bwd(g, tensors, saved, needs, block, target=None):
         gfull, layer = target
         gbuf = gfull if layer is None else gfull[layer]
     tl = targets.long()
+    fused = _fused(h, E)
+    if fused:
+        from . import kernels
+        ti, gwc = targets.to(torch.int32).contiguous(), gw.contiguous()
     for s, e in _blocks(E.shape[0], block):
-        logits = _block_logits(h, E[s:e])
-        d = torch.exp(logits - logZ[:, None])
-        inb = (tl >= s) & (tl < e)
-        d.scatter_add_(1, (tl - s).clamp(0, e - s - 1).unsqueeze(1), -inb.to(d.dtype).unsqueeze(1))
-        d = d * gw[:, None]
+        if fused:
+            db = kernels.linear_ce_dlogits(h, E[s:e], ti, gwc, logZ, s)
+        else:
+            logits = _block_logits(h, E[s:e])
+            d = torch.exp(logits - logZ[:, None])
+            inb = (tl >= s) & (tl < e)
+            d.scatter_add_(1, (tl - s).clamp(0, e - s - 1).unsqueeze(1), -inb.to(d.dtype).unsqueeze(1))
+            d = d * gw[:, None]
         if kern:
-            db = d.to(torch.bfloat16)
+            if not fused:
+                db = d.to(torch.bfloat16)
             if need_h:
                 _gemm.gemm_raw(db, E[s:e], False, False, torch.float32, out=g_h, accumulate=True)
             if need_E:
@@ -125,6 +148,9 @@ def per_token_ce(h: torch.Tensor, E: torch.Tensor, targets: torch.Tensor, block:
     """``[N]`` cross-entropy of every row, forward only."""
     if block <= 0:
         return ref.per_token_ce_dense(h, E, targets)
+    if _fused(h, E):
+        from . import kernels
+        return kernels.linear_ce_fwd(h, E, targets)[1]
     return _stream_lse(h, E, block) - _target_logit(h, E, targets)
 
 

@@ -249,3 +249,52 @@ def attention_fwd(q, k, v, scale, causal):
 
 def attention_supported(q, k) -> bool:
     return q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and (q.shape[2] % k.shape[2] == 0)
+
+
+# =============================================================================== linear + cross-entropy family
+_lib.register("dttt_linear_ce_scratch_elems", _ll, [_i, _i])
+_lib.register("dttt_linear_ce_fwd", _i, [_vp, _vp, _vp, _i, _i, _i, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp])
+_lib.register("dttt_linear_ce_dlogits", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _i, _vp, _vp])
+_SYMBOL.update(linear_ce="dttt_linear_ce_fwd")
+
+
+def _rows_bf16(t):
+    """A 2-D bf16 view whose row stride and base are 16-byte aligned (copying only when they are not)."""
+    if t.stride(-1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+def linear_ce_supported(h, E) -> bool:
+    return h.is_cuda and h.dtype == torch.bfloat16 and E.dtype == torch.bfloat16 and h.shape[-1] % 8 == 0
+
+
+def linear_ce_fwd(h, E, targets):
+    """``(lse [N], nll [N])`` (f32) of the logits ``h @ E^T`` without writing them: the GEMM's epilogue reduces every
+    128 x 256 logit tile to a (max, sum-exp) pair in a scratch buffer and a second small kernel combines the pairs."""
+    N, K = h.shape
+    V = E.shape[0]
+    hc, Ec = _rows_bf16(h), _rows_bf16(E)
+    ti = targets.to(torch.int32).contiguous()
+    scratch = torch.empty(int(_lib.lib().dttt_linear_ce_scratch_elems(N, V)), 2, dtype=torch.float32, device=h.device)
+    tgt = torch.zeros(N, dtype=torch.float32, device=h.device)
+    lse = torch.empty(N, dtype=torch.float32, device=h.device)
+    nll = torch.empty(N, dtype=torch.float32, device=h.device)
+    st = _lib.status_tensor(h.device)
+    _check(_lib.lib().dttt_linear_ce_fwd(_p(hc), _p(Ec), _p(ti), N, V, K, hc.stride(0), Ec.stride(0), _p(scratch), _p(tgt), _p(lse),
+                                         _p(nll), _p(st), _stream()), "linear_ce_fwd")
+    global LAUNCHES
+    LAUNCHES += 1                                   # the combine kernel
+    return lse, nll
+
+
+def linear_ce_dlogits(h, Eb, targets_i32, coef, lse, col0):
+    """``coef[:, None] * (softmax(h @ E^T)[:, col0:col0 + len(Eb)] - onehot(targets))`` in bf16, from the GEMM's epilogue."""
+    N, K = h.shape
+    nb = Eb.shape[0]
+    hc, Ec = _rows_bf16(h), _rows_bf16(Eb)
+    D = torch.empty(N, nb, dtype=torch.bfloat16, device=h.device)
+    st = _lib.status_tensor(h.device)
+    _check(_lib.lib().dttt_linear_ce_dlogits(_p(hc), _p(Ec), _p(targets_i32), _p(coef), _p(lse), _p(D), N, nb, K, hc.stride(0),
+                                             Ec.stride(0), D.stride(0), int(col0), _p(st), _stream()), "linear_ce_dlogits")
+    return D
