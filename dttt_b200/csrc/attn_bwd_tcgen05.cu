@@ -1,0 +1,429 @@
+// Chunk-window flash attention, backward, on tcgen05 tensor cores (head dimension 64).
+//
+// Given Q, K, V, O, dO and the forward's LSE (layouts of attn_fwd_tcgen05.cu) this produces dQ, dK, dV of
+//   O = softmax(scale * Q K^T + mask) V        (reference src/ttt/attention.py:181-201, first-order VJP).
+//
+// One CTA owns one block of 128 keys of one (sequence, KV head) and walks over every query tile that sees it,
+// for each of the rep = nh / nkv query heads of the group; dK and dV of the block accumulate in tensor memory over
+// the whole walk (so GQA needs no atomics for them), dQ tiles are produced per step and added into an f32 buffer.
+// Everything is computed transposed (keys on TMEM lanes, queries on columns) so that P^T and dS^T, written back to
+// tensor memory as bf16 pairs by the thread that owns the key row, are directly the A operands of
+//   dV += P^T dO      dK += dS^T Q                      (A from TMEM)
+// and dS^T, also written to shared memory, is the M-major A operand of  dQ = dS K.
+// Per step:   S^T = K Q^T,  dP^T = V dO^T   ->   P^T = exp2(S^T sl2 - LSE),  dS^T = P^T (dP^T - D) scale.
+//
+//   warp 0      TMA: K, V once; Q and dO tiles into two stages
+//   warp 1      tcgen05.mma issuer, TMEM owner
+//   warps 2-9   two per TMEM lane quarter (one per 64-query half): softmax-backward math, then the reduction of the
+//               step's dQ tile into global memory (red.global.add.v4.f32), then the final dK / dV stores
+// TMEM columns: S^T / P^T [0,128)  dP^T / dS^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448).
+// Every wait is bounded (ptx_sm100.cuh); on a timeout the roles leave through the common exit and TMEM is freed.
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace dttt {
+
+constexpr int BQ = 128, BKEY = 128, HD = 64;
+
+struct AttnBwdParams {
+  int n, Cq, Kn, nh, nkv, causal;
+  float scale;
+  const float* lse;     // [n, nh, Cq]
+  const float* delta;   // [n, nh, Cq]  rowsum(dO * O)
+  float* dQ;            // [n, Cq, nh, 64] f32, accumulated into
+  __nv_bfloat16* dK;    // [n, Kn, nkv, 64]
+  __nv_bfloat16* dV;
+  int* status;
+};
+
+struct BwdSmem {
+  static constexpr int TILE = 128 * HD * 2;                 // 16 KB: one [128, 64] bf16 tile
+  static constexpr int DS_BYTES = 128 * 128 * 2;            // dS^T for the dQ product
+  static constexpr int STAGES = 2;
+  static constexpr int AUX = 2 * 2 * 128 * 4;               // LSE and D, two buffers
+  static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + DS_BYTES + AUX + 1024 + 1024;
+};
+
+__device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Barrier `id` over `nthreads` threads that also ANDs a per-thread flag: every participant gets the same verdict.
+__device__ __forceinline__ int bar_red_and(int id, int nthreads, int flag) {
+  int out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, %2, %3, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t}"
+      : "=r"(out) : "r"(flag), "r"(id), "r"(nthreads) : "memory");
+  return out;
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; eight threads per row of 64.
+__global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                      float* __restrict__ delta, long long rows, int Cq, int nh) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid >> 3;                            // row = (b * Cq + i) * nh + h
+  const int part = (int)(gid & 7);
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(O + row * HD + part * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + row * HD + part * 8);
+    const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float2 x = __bfloat1622float2(ab[q]), y = __bfloat1622float2(gb[q]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (part == 0 && row < rows) {
+    const long long bi = row / nh;                           // b * Cq + i
+    const int h = (int)(row - bi * nh);
+    const long long b = bi / Cq;
+    const int i = (int)(bi - b * Cq);
+    delta[(b * nh + h) * Cq + i] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(320, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
+                const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const AttnBwdParams p) {
+  using L = BwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + L::TILE;
+  uint8_t* sST = sV + L::TILE;                               // stages: [Q tile | dO tile]
+  uint8_t* sDS = sST + L::STAGES * 2 * L::TILE;
+  float* sLSE = reinterpret_cast<float*>(sDS + L::DS_BYTES); // [2][128], premultiplied by log2(e)
+  float* sDel = sLSE + 2 * 128;                              // [2][128], premultiplied by scale
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sDel + 2 * 128));
+  uint64_t* kv_full = bars;
+  uint64_t* st_full = bars + 1;                              // [2]
+  uint64_t* st_empty = st_full + 2;                          // [2]
+  uint64_t* s_full = st_empty + 2;
+  uint64_t* pds_ready = s_full + 1;
+  uint64_t* dq_full = pds_ready + 1;
+  uint64_t* dq_empty = dq_full + 1;
+  uint64_t* acc_final = dq_empty + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_final + 1);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int rep = p.nh / p.nkv;
+  const int off = p.Kn - p.Cq;
+  const int nqt = (p.Cq + BQ - 1) / BQ;
+  int qt_start = 0;
+  if (p.causal) { const int lo = jb * BKEY - off; qt_start = lo > 0 ? lo / BQ : 0; }
+  const int nq_it = max(0, nqt - qt_start);
+  const int n_it = rep * nq_it;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&st_full[s], 1); mbar_init(&st_empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(pds_ready, 256);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 256);
+    mbar_init(acc_final, 1);
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapdO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one() && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * L::TILE);
+      tma_load_4d_b(sK, &mapK, kv_full, 0, hk, jb * BKEY, b);
+      tma_load_4d_b(sV, &mapV, kv_full, 0, hk, jb * BKEY, b);
+      for (int it = 0; it < n_it; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&st_empty[s], ((it >> 1) & 1) ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
+        const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+        uint8_t* sQ = sST + s * 2 * L::TILE;
+        mbar_expect_tx(&st_full[s], 2 * L::TILE);
+        tma_load_4d_b(sQ, &mapQ, &st_full[s], 0, h, qt * BQ, b);
+        tma_load_4d_b(sQ + L::TILE, &mapdO, &st_full[s], 0, h, qt * BQ, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one() && n_it > 0) {
+      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);        // S^T, dP^T: both operands K-major ([rows, d])
+      const uint32_t id_kv = make_idesc_bf16(128, HD, 0, 1);        // dV, dK: A from TMEM, B = [q rows, d] N-major
+      const uint32_t id_q = make_idesc_bf16(128, HD, 1, 1);         // dQ: A = dS^T (M-major), B = K (N-major)
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_word, p.status, ERR_WAIT_FULL);
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&st_full[s], (it >> 1) & 1, abort_word, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sST + s * 2 * L::TILE), aDO = aQ + L::TILE;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem + C_S, make_smem_desc(aK + k * 32, 16, 1024), make_smem_desc(aQ + k * 32, 16, 1024), id_s, k ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem + C_DP, make_smem_desc(aV + k * 32, 16, 1024), make_smem_desc(aDO + k * 32, 16, 1024), id_s, k ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(pds_ready, it & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)                            // contraction over the 128 queries of the tile
+          umma_f16_ts(tmem + C_DV, tmem + C_S + k * 8, make_smem_desc(aDO + k * 2048, 16384, 1024), id_kv, (it | k) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < BQ / 16; ++k)
+          umma_f16_ts(tmem + C_DK, tmem + C_DP + k * 8, make_smem_desc(aQ + k * 2048, 16384, 1024), id_kv, (it | k) ? 1u : 0u);
+        umma_commit(&st_empty[s]);                                    // Q and dO of this stage are consumed
+        if (!mbar_wait_bounded(dq_empty, (it & 1) ^ 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < BKEY / 16; ++k)                          // contraction over the 128 keys of the block
+          umma_f16(tmem + C_DQ, make_smem_desc(aDS + k * 2048, 16384, 1024), make_smem_desc(aK + k * 2048, 16384, 1024), id_q, k ? 1u : 0u);
+        umma_commit(dq_full);
+      }
+      if (ok) umma_commit(acc_final);
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax backward, dQ reduction, dK / dV stores
+    const int w = warp - 2;                                  // 0..7
+    const int quarter = warp & 3;                            // TMEM lane quarter of this warp
+    const int half = w >> 2;                                 // which 64 columns this warp handles
+    const int tid = threadIdx.x - 64;                        // 0..255
+    const int kr = quarter * 32 + lane;                      // key row within the block == TMEM lane
+    const int kj = jb * BKEY + kr;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    bool ok = n_it > 0;
+    // stage the first step's LSE / D
+    auto load_aux = [&](int it, float& val) {
+      const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+      const int qi = qt * BQ + (tid & 127);
+      const long long base = ((long long)b * p.nh + h) * p.Cq;
+      if (tid < 128) val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
+      else val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
+    };
+    if (ok) {
+      float v0;
+      load_aux(0, v0);
+      if (tid < 128) sLSE[tid] = v0; else sDel[tid - 128] = v0;
+    }
+    for (int it = 0; it < n_it && ok; ++it) {
+      float vnext = 0.f;
+      if (it + 1 < n_it) load_aux(it + 1, vnext);
+      const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+      const float* lse2 = sLSE + (it & 1) * 128;
+      const float* del = sDel + (it & 1) * 128;
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(s_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      // one verdict for all eight warps (they meet at barriers below); also publishes this step's LSE / D
+      if (!bar_red_and(1, 256, got)) { ok = false; break; }
+      tc_fence_after();
+      // entry (key kj, query qi) is visible iff kj <= qi + off (causal) and kj < Kn
+      const bool key_ok = kj < p.Kn;
+      const bool need_mask = p.causal && (jb * BKEY + BKEY - 1 > qt * BQ + off);
+      const int c0 = half * 64;                              // first query column of this warp
+      uint32_t pp[32], dd[32];
+      {
+        uint32_t sr[64], dr[64];
+        tmem_ld_32x32(tmem + C_S + lane_addr + c0, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+        tmem_ld_32x32(tmem + C_S + lane_addr + c0 + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+        tmem_ld_32x32(tmem + C_DP + lane_addr + c0, reinterpret_cast<uint32_t(&)[32]>(dr[0]));
+        tmem_ld_32x32(tmem + C_DP + lane_addr + c0 + 32, reinterpret_cast<uint32_t(&)[32]>(dr[32]));
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);     // broadcast reads
+          const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);      // D * scale
+          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
+            if (!key_ok || (need_mask && kj > qt * BQ + c0 + i + u + off)) pe = 0.f;
+            pv[u] = pe;
+            dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u += 2) {
+            __nv_bfloat162 pb = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+            __nv_bfloat162 db = __floats2bfloat162_rn(dv[u], dv[u + 1]);
+            pp[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&pb);
+            dd[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&db);
+          }
+        }
+      }
+      // every warp has read its S^T / dP^T columns: the packed results may now overwrite them
+      tc_fence_before();
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      tc_fence_after();
+      tmem_st_32x32(tmem + C_S + lane_addr + c0 / 2, pp);    // 64 queries -> 32 columns of bf16 pairs
+      tmem_st_32x32(tmem + C_DP + lane_addr + c0 / 2, dd);
+      {
+        // dS^T row kr, queries c0..c0+63, into the M-major A tile: 64-query block `half`, 128-byte rows indexed by key
+        uint8_t* base = sDS + half * (128 * 128) + (kr / 8) * 1024 + (kr % 8) * 128;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(base + ((q ^ (kr % 8)) * 16)) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+      }
+      tmem_st_wait();
+      fence_async_proxy();
+      tc_fence_before();
+      mbar_arrive(pds_ready);
+      // next step's LSE / D into the other buffer (its last readers passed barrier 1 of this step)
+      if (it + 1 < n_it) {
+        if (tid < 128) sLSE[((it + 1) & 1) * 128 + tid] = vnext; else sDel[((it + 1) & 1) * 128 + tid - 128] = vnext;
+      }
+      // dQ tile of this step: lanes = queries, 64 columns; this warp adds its 32 lanes x 32 columns
+      if (lane == 0) got = mbar_wait_bounded(dq_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!bar_red_and(3, 256, got)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + C_DQ + lane_addr + half * 32, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_empty);
+        const int qi = qt * BQ + kr;                         // lane index doubles as the query row here
+        if (qi < p.Cq) {
+          float* dst = p.dQ + (((long long)b * p.Cq + qi) * p.nh + h) * HD + half * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4(dst + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+      }
+    }
+    // dK, dV of the block
+    if (ok) {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(acc_final, 0, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got) {
+        tc_fence_after();
+        uint32_t rv[32], rk[32];
+        tmem_ld_32x32(tmem + C_DV + lane_addr + half * 32, rv);
+        tmem_ld_32x32(tmem + C_DK + lane_addr + half * 32, rk);
+        tmem_ld_wait();
+        if (kj < p.Kn) {
+          const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + half * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v, k;
+            __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+            __nv_bfloat162* kb = reinterpret_cast<__nv_bfloat162*>(&k);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              vb[q] = __floats2bfloat162_rn(__uint_as_float(rv[i + 2 * q]), __uint_as_float(rv[i + 2 * q + 1]));
+              kb[q] = __floats2bfloat162_rn(__uint_as_float(rk[i + 2 * q]), __uint_as_float(rk[i + 2 * q + 1]));
+            }
+            *reinterpret_cast<uint4*>(p.dV + o + i) = v;
+            *reinterpret_cast<uint4*>(p.dK + o + i) = k;
+          }
+        }
+      }
+    } else if (n_it == 0 && kj < p.Kn) {
+      // no query sees this key block: its gradients are zero
+      const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + half * 32;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        *reinterpret_cast<uint4*>(p.dV + o + i) = z;
+        *reinterpret_cast<uint4*>(p.dK + o + i) = z;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
+typedef CUresult (*EncodeTiledFnB)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFnB bwd_encode_fn() {
+  static EncodeTiledFnB fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFnB>(ptr);
+  });
+  return fn;
+}
+
+static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads) {
+  EncodeTiledFnB enc = bwd_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)heads * HD * 2, (cuuint64_t)rows * heads * HD * 2};
+  cuuint32_t box[4] = {64, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+}  // namespace dttt
+
+using namespace dttt;
+
+// Q, O, dO [n, Cq, nh, 64]; K, V, dK, dV [n, Kn, nkv, 64] (bf16, contiguous); lse [n, nh, Cq] f32 from the forward;
+// delta [n, nh, Cq] f32 scratch (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).
+extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* lse,
+                             float* delta, float* dQ, void* dK, void* dV, int n, int Cq, int Kn, int nh, int nkv, int d,
+                             float scale, int causal, int* status, cudaStream_t stream) {
+  if (d != HD || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
+  if (causal && Kn < Cq) return -3;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
+  CUtensorMap mq, mdo, mk, mv;
+  int r;
+  if ((r = make_map4b(&mq, Q, n, Cq, nh))) return 100 + r;
+  if ((r = make_map4b(&mdo, dO, n, Cq, nh))) return 200 + r;
+  if ((r = make_map4b(&mk, K, n, Kn, nkv))) return 300 + r;
+  if ((r = make_map4b(&mv, V, n, Kn, nkv))) return 400 + r;
+  const long long rows = (long long)n * Cq * nh;
+  attn_bwd_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, rows, Cq, nh);
+  AttnBwdParams p;
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
+  p.lse = lse; p.delta = delta; p.dQ = dQ;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dK); p.dV = reinterpret_cast<__nv_bfloat16*>(dV); p.status = status;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
+  dim3 grid((Kn + BKEY - 1) / BKEY, nkv, n);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

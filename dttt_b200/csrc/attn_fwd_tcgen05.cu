@@ -280,6 +280,258 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Second version: two 128-row query tiles per CTA in ping-pong, P kept in tensor memory.
+//
+//   warp 0      TMA: Q (both tiles) once, then K / V stages
+//   warp 1      tcgen05.mma issuer.  Per key block and tile: O_t += P_t V (A operand read from TMEM), then the
+//               next S_t = Q_t K^T into the same TMEM columns P_t occupied; the tensor pipe runs its queue in order,
+//               so tile A's products run while tile B's softmax computes and the other way round
+//   warps 2-5   softmax of tile A, warps 6-9 of tile B: one thread per row holds the 128 scores of the block in
+//               registers, writes P (bf16 pairs) back over the first 64 columns of its S row
+// The running maximum is only raised when a row's block maximum exceeds it by more than 2^8 (in the exponent's
+// units), so most blocks skip the read-modify-write of the O row; the final O / l and the LSE are exact either way.
+// TMEM columns: S_A / P_A [0,128)  S_B / P_B [128,256)  O_A [256,256+D)  O_B [256+D,256+2D).
+template <int D>
+struct Attn2Smem {
+  static constexpr int Q_BYTES = 2 * AQ * D * 2;
+  static constexpr int KV_BYTES = 2 * AK * D * 2;
+  static constexpr int STAGES = (D == 64) ? 4 : 2;
+  static constexpr int TOTAL = Q_BYTES + STAGES * KV_BYTES + 1024 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(320, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                 const __grid_constant__ CUtensorMap mapV, const AttnParams p) {
+  using L = Attn2Smem<D>;
+  constexpr int DB = D / 64;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + L::Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + L::STAGES * L::KV_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;
+  uint64_t* kv_empty = kv_full + L::STAGES;
+  uint64_t* s_full = kv_empty + L::STAGES;     // [2] one per tile
+  uint64_t* p_ready = s_full + 2;              // [2]
+  uint64_t* o_final = p_ready + 2;             // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_final + 2);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = gridDim.x - 1 - blockIdx.x;                // longest (latest) query tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.nh / p.nkv);
+  const int q0 = qt * 2 * AQ;
+  const int off = p.Kn - p.Cq;
+  int nb[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int last_key = p.Kn - 1;
+    if (p.causal) last_key = min(last_key, q0 + t * AQ + AQ - 1 + off);
+    nb[t] = (q0 + t * AQ < p.Cq) ? last_key / AK + 1 : 0;
+  }
+  const int nbmax = max(nb[0], nb[1]);
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t O_COL = 256;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < L::STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 128); mbar_init(&o_final[t], 1); }
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (elect_one()) {
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int db = 0; db < DB; ++db)
+          tma_load_4d(sQ + t * (AQ * D * 2) + db * (AQ * 128), &mapQ, q_full, db * 64, h, q0 + t * AQ, b);
+      for (int j = 0; j < nbmax; ++j) {
+        const int s = j % L::STAGES;
+        const uint32_t ph = (j / L::STAGES) & 1;
+        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
+        uint8_t* sK = sKV + s * L::KV_BYTES;
+        uint8_t* sV = sK + AK * D * 2;
+        mbar_expect_tx(&kv_full[s], L::KV_BYTES);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_4d(sK + db * (AK * 128), &mapK, &kv_full[s], db * 64, hk, j * AK, b);
+          tma_load_4d(sV + db * (AK * 128), &mapV, &kv_full[s], db * 64, hk, j * AK, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc_s = make_idesc_bf16(AQ, AK, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(AQ, D, 0, 1);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_word, p.status, ERR_WAIT_FULL);
+      int loaded = -1;                                       // newest key block whose stage is known to be full
+      auto issue_s = [&](int t, int j) -> bool {
+        const int s = j % L::STAGES;
+        if (j > loaded) {
+          if (!mbar_wait_bounded(&kv_full[s], (j / L::STAGES) & 1, abort_word, p.status, ERR_WAIT_FULL)) return false;
+          tc_fence_after();
+          loaded = j;
+        }
+        const uint32_t aQ = smem_u32(sQ + t * (AQ * D * 2));
+        const uint32_t aK = smem_u32(sKV + s * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t koff = (k / 4) * (AQ * 128) + (k % 4) * 32;
+          umma_f16(tmem + t * 128, make_smem_desc(aQ + koff, 16, 1024), make_smem_desc(aK + koff, 16, 1024), idesc_s, k ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+        return true;
+      };
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (ok && nb[t] > 0) ok = issue_s(t, 0);
+      for (int j = 0; j < nbmax && ok; ++j) {
+        const int s = j % L::STAGES;
+        const uint32_t aV = smem_u32(sKV + s * L::KV_BYTES + AK * D * 2);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || j >= nb[t]) continue;
+          if (!mbar_wait_bounded(&p_ready[t], j & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < AK / 16; ++k)                  // 16 keys = 8 TMEM columns of packed bf16 pairs
+            umma_f16_ts(tmem + O_COL + t * D, tmem + t * 128 + k * 8, make_smem_desc(aV + k * (16 * 128), AK * 128, 1024),
+                        idesc_o, (j | k) ? 1u : 0u);
+          if (j + 1 < nb[t]) ok = issue_s(t, j + 1);
+          else umma_commit(&o_final[t]);
+        }
+        if (ok) umma_commit(&kv_empty[s]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue
+    const int t = (warp - 2) >> 2;                          // tile of this warpgroup
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qi = q0 + t * AQ + row;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + t * 128 + lane_addr;
+    const uint32_t o_addr = tmem + O_COL + t * D + lane_addr;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int limit = p.causal ? (qi + off) : (p.Kn - 1);
+    float m = -1e30f, l = 0.f;
+    bool ok = true;
+    const int nbt = nb[t];
+    for (int j = 0; j < nbt; ++j) {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(&s_full[t], j & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sr[128];
+      tmem_ld_32x32(s_addr + 0, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+      tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+      tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sr[64]));
+      tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sr[96]));
+      tmem_ld_wait();
+      const int kbase = j * AK;
+      if ((kbase + AK - 1 > limit) || (kbase + AK > p.Kn)) {
+        const int lim = min(limit, p.Kn - 1) - kbase;        // last visible column of this block for this row
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i > lim) sr[i] = __float_as_uint(-1e30f);
+      }
+      float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));     mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // raise the reference maximum only on a large jump (warp-uniform decision: the TMEM accesses are collective)
+      if (__any_sync(0xffffffffu, (mx - m) * sl2 > 8.f)) {
+        const float m_new = fmaxf(m, mx);
+        const float alpha = exp2f((m - m_new) * sl2);
+        m = m_new;
+        l *= alpha;
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_addr + c, o);
+          }
+        }
+      }
+      const float mneg = -m * sl2;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 2) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), sl2, mneg));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), sl2, mneg));
+        sum0 += p0; sum1 += p1;
+        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        pk[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
+      }
+      l += sum0 + sum1;
+      tmem_st_32x32(s_addr + 0, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+      tmem_st_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_ready[t]);
+    }
+    if (ok && nbt > 0) {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(&o_final[t], 0, abort_word, p.status, ERR_WAIT_TMEM_EMPTY) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got) {
+        tc_fence_after();
+        const float inv = 1.f / l;
+        __nv_bfloat16* out = p.O + (((long long)b * p.Cq + qi) * p.nh + h) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_addr + c, r);
+          tmem_ld_wait();
+          if (qi < p.Cq) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                vb[q] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * q]) * inv, __uint_as_float(r[i + 2 * q + 1]) * inv);
+              *reinterpret_cast<uint4*>(out + c + i) = v;
+            }
+          }
+        }
+        if (qi < p.Cq && p.lse) p.lse[((long long)b * p.nh + h) * p.Cq + qi] = m * p.scale + logf(l);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, TMEM_COLS); }
+}
+
 typedef CUresult (*EncodeTiledFn4)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -315,8 +567,9 @@ static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int hea
 using namespace dttt;
 
 // Q [n, Cq, nh, d], K / V [n, Kn, nkv, d], O [n, Cq, nh, d] (bf16, contiguous), lse [n, nh, Cq] f32 or null.  d in {64, 128}.
+// variant 0: two query tiles per CTA, P in tensor memory (the default); 1: one tile per CTA, P through shared memory.
 extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, void* O, float* lse, int n, int Cq, int Kn, int nh,
-                             int nkv, int d, float scale, int causal, int* status, cudaStream_t stream) {
+                             int nkv, int d, float scale, int causal, int variant, int* status, cudaStream_t stream) {
   if ((d != 64 && d != 128) || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
   if (causal && Kn < Cq) return -3;
   static thread_local bool ctx_bound = false;
@@ -329,6 +582,19 @@ extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, void* 
   AttnParams p;
   p.n = n; p.Cq = Cq; p.Kn = Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
   p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
+  if (variant == 0) {
+    dim3 grid2((Cq + 2 * AQ - 1) / (2 * AQ), nh, n);
+    static bool a64 = false, a128 = false;
+    if (d == 64) {
+      if (!a64) { cudaFuncSetAttribute(attn_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<64>::TOTAL); a64 = true; }
+      attn_fwd2_kernel<64><<<grid2, 320, Attn2Smem<64>::TOTAL, stream>>>(mq, mk, mv, p);
+    } else {
+      if (!a128) { cudaFuncSetAttribute(attn_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<128>::TOTAL); a128 = true; }
+      attn_fwd2_kernel<128><<<grid2, 320, Attn2Smem<128>::TOTAL, stream>>>(mq, mk, mv, p);
+    }
+    cudaError_t e2 = cudaGetLastError();
+    return e2 == cudaSuccess ? 0 : 1000 + (int)e2;
+  }
   dim3 grid((Cq + AQ - 1) / AQ, nh, n);
   static bool attr64 = false, attr128 = false;
   if (d == 64) {

@@ -194,7 +194,7 @@ def _fast_fwd(q, K, V, scale, causal):
 def _fast_bwd(g, tensors, saved, needs, scale, causal):
     from . import kernels
     q, K, V = tensors
-    if kernels.available("attention_bwd") and saved:
+    if saved and kernels.available("attention_bwd") and kernels.attention_bwd_supported(q, K):
         return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, causal)
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))

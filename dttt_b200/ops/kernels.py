@@ -13,8 +13,11 @@ import torch
 
 from . import _lib
 
+import os
+
 _FAMILIES: Dict[str, bool] = {}
-_DISABLED = set()
+# DTTT_DISABLE_KERNELS=attention,linear_ce,... switches families off (ablations; the op falls back to its staged statement)
+_DISABLED = set(x for x in os.environ.get("DTTT_DISABLE_KERNELS", "").split(",") if x)
 LAUNCHES = 0
 
 
@@ -228,11 +231,12 @@ def seq_axpy(w, g, coef, want_lo=False):
 
 
 # =============================================================================== attention family
-_lib.register("dttt_attn_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp])
+_lib.register("dttt_attn_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp])
+ATTN_VARIANT = int(os.environ.get("DTTT_ATTN_VARIANT", "0"))
 _SYMBOL.update(attention="dttt_attn_fwd")
 
 
-def attention_fwd(q, k, v, scale, causal):
+def attention_fwd(q, k, v, scale, causal, variant=None):
     """Flash attention forward on the tcgen05 kernel.  ``q [n, Cq, nh, d]``, ``k / v [n, Kn, nkv, d]`` bf16, every key
     valid, ``causal`` aligned to the end of the key axis.  Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
     n, Cq, nh, d = q.shape
@@ -243,7 +247,7 @@ def attention_fwd(q, k, v, scale, causal):
     lse = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
     st = _lib.status_tensor(q.device)
     _check(_lib.lib().dttt_attn_fwd(_p(qc), _p(kc), _p(vc), _p(o), _p(lse), n, Cq, Kn, nh, nkv, d, float(scale), 1 if causal else 0,
-                                    _p(st), _stream()), "attn_fwd")
+                                    ATTN_VARIANT if variant is None else int(variant), _p(st), _stream()), "attn_fwd")
     return o, lse
 
 
@@ -298,3 +302,28 @@ def linear_ce_dlogits(h, Eb, targets_i32, coef, lse, col0):
     _check(_lib.lib().dttt_linear_ce_dlogits(_p(hc), _p(Ec), _p(targets_i32), _p(coef), _p(lse), _p(D), N, nb, K, hc.stride(0),
                                              Ec.stride(0), D.stride(0), int(col0), _p(st), _stream()), "linear_ce_dlogits")
     return D
+
+
+_lib.register("dttt_attn_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp])
+_SYMBOL.update(attention_bwd="dttt_attn_bwd")
+
+
+def attention_bwd_supported(q, k) -> bool:
+    return attention_supported(q, k) and q.shape[-1] == 64
+
+
+def attention_bwd(g, q, k, v, o, lse, scale, causal):
+    """First-order backward of ``attention_fwd`` on the tcgen05 kernel: ``(dq, dk, dv)``.  ``dq`` is accumulated in f32
+    by the kernel (one ``[128, 64]`` tile per key block and query tile) and cast once at the end."""
+    n, Cq, nh, d = q.shape
+    Kn, nkv = k.shape[1], k.shape[2]
+    qc, kc, vc, oc, gc = q.contiguous(), k.contiguous(), v.contiguous(), o.contiguous(), g.contiguous()
+    dq32 = torch.zeros(n, Cq, nh, d, dtype=torch.float32, device=q.device)
+    delta = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
+    dk, dv = torch.empty_like(kc), torch.empty_like(vc)
+    st = _lib.status_tensor(q.device)
+    _check(_lib.lib().dttt_attn_bwd(_p(qc), _p(kc), _p(vc), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv), n, Cq, Kn,
+                                    nh, nkv, d, float(scale), 1 if causal else 0, _p(st), _stream()), "attn_bwd")
+    global LAUNCHES
+    LAUNCHES += 1                                   # the delta kernel
+    return dq32.to(q.dtype), dk, dv

@@ -119,17 +119,30 @@ def bench_attn(a, out):
     q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
     k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
-    ms = timeit(lambda: kernels.attention_fwd(q, k, v, d ** -0.5, a.causal), a.iters, a.once)
+    ms = timeit(lambda: kernels.attention_fwd(q, k, v, d ** -0.5, a.causal, a.variant), a.iters, a.once)
     _, flops, src = peaks()
     pairs = Cq * Kn - (Cq * (Cq - 1) // 2 if a.causal else 0)             # visible (query, key) pairs
     fl = 4.0 * n * nh * d * pairs
     res = {"kernel": "attn_fwd_tcgen05", "seqs": n, "Cq": Cq, "Kn": Kn, "heads": nh, "kv_heads": nkv, "head_dim": d,
-           "causal": a.causal, "ms": ms, "tflops": fl / ms / 1e9, "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src}
+           "causal": a.causal, "variant": a.variant, "ms": ms, "tflops": fl / ms / 1e9, "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src}
     if a.compare and not a.once:
         with torch.no_grad():
             mt = timeit(lambda: _sdpa_fast(q, k, v, d ** -0.5, a.causal), a.iters)
         res.update(ms_library=mt, tflops_library=fl / mt / 1e9, vs_library=mt / ms)
     out(res)
+    if a.bwd:
+        o, lse = kernels.attention_fwd(q, k, v, d ** -0.5, a.causal, a.variant)
+        g = torch.randn_like(o)
+        mb = timeit(lambda: kernels.attention_bwd(g, q, k, v, o, lse, d ** -0.5, a.causal), a.iters, a.once)
+        resb = {"kernel": "attn_bwd_tcgen05", "seqs": n, "Cq": Cq, "Kn": Kn, "heads": nh, "kv_heads": nkv, "head_dim": d,
+                "causal": a.causal, "ms": mb, "tflops": 2.5 * fl / mb / 1e9, "frac_of_cublas_peak": 2.5 * fl / (mb * 1e-3) / flops,
+                "note": "2.5 x forward FLOPs (five products); includes the delta kernel, the f32 dQ zero-fill and its cast", "peaks": src}
+        if a.compare and not a.once:
+            qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+            oo = _sdpa_fast(qq, kk, vv, d ** -0.5, a.causal)
+            ml = timeit(lambda: torch.autograd.grad(oo, (qq, kk, vv), g, retain_graph=True), a.iters)
+            resb.update(ms_library=ml, vs_library=ml / mb)
+        out(resb)
 
 
 def main(argv=None):
@@ -137,7 +150,7 @@ def main(argv=None):
     ap.add_argument("cmd", choices=["gemm", "attn", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
     ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
-    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1); ap.add_argument("--ta", action="store_true"); ap.add_argument("--tb", action="store_true")
     ap.add_argument("--f32acc", action="store_true"); ap.add_argument("--compare", action="store_true")
@@ -164,7 +177,7 @@ def main(argv=None):
             a.m, a.n, a.k, a.batch, a.ta, a.tb, a.f32acc = M, N, K, B, bool(ta), bool(tb), bool(acc)
             bench_gemm(a, out)
         for n, Cq, Kn, causal in ((8, 1024, 9216, True), (8, 1024, 9216, False), (16, 1024, 1024, True), (8, 1024, 4096, True)):
-            a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim = n, Cq, Kn, causal, 32, 8, 64
+            a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim, a.bwd = n, Cq, Kn, causal, 32, 8, 64, True
             bench_attn(a, out)
         for cmd, R, D in (("rmsnorm", 49152, 2048), ("swiglu", 49152, 8192), ("rope", 49152, 2048), ("adamw", 16384, 8192)):
             a.cmd, a.rows, a.dim = cmd, R, D

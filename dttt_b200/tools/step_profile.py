@@ -1,0 +1,75 @@
+"""Where one training step spends its time: phase ranges (CUDA events) and a per-kernel table.
+
+    python -m dttt_b200.tools.step_profile --config configs/b200_1b_8k --seq-len 8192 --batch 2 [--kernels] [--trace out.json]
+
+Runs two warm-up steps, then one step with the phase ranges of ``utils.prof`` switched on (the ranges synchronise,
+so the wall time of that step is an upper bound), and with ``--kernels`` one more step under ``torch.profiler`` whose
+device-time table is printed by kernel name (top 45) -- the reference gets the same view from ``--profile_dir``
+traces (reference src/ttt/train.py:1096-1110).  ``--trace`` also writes the Chrome trace of that step.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import time
+
+import torch
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.step_profile")
+    ap.add_argument("--config", default="configs/b200_1b_8k")
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--kernels", action="store_true")
+    ap.add_argument("--trace", default="")
+    a = ap.parse_args(argv)
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path.insert(0, root)
+    from dttt_b200.engine import Engine
+    from dttt_b200.ops import gemm, kernels
+    from dttt_b200.schema import ModelConfig, TrainConfig
+    from dttt_b200.utils import prof
+
+    dev = torch.device("cuda", 0)
+    mc = ModelConfig.load(a.config if os.path.isabs(a.config) else os.path.join(root, a.config))
+    tc = TrainConfig(seq_len=a.seq_len, batch_size=a.batch, steps=10000, seed=0, inner_task="causal", outer_shift=True)
+    eng = Engine(mc, tc, device=dev)
+    ids = torch.randint(0, min(mc.vocab_size, 128000), (a.batch, a.seq_len))
+    for s in range(2):
+        t0 = time.time()
+        eng.train_step(ids, s)
+        torch.cuda.synchronize()
+        print(f"warm-up step {s}: {time.time() - t0:.3f} s", flush=True)
+    prof.enable(True)
+    n0 = gemm.LAUNCHES, kernels.LAUNCHES
+    t0 = time.time()
+    eng.train_step(ids, 2)
+    torch.cuda.synchronize()
+    wall = time.time() - t0
+    print(f"step with ranges: {wall:.3f} s  ({a.batch * a.seq_len / wall:.0f} tokens/s)  launches: gemm {gemm.LAUNCHES - n0[0]}, "
+          f"other kernels {kernels.LAUNCHES - n0[1]}")
+    print(prof.format_report(prof.report()))
+    prof.enable(False)
+    print(f"peak device memory: {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB")
+    if a.kernels or a.trace:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as p:
+            eng.train_step(ids, 3)
+            torch.cuda.synchronize()
+        ka = p.key_averages()
+        total = sum(e.self_device_time_total for e in ka) / 1e3
+        print(f"device time by kernel / op (total {total:.1f} ms):")
+        for e in sorted(ka, key=lambda e: -e.self_device_time_total)[:45]:
+            print(f"  {e.key[:90]:90s} n={e.count:6d}  {e.self_device_time_total / 1e3:9.1f} ms")
+        print("host time by op:")
+        for e in sorted(ka, key=lambda e: -e.self_cpu_time_total)[:10]:
+            print(f"  {e.key[:90]:90s} n={e.count:6d}  {e.self_cpu_time_total / 1e3:9.1f} ms")
+        if a.trace:
+            p.export_chrome_trace(a.trace)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -31,8 +31,11 @@ def _ref(q, k, v, scale, causal):
     (1, 100, 100, 2, 1, 64, True),
     (1, 384, 640, 4, 1, 128, True),
     (1, 1024, 9216, 8, 2, 64, True),
+    (2, 640, 1664, 4, 2, 64, True),
+    (1, 512, 512, 4, 2, 128, True),
 ])
-def test_attn_fwd(n, Cq, Kn, nh, nkv, d, causal):
+@pytest.mark.parametrize("variant", [0, 1])
+def test_attn_fwd(n, Cq, Kn, nh, nkv, d, causal, variant):
     from dttt_b200.ops import _lib, kernels
     assert kernels.available("attention"), "the attention kernel is not in the loaded library"
     torch.manual_seed(3)
@@ -40,7 +43,7 @@ def test_attn_fwd(n, Cq, Kn, nh, nkv, d, causal):
     k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
     scale = d ** -0.5
-    o, lse = kernels.attention_fwd(q, k, v, scale, causal)
+    o, lse = kernels.attention_fwd(q, k, v, scale, causal, variant)
     torch.cuda.synchronize()
     _lib.check_status()
     oref, lref = _ref(q, k, v, scale, causal)
@@ -49,7 +52,8 @@ def test_attn_fwd(n, Cq, Kn, nh, nkv, d, causal):
     assert (lse - lref).abs().max().item() < 2e-3
 
 
-def test_attn_fwd_large_magnitude():
+@pytest.mark.parametrize("variant", [0, 1])
+def test_attn_fwd_large_magnitude(variant):
     """Scores far from zero: the running-max rescale has to carry the sum across key blocks."""
     from dttt_b200.ops import kernels
     torch.manual_seed(4)
@@ -57,7 +61,39 @@ def test_attn_fwd_large_magnitude():
     q = 4.0 * torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
     k = 4.0 * torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
-    o, lse = kernels.attention_fwd(q, k, v, d ** -0.5, False)
+    o, lse = kernels.attention_fwd(q, k, v, d ** -0.5, False, variant)
     oref, lref = _ref(q, k, v, d ** -0.5, False)
     assert (o.float() - oref).abs().max().item() < 3e-2
     assert ((lse - lref).abs() / lref.abs().clamp_min(1.0)).max().item() < 2e-3
+
+
+@pytest.mark.parametrize("n,Cq,Kn,nh,nkv,causal", [
+    (1, 128, 128, 1, 1, False),
+    (1, 128, 128, 2, 1, True),
+    (2, 256, 640, 4, 2, True),
+    (2, 256, 640, 4, 2, False),
+    (1, 200, 333, 4, 4, False),
+    (1, 100, 100, 2, 1, True),
+    (1, 1024, 3072, 8, 2, True),
+])
+def test_attn_bwd(n, Cq, Kn, nh, nkv, causal):
+    from dttt_b200.ops import _lib, kernels
+    assert kernels.available("attention_bwd")
+    torch.manual_seed(5)
+    d = 64
+    q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    o, lse = kernels.attention_fwd(q, k, v, scale, causal)
+    dq, dk, dv = kernels.attention_bwd(g, q, k, v, o, lse, scale, causal)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    q32, k32, v32 = (t.float().requires_grad_() for t in (q, k, v))
+    oref, _ = _ref(q32, k32, v32, scale, causal)
+    dqr, dkr, dvr = torch.autograd.grad(oref, (q32, k32, v32), g.float())
+    rel = lambda a, b: (a.float() - b).abs().max().item() / (b.abs().max().item() + 1e-12)
+    assert rel(dv, dvr) < 2e-2, ("dv", rel(dv, dvr))
+    assert rel(dk, dkr) < 2e-2, ("dk", rel(dk, dkr))
+    assert rel(dq, dqr) < 2e-2, ("dq", rel(dq, dqr))
