@@ -534,3 +534,75 @@ extern "C" int dttt_linear_ce_dlogits(const void* h, const void* Eb, const int* 
   p.targets = targets; p.row_coef = coef; p.row_lse = lse; p.col0 = col0;
   return launch_gemm<256, EPI_CE_DLOGITS>(mapA, mapB, p, 0, stream);
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// dttt_linear_ce_fwd without a caller-provided scratch buffer (see linear_ce_static.h for the contract).
+#include "linear_ce_static.h"
+
+static __device__ __align__(256) float2 g_linear_ce_scratch[DTTT_LINEAR_CE_STATIC_MAX_ELEMS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float2* g_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_scratch_mutex;
+
+// Device address of the array on the current device.  The array's name is a host-side handle, not a device
+// pointer: the address comes from cudaGetSymbolAddress, once per device.
+int static_scratch(float2** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
+  // The tensor-map encoder is a driver call: the device's primary context has to be current in the calling thread.
+  static thread_local int bound_dev = -1;
+  if (bound_dev != dev) {
+    if (cudaSetDevice(dev) != cudaSuccess) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
+    bound_dev = dev;
+  }
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (!g_scratch_addr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_linear_ce_scratch) != cudaSuccess || !ptr) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
+    g_scratch_addr[dev] = reinterpret_cast<float2*>(ptr);
+    if (g_num_sms == 0) cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" const char* dttt_linear_ce_static_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case DTTT_LINEAR_CE_STATIC_TOO_LARGE:
+      return "dttt_linear_ce_fwd_static: ceil(rows/128)*128 * ceil(classes/256) exceeds the fixed scratch of 2097152 pairs "
+             "(16 MiB); use dttt_linear_ce_fwd with a caller-allocated scratch buffer";
+    case DTTT_LINEAR_CE_STATIC_SETUP_FAILED:
+      return "dttt_linear_ce_fwd_static: could not resolve the device address of the scratch array on the current device";
+    case -2: return "dttt_linear_ce_fwd_static: operands must be 16-byte aligned with row strides that are multiples of 8 elements";
+    default: return "dttt_linear_ce_fwd_static: launch failed (tensor-map encoding or kernel launch error)";
+  }
+}
+
+extern "C" int dttt_linear_ce_fwd_static(const void* h, const void* E, const int* targets, int rows, int classes, int K,
+                                         long long ldh, long long ldE, float* tgt_logit, float* lse, float* nll, int* status,
+                                         cudaStream_t stream) {
+  if (rows <= 0 || classes <= 0 || K <= 0) return 0;
+  if (dttt_linear_ce_scratch_elems(rows, classes) > DTTT_LINEAR_CE_STATIC_MAX_ELEMS) return DTTT_LINEAR_CE_STATIC_TOO_LARGE;
+  if ((ldh % 8) || (ldE % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(E) & 15)) return -2;
+  float2* scratch = nullptr;
+  int r = static_scratch(&scratch);
+  if (r) return r;
+  CUtensorMap mapA, mapB;
+  if ((r = make_map(&mapA, h, K, rows, 1, ldh, 0, BM))) return 100 + r;
+  if ((r = make_map(&mapB, E, K, classes, 1, ldE, 0, 256))) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = rows; p.N = classes; p.K = K; p.batch = 1; p.alpha = 1.f; p.status = status;
+  p.tiles_m = (rows + BM - 1) / BM;
+  p.tiles_n = (classes + 255) / 256;
+  p.targets = targets; p.part = scratch; p.tgt_logit = tgt_logit;
+  p.part_stride = (long long)p.tiles_m * BM;
+  if ((r = launch_gemm<256, EPI_CE_PARTIAL>(mapA, mapB, p, 0, stream))) return r;
+  ce_combine_kernel<<<(rows + 31) / 32, dim3(32, 8), 0, stream>>>(scratch, p.part_stride, p.tiles_n, rows, tgt_logit, lse, nll);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 2000 + (int)e;
+}
