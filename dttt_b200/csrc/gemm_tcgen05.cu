@@ -30,6 +30,8 @@ constexpr int BM = 128;
 constexpr int BK = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 
+#define DTTT_MAX_TP 8
+
 struct GemmParams {
   int M, N, K, batch;
   int a_mn_major, b_mn_major;
@@ -49,6 +51,18 @@ struct GemmParams {
   float* tgt_logit;         // MODE 1: [M] logit of the target class
   long long part_stride;
   int col0;                 // class index of column 0
+  // fused collectives (MODE 3 / 4): one process per GPU, every pointer below is valid on THIS GPU (CUDA IPC)
+  int m_rotate;             // tile rows are visited starting at this m-block (own rows first)
+  int tp, self_rank, epoch;
+  int rows_per_rank;        // M / tp, a multiple of BM
+  long long a_row_bytes;    // MODE 3: bytes of one row of A that carry data (K * 2)
+  long long lda_bytes;      // MODE 3: row stride of the gather buffer in bytes
+  void* peer_a[DTTT_MAX_TP];      // MODE 3: rank r's gather buffer [M, K] (entry self_rank is the local one)
+  int* peer_flags[DTTT_MAX_TP];   // rank r's flag words: [0, tp) "shard of rank s is in place", [tp, 2 tp) "partials of rank s have landed"
+  int* ready;               // MODE 3: local [tiles_m] words, epoch of the last completed copy of that m-block
+  void* peer_c[DTTT_MAX_TP];      // MODE 4: rank r's slot buffer [tp][rows_per_rank][N] bf16
+  int* done_counter;        // MODE 4: local CTA counter, never reset
+  int done_target;          // MODE 4: its value once every CTA of this launch has finished
 };
 
 // Epilogue modes of the kernel below.
@@ -57,7 +71,63 @@ struct GemmParams {
 //      (the forward of linear + cross-entropy, reference src/ttt/fused_ce.py:42-73)
 //   2  C = coef[row] * (exp(acc - lse[row]) - [col == target[row]])  in bf16
 //      (d loss / d logits, reference fused_ce.py:93-104), consumed by the two gradient GEMMs
-constexpr int EPI_STORE = 0, EPI_CE_PARTIAL = 1, EPI_CE_DLOGITS = 2;
+//   3  the GEMM with the all-gather of A fused in: rows of A owned by other ranks are pulled from their memory over
+//      NVLink by four copy warps per CTA into the local gather buffer while the tensor core works on the rows that
+//      are already here; the TMA producer waits (bounded) on a per-m-block ready word before touching a pulled block
+//   4  the GEMM with the reduce-scatter of C fused in: every finished tile is stored straight into the slot
+//      [this rank] of the rank that owns those rows; the last CTA to finish raises this rank's flag at every peer
+constexpr int EPI_STORE = 0, EPI_CE_PARTIAL = 1, EPI_CE_DLOGITS = 2, EPI_AG = 3, EPI_RS = 4;
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Barrier `id` over 128 threads that also ANDs a per-thread flag (one verdict for the four copy warps).
+__device__ __forceinline__ int bar_red_and_128(int id, int flag) {
+  int out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, %2, 128, p;\n\t"
+      "selp.b32 %0, 1, 0, q;\n\t}"
+      : "=r"(out) : "r"(flag), "r"(id) : "memory");
+  return out;
+}
+// Spin until *flag >= target, for at most a second; on a timeout record `err` and raise the CTA's abort word.
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag_ge(const int* flag, int target, volatile int* abort_word, int* status, int err) {
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    const int v = SYS ? ld_acquire_sys(flag) : ld_acquire_gpu(flag);
+    if (v - target >= 0) return true;
+    if (*abort_word) return false;
+    if ((++spins & 63u) == 0 && global_timer_ns() - t0 > 1000000000ull) {
+      *abort_word = 1;
+      if (status) atomicCAS(status, 0, err);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+
 
 template <int BN>
 struct SmemLayout {
@@ -81,10 +151,11 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   int r = t - band * GROUP * p.tiles_n;
   tm = first_m + (r % rows);
   tn = r / rows;
+  if (p.m_rotate) tm = (tm + p.m_rotate) % p.tiles_m;
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(MODE == 3 ? 320 : 192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const GemmParams p) {
   using L = SmemLayout<BN>;
@@ -130,6 +201,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         int b, tm, tn;
         tile_coords(tile, p, b, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if constexpr (MODE == EPI_AG) {
+          // rows pulled from another rank: wait until the copy warps (of whichever CTA took that block) have
+          // finished it; their stores were generic-proxy writes, the loads below go through the async proxy
+          if (m0 / p.rows_per_rank != p.self_rank) {
+            if (!wait_flag_ge<false>(p.ready + tm, p.epoch, abort_word, p.status, ERR_WAIT_PEER)) { ok = false; break; }
+            fence_async_proxy();
+          }
+        }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t ph = (it / L::STAGES) & 1;
@@ -194,6 +273,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ copy warps (MODE 3 only): the all-gather
+    if constexpr (MODE == EPI_AG) {
+      const int ct = threadIdx.x - 192;                              // 0..127
+      if (blockIdx.x == 0 && ct < p.tp) st_release_sys(p.peer_flags[ct] + p.self_rank, p.epoch);   // my shard is in place
+      const int bpr = p.rows_per_rank / BM;                          // m-blocks per rank
+      const int n_remote = p.tiles_m - bpr;
+      const int vec_per_row = (int)(p.a_row_bytes / 16);
+      const int total = BM * vec_per_row;
+      for (int i = blockIdx.x; i < n_remote; i += gridDim.x) {
+        const int tm = (bpr + i + p.self_rank * bpr) % p.tiles_m;     // the order the tiles are visited in
+        const int src = tm / bpr;
+        int got = 1;
+        if (lane == 0) got = wait_flag_ge<true>(p.peer_flags[p.self_rank] + src, p.epoch, abort_word, p.status, ERR_WAIT_PEER) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        if (!bar_red_and_128(4, got)) break;
+        const char* from = reinterpret_cast<const char*>(p.peer_a[src]) + (long long)tm * BM * p.lda_bytes;
+        char* to = reinterpret_cast<char*>(p.peer_a[p.self_rank]) + (long long)tm * BM * p.lda_bytes;
+        for (int v0 = ct; v0 < total; v0 += 128 * 8) {
+          uint4 buf[8];
+          long long offs[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int idx = v0 + u * 128;
+            const int row = idx / vec_per_row, col = idx - row * vec_per_row;
+            offs[u] = (long long)row * p.lda_bytes + (long long)col * 16;
+            if (idx < total) buf[u] = ld_relaxed_sys_v4(from + offs[u]);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (v0 + u * 128 < total) *reinterpret_cast<uint4*>(to + offs[u]) = buf[u];
+        }
+        __threadfence();
+        asm volatile("bar.sync 4, 128;" ::: "memory");
+        if (ct == 0) { fence_async_proxy(); st_release_gpu(p.ready + tm, p.epoch); }
+      }
+    }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;
@@ -215,7 +331,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.M;
-      const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+      long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+      void* cbase = p.C;
+      if constexpr (MODE == EPI_RS) {
+        // the rows of this tile belong to rank `owner`: store into its slot [self_rank][row - owner * rows_per_rank]
+        const int owner = min(row / p.rows_per_rank, p.tp - 1);
+        cbase = p.peer_c[owner];
+        row_off = ((long long)p.self_rank * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
+      }
       if constexpr (MODE == EPI_CE_PARTIAL) {
         constexpr float LOG2E = 1.4426950408889634f;
         float mx = -3.0e38f;
@@ -266,7 +389,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if (row_ok && col < p.N) {
           const bool full_chunk = (col + 32 <= p.N);
           if (p.c_is_f32) {
-            float* out = reinterpret_cast<float*>(p.C) + row_off + col;
+            float* out = reinterpret_cast<float*>(cbase) + row_off + col;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -286,7 +409,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               }
             }
           } else {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col;
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(cbase) + row_off + col;
             if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -321,6 +444,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[acc]);
+    }
+    if constexpr (MODE == EPI_RS) {
+      // every partial tile of this CTA is on its way to its owner: order the stores at system scope, count the CTA,
+      // and let the last one raise this rank's "partials have landed" flag at every peer
+      __threadfence_system();
+      asm volatile("bar.sync 5, 128;" ::: "memory");
+      if (threadIdx.x == 64 && ok) {
+        const int prev = atomicAdd(p.done_counter, 1);
+        if (prev + 1 == p.done_target) {
+          __threadfence_system();
+          for (int r = 0; r < p.tp; ++r) st_release_sys(p.peer_flags[r] + p.tp + p.self_rank, p.epoch);
+        }
+      }
     }
   }
 
@@ -398,7 +534,7 @@ static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const G
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   int grid = (int)(tiles < cap ? tiles : cap);
-  gemm_bf16_kernel<BN, MODE><<<grid, 192, SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+  gemm_bf16_kernel<BN, MODE><<<grid, MODE == EPI_AG ? 320 : 192, SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
@@ -533,6 +669,142 @@ extern "C" int dttt_linear_ce_dlogits(const void* h, const void* Eb, const int* 
   p.tiles_n = (ncols + 255) / 256;
   p.targets = targets; p.row_coef = coef; p.row_lse = lse; p.col0 = col0;
   return launch_gemm<256, EPI_CE_DLOGITS>(mapA, mapB, p, 0, stream);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Tensor-parallel products with their collective inside the kernel (EPI_AG / EPI_RS above).
+
+namespace dttt {
+// out[i] = residual[i] + sum_s slot[s][i]: the reduction half of the fused GEMM -> reduce-scatter.  Each block first
+// waits (bounded) until every rank's "partials have landed" flag has reached this epoch.
+__global__ void tp_slot_reduce_kernel(const __nv_bfloat16* __restrict__ slots, const int* __restrict__ flags, int tp, int epoch,
+                                      long long n_per_slot, const __nv_bfloat16* __restrict__ residual,
+                                      __nv_bfloat16* __restrict__ out, int* status) {
+  __shared__ int s_ok;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    int ok = 1;
+    for (int r = 0; r < tp && ok; ++r) ok = wait_flag_ge<true>(flags + r, epoch, &s_abort, status, ERR_WAIT_PEER) ? 1 : 0;
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const long long n8 = n_per_slot / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+    if (residual) {
+      const uint4 rv = reinterpret_cast<const uint4*>(residual)[i];
+      const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(rb[q]); acc[2 * q] = f.x; acc[2 * q + 1] = f.y; }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    }
+    for (int s = 0; s < tp; ++s) {
+      const uint4 v = reinterpret_cast<const uint4*>(slots + (long long)s * n_per_slot)[i];
+      const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { const float2 f = __bfloat1622float2(vb[q]); acc[2 * q] += f.x; acc[2 * q + 1] += f.y; }
+    }
+    uint4 o;
+    __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) ob[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+static std::mutex g_done_mutex;
+static std::unordered_map<const void*, int> g_done_count;      // per counter word: CTAs counted so far
+}  // namespace dttt
+
+// C = [A_0; A_1; ...; A_{tp-1}] x B where rank r's rows live in rank r's gather buffer at the same offset.
+//   peer_a[r]      rank r's gather buffer [M, K] bf16, row stride lda (elements); rank `self` has already written its
+//                  own rows [self * M / tp, (self + 1) * M / tp) into peer_a[self] on this stream
+//   peer_flags[r]  rank r's flag words (2 * tp ints, zero at allocation); ready: local [M / 128] ints (zero at allocation)
+//   epoch          a number that grows by one per call on this set of buffers, the same on every rank
+// On return (stream order) peer_a[self] holds all M rows.  M must be a multiple of 128 * tp.
+extern "C" int dttt_gemm_ag_bf16(void* const* peer_a, int* const* peer_flags, int* ready, const void* B, void* C, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, int b_mn_major, int c_is_f32, int tp, int self,
+                                 int epoch, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tp < 1 || tp > DTTT_MAX_TP || M % (BM * tp) || (K % 8) || (lda % 8) || (ldb % 8)) return -2;
+  const void* A = peer_a[self];
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -2;
+  bind_thread_context();
+  const int bn = 256;
+  CUtensorMap mapA, mapB;
+  int r;
+  if ((r = make_map(&mapA, A, K, M, 1, lda, 0, BM))) return 100 + r;
+  if (!b_mn_major) r = make_map(&mapB, B, K, N, 1, ldb, 0, bn);
+  else             r = make_map(&mapB, B, N, K, 1, ldb, 0, BK);
+  if (r) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.batch = 1; p.b_mn_major = b_mn_major;
+  p.ldc = ldc; p.c_is_f32 = c_is_f32; p.alpha = 1.f; p.C = C; p.status = status;
+  p.tiles_m = M / BM; p.tiles_n = (N + bn - 1) / bn;
+  p.tp = tp; p.self_rank = self; p.epoch = epoch; p.rows_per_rank = M / tp;
+  p.m_rotate = self * (p.rows_per_rank / BM);
+  p.a_row_bytes = (long long)K * 2; p.lda_bytes = lda * 2; p.ready = ready;
+  for (int i = 0; i < tp; ++i) { p.peer_a[i] = peer_a[i]; p.peer_flags[i] = peer_flags[i]; }
+  return launch_gemm<256, EPI_AG>(mapA, mapB, p, 0, stream);
+}
+
+// Partial product of this rank, reduce-scattered by rows: slot[self] of the owner of each row block receives
+// alpha-free A x B tiles as they finish.  peer_c[r]: rank r's slot buffer [tp][M / tp][N] bf16; done_counter: a local
+// int (zero at allocation) used only by this entry point.  Follow with dttt_tp_slot_reduce on every rank.
+extern "C" int dttt_gemm_rs_bf16(const void* A, const void* B, void* const* peer_c, int* const* peer_flags, int* done_counter, int M,
+                                 int N, int K, long long lda, long long ldb, int a_mn_major, int b_mn_major, int tp, int self,
+                                 int epoch, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tp < 1 || tp > DTTT_MAX_TP || M % (BM * tp) || (N % 8) || (lda % 8) || (ldb % 8) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -2;
+  bind_thread_context();
+  const int bn = (N > 128) ? 256 : 128;
+  CUtensorMap mapA, mapB;
+  int r;
+  if (!a_mn_major) r = make_map(&mapA, A, K, M, 1, lda, 0, BM);
+  else             r = make_map(&mapA, A, M, K, 1, lda, 0, BK);
+  if (r) return 100 + r;
+  if (!b_mn_major) r = make_map(&mapB, B, K, N, 1, ldb, 0, bn);
+  else             r = make_map(&mapB, B, N, K, 1, ldb, 0, BK);
+  if (r) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.batch = 1; p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
+  p.ldc = N; p.c_is_f32 = 0; p.alpha = 1.f; p.status = status;
+  p.tiles_m = M / BM; p.tiles_n = (N + bn - 1) / bn;
+  p.tp = tp; p.self_rank = self; p.epoch = epoch; p.rows_per_rank = M / tp;
+  for (int i = 0; i < tp; ++i) { p.peer_c[i] = peer_c[i]; p.peer_flags[i] = peer_flags[i]; }
+  p.done_counter = done_counter;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n;
+  const int grid = (int)(tiles < g_num_sms ? tiles : g_num_sms);
+  {
+    std::lock_guard<std::mutex> lock(g_done_mutex);
+    p.done_target = (g_done_count[done_counter] += grid);
+  }
+  if (bn == 256) return launch_gemm<256, EPI_RS>(mapA, mapB, p, 0, stream);
+  return launch_gemm<128, EPI_RS>(mapA, mapB, p, 0, stream);
+}
+
+// out = residual + sum over the tp slots (bf16, n_per_slot elements each, a multiple of 8); waits for every rank's flag.
+extern "C" int dttt_tp_slot_reduce(const void* slots, const int* landed_flags, int tp, int epoch, long long n_per_slot,
+                                   const void* residual, void* out, int* status, cudaStream_t stream) {
+  if (n_per_slot <= 0) return 0;
+  if (n_per_slot % 8) return -2;
+  const long long n8 = n_per_slot / 8;
+  const int threads = 256;
+  long long blocks = (n8 + threads - 1) / threads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  tp_slot_reduce_kernel<<<(int)blocks, threads, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(slots), landed_flags, tp, epoch,
+                                                            n_per_slot, reinterpret_cast<const __nv_bfloat16*>(residual),
+                                                            reinterpret_cast<__nv_bfloat16*>(out), status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
 
 // ------------------------------------------------------------------------------------------------------------------

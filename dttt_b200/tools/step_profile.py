@@ -24,6 +24,7 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--trace", default="")
+    ap.add_argument("--shapes", action="store_true", help="also group the framework ops by input shapes")
     a = ap.parse_args(argv)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -55,7 +56,7 @@ def main(argv=None) -> int:
     print(f"peak device memory: {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB")
     if a.kernels or a.trace:
         from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as p:
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=a.shapes) as p:
             eng.train_step(ids, 3)
             torch.cuda.synchronize()
         ka = p.key_averages()
@@ -66,6 +67,12 @@ def main(argv=None) -> int:
         print("host time by op:")
         for e in sorted(ka, key=lambda e: -e.self_cpu_time_total)[:10]:
             print(f"  {e.key[:90]:90s} n={e.count:6d}  {e.self_cpu_time_total / 1e3:9.1f} ms")
+        if a.shapes:
+            print("device time by op and input shapes:")
+            ks = p.key_averages(group_by_input_shape=True)
+            for e in sorted(ks, key=lambda e: -e.self_device_time_total)[:60]:
+                if e.key.startswith(("aten::", "_")):
+                    print(f"  {e.key[:28]:28s} n={e.count:5d} {e.self_device_time_total / 1e3:8.1f} ms  {str(e.input_shapes)[:150]}")
         if a.trace:
             p.export_chrome_trace(a.trace)
     return 0
