@@ -240,6 +240,35 @@ __global__ void seq_axpy_kernel(const float* __restrict__ w, const T* __restrict
   }
 }
 
+// out[b] += sum_i a[b, i] * g[b, i]   (a f32, g f32 or bf16)
+template <typename T>
+__global__ void seq_dot_kernel(const float* __restrict__ a, const T* __restrict__ g, float* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const long long off = (long long)b * n;
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    s += a[off + i] * (float)g[off + i];
+  s = warp_sum(s);
+  __shared__ float red[32];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(&out[b], s);
+  }
+}
+// out[b, i] = alpha[b] * a[b, i] + beta[b] * g[b, i]   (a f32; g and out f32 or bf16, same type)
+template <typename T>
+__global__ void seq_lincomb_kernel(const float* __restrict__ a, const T* __restrict__ g, const float* __restrict__ alpha,
+                                   const float* __restrict__ beta, T* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const float al = alpha[b], be = beta[b];
+  const long long off = (long long)b * n;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[off + i] = (T)(al * a[off + i] + be * (float)g[off + i]);
+}
+
 inline int grid_for(long long n, int block, int cap = 148 * 16) {
   long long g = (n + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > cap ? cap : g));
@@ -317,5 +346,20 @@ extern "C" int dttt_seq_axpy(const float* w, const void* g, const float* coef, f
   dim3 grid(grid_for(n, 256, 148 * 4), B);
   if (g_is_bf16) seq_axpy_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(w, (const __nv_bfloat16*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
   else seq_axpy_kernel<float><<<grid, 256, 0, s>>>(w, (const float*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_seq_dot(const float* a, const void* g, float* out, int B, long long n, int g_is_bf16, cudaStream_t s) {
+  dim3 grid(grid_for(n, 256, 148 * 2), B);
+  if (g_is_bf16) seq_dot_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, out, n);
+  else seq_dot_kernel<float><<<grid, 256, 0, s>>>(a, (const float*)g, out, n);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_seq_lincomb(const float* a, const void* g, const float* alpha, const float* beta, void* out, int B, long long n,
+                                int g_is_bf16, cudaStream_t s) {
+  dim3 grid(grid_for(n, 256, 148 * 4), B);
+  if (g_is_bf16) seq_lincomb_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, alpha, beta, (__nv_bfloat16*)out, n);
+  else seq_lincomb_kernel<float><<<grid, 256, 0, s>>>(a, (const float*)g, alpha, beta, (float*)out, n);
   return (int)cudaGetLastError();
 }

@@ -137,6 +137,9 @@ struct SmemLayout {
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int BAR_BYTES = 1024;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + alignment slack
+  // EPI_RS stages finished tiles through shared memory so rows leave in 256-byte pieces: 4 warps x 32 rows x 128 columns
+  static constexpr int RS_STAGE_BYTES = 4 * 32 * 128 * 2;
+  static constexpr int TOTAL_RS = TOTAL + RS_STAGE_BYTES;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& b, int& tm, int& tn) {
@@ -339,7 +342,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         cbase = p.peer_c[owner];
         row_off = ((long long)p.self_rank * p.rows_per_rank + (row - owner * p.rows_per_rank)) * p.ldc;
       }
-      if constexpr (MODE == EPI_CE_PARTIAL) {
+      if constexpr (MODE == EPI_RS) {
+        // Peer stores want long contiguous pieces: transpose each 32-row x 128-column piece through this warp's
+        // staging area (16-byte chunks XOR-swizzled by row) and write 256 bytes of one row per half-warp.
+        uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
+        const int row_base = tm * BM + quarter * 32;
+        const int owner = min(row_base / p.rows_per_rank, p.tp - 1);
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer_c[owner]) +
+                             ((long long)p.self_rank * p.rows_per_rank + (row_base - owner * p.rows_per_rank)) * p.ldc;
+#pragma unroll 1
+        for (int hc = 0; hc < BN; hc += 128) {
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + hc + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                vb[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * e]), __uint_as_float(r[8 * q + 2 * e + 1]));
+              const int chunk = c / 8 + q;                                   // 16-byte chunk within the 256-byte row
+              *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = v;
+            }
+          }
+          __syncwarp();
+          const int j = lane & 15;
+          const int col = n0 + hc + j * 8;
+#pragma unroll 4
+          for (int i = 0; i < 32; i += 2) {
+            const int rr = i + (lane >> 4);
+            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((j ^ (rr & 15)) * 16));
+            if (col < p.N && row_base + rr < p.M) *reinterpret_cast<uint4*>(dst + (long long)rr * p.ldc + col) = v;
+          }
+          __syncwarp();
+        }
+      } else if constexpr (MODE == EPI_CE_PARTIAL) {
         constexpr float LOG2E = 1.4426950408889634f;
         float mx = -3.0e38f;
 #pragma unroll 1
@@ -528,13 +568,14 @@ template <int BN, int MODE>
 static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, int max_ctas, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout<BN>::TOTAL);
+    cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL);
     attr_set = true;
   }
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
   int grid = (int)(tiles < cap ? tiles : cap);
-  gemm_bf16_kernel<BN, MODE><<<grid, MODE == EPI_AG ? 320 : 192, SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+  gemm_bf16_kernel<BN, MODE><<<grid, MODE == EPI_AG ? 320 : 192, MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

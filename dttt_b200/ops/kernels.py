@@ -64,6 +64,8 @@ _lib.register("dttt_swiglu_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _ll, _vp])
 _lib.register("dttt_adamw", _i, [_vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _vp])
 _lib.register("dttt_seq_sumsq", _i, [_vp, _vp, _i, _ll, _i, _vp])
 _lib.register("dttt_seq_axpy", _i, [_vp, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp])
+_lib.register("dttt_seq_dot", _i, [_vp, _vp, _vp, _i, _ll, _i, _vp])
+_lib.register("dttt_seq_lincomb", _i, [_vp, _vp, _vp, _vp, _vp, _i, _ll, _i, _vp])
 _SYMBOL.update(rmsnorm="dttt_rmsnorm_fwd", rope="dttt_rope", swiglu="dttt_swiglu_fwd", adamw="dttt_adamw",
                seq="dttt_seq_sumsq")
 
@@ -228,6 +230,27 @@ def seq_axpy(w, g, coef, want_lo=False):
     _check(_lib.lib().dttt_seq_axpy(_p(wc), _p(gc), _p(coef.float().contiguous()), _p(out), _p(lo), B, wc.numel() // B,
                                     1 if gc.dtype == torch.bfloat16 else 0, _stream()), "seq_axpy")
     return (out, lo) if want_lo else out
+
+
+def seq_dot(a_list, g_list):
+    """``[B]`` f32: sum over the pairs of ``sum(a * g)`` per sequence (``a`` f32, ``g`` f32 or bf16, ``[B, ...]`` each)."""
+    B = a_list[0].shape[0]
+    out = torch.zeros(B, dtype=torch.float32, device=a_list[0].device)
+    for a, g in zip(a_list, g_list):
+        ac, gc = a.contiguous(), g.contiguous()
+        _check(_lib.lib().dttt_seq_dot(_p(ac), _p(gc), _p(out), B, ac.numel() // B, 1 if gc.dtype == torch.bfloat16 else 0, _stream()),
+               "seq_dot")
+    return out
+
+
+def seq_lincomb(a, g, alpha, beta):
+    """``alpha[b] * a + beta[b] * g`` per sequence in ``g``'s dtype (``a`` f32)."""
+    B = a.shape[0]
+    ac, gc = a.contiguous(), g.contiguous()
+    out = torch.empty_like(gc)
+    _check(_lib.lib().dttt_seq_lincomb(_p(ac), _p(gc), _p(alpha.float().contiguous()), _p(beta.float().contiguous()), _p(out), B,
+                                       ac.numel() // B, 1 if gc.dtype == torch.bfloat16 else 0, _stream()), "seq_lincomb")
+    return out
 
 
 # =============================================================================== attention family

@@ -345,6 +345,67 @@ def inner_grad(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid, f
     return list(g), terms
 
 
+# The plain step as one autograd node with fused kernels (False: the chain of differentiable torch ops; "force": also
+# for CPU tensors, where the node's pieces are torch statements -- used by the tests).
+FUSED_PLAIN_STEP = [True]
+
+
+def _seq_ops(t: torch.Tensor):
+    """(sumsq, axpy, dot, lincomb) per sequence: the CUDA kernels, or torch statements of the same on the CPU."""
+    from ..ops import kernels
+    if t.is_cuda and kernels.available("seq"):
+        return kernels.seq_sumsq, kernels.seq_axpy, kernels.seq_dot, kernels.seq_lincomb
+    B = t.shape[0]
+    sumsq = lambda ts: sum(x.float().flatten(1).pow(2).sum(1) for x in ts)
+    axpy = lambda w, g, c: w - c.view(B, *([1] * (w.dim() - 1))) * g.float()
+    dot = lambda a_, g_: sum((x.float() * y.float()).flatten(1).sum(1) for x, y in zip(a_, g_))
+    lincomb = lambda a, g, al, be: (al.view(B, *([1] * (a.dim() - 1))) * a + be.view(B, *([1] * (a.dim() - 1))) * g.float()).to(g.dtype)
+    return sumsq, axpy, dot, lincomb
+
+
+class _PlainStep(torch.autograd.Function):
+    """``W'_i = W_i - eta_f s_b g_i`` with ``s_b = min(1, clip / ||g||_b)`` over every matrix of a sequence (reference
+    inner_loop.py:435-481, the default rule), forward and first-order backward each a handful of fused passes:
+
+        dW_i  = dW'_i
+        dg_i  = -eta_f s_b dW'_i + [clipped_b] (clip / ||g||_b^3) (sum_j eta_fj <dW'_j, g_j>_b) g_i + (dnorm_b / ||g||_b) g_i
+        deta_f = -sum_b s_b sum_{i in f} <dW'_i, g_i>_b
+
+    The backward is the meta-gradient's path through the write (reference chunk_scan.py:604-625); nothing
+    differentiates it again."""
+
+    @staticmethod
+    def forward(ctx, clip, eta, n, *Wg):
+        W, g = Wg[:n], Wg[n:]
+        sumsq, axpy, _, _ = _seq_ops(W[0])
+        norm = torch.sqrt(sumsq(list(g)) + 1e-8)
+        s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
+        new = [axpy(W[i], g[i], s * eta[i // 3]) for i in range(n)]
+        ctx.save_for_backward(eta, norm, s, *g)
+        ctx.clip, ctx.n = clip, n
+        return (*new, norm)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, *grads):
+        n, clip = ctx.n, ctx.clip
+        eta, norm, s, *g = ctx.saved_tensors
+        dnew, dnorm = list(grads[:n]), grads[n]
+        _, _, dot, lincomb = _seq_ops(g[0])
+        dnew = [torch.zeros_like(gi, dtype=torch.float32) if d is None else d.float() for d, gi in zip(dnew, g)]
+        F_ = n // 3
+        dots = [dot(dnew[3 * f:3 * f + 3], g[3 * f:3 * f + 3]) for f in range(F_)]          # [F] x [B]
+        wdot = sum(eta[f] * dots[f] for f in range(F_))
+        beta = torch.zeros_like(norm)
+        if clip > 0:
+            beta = torch.where(norm > clip, wdot * clip / norm.pow(3), beta)
+        if dnorm is not None:
+            beta = beta + dnorm / norm
+        dg = [lincomb(dnew[i], g[i], -eta[i // 3] * s, beta) for i in range(n)] if any(ctx.needs_input_grad[3 + n:]) else [None] * n
+        deta = torch.stack([-(s * dots[f]).sum() for f in range(F_)]) if ctx.needs_input_grad[1] else None
+        return (None, deta, None, *dnew, *dg)
+
+
 def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, rule: str = "sgd", *, inner_mask=None,
                 h_clean=None, loss=None, frac: float = 1.0, unit_mask=None, scale=None, W0: Optional[FastW] = None):
     """The step of gradient ``g``: ``(W', pre-clip norm [B])`` (reference inner_loop.py:435-481)."""
@@ -356,23 +417,21 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
              and not net.cw.has("inner_decay_logit"))
     if plain:
         # the main line: one norm, one fused multiply-add per matrix
-        norm = seq_norm(g)
-        s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
-        B = Wl[0].shape[0]
         eta = torch.full((len(W),), float(lr), dtype=torch.float32, device=Wl[0].device)
         if net.cw.has("inner_step_log"):
             eta = eta * torch.exp(net.p("inner_step_log").float())
+        if FUSED_PLAIN_STEP[0] and (Wl[0].is_cuda or FUSED_PLAIN_STEP[0] == "force"):
+            out = _PlainStep.apply(float(clip), eta, len(Wl), *Wl, *g)
+            return unflat(list(out[:-1])), out[-1]
+        norm = seq_norm(g)
+        s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
+        B = Wl[0].shape[0]
         coef = s[:, None] * eta[None, :]                                    # [B, F]
-        from ..ops import kernels
-        fused = Wl[0].is_cuda and not torch.is_grad_enabled() and kernels.available("seq")
         new = []
         for f in range(len(W)):
             for j in range(3):
                 p, d = Wl[3 * f + j], g[3 * f + j]
-                if fused:
-                    new.append(kernels.seq_axpy(p, d, coef[:, f]))
-                else:
-                    new.append(torch.addcmul(p, coef[:, f].view(B, 1, 1), d, value=-1.0))
+                new.append(torch.addcmul(p, coef[:, f].view(B, 1, 1), d, value=-1.0))
         return unflat(new), norm
     if unit_mask is not None:
         g = mask_units(g, unit_mask)

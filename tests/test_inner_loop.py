@@ -1,4 +1,5 @@
 """The write: batched inner gradient == per-sequence gradients of an unrolled statement; clipping; lr ramp."""
+import pytest
 import torch
 
 from util import loss_config, make_engine, tiny_model
@@ -87,3 +88,26 @@ def test_directions_keep_the_gradient_norm():
 def test_inner_lr_ramp():
     assert abs(IN.inner_lr(0, 1.0, 100) - 0.1) < 1e-9 and abs(IN.inner_lr(50, 1.0, 100) - 0.55) < 1e-9
     assert IN.inner_lr(100, 1.0, 100) == 1.0 and IN.inner_lr(3, 0.7, 0) == 0.7
+
+
+@pytest.mark.parametrize("clip", [0.5, 100.0, 0.0])
+def test_fused_plain_step_node_matches_autograd(clip):
+    """The one-node form of the default write (fused passes, hand-written meta-gradient) against the chain of torch ops."""
+    from dttt_b200.ttt import inner
+    torch.manual_seed(0)
+    B, F = 3, 2
+    W = [torch.randn(B, 8, 16, requires_grad=True) for _ in range(3 * F)]
+    g = [(torch.randn(B, 8, 16) * s).requires_grad_() for s in (0.1, 0.2, 0.3, 0.05, 0.4, 0.1)]
+    eta = torch.tensor([0.5, 0.7], requires_grad=True)
+    norm = inner.seq_norm(g)
+    s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
+    new_r = [W[i] - (s * eta[i // 3]).view(B, 1, 1) * g[i] for i in range(6)]
+    out = inner._PlainStep.apply(clip, eta, 6, *W, *g)
+    ws, wn = [torch.randn_like(x) for x in new_r], torch.randn(B)
+    L_r = sum((a * b).sum() for a, b in zip(new_r, ws)) + (norm * wn).sum()
+    L_f = sum((a * b).sum() for a, b in zip(out[:-1], ws)) + (out[-1] * wn).sum()
+    gr = torch.autograd.grad(L_r, [eta] + W + g)
+    gf = torch.autograd.grad(L_f, [eta] + W + g)
+    assert abs(L_r.item() - L_f.item()) < 1e-4
+    for a, b in zip(gr, gf):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
