@@ -176,6 +176,21 @@ class Engine:
         out["overflow"] = self.overflow
         return out
 
+    def grad_of(self, batch: Batch, key: torch.Tensor, step: int, lcfg: Optional[LossConfig] = None, weight: str = "sum"):
+        """Gradient of one batch's loss into ``store.grad`` (no reduction, no optimiser step): ``weight = "sum"`` scales the
+        mean loss by its scored-token count (a sequence's share of a batch gradient), ``"mean"`` leaves it.  Returns
+        ``(loss, scored tokens)``.  Analysis tools use this (gradient noise, Jacobian probes)."""
+        lcfg = lcfg or self.lcfg
+        st = self.store
+        st.zero_grad()
+        cw = ComputeWeights(st, train=True)
+        net = Net(self.mc, cw)
+        loss, stats = loss_fn(net, batch, key, step, lcfg)
+        w = stats["mask_count"].detach() + 1e-6
+        (loss * w if weight == "sum" else loss).backward()
+        cw.fold_grads()
+        return float(loss.detach()), float(w)
+
     def _as_micro_batches(self, batch):
         if isinstance(batch, Batch):
             return [batch]

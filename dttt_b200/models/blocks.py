@@ -137,12 +137,14 @@ class Net:
         q, k, v = self.qkv("prefix", l, x, pos_k, pos_q)                       # [B, S, T, heads, d]
         kc, vc = k[:, CLEAN], v[:, CLEAN]
         k_prev, v_prev = (None, None) if kv_win is None else kv_win
-        k_win = A.window_gather(kc, C, Wn, k_prev)                             # [B, nc, W*C, nkv, d]
-        v_win = A.window_gather(vc, C, Wn, v_prev)
         nv_of = [A.valid_window_chunks(first_chunk + c, Wn, reach) for c in range(nc)]
         groups: Dict[int, List[int]] = {}
         for c, nv in enumerate(nv_of):
             groups.setdefault(nv, []).append(c)
+        # the clean KV windows of every run of chunks with the same number of visible window chunks, [B * run, nv * C, nkv, d]
+        glist = [(nv, cs[0], len(cs)) for nv, cs in groups.items()]
+        k_wins = dict(zip(groups, A.window_groups(kc, C, Wn, k_prev, glist)))
+        v_wins = dict(zip(groups, A.window_groups(vc, C, Wn, v_prev, glist)))
         outs = []
         for s in range(S):
             qs = q[:, s].unflatten(1, (nc, C))                                  # [B, nc, C, nh, d]
@@ -159,7 +161,7 @@ class Net:
                 fl = lambda t: t.flatten(0, 1)
                 if read_block and s == OUTER:
                     extra = (fl(sel(kc.unflatten(1, (nc, C)))), fl(sel(vc.unflatten(1, (nc, C)))))
-                a = A.attend_window(fl(sel(qs)), fl(sel(ks)), fl(sel(vs)), fl(sel(k_win)), fl(sel(v_win)), nv, C,
+                a = A.attend_window(fl(sel(qs)), fl(sel(ks)), fl(sel(vs)), k_wins[nv], v_wins[nv], nv, C,
                                     self.scale, own=own if own != "read" else "full", own_mask=own_mask, extra_own=extra)
                 a = a.unflatten(0, (B, len(cs)))
                 for j, c in enumerate(cs):

@@ -37,6 +37,56 @@ def window_gather(x: torch.Tensor, chunk: int, window: int, prev: Optional[torch
     return xp[:, idx]
 
 
+class _WindowGroups(torch.autograd.Function):
+    """The KV windows of runs of chunks that see the same number of window chunks, cut out of ``[prev | x]`` in one
+    node: ``groups = ((n_valid, first_chunk, count), ...)`` -> one ``[B * count, n_valid * chunk, ...]`` tensor per
+    group holding, for every chunk of the run, the newest ``n_valid`` chunks before it.  One node means one gradient
+    buffer: the backward adds every window's gradient into a single ``[prev | x]``-shaped tensor instead of
+    materialising a full-size zero tensor per slice."""
+
+    @staticmethod
+    def forward(ctx, x, prev, chunk, window, groups):
+        B, T = x.shape[:2]
+        rest = tuple(x.shape[2:])
+        WC = window * chunk
+        pad = x.new_zeros((B, WC) + rest) if prev is None else prev.to(x.dtype)
+        xp = torch.cat([pad, x], dim=1).contiguous()
+        sB, sT = xp.stride(0), xp.stride(1)
+        outs = []
+        for nv, c0, cnt in groups:
+            if nv == 0:
+                outs.append(x.new_zeros((B * cnt, 0) + rest))
+                continue
+            v = xp.as_strided((B, cnt, nv * chunk) + rest, (sB, chunk * sT, sT) + tuple(xp.stride()[2:]),
+                              xp.storage_offset() + (c0 + window - nv) * chunk * sT)
+            outs.append(v.reshape((B * cnt, nv * chunk) + rest))
+        ctx.meta = (B, T, rest, chunk, window, tuple(groups), prev is not None)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *gs):
+        B, T, rest, chunk, window, groups, has_prev = ctx.meta
+        WC = window * chunk
+        gxp = None
+        for (nv, c0, cnt), g in zip(groups, gs):
+            if g is None or nv == 0:
+                continue
+            if gxp is None:
+                gxp = g.new_zeros((B, WC + T) + rest)
+            g5 = g.reshape((B, cnt, nv, chunk) + rest)
+            for j in range(nv):
+                a = (c0 + window - nv + j) * chunk
+                gxp[:, a:a + cnt * chunk] += g5[:, :, j].reshape((B, cnt * chunk) + rest)
+        if gxp is None:
+            return None, None, None, None, None
+        return gxp[:, WC:], (gxp[:, :WC] if has_prev else None), None, None, None
+
+
+def window_groups(x: torch.Tensor, chunk: int, window: int, prev: Optional[torch.Tensor], groups):
+    """See ``_WindowGroups``; ``groups`` as ``[(n_valid, first_chunk, count), ...]`` with chunk indices relative to ``x``."""
+    return _WindowGroups.apply(x, prev, chunk, window, tuple(groups))
+
+
 def valid_window_chunks(chunk_idx: int, window: int, reach: Optional[int]) -> int:
     """How many of the newest window chunks chunk ``chunk_idx`` may see."""
     n = min(chunk_idx, window)

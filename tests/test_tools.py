@@ -1,0 +1,86 @@
+"""The offline analysis tools on a tiny run made by the training CLI: paired comparison of two runs' evaluation files,
+reproduction check, likelihood bound, gradient-noise decomposition, and the statistics they share."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from util import ROOT
+from dttt_b200.data.synth import write_stream, zipf_tokens
+
+
+@pytest.fixture(scope="module")
+def runs(tmp_path_factory):
+    d = tmp_path_factory.mktemp("tools")
+    for i, n in enumerate(("a", "b")):
+        write_stream(str(d / "data" / n), zipf_tokens(120_000, 1024, seed=i, eos=1022, mean_doc=150), 1022, n, 1024)
+    base = {"model_config": os.path.join(ROOT, "configs/tiny_baseline"), "data_root": str(d / "data"), "sources": "a=a:0.6,b=b:0.4",
+            "seq_len": 256, "batch_size": 2, "grad_accum": 1, "steps": 3, "seed": 0, "lr": 0.001, "warmup_steps": 2,
+            "inner_lr_warmup_steps": 0, "inner_task": "causal", "outer_shift": True, "cart_window": 32, "holdout": 20000,
+            "eval_batches": 2, "eval_interval": 2, "eval_step0": False, "ckpt_interval": 2, "keep_checkpoints": 0, "log_interval": 1,
+            "fused_ce_block": 0, "compute_dtype": "float32"}
+    out = {}
+    for name, lr in (("A", 0.001), ("B", 0.003)):
+        cfg = dict(base, lr=lr, ckpt_dir=str(d / name), log_dir=str(d / name))
+        (d / f"{name}.json").write_text(json.dumps(cfg))
+        r = subprocess.run([sys.executable, "-m", "dttt_b200.train", "--config", str(d / f"{name}.json")], cwd=ROOT, capture_output=True,
+                           text=True, timeout=900, env=dict(os.environ, OMP_NUM_THREADS="2"))
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        (d / name / "train_main.log").write_text(r.stdout)
+        out[name] = d / name
+    return out
+
+
+def _step_dir(run):
+    return sorted(p for p in os.listdir(run) if p.startswith("step_"))[-1]
+
+
+def test_evalstats_cluster_bootstrap_is_wider_for_correlated_clusters():
+    from dttt_b200.tools import evalstats as S
+    rng = np.random.default_rng(0)
+    docs = np.repeat(np.arange(40), 5)
+    x = rng.normal(size=40)[docs] + 0.1 * rng.normal(size=200)            # sequences of one document move together
+    naive, clustered = S.weighted_se(x), S.cluster_se(x, docs)
+    assert clustered > 1.5 * naive
+    assert abs(S.cluster_se(x, np.arange(200)) - naive) < 0.2 * naive     # independent units: the two agree
+    m, se_n, se_c = S.mix_stat(x, np.array(["s"] * 200), docs, {"s": 1.0})
+    assert abs(m - x.mean()) < 1e-12 and se_c > se_n
+
+
+def test_paired_diff_and_compare_eval(runs, capsys):
+    from dttt_b200.tools import compare_eval, paired_diff
+    files = sorted(f for f in os.listdir(runs["A"]) if f.startswith("eval_") and f.endswith(".npz"))
+    assert files, os.listdir(runs["A"])
+    step = int(files[-1][5:-4])
+    assert paired_diff.main(["--step", str(step), f"A={runs['A']}", f"B={runs['B']}", "--n_boot", "200"]) == 0
+    out = capsys.readouterr().out
+    assert "| B - A |" in out and "cluster ±" in out and "per-source headline differences" in out
+    assert compare_eval.main([str(runs["A"] / files[-1]), str(runs["B"] / files[-1])]) == 0
+    out = capsys.readouterr().out
+    assert "sources    identical" in out and "loss_1.0" in out
+
+
+def test_elbo_eval_bound_and_pairing(runs, tmp_path):
+    from dttt_b200.tools import elbo_eval
+    ck = runs["A"] / _step_dir(runs["A"])
+    assert elbo_eval.main(["--ckpt", str(ck), "--n_per_source", "2", "--n_t", "3", "--out", str(tmp_path / "elbo.npz")]) == 0
+    d = np.load(tmp_path / "elbo.npz")
+    assert d["ce"].shape == (3, 2, 4) and d["count"].shape == (3, 2, 4)
+    assert np.all(np.diff(d["count"][:, 0].sum(-1)) > 0)                  # more masked tokens at higher noise levels
+    assert np.array_equal(d["count"][:, 0], d["count"][:, 1])             # write on / off score the same masks
+    assert np.all(np.isfinite(d["bound"])) and 3.0 < d["bound"][0] < 9.0
+
+
+def test_grad_noise_decomposition(runs, tmp_path):
+    from dttt_b200.tools import grad_noise
+    ck = runs["A"] / _step_dir(runs["A"])
+    assert grad_noise.main(["--ckpt", str(ck), "--n_seq", "3", "--n_masks", "2", "--out", str(tmp_path / "noise.json")]) == 0
+    r = json.load(open(tmp_path / "noise.json"))
+    t = r["views_1"]["total"]
+    assert t["W"] > 0 and np.isfinite(t["D"]) and np.isfinite(t["G2"])
+    assert set(r["views_1"]) >= {"embed", "prefix", "suffix", "total"}
+    parts = sum(v["W"] for g, v in r["views_1"].items() if g != "total")
+    assert abs(parts - t["W"]) < 1e-6 * abs(t["W"]) + 1e-12
