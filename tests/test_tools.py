@@ -84,3 +84,55 @@ def test_grad_noise_decomposition(runs, tmp_path):
     assert set(r["views_1"]) >= {"embed", "prefix", "suffix", "total"}
     parts = sum(v["W"] for g, v in r["views_1"].items() if g != "total")
     assert abs(parts - t["W"]) < 1e-6 * abs(t["W"]) + 1e-12
+
+
+def test_convert_dolma_removes_test_books_and_groups_pages(tmp_path):
+    import gzip
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from dttt_b200.tools.data import convert_dolma
+    rng = np.random.default_rng(0)
+    words = lambda n, seed: " ".join(f"w{int(x)}" for x in np.random.default_rng(seed).integers(0, 5000, n))
+    book = words(600, 1)
+    pq.write_table(pa.table({"url": ["https://www.gutenberg.org/ebooks/4242"], "text": [book], "title": ["The Test Book"]}), tmp_path / "test.parquet")
+    recs = [{"id": "a", "text": words(300, 2), "metadata": {"title": "fresh"}},
+            {"id": "b", "text": "intro " + book[:2500] + " outro", "metadata": {"title": "copy of the book"}},
+            {"id": "c", "text": words(50, 3), "metadata": {"title": "by id", "url": "https://www.gutenberg.org/ebooks/4242"}},
+            {"id": "d", "text": words(200, 4), "metadata": {}}]
+    (tmp_path / "src").mkdir()
+    with gzip.open(tmp_path / "src" / "part0.json.gz", "wt") as fh:
+        fh.writelines(json.dumps(r) + "\n" for r in recs)
+    rc = convert_dolma.main(["--src", str(tmp_path / "src"), "--out", str(tmp_path / "out"), "--pg19_test", str(tmp_path / "test.parquet"),
+                             "--stride", "4", "--workers", "1"])
+    assert rc == 0
+    t = pq.read_table(tmp_path / "out" / "part0.parquet")
+    assert t.column("id").to_pylist() == ["a", "d"]
+    removed = [json.loads(l) for l in open(tmp_path / "out" / "removed.jsonl")]
+    assert {r["id"] for r in removed} == {"b", "c"} and any("id 4242" in r["why"] for r in removed)
+    s = json.load(open(tmp_path / "out" / "summary.json"))
+    assert s["docs_in"] == 4 and s["docs_out"] == 2 and s["removed_by_id"] == 1
+    # pages of one volume become one document, in page order
+    pages = [{"id": f"p{i}", "item_id": "vol1", "page_num": str(n), "text": f"page {n} " + words(30, 10 + n), "metadata": {}} for i, n in enumerate((2, 10, 1))]
+    pages.append({"id": "q", "item_id": "vol2", "page_num": "1", "text": "other volume " + words(30, 99), "metadata": {}})
+    (tmp_path / "src2").mkdir()
+    with gzip.open(tmp_path / "src2" / "vols.json.gz", "wt") as fh:
+        fh.writelines(json.dumps(r) + "\n" for r in pages)
+    assert convert_dolma.main(["--src", str(tmp_path / "src2"), "--out", str(tmp_path / "out2"), "--pg19_test", str(tmp_path / "test.parquet"),
+                               "--group", "item_id:page_num", "--workers", "1"]) == 0
+    t = pq.read_table(tmp_path / "out2" / "vols.parquet")
+    assert t.column("id").to_pylist() == ["vol1", "vol2"]
+    txt = t.column("text").to_pylist()[0]
+    assert txt.index("page 1 ") < txt.index("page 2 ") < txt.index("page 10 ")
+
+
+def test_round_compare_sections(runs, tmp_path, capsys):
+    from dttt_b200.tools import elbo_eval, round_compare
+    for n in ("A", "B"):
+        ck = runs[n] / _step_dir(runs[n])
+        assert elbo_eval.main(["--ckpt", str(ck), "--n_per_source", "2", "--n_t", "2", "--out", str(runs[n] / "elbo.npz")]) == 0
+    files = sorted(f for f in os.listdir(runs["A"]) if f.startswith("eval_") and f.endswith(".npz"))
+    step = int(files[-1][5:-4])
+    capsys.readouterr()
+    assert round_compare.main(["--step", str(step), f"A={runs['A']}", f"B={runs['B']}", "--pairs", "B-A"]) == 0
+    out = capsys.readouterr().out
+    assert "## 8K" in out and "B - A" in out and "## bound" in out and "memory's part" in out
