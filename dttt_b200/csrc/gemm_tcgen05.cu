@@ -821,6 +821,9 @@ extern "C" int dttt_gemm_rs_bf16(const void* A, const void* B, void* const* peer
   p.tiles_m = M / BM; p.tiles_n = (N + bn - 1) / bn;
   p.tp = tp; p.self_rank = self; p.epoch = epoch; p.rows_per_rank = M / tp;
   for (int i = 0; i < tp; ++i) { p.peer_c[i] = peer_c[i]; p.peer_flags[i] = peer_flags[i]; }
+  // every rank starts with its own rows and walks the owners in ring order, so at any moment the ranks write to
+  // different owners instead of all converging on one GPU's inbound links
+  p.m_rotate = self * (p.rows_per_rank / BM);
   p.done_counter = done_counter;
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < g_num_sms ? tiles : g_num_sms);

@@ -27,10 +27,13 @@ def main():
     assert eng.store.fused == fused
     ids = torch.randint(0, 2000, (2 * world, 256), generator=torch.Generator().manual_seed(0))[2 * rank:2 * rank + 2]
     ms = [eng.train_step(ids, s) for s in range(3)]
+    # the reduced gradient of the last step as the optimiser saw it (this rank's slice), gathered over the ranks
+    gs = [torch.empty_like(eng.store.grad_shard) for _ in range(world)]
+    dist.all_gather(gs, eng.store.grad_shard)
     full = {k: eng.store.gather_full(k).cpu() for k in eng.store.names()}
     lo = {k: eng.store.lo_view(k).float().cpu() for k in eng.store.names()}
     if rank == 0:
-        torch.save({"params": full, "lo": lo, "metrics": ms}, os.path.join(out, f"fused{int(fused)}.pt"))
+        torch.save({"params": full, "lo": lo, "metrics": ms, "grad": torch.stack(gs).cpu()}, os.path.join(out, f"fused{int(fused)}.pt"))
     dist.barrier()
     dist.destroy_process_group()
 

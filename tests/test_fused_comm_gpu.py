@@ -21,18 +21,20 @@ def test_fused_step_matches_nccl_step(tmp_path):
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     a = torch.load(tmp_path / "fused1.pt", weights_only=False)
     b = torch.load(tmp_path / "fused0.pt", weights_only=False)
-    # The two paths add the ranks' gradients in a different order.  Where a gradient is numerical noise around zero,
-    # Adam's m / sqrt(v) turns that last-bit difference into a full-size step, so a few elements may differ by up to
-    # the sum of the learning rates; everything else has to agree closely.
-    worst = {}
+    # Step 0 starts from identical weights: the fused reduce-scatter + norm must reproduce NCCL's gradient norm.
+    g0a, g0b = a["metrics"][0]["grad_norm"], b["metrics"][0]["grad_norm"]
+    assert abs(g0a - g0b) < 1e-4 * g0b, (g0a, g0b)
+    # Every rank's compute copy is the cast of the master it was gathered from.
+    for k in a["params"]:
+        assert torch.allclose(a["lo"][k], a["params"][k], atol=1e-2, rtol=1e-2), k
+    # After three Adam steps the parameters agree except where a gradient is numerical noise around zero: there
+    # m / sqrt(v) turns a last-bit difference in the summation order (and in the embedding's atomic scatter-add) into a
+    # step of the order of the learning rate.  So: small on average, and never more than a few learning rates.
     for k in a["params"]:
         d = (a["params"][k] - b["params"][k]).abs()
-        tol = 2e-5 + 2e-3 * b["params"][k].abs()
-        frac_bad = (d > tol).float().mean().item()
-        worst[k] = (frac_bad, d.max().item())
-        assert frac_bad < 5e-3, (k, worst[k])
-        assert d.max().item() < 2e-3, (k, worst[k])
-        assert torch.allclose(a["lo"][k], a["params"][k], atol=1e-2, rtol=1e-2), k         # every rank's compute copy was refreshed
-    gn_a, gn_b = a["metrics"][-1]["grad_norm"], b["metrics"][-1]["grad_norm"]
-    assert abs(gn_a - gn_b) < 2e-2 * gn_b, (gn_a, gn_b, worst)
-    assert abs(a["metrics"][0]["grad_norm"] - b["metrics"][0]["grad_norm"]) < 1e-4 * b["metrics"][0]["grad_norm"]
+        assert d.mean().item() < 1e-4, (k, d.mean().item())
+        assert d.max().item() < 3e-3, (k, d.max().item())
+    # The reduced gradients of the last step, element by element (the weights differ slightly by then, so loosely).
+    ga, gb = a["grad"], b["grad"]
+    cos = torch.nn.functional.cosine_similarity(ga.flatten(), gb.flatten(), dim=0).item()
+    assert cos > 0.99, cos
