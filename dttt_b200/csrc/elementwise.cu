@@ -205,6 +205,128 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
   }
 }
 
+// four elements per thread and iteration (16-byte accesses); n4 = n / 4
+__global__ void adamw_kernel_v4(float4* __restrict__ p, float4* __restrict__ m, float4* __restrict__ v,
+                                const float4* __restrict__ g, long long n4, float lr, float b1, float b2, float eps, float wd,
+                                float bc1, float bc2, float gscale) {
+  const float ib1 = 1.f / bc1, ib2 = 1.f / bc2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 g4 = g[i];
+    float4 m4 = m[i], v4 = v[i], p4 = p[i];
+    const float gg[4] = {g4.x * gscale, g4.y * gscale, g4.z * gscale, g4.w * gscale};
+    float* mp = reinterpret_cast<float*>(&m4);
+    float* vp = reinterpret_cast<float*>(&v4);
+    float* pp = reinterpret_cast<float*>(&p4);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      mp[k] = b1 * mp[k] + (1.f - b1) * gg[k];
+      vp[k] = b2 * vp[k] + (1.f - b2) * gg[k] * gg[k];
+      const float upd = (mp[k] * ib1) / (sqrtf(vp[k] * ib2) + eps) + wd * pp[k];
+      pp[k] -= lr * upd;
+    }
+    m[i] = m4; v[i] = v4; p[i] = p4;
+  }
+}
+
+// Per-sequence kernels, 16 bytes per access: a row of n elements is n / VEC vectors.
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+  using type = float4;
+  __device__ static void load(const float* p, float (&f)[4]) { const float4 v = *reinterpret_cast<const float4*>(p); f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
+  __device__ static void store(float* p, const float (&f)[4]) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec<__nv_bfloat16> {
+  __device__ static void load(const __nv_bfloat16* p, float (&f)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&f)[4]) {
+    uint2 v;
+    *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(f[0], f[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(f[2], f[3]);
+    *reinterpret_cast<uint2*>(p) = v;
+  }
+};
+
+__device__ __forceinline__ void block_sum_to(float s, float* dst) {
+  s = warp_sum(s);
+  __shared__ float red[32];
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) atomicAdd(dst, s);
+  }
+}
+
+template <typename T>
+__global__ void seq_sumsq_v4(const T* __restrict__ x, float* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const T* xb = x + (long long)b * n;
+  float s = 0.f;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float f[4];
+    Vec<T>::load(xb + i, f);
+    s += f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3];
+  }
+  block_sum_to(s, &out[b]);
+}
+
+template <typename T>
+__global__ void seq_axpy_v4(const float* __restrict__ w, const T* __restrict__ g, const float* __restrict__ coef,
+                            float* __restrict__ w_new, __nv_bfloat16* __restrict__ w_lo, long long n) {
+  const int b = blockIdx.y;
+  const float c = coef[b];
+  const long long off = (long long)b * n;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float wv[4], gv[4];
+    Vec<float>::load(w + off + i, wv);
+    Vec<T>::load(g + off + i, gv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) wv[k] -= c * gv[k];
+    Vec<float>::store(w_new + off + i, wv);
+    if (w_lo) Vec<__nv_bfloat16>::store(w_lo + off + i, wv);
+  }
+}
+
+template <typename T>
+__global__ void seq_dot_v4(const float* __restrict__ a, const T* __restrict__ g, float* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const long long off = (long long)b * n;
+  float s = 0.f;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float av[4], gv[4];
+    Vec<float>::load(a + off + i, av);
+    Vec<T>::load(g + off + i, gv);
+    s += av[0] * gv[0] + av[1] * gv[1] + av[2] * gv[2] + av[3] * gv[3];
+  }
+  block_sum_to(s, &out[b]);
+}
+
+template <typename T>
+__global__ void seq_lincomb_v4(const float* __restrict__ a, const T* __restrict__ g, const float* __restrict__ alpha,
+                               const float* __restrict__ beta, T* __restrict__ out, long long n) {
+  const int b = blockIdx.y;
+  const float al = alpha[b], be = beta[b];
+  const long long off = (long long)b * n;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float av[4], gv[4];
+    Vec<float>::load(a + off + i, av);
+    Vec<T>::load(g + off + i, gv);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) gv[k] = al * av[k] + be * gv[k];
+    Vec<T>::store(out + off + i, gv);
+  }
+}
+
+inline bool vec_ok(long long n, const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr) {
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return n % 4 == 0 && al(a) && al(b) && al(c) && al(d);
+}
+
 // ------------------------------------------------------------------ inner step pieces (per sequence)
 // out[b] += sum over the n elements of sequence b of x^2   (x: [B, n] f32 or bf16)
 template <typename T>
@@ -330,12 +452,21 @@ extern "C" int dttt_swiglu_bwd(const void* g, const void* u, const void* dy, voi
 
 extern "C" int dttt_adamw(float* p, float* m, float* v, const float* g, long long n, float lr, float b1, float b2, float eps,
                           float wd, float bc1, float bc2, float gscale, cudaStream_t s) {
-  adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(p, m, v, g, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
+  if (vec_ok(n, p, m, v, g))
+    adamw_kernel_v4<<<grid_for(n / 4, 256, 148 * 8), 256, 0, s>>>((float4*)p, (float4*)m, (float4*)v, (const float4*)g, n / 4, lr, b1, b2,
+                                                               eps, wd, bc1, bc2, gscale);
+  else
+    adamw_kernel<<<grid_for(n, 256, 148 * 16), 256, 0, s>>>(p, m, v, g, n, lr, b1, b2, eps, wd, bc1, bc2, gscale);
   return (int)cudaGetLastError();
 }
 
 extern "C" int dttt_seq_sumsq(const void* x, float* out, int B, long long n, int is_bf16, cudaStream_t s) {
-  dim3 grid(grid_for(n, 256, 148 * 2), B);
+  dim3 grid(grid_for(n / 4, 256, 148 * 2), B);
+  if (vec_ok(n, x) && (is_bf16 ? n % 8 == 0 : true)) {
+    if (is_bf16) seq_sumsq_v4<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, out, n);
+    else seq_sumsq_v4<float><<<grid, 256, 0, s>>>((const float*)x, out, n);
+    return (int)cudaGetLastError();
+  }
   if (is_bf16) seq_sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, out, n);
   else seq_sumsq_kernel<float><<<grid, 256, 0, s>>>((const float*)x, out, n);
   return (int)cudaGetLastError();
@@ -343,14 +474,24 @@ extern "C" int dttt_seq_sumsq(const void* x, float* out, int B, long long n, int
 
 extern "C" int dttt_seq_axpy(const float* w, const void* g, const float* coef, float* w_new, void* w_lo, int B, long long n,
                              int g_is_bf16, cudaStream_t s) {
-  dim3 grid(grid_for(n, 256, 148 * 4), B);
+  dim3 grid(grid_for(n / 4, 256, 148 * 4), B);
+  if (vec_ok(n, w, g, w_new, w_lo) && n % 8 == 0) {
+    if (g_is_bf16) seq_axpy_v4<__nv_bfloat16><<<grid, 256, 0, s>>>(w, (const __nv_bfloat16*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
+    else seq_axpy_v4<float><<<grid, 256, 0, s>>>(w, (const float*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
+    return (int)cudaGetLastError();
+  }
   if (g_is_bf16) seq_axpy_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(w, (const __nv_bfloat16*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
   else seq_axpy_kernel<float><<<grid, 256, 0, s>>>(w, (const float*)g, coef, w_new, (__nv_bfloat16*)w_lo, n);
   return (int)cudaGetLastError();
 }
 
 extern "C" int dttt_seq_dot(const float* a, const void* g, float* out, int B, long long n, int g_is_bf16, cudaStream_t s) {
-  dim3 grid(grid_for(n, 256, 148 * 2), B);
+  dim3 grid(grid_for(n / 4, 256, 148 * 2), B);
+  if (vec_ok(n, a, g) && n % 8 == 0) {
+    if (g_is_bf16) seq_dot_v4<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, out, n);
+    else seq_dot_v4<float><<<grid, 256, 0, s>>>(a, (const float*)g, out, n);
+    return (int)cudaGetLastError();
+  }
   if (g_is_bf16) seq_dot_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, out, n);
   else seq_dot_kernel<float><<<grid, 256, 0, s>>>(a, (const float*)g, out, n);
   return (int)cudaGetLastError();
@@ -358,7 +499,12 @@ extern "C" int dttt_seq_dot(const float* a, const void* g, float* out, int B, lo
 
 extern "C" int dttt_seq_lincomb(const float* a, const void* g, const float* alpha, const float* beta, void* out, int B, long long n,
                                 int g_is_bf16, cudaStream_t s) {
-  dim3 grid(grid_for(n, 256, 148 * 4), B);
+  dim3 grid(grid_for(n / 4, 256, 148 * 4), B);
+  if (vec_ok(n, a, g, out) && n % 8 == 0) {
+    if (g_is_bf16) seq_lincomb_v4<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, alpha, beta, (__nv_bfloat16*)out, n);
+    else seq_lincomb_v4<float><<<grid, 256, 0, s>>>(a, (const float*)g, alpha, beta, (float*)out, n);
+    return (int)cudaGetLastError();
+  }
   if (g_is_bf16) seq_lincomb_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a, (const __nv_bfloat16*)g, alpha, beta, (__nv_bfloat16*)out, n);
   else seq_lincomb_kernel<float><<<grid, 256, 0, s>>>(a, (const float*)g, alpha, beta, (float*)out, n);
   return (int)cudaGetLastError();

@@ -3,6 +3,7 @@
     python -m dttt_b200.tools.kernel_bench gemm --m 8192 --n 8192 --k 8192 [--ta] [--tb] [--batch B] [--f32acc]
     python -m dttt_b200.tools.kernel_bench rmsnorm|rope|swiglu|adamw --rows R --dim D
     python -m dttt_b200.tools.kernel_bench attn --seqs 8 --cq 1024 --kn 9216 --heads 32 --kv-heads 8 --head-dim 64 [--causal]
+    python -m dttt_b200.tools.kernel_bench ce --rows 2048 --k 2048 --vocab 128256
     python -m dttt_b200.tools.kernel_bench suite            (the shapes of the 1B model)
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, best of ``--iters``; between timed launches a
@@ -145,12 +146,42 @@ def bench_attn(a, out):
         out(resb)
 
 
+def bench_ce(a, out):
+    """Linear + cross-entropy: the forward (GEMM with the per-tile softmax-partials epilogue + combine) and one vocabulary
+    block of the backward's dlogits GEMM, against the unfused statement (f32 logits GEMM + torch logsumexp)."""
+    from dttt_b200.ops import gemm, kernels
+    N, K, V = a.rows, a.k, a.vocab
+    h = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    E = (torch.randn(V, K, device="cuda") * 0.02).to(torch.bfloat16)
+    y = torch.randint(0, V, (N,), device="cuda")
+    _, flops, src = peaks()
+    ms = timeit(lambda: kernels.linear_ce_fwd(h, E, y), a.iters, a.once)
+    fl = 2.0 * N * K * V
+    res = {"kernel": "linear_ce_fwd (gemm_bf16_kernel<256,1> + ce_combine)", "rows": N, "K": K, "classes": V, "ms": ms,
+           "tflops": fl / ms / 1e9, "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src}
+    if a.compare and not a.once:
+        def unfused():
+            lg = gemm.gemm_raw(h, E, False, True, torch.float32)
+            return torch.logsumexp(lg, -1) - lg.gather(1, y[:, None]).squeeze(1)
+        mt = timeit(unfused, a.iters)
+        res.update(ms_unfused=mt, vs_unfused=mt / ms)
+    out(res)
+    lse, _ = kernels.linear_ce_fwd(h, E, y)
+    coef = torch.rand(N, device="cuda")
+    blk = min(8192, V)
+    yi = y.to(torch.int32)
+    ms = timeit(lambda: kernels.linear_ce_dlogits(h, E[:blk], yi, coef, lse, 0), a.iters, a.once)
+    fl = 2.0 * N * K * blk
+    out({"kernel": "linear_ce_dlogits (gemm_bf16_kernel<256,2>)", "rows": N, "K": K, "classes_block": blk, "ms": ms, "tflops": fl / ms / 1e9,
+         "frac_of_cublas_peak": fl / (ms * 1e-3) / flops, "peaks": src})
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.kernel_bench")
-    ap.add_argument("cmd", choices=["gemm", "attn", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
+    ap.add_argument("cmd", choices=["gemm", "attn", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
     ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
-    ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--vocab", type=int, default=128256); ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=8192); ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--batch", type=int, default=1); ap.add_argument("--ta", action="store_true"); ap.add_argument("--tb", action="store_true")
     ap.add_argument("--f32acc", action="store_true"); ap.add_argument("--compare", action="store_true")
@@ -168,6 +199,10 @@ def main(argv=None):
         bench_gemm(a, out)
     elif a.cmd == "attn":
         bench_attn(a, out)
+    elif a.cmd == "ce":
+        a.rows = 2048 if a.rows == 49152 else a.rows
+        a.k = 2048 if a.k == 8192 else a.k
+        bench_ce(a, out)
     elif a.cmd == "suite":
         a.compare = True
         shapes = [(8192, 8192, 8192, 1, 0, 0, 0), (49152, 2048, 2048, 1, 0, 0, 0), (49152, 8192, 2048, 1, 0, 0, 0), (49152, 2048, 8192, 1, 0, 0, 0),
@@ -179,6 +214,8 @@ def main(argv=None):
         for n, Cq, Kn, causal in ((8, 1024, 9216, True), (8, 1024, 9216, False), (16, 1024, 1024, True), (8, 1024, 4096, True)):
             a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim, a.bwd = n, Cq, Kn, causal, 32, 8, 64, True
             bench_attn(a, out)
+        a.rows, a.k, a.vocab = 2048, 2048, 128256
+        bench_ce(a, out)
         for cmd, R, D in (("rmsnorm", 49152, 2048), ("swiglu", 49152, 8192), ("rope", 49152, 2048), ("adamw", 16384, 8192)):
             a.cmd, a.rows, a.dim = cmd, R, D
             bench_elementwise(a, out)

@@ -139,6 +139,32 @@ def test_adamw_and_seq_ops():
     assert _rel(out, refv) < 1e-6 and _rel(lo, refv) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(3, 700, 33), (2, 256, 512)])          # odd sizes take the scalar kernels, aligned ones the 16-byte ones
+def test_seq_kernels_scalar_and_vector_paths(shape):
+    from dttt_b200.ops import kernels
+    torch.manual_seed(17)
+    B = shape[0]
+    w, a = torch.randn(*shape, device="cuda"), torch.randn(*shape, device="cuda")
+    for gdt in (torch.float32, torch.bfloat16):
+        g = torch.randn(*shape, device="cuda").to(gdt)
+        v1 = lambda t: t.view(B, 1, 1)
+        coef, al, be = torch.rand(B, device="cuda"), torch.randn(B, device="cuda"), torch.randn(B, device="cuda")
+        assert _rel(kernels.seq_sumsq([w, g]), w.pow(2).flatten(1).sum(1) + g.float().pow(2).flatten(1).sum(1)) < 1e-4
+        out, lo = kernels.seq_axpy(w, g, coef, want_lo=True)
+        assert _rel(out, w - v1(coef) * g.float()) < 1e-6 and _rel(lo, w - v1(coef) * g.float()) < 1e-2
+        assert _rel(kernels.seq_dot([a, w], [g, g]), ((a + w) * g.float()).flatten(1).sum(1)) < 1e-3
+        lc = kernels.seq_lincomb(a, g, al, be)
+        assert lc.dtype == gdt and _rel(lc, v1(al) * a + v1(be) * g.float()) < (1e-6 if gdt == torch.float32 else 1e-2)
+    n = 1 << 20
+    p, m, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v = v.abs()
+    p0, m0, v0 = p.clone(), m.clone(), v.clone()
+    kernels.adamw(p, m, v, g, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 0.5)
+    gg = g * 0.5
+    mr, vr = 0.9 * m0 + 0.1 * gg, 0.95 * v0 + 0.05 * gg * gg
+    assert _rel(p, p0 - 1e-3 * ((mr / 0.1) / ((vr / 0.05).sqrt() + 1e-8) + 0.1 * p0)) < 1e-5 and _rel(m, mr) < 1e-6 and _rel(v, vr) < 1e-6
+
+
 def test_weighted_ce_matches_dense_with_grads():
     from dttt_b200.ops import ce as CE, reference as ref
     torch.manual_seed(8)
