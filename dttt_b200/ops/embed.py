@@ -16,7 +16,7 @@ class _Embedding(torch.autograd.Function):
     def forward(ctx, table, ids, dtype, gradbuf):
         ctx.save_for_backward(ids)
         ctx.gradbuf, ctx.shape, ctx.tdtype = gradbuf, table.shape, table.dtype
-        return table.detach()[ids].to(dtype)
+        return _gather(table.detach(), ids, dtype)
 
     @staticmethod
     def backward(ctx, g):
@@ -24,8 +24,24 @@ class _Embedding(torch.autograd.Function):
         if torch.is_grad_enabled() or ctx.gradbuf is None:
             gt = torch.zeros(ctx.shape, dtype=torch.float32, device=g.device).index_add(0, ids.flatten(), g.float().flatten(0, -2))
             return gt.to(ctx.tdtype), None, None, None
-        ctx.gradbuf.index_add_(0, ids.flatten(), g.float().flatten(0, -2))
+        if _kernel_ok(g, ctx.gradbuf) and g.dtype == torch.bfloat16 and ctx.gradbuf.is_contiguous():
+            from . import kernels
+            kernels.embed_scatter_f32(g, ids, ctx.gradbuf)
+        else:
+            ctx.gradbuf.index_add_(0, ids.flatten(), g.float().flatten(0, -2))
         return None, None, None, None
+
+
+def _kernel_ok(*ts) -> bool:
+    from . import kernels
+    return all(t.is_cuda for t in ts) and kernels.available("embed")
+
+
+def _gather(table: torch.Tensor, ids: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if _kernel_ok(table) and table.dtype == torch.bfloat16 and dtype == torch.bfloat16 and table.shape[1] % 8 == 0:
+        from . import kernels
+        return kernels.embed_gather(table, ids)
+    return table[ids].to(dtype)
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, dtype: torch.dtype, gradbuf=None) -> torch.Tensor:
@@ -34,4 +50,4 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, dtype: torch.dtype, gradbu
     ids = ids.long()
     if table.requires_grad and torch.is_grad_enabled():
         return _Embedding.apply(table, ids, dtype, gradbuf)
-    return table.detach()[ids].to(dtype)
+    return _gather(table.detach(), ids, dtype)

@@ -350,3 +350,54 @@ def attention_bwd(g, q, k, v, o, lse, scale, causal):
     global LAUNCHES
     LAUNCHES += 1                                   # the delta kernel
     return dq32.to(q.dtype), dk, dv
+
+
+# =============================================================================== embedding / objective family
+_lib.register("dttt_embed_gather", _i, [_vp, _vp, _vp, _ll, _i, _vp])
+_lib.register("dttt_embed_scatter_f32", _i, [_vp, _vp, _vp, _ll, _i, _vp])
+_lib.register("dttt_cart_band", _i, [_vp, _vp, _vp, _i, _i, _i, _vp])
+_lib.register("dttt_threefry_uniform", _i, [_vp, _i, _ll, _vp, _vp, _vp, _vp])
+_SYMBOL.update(embed="dttt_embed_gather", cart="dttt_cart_band", mask_rng="dttt_threefry_uniform")
+
+
+def embed_gather(table, ids):
+    """Rows ``ids`` of the bf16 ``table [V, H]`` -> ``[*ids.shape, H]``."""
+    idc = ids.reshape(-1).long().contiguous()
+    H = table.shape[1]
+    out = torch.empty(idc.numel(), H, dtype=torch.bfloat16, device=table.device)
+    _check(_lib.lib().dttt_embed_gather(_p(table.contiguous()), _p(idc), _p(out), idc.numel(), H, _stream()), "embed_gather")
+    return out.view(*ids.shape, H)
+
+
+def embed_scatter_f32(dh, ids, grad_table):
+    """``grad_table[ids[i]] += dh[i]`` in f32 (``dh`` bf16 ``[n, H]`` rows, ``grad_table`` f32 ``[V, H]`` contiguous)."""
+    idc = ids.reshape(-1).long().contiguous()
+    d2 = dh.reshape(-1, dh.shape[-1]).contiguous()
+    _check(_lib.lib().dttt_embed_scatter_f32(_p(d2), _p(idc), _p(grad_table), idc.numel(), d2.shape[1], _stream()), "embed_scatter")
+
+
+def cart_band(visible, kernel):
+    """``out[b, t] = sum_d kernel[d + W] visible[b, t + d]`` (zero padded); ``visible [B, T]``, ``kernel [2 W + 1]``."""
+    x = visible.float().contiguous()
+    k = kernel.float().contiguous()
+    W = (k.numel() - 1) // 2
+    if (4 * W + 257) * 4 > 48 * 1024:
+        from . import reference as _r
+        return _r.band_correlate(visible, kernel)
+    out = torch.empty_like(x)
+    _check(_lib.lib().dttt_cart_band(_p(x), _p(k), _p(out), x.shape[0], x.shape[1], W, _stream()), "cart_band")
+    return out
+
+
+def threefry_uniform(keys, n, thresh=None):
+    """``keys [R, 2]`` (int64 halves) -> uniforms ``[R, n]`` f32 in [0, 1) identical to ``utils.rng.uniform``; with
+    ``thresh [R]`` returns the boolean mask ``u < thresh`` instead (one pass, no float tensor)."""
+    kc = keys.reshape(-1, 2).long().contiguous()
+    R = kc.shape[0]
+    if thresh is None:
+        u = torch.empty(R, n, dtype=torch.float32, device=keys.device)
+        _check(_lib.lib().dttt_threefry_uniform(_p(kc), R, n, _p(u), _p(None), _p(None), _stream()), "threefry_uniform")
+        return u
+    m = torch.empty(R, n, dtype=torch.uint8, device=keys.device)
+    _check(_lib.lib().dttt_threefry_uniform(_p(kc), R, n, _p(None), _p(thresh.float().contiguous()), _p(m), _stream()), "threefry_mask")
+    return m.bool()

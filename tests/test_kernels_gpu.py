@@ -227,3 +227,34 @@ def test_train_step_bf16_close_to_f32_cpu():
     for k in ("main_loss", "inner_loss", "grad_norm", "inner_grad_norm"):
         a, b = out["gpu"][k], out["cpu"][k]
         assert abs(a - b) / (abs(b) + 1e-6) < 0.05, (k, a, b)
+
+
+def test_embedding_gather_and_f32_scatter():
+    from dttt_b200.ops import kernels
+    torch.manual_seed(21)
+    V, H, n = 1000, 256, 5000
+    table = torch.randn(V, H, device="cuda").to(torch.bfloat16)
+    ids = torch.randint(0, V, (5, n // 5), device="cuda")
+    ids[0, :300] = 7                                                       # a row hit many times (the mask token)
+    out = kernels.embed_gather(table, ids)
+    assert torch.equal(out, table[ids])
+    dh = torch.randn(5, n // 5, H, device="cuda").to(torch.bfloat16)
+    grad = torch.ones(V, H, device="cuda")
+    kernels.embed_scatter_f32(dh, ids, grad)
+    ref = torch.ones(V, H, device="cuda").index_add_(0, ids.flatten(), dh.float().flatten(0, 1))
+    assert _rel(grad, ref) < 1e-5
+
+
+def test_cart_band_and_threefry_match_the_host_statements():
+    from dttt_b200.ops import kernels, reference as ref
+    from dttt_b200.utils import rng
+    torch.manual_seed(22)
+    vis = (torch.rand(3, 2000, device="cuda") < 0.6)
+    kern = torch.rand(2 * 512 + 1, device="cuda")
+    assert _rel(kernels.cart_band(vis, kern), ref.band_correlate(vis.float(), kern)) < 1e-5
+    keys = torch.stack([rng.key(5), rng.fold_in(rng.key(5), 3), rng.key(2 ** 40 + 17)]).cuda()
+    u = kernels.threefry_uniform(keys, 1000)
+    u_ref = torch.stack([rng.uniform(k.cpu(), (1000,)) for k in keys])
+    assert torch.equal(u.cpu(), u_ref)
+    th = torch.tensor([0.1, 0.5, 0.9], device="cuda")
+    assert torch.equal(kernels.threefry_uniform(keys, 1000, th).cpu(), u_ref < th.cpu()[:, None])
