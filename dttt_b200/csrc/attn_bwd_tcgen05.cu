@@ -11,11 +11,17 @@
 //   dV += P^T dO      dK += dS^T Q                      (A from TMEM)
 // and dS^T, also written to shared memory, is the M-major A operand of  dQ = dS K.
 // Per step:   S^T = K Q^T,  dP^T = V dO^T   ->   P^T = exp2(S^T sl2 - LSE),  dS^T = P^T (dP^T - D) scale.
+// A step works on its 128 queries as two halves of 64: while the warps do the elementwise work of one half the tensor
+// core runs dV / dK of the other half and already the S^T / dP^T of the next step's first half (the TMEM columns of a
+// half are free as soon as its dV / dK products have been issued; the tensor pipe runs its queue in order).  The dQ
+// tile of a step is reduced into global memory during the next step, and dS^T alternates between two shared-memory
+// tiles so that the next step may overwrite one while dQ still reads the other.
 //
 //   warp 0      TMA: K, V once; Q and dO tiles into two stages
 //   warp 1      tcgen05.mma issuer, TMEM owner
-//   warps 2-9   two per TMEM lane quarter (one per 64-query half): softmax-backward math, then the reduction of the
-//               step's dQ tile into global memory (red.global.add.v4.f32), then the final dK / dV stores
+//   warps 2-9   two per TMEM lane quarter: softmax-backward math, then the step's dQ tile goes through shared memory
+//               into global memory as ONE bulk tensor reduction (cp.reduce.async.bulk.tensor, f32 add), then the
+//               final dK / dV stores
 // TMEM columns: S^T / P^T [0,128)  dP^T / dS^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448).
 // Every wait is bounded (ptx_sm100.cuh); on a timeout the roles leave through the common exit and TMEM is freed.
 #include "ptx_sm100.cuh"
@@ -42,7 +48,8 @@ struct BwdSmem {
   static constexpr int DS_BYTES = 128 * 128 * 2;            // dS^T for the dQ product
   static constexpr int STAGES = 2;
   static constexpr int AUX = 2 * 2 * 128 * 4;               // LSE and D, two buffers
-  static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + DS_BYTES + AUX + 1024 + 1024;
+  static constexpr int DQ_BYTES = 128 * HD * 4;                // f32 dQ tile staged for the bulk reduction
+  static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + 2 * DS_BYTES + DQ_BYTES + AUX + 1024 + 1024;
 };
 
 __device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
@@ -64,9 +71,14 @@ __device__ __forceinline__ int bar_red_and(int id, int nthreads, int flag) {
   return out;
 }
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// dst[tile] += smem tile, as one bulk tensor reduction (f32 add) issued by a single thread
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; eight threads per row of 64.
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
@@ -100,23 +112,25 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
-                const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                const __grid_constant__ CUtensorMap mapdQ, const AttnBwdParams p) {
   using L = BwdSmem;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + L::TILE;
   uint8_t* sST = sV + L::TILE;                               // stages: [Q tile | dO tile]
-  uint8_t* sDS = sST + L::STAGES * 2 * L::TILE;
-  float* sLSE = reinterpret_cast<float*>(sDS + L::DS_BYTES); // [2][128], premultiplied by log2(e)
+  uint8_t* sDS = sST + L::STAGES * 2 * L::TILE;              // two dS^T tiles (steps alternate)
+  float* sDQ = reinterpret_cast<float*>(sDS + 2 * L::DS_BYTES);    // [128 queries][64] f32, the step's dQ tile
+  float* sLSE = sDQ + 128 * HD;                              // [2][128], premultiplied by log2(e)
   float* sDel = sLSE + 2 * 128;                              // [2][128], premultiplied by scale
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sDel + 2 * 128));
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;                              // [2]
   uint64_t* st_empty = st_full + 2;                          // [2]
-  uint64_t* s_full = st_empty + 2;
-  uint64_t* pds_ready = s_full + 1;
-  uint64_t* dq_full = pds_ready + 1;
+  uint64_t* s_full = st_empty + 2;                           // [2] one per 64-query half
+  uint64_t* pds_ready = s_full + 2;                          // [2]
+  uint64_t* dq_full = pds_ready + 2;
   uint64_t* dq_empty = dq_full + 1;
   uint64_t* acc_final = dq_empty + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_final + 1);
@@ -136,15 +150,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&st_full[s], 1); mbar_init(&st_empty[s], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(pds_ready, 256);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&st_full[s], 1); mbar_init(&st_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&pds_ready[s], 256);
+    }
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 256);
     mbar_init(acc_final, 1);
     *abort_word = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapdO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapdO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapdQ);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -172,38 +187,58 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (elect_one() && n_it > 0) {
-      const uint32_t id_s = make_idesc_bf16(128, 128, 0, 0);        // S^T, dP^T: both operands K-major ([rows, d])
+      const uint32_t id_s = make_idesc_bf16(128, 64, 0, 0);         // S^T, dP^T of one 64-query half: operands K-major
       const uint32_t id_kv = make_idesc_bf16(128, HD, 0, 1);        // dV, dK: A from TMEM, B = [q rows, d] N-major
       const uint32_t id_q = make_idesc_bf16(128, HD, 1, 1);         // dQ: A = dS^T (M-major), B = K (N-major)
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aDS = smem_u32(sDS);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
       bool ok = mbar_wait_bounded(kv_full, 0, abort_word, p.status, ERR_WAIT_FULL);
+      // S^T and dP^T of half `hf` of step `it` (its Q / dO stage must be full)
+      auto issue_scores = [&](int it, int hf) {
+        const uint32_t aQ = smem_u32(sST + (it & 1) * 2 * L::TILE), aDO = aQ + L::TILE;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem + C_S + hf * 64, make_smem_desc(aK + k * 32, 16, 1024), make_smem_desc(aQ + hf * 8192 + k * 32, 16, 1024), id_s, k ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_f16(tmem + C_DP + hf * 64, make_smem_desc(aV + k * 32, 16, 1024), make_smem_desc(aDO + hf * 8192 + k * 32, 16, 1024), id_s, k ? 1u : 0u);
+        umma_commit(&s_full[hf]);
+      };
+      // dV += P^T dO and dK += dS^T Q over the 64 queries of half `hf`
+      auto issue_kv = [&](int it, int hf) {
+        const uint32_t aQ = smem_u32(sST + (it & 1) * 2 * L::TILE), aDO = aQ + L::TILE;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16_ts(tmem + C_DV, tmem + C_S + hf * 64 + k * 8, make_smem_desc(aDO + hf * 8192 + k * 2048, 16384, 1024), id_kv,
+                      (it | hf | k) ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_f16_ts(tmem + C_DK, tmem + C_DP + hf * 64 + k * 8, make_smem_desc(aQ + hf * 8192 + k * 2048, 16384, 1024), id_kv,
+                      (it | hf | k) ? 1u : 0u);
+      };
+      if (ok) ok = mbar_wait_bounded(&st_full[0], 0, abort_word, p.status, ERR_WAIT_FULL);
+      if (ok) { tc_fence_after(); issue_scores(0, 0); issue_scores(0, 1); }
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait_bounded(&st_full[s], (it >> 1) & 1, abort_word, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+        const bool more = it + 1 < n_it;
+        if (!mbar_wait_bounded(&pds_ready[0], it & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sST + s * 2 * L::TILE), aDO = aQ + L::TILE;
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_f16(tmem + C_S, make_smem_desc(aK + k * 32, 16, 1024), make_smem_desc(aQ + k * 32, 16, 1024), id_s, k ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k)
-          umma_f16(tmem + C_DP, make_smem_desc(aV + k * 32, 16, 1024), make_smem_desc(aDO + k * 32, 16, 1024), id_s, k ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait_bounded(pds_ready, it & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        issue_kv(it, 0);
+        if (more) {
+          if (!mbar_wait_bounded(&st_full[(it + 1) & 1], ((it + 1) >> 1) & 1, abort_word, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          issue_scores(it + 1, 0);                                   // half 0's columns are free once dV / dK above have run
+        }
+        if (!mbar_wait_bounded(&pds_ready[1], it & 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)                            // contraction over the 128 queries of the tile
-          umma_f16_ts(tmem + C_DV, tmem + C_S + k * 8, make_smem_desc(aDO + k * 2048, 16384, 1024), id_kv, (it | k) ? 1u : 0u);
-#pragma unroll
-        for (int k = 0; k < BQ / 16; ++k)
-          umma_f16_ts(tmem + C_DK, tmem + C_DP + k * 8, make_smem_desc(aQ + k * 2048, 16384, 1024), id_kv, (it | k) ? 1u : 0u);
-        umma_commit(&st_empty[s]);                                    // Q and dO of this stage are consumed
+        issue_kv(it, 1);
+        umma_commit(&st_empty[it & 1]);                               // Q and dO of this step are consumed
         if (!mbar_wait_bounded(dq_empty, (it & 1) ^ 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t aDS = smem_u32(sDS + (it & 1) * L::DS_BYTES);
 #pragma unroll
         for (int k = 0; k < BKEY / 16; ++k)                          // contraction over the 128 keys of the block
           umma_f16(tmem + C_DQ, make_smem_desc(aDS + k * 2048, 16384, 1024), make_smem_desc(aK + k * 2048, 16384, 1024), id_q, k ? 1u : 0u);
         umma_commit(dq_full);
+        if (more) issue_scores(it + 1, 1);
       }
       if (ok) umma_commit(acc_final);
     }
@@ -212,21 +247,53 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // ---------------------------------------------------------------- softmax backward, dQ reduction, dK / dV stores
     const int w = warp - 2;                                  // 0..7
     const int quarter = warp & 3;                            // TMEM lane quarter of this warp
-    const int half = w >> 2;                                 // which 64 columns this warp handles
+    const int sub = w >> 2;                                  // which 32 of a half's 64 query columns
     const int tid = threadIdx.x - 64;                        // 0..255
     const int kr = quarter * 32 + lane;                      // key row within the block == TMEM lane
     const int kj = jb * BKEY + kr;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr float LOG2E = 1.4426950408889634f;
+    const bool key_ok = kj < p.Kn;
     bool ok = n_it > 0;
-    // stage the first step's LSE / D
     auto load_aux = [&](int it, float& val) {
       const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
       const int qi = qt * BQ + (tid & 127);
       const long long base = ((long long)b * p.nh + h) * p.Cq;
       if (tid < 128) val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
       else val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
+    };
+    // add the dQ tile of step `it` (lanes = queries) into global memory: the eight warps copy it from TMEM into a
+    // shared-memory tile and one thread issues a single bulk tensor reduction (f32 add) for the whole 128 x 64 tile;
+    // rows past the end of the sequence are clipped by the tensor map
+    auto reduce_dq = [&](int it) -> bool {
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(dq_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (tid == 0) bulk_wait_read0();                       // the previous reduction has finished reading the tile
+      if (!bar_red_and(3, 256, got)) return false;
+      tc_fence_after();
+      uint32_t r[32];
+      tmem_ld_32x32(tmem + C_DQ + lane_addr + sub * 32, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+      // two [128 x 32] f32 boxes (one per 32-column half), rows of 128 bytes with the 16-byte pieces XOR-swizzled by row
+      // (the tensor map's 128-byte swizzle), which also spreads the lanes' stores over the banks
+      float* row = sDQ + sub * (128 * 32) + kr * 32;          // the lane index doubles as the query row here
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(row + 4 * (j ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      fence_async_proxy();
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (tid == 0) {
+        const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+        tma_reduce_add_4d(&mapdQ, sDQ, 0, h, qt * BQ, b);
+        tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, 32, h, qt * BQ, b);
+        bulk_commit();
+      }
+      return true;
     };
     if (ok) {
       float v0;
@@ -236,90 +303,75 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     for (int it = 0; it < n_it && ok; ++it) {
       float vnext = 0.f;
       if (it + 1 < n_it) load_aux(it + 1, vnext);
-      const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+      const int qt = qt_start + it % nq_it;
       const float* lse2 = sLSE + (it & 1) * 128;
       const float* del = sDel + (it & 1) * 128;
-      int got = 1;
-      if (lane == 0) got = mbar_wait_bounded(s_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      // one verdict for all eight warps (they meet at barriers below); also publishes this step's LSE / D
-      if (!bar_red_and(1, 256, got)) { ok = false; break; }
-      tc_fence_after();
-      // entry (key kj, query qi) is visible iff kj <= qi + off (causal) and kj < Kn
-      const bool key_ok = kj < p.Kn;
       const bool need_mask = p.causal && (jb * BKEY + BKEY - 1 > qt * BQ + off);
-      const int c0 = half * 64;                              // first query column of this warp
-      uint32_t pp[32], dd[32];
-      {
-        uint32_t sr[64], dr[64];
-        tmem_ld_32x32(tmem + C_S + lane_addr + c0, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-        tmem_ld_32x32(tmem + C_S + lane_addr + c0 + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
-        tmem_ld_32x32(tmem + C_DP + lane_addr + c0, reinterpret_cast<uint32_t(&)[32]>(dr[0]));
-        tmem_ld_32x32(tmem + C_DP + lane_addr + c0 + 32, reinterpret_cast<uint32_t(&)[32]>(dr[32]));
-        tmem_ld_wait();
+      uint8_t* ds_tile = sDS + (it & 1) * L::DS_BYTES;
+#pragma unroll 1
+      for (int hf = 0; hf < 2 && ok; ++hf) {
+        int got = 1;
+        if (lane == 0) got = mbar_wait_bounded(&s_full[hf], it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+        got = __shfl_sync(0xffffffffu, got, 0);
+        // one verdict for all eight warps (they meet at barriers below); at hf == 0 it also publishes this step's LSE / D
+        if (!bar_red_and(1, 256, got)) { ok = false; break; }
+        tc_fence_after();
+        const int c0 = hf * 64 + sub * 32;                   // first query column of this warp in this half
+        uint32_t pp[16], dd[16];
+        {
+          uint32_t sr[32], dr[32];
+          tmem_ld_32x32(tmem + C_S + lane_addr + c0, sr);
+          tmem_ld_32x32(tmem + C_DP + lane_addr + c0, dr);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);     // broadcast reads
-          const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);      // D * scale
-          const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-          float pv[4], dv[4];
+          for (int i = 0; i < 32; i += 4) {
+            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);     // broadcast reads
+            const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);      // D * scale
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+            float pv[4], dv[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
-            if (!key_ok || (need_mask && kj > qt * BQ + c0 + i + u + off)) pe = 0.f;
-            pv[u] = pe;
-            dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
-          }
+            for (int u = 0; u < 4; ++u) {
+              float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
+              if (!key_ok || (need_mask && kj > qt * BQ + c0 + i + u + off)) pe = 0.f;
+              pv[u] = pe;
+              dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
+            }
 #pragma unroll
-          for (int u = 0; u < 4; u += 2) {
-            __nv_bfloat162 pb = __floats2bfloat162_rn(pv[u], pv[u + 1]);
-            __nv_bfloat162 db = __floats2bfloat162_rn(dv[u], dv[u + 1]);
-            pp[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&pb);
-            dd[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&db);
+            for (int u = 0; u < 4; u += 2) {
+              __nv_bfloat162 pb = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+              __nv_bfloat162 db = __floats2bfloat162_rn(dv[u], dv[u + 1]);
+              pp[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&pb);
+              dd[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&db);
+            }
           }
         }
-      }
-      // every warp has read its S^T / dP^T columns: the packed results may now overwrite them
-      tc_fence_before();
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      tc_fence_after();
-      tmem_st_32x32(tmem + C_S + lane_addr + c0 / 2, pp);    // 64 queries -> 32 columns of bf16 pairs
-      tmem_st_32x32(tmem + C_DP + lane_addr + c0 / 2, dd);
-      {
-        // dS^T row kr, queries c0..c0+63, into the M-major A tile: 64-query block `half`, 128-byte rows indexed by key
-        uint8_t* base = sDS + half * (128 * 128) + (kr / 8) * 1024 + (kr % 8) * 128;
+        // both warps of a lane quarter have read this half's columns: the packed results may now overwrite them
+        tc_fence_before();
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        tc_fence_after();
+        tmem_st_32x16(tmem + C_S + lane_addr + hf * 64 + sub * 16, pp);     // 32 queries -> 16 columns of bf16 pairs
+        tmem_st_32x16(tmem + C_DP + lane_addr + hf * 64 + sub * 16, dd);
+        {
+          // dS^T row kr, queries c0..c0+31, into the M-major A tile: 64-query block hf, 128-byte rows indexed by key
+          uint8_t* base = ds_tile + hf * (128 * 128) + (kr / 8) * 1024 + (kr % 8) * 128;
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          *reinterpret_cast<uint4*>(base + ((q ^ (kr % 8)) * 16)) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(base + (((sub * 4 + q) ^ (kr % 8)) * 16)) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+        }
+        tmem_st_wait();
+        fence_async_proxy();
+        tc_fence_before();
+        mbar_arrive(&pds_ready[hf]);
+        if (hf == 0 && it > 0) ok = reduce_dq(it - 1);       // the previous step's dQ, while this step's half 1 is computed
       }
-      tmem_st_wait();
-      fence_async_proxy();
-      tc_fence_before();
-      mbar_arrive(pds_ready);
+      if (!ok) break;
       // next step's LSE / D into the other buffer (its last readers passed barrier 1 of this step)
       if (it + 1 < n_it) {
         if (tid < 128) sLSE[((it + 1) & 1) * 128 + tid] = vnext; else sDel[((it + 1) & 1) * 128 + tid - 128] = vnext;
       }
-      // dQ tile of this step: lanes = queries, 64 columns; this warp adds its 32 lanes x 32 columns
-      if (lane == 0) got = mbar_wait_bounded(dq_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!bar_red_and(3, 256, got)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + C_DQ + lane_addr + half * 32, r);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(dq_empty);
-        const int qi = qt * BQ + kr;                         // lane index doubles as the query row here
-        if (qi < p.Cq) {
-          float* dst = p.dQ + (((long long)b * p.Cq + qi) * p.nh + h) * HD + half * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4(dst + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-        }
-      }
     }
+    if (ok) ok = reduce_dq(n_it - 1);
+    if (tid == 0) bulk_wait0();                              // the last dQ reduction has been performed
     // dK, dV of the block
     if (ok) {
       int got = 1;
@@ -328,11 +380,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       if (got) {
         tc_fence_after();
         uint32_t rv[32], rk[32];
-        tmem_ld_32x32(tmem + C_DV + lane_addr + half * 32, rv);
-        tmem_ld_32x32(tmem + C_DK + lane_addr + half * 32, rk);
+        tmem_ld_32x32(tmem + C_DV + lane_addr + sub * 32, rv);
+        tmem_ld_32x32(tmem + C_DK + lane_addr + sub * 32, rk);
         tmem_ld_wait();
         if (kj < p.Kn) {
-          const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + half * 32;
+          const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + sub * 32;
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v, k;
@@ -350,7 +402,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
     } else if (n_it == 0 && kj < p.Kn) {
       // no query sees this key block: its gradients are zero
-      const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + half * 32;
+      const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + sub * 32;
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
@@ -381,6 +433,20 @@ static EncodeTiledFnB bwd_encode_fn() {
   return fn;
 }
 
+// f32 [n, rows, heads, 64], box = 32 x 1 head x 128 rows x 1, 128-byte swizzle: the dQ accumulation target of the bulk reduction
+static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int heads) {
+  EncodeTiledFnB enc = bwd_encode_fn();
+  if (!enc) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 4, (cuuint64_t)heads * HD * 4, (cuuint64_t)rows * heads * HD * 4};
+  cuuint32_t box[4] = {32, 1, 128, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
 static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads) {
   EncodeTiledFnB enc = bwd_encode_fn();
   if (!enc) return -1;
@@ -407,8 +473,9 @@ extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const 
   if (causal && Kn < Cq) return -3;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
-  CUtensorMap mq, mdo, mk, mv;
+  CUtensorMap mq, mdo, mk, mv, mdq;
   int r;
+  if ((r = make_map4f(&mdq, dQ, n, Cq, nh))) return 500 + r;
   if ((r = make_map4b(&mq, Q, n, Cq, nh))) return 100 + r;
   if ((r = make_map4b(&mdo, dO, n, Cq, nh))) return 200 + r;
   if ((r = make_map4b(&mk, K, n, Kn, nkv))) return 300 + r;
@@ -423,7 +490,7 @@ extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const 
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
   dim3 grid((Kn + BKEY - 1) / BKEY, nkv, n);
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, p);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mdq, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -43,8 +43,43 @@ def _block_spec(prefix: str, n: int, cfg: ModelConfig) -> List[Tuple[str, Tuple[
     return out
 
 
-def param_spec(cfg: ModelConfig) -> "OrderedDict[str, Tuple[Tuple[int, ...], str]]":
-    """Ordered ``name -> (shape, init kind)``; the order is the checkpoint's leaf order."""
+_TP_COL = re.compile(r"^(prefix|suffix)\.(attn\.(q|k|v)|mlp\.(gate|up))\.(weight|bias)$")
+_TP_ROW = re.compile(r"^(prefix|suffix)\.(attn\.o|mlp\.down)\.weight$")
+
+
+def tp_layout(name: str) -> Optional[Tuple[str, int]]:
+    """How a parameter is split over a tensor-parallel group: ``("col", axis)`` for the output features of the Q / K / V and
+    MLP gate / up projections (whole heads per rank), ``("row", axis)`` for the input features of the attention-out and MLP
+    down projections, ``None`` for everything that stays whole on every rank (norms, embedding, the fast-weight template:
+    the fast-weight MLP runs per sequence and sequences, not its features, are divided over the group)."""
+    if _TP_COL.match(name):
+        return "col", (1 if name.endswith("bias") else 2)
+    if _TP_ROW.match(name):
+        return "row", 1
+    return None
+
+
+def tp_slice(name: str, t: torch.Tensor, tp: int, index: int) -> torch.Tensor:
+    lay = tp_layout(name)
+    if tp == 1 or lay is None:
+        return t
+    n = t.shape[lay[1]] // tp
+    return t.narrow(lay[1], index * n, n).contiguous()
+
+
+def param_spec(cfg: ModelConfig, tp: int = 1) -> "OrderedDict[str, Tuple[Tuple[int, ...], str]]":
+    """Ordered ``name -> (shape, init kind)``; the order is the checkpoint's leaf order.  ``tp > 1``: the shapes one rank
+    of a tensor-parallel group holds (``tp_layout``)."""
+    if tp > 1:
+        if cfg.memory == "gdn" or cfg.num_key_value_heads % tp or cfg.intermediate_size % tp:
+            raise ValueError(f"tensor parallel {tp}: needs the fast-weight memory and kv heads / MLP width divisible by it")
+        out = OrderedDict()
+        for n, (shape, kind) in param_spec(cfg).items():
+            lay = tp_layout(n)
+            if lay is not None:
+                shape = tuple(d // tp if a == lay[1] else d for a, d in enumerate(shape))
+            out[n] = (shape, kind)
+        return out
     H, V = cfg.hidden_size, cfg.vocab_size
     S, F, Ip = cfg.suffix_len, cfg.fast_len, cfg.prime_intermediate_size
     spec: List[Tuple[str, Tuple[int, ...], str]] = [("embed", (V, H), "normal")]
@@ -100,7 +135,7 @@ def init_params(cfg: ModelConfig, seed: int, device="cpu") -> "OrderedDict[str, 
     return OrderedDict(iter_init(cfg, seed, device))
 
 
-def iter_init(cfg: ModelConfig, seed: int, device="cpu"):
+def iter_init(cfg: ModelConfig, seed: int, device="cpu", tp: int = 1, tp_index: int = 0):
     """Yield ``(name, f32 tensor)`` in checkpoint order, one parameter at a time.  Every leaf draws from its own counter-based key (the seed folded with
     the leaf's index, then with the layer index for stacked leaves), so the values do not depend on the
     device, the process count or how the tree is later sharded.  Normal leaves have std
@@ -132,7 +167,7 @@ def iter_init(cfg: ModelConfig, seed: int, device="cpu"):
             t[..., -1] = 1.0                                     # identity filter: the option starts as "no conv"
         else:
             raise ValueError(kind)
-        yield name, t.to(device=device, dtype=torch.float32).contiguous()
+        yield name, tp_slice(name, t, tp, tp_index).to(device=device, dtype=torch.float32).contiguous()
 
 
 # parameters that stay f32 leaves in the compute view (everything that is not a matrix operand of a GEMM)

@@ -123,6 +123,9 @@ class inner_backward:
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w (+ bias)``; ``w [in, out]`` (reference model.py:137-148) or per-sequence ``[B, in, out]``
     with ``x [B, C, in]``."""
+    if getattr(w, "tp", None) is not None:
+        from ..parallel.tp import tp_linear
+        return tp_linear(x, w, bias)
     if w.dim() == 3:
         y = mm(x, w.to(x.dtype) if w.dtype != x.dtype else w)
     else:

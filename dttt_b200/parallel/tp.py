@@ -227,3 +227,149 @@ def column_linear(x_shard: torch.Tensor, w: torch.Tensor, ws: Workspace) -> torc
 
 def row_linear(x: torch.Tensor, w: torch.Tensor, ws: Workspace, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     return RowParallelLinear.apply(x, w, ws, residual)
+
+
+# ======================================================================================================================
+# The model-facing form: ``tp_linear`` is what ``ops.functional.linear`` calls for a weight that carries ``w.tp``.
+# Sequences, not features, are divided over the group outside the trunk GEMMs: a rank holds the residual stream,
+# the fast weights and the losses of its own ``B / tp`` sequences; a column-parallel product turns ``[B / tp, ...]`` rows
+# into ``[B, ..., N / tp]`` (all rows, this rank's heads / MLP columns), a row-parallel one back into ``[B / tp, ..., N]``.
+class TPContext:
+    """A tensor-parallel group as the ops see it: the process group, its size, this rank's index and (on GPUs) the
+    peer-memory workspace of the fused kernels."""
+
+    def __init__(self, group, size: int, index: int, device: torch.device, workspace_bytes: int = 2 << 30):
+        self.group, self.size, self.index, self.device = group, size, index, device
+        self.ws: Optional[Workspace] = Workspace(group, device, workspace_bytes) if device.type == "cuda" else None
+
+
+def _all_gather_rows(x: torch.Tensor, ctx: TPContext) -> torch.Tensor:
+    parts = [torch.empty_like(x) for _ in range(ctx.size)]
+    dist.all_gather(parts, x.contiguous(), group=ctx.group)
+    return torch.cat(parts, 0)
+
+
+def _reduce_scatter_rows(y: torch.Tensor, ctx: TPContext) -> torch.Tensor:
+    y = y.contiguous()
+    rows = y.shape[0] // ctx.size
+    if y.is_cuda:
+        out = torch.empty((rows,) + tuple(y.shape[1:]), dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out, y, group=ctx.group)
+        return out
+    dist.all_reduce(y, group=ctx.group)                    # gloo has no reduce-scatter
+    return y[ctx.index * rows:(ctx.index + 1) * rows].clone()
+
+
+class _GatherRows(torch.autograd.Function):
+    """All-gather of the rows over the group; its adjoint is the reduce-scatter (and the other way round), so the pair
+    is differentiable to any order."""
+
+    @staticmethod
+    def forward(ctx, x, tpc):
+        ctx.tpc = tpc
+        return _all_gather_rows(x, tpc)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _ScatterRows.apply(g, ctx.tpc), None
+
+
+class _ScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, tpc):
+        ctx.tpc = tpc
+        return _reduce_scatter_rows(y, tpc)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _GatherRows.apply(g, ctx.tpc), None
+
+
+def _ref_linear(x2: torch.Tensor, w: torch.Tensor, kind: str, tpc: TPContext) -> torch.Tensor:
+    """The library-collective statement (NCCL / gloo + a differentiable matmul): the meaning of the fused kernels, the CPU
+    path, and what a recorded backward differentiates."""
+    from ..ops.functional import mm
+    wc = w if w.dtype == x2.dtype else w.to(x2.dtype)
+    if kind == "col":
+        return mm(_GatherRows.apply(x2, tpc), wc)
+    return _ScatterRows.apply(mm(x2, wc), tpc)
+
+
+class _TPLinear(torch.autograd.Function):
+    """Fused forward and first-order backward (``ag_gemm`` / ``gemm_rs``); a backward that is being recorded (the inner
+    step under the meta-gradient) is computed from ``_ref_linear`` instead, so it can be differentiated again.  The
+    first-order weight gradient goes straight into the f32 master gradient buffer when the leaf carries ``grad_target``."""
+
+    @staticmethod
+    def forward(ctx, x2, w, kind, tpc):
+        ctx.kind, ctx.tpc = kind, tpc
+        ctx.target = getattr(w, "grad_target", None)
+        if kind == "col":
+            y, full = ag_gemm(tpc.ws, x2, w)
+            ctx.save_for_backward(x2, w, full.clone())
+        else:
+            y = gemm_rs(tpc.ws, x2, w)
+            ctx.save_for_backward(x2, w)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops.functional import _INNER_BACKWARD
+        kind, tpc = ctx.kind, ctx.tpc
+        x2, w = ctx.saved_tensors[:2]
+        want_w = ctx.needs_input_grad[1] and not _INNER_BACKWARD[0]
+        if torch.is_grad_enabled():
+            with torch.enable_grad():
+                xi = x2 if x2.requires_grad else x2.detach().requires_grad_(ctx.needs_input_grad[0])
+                wi = w if w.requires_grad else w.detach().requires_grad_(want_w)
+                out = _ref_linear(xi, wi, kind, tpc)
+                wrt = [t for t, nd in ((xi, ctx.needs_input_grad[0]), (wi, want_w)) if nd]
+                grads = list(torch.autograd.grad(out, wrt, g, create_graph=True, allow_unused=True))
+            gx = grads.pop(0) if ctx.needs_input_grad[0] else None
+            gw = grads.pop(0) if want_w else None
+            return gx, gw, None, None
+        g = (g if g.dtype == torch.bfloat16 else g.to(torch.bfloat16)).contiguous()
+        gx = gw = None
+        if kind == "col":
+            x_full = ctx.saved_tensors[2]
+            if ctx.needs_input_grad[0]:
+                gx = gemm_rs(tpc.ws, g, w, w_is_kn=False)                          # (g @ w^T), reduce-scattered by rows
+            a_full, g_full = x_full, g
+        else:
+            gx_full, g_full = ag_gemm(tpc.ws, g, w, w_is_kn=False)                 # gather_rows(g) @ w^T
+            gx = gx_full if ctx.needs_input_grad[0] else None
+            a_full = x2
+        if want_w:
+            if ctx.target is not None:
+                gbuf, layer = ctx.target
+                _gemm.gemm_raw(a_full, g_full, True, False, torch.float32, out=gbuf if layer is None else gbuf[layer], accumulate=True)
+            else:
+                gw = _gemm.gemm_raw(a_full, g_full, True, False)
+        return gx, gw, None, None
+
+
+def tp_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w`` for a tensor-parallel weight leaf (``w.tp = (kind, TPContext)``).  ``kind == "col"``: ``x [B / tp, ..., K]`` ->
+    ``[B, ..., N / tp]`` (+ this rank's slice of the bias); ``"row"``: ``x [B, ..., K / tp]`` -> ``[B / tp, ..., N]``."""
+    from ..ops.functional import use_kernels
+    kind, tpc = w.tp
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    rows = x2.shape[0]
+    fused = (tpc.ws is not None and use_kernels(x2) and w.dtype == torch.bfloat16
+             and (rows % BLOCK == 0 if kind == "col" else rows % (BLOCK * tpc.size) == 0))
+    if fused and (torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad)):
+        y2 = _TPLinear.apply(x2, w, kind, tpc)
+    elif fused:
+        y2 = ag_gemm(tpc.ws, x2, w)[0] if kind == "col" else gemm_rs(tpc.ws, x2, w)
+    else:
+        y2 = _ref_linear(x2, w, kind, tpc)
+    if kind == "col":
+        y = y2.view(lead[0] * tpc.size, *lead[1:], w.shape[-1])
+    else:
+        if lead[0] % tpc.size:
+            raise ValueError(f"row-parallel product: {lead[0]} sequences do not divide over {tpc.size} ranks")
+        y = y2.view(lead[0] // tpc.size, *lead[1:], w.shape[-1])
+    if bias is not None:
+        y = y + bias.to(y.dtype)
+    return y
