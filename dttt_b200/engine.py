@@ -74,9 +74,14 @@ class Engine:
         self.mesh = mesh or Mesh(device=device or torch.device("cuda" if torch.cuda.is_available() else "cpu"))
         self.device = device or self.mesh.device
         self.dtype = torch_dtype(train_cfg.compute_dtype)
-        self.spec = param_spec(model_cfg)
+        tp = self.mesh.tp
+        self.spec = param_spec(model_cfg, tp)
+        self.tp_ctx = None
+        if tp > 1:
+            from .parallel.tp import TPContext
+            self.tp_ctx = TPContext(self.mesh.tp_group, tp, self.mesh.tp_index, self.device)
         self.store = ParamStore(self.spec, self.mesh, self.dtype, self.device, trainable=trainable,
-                                fused_comm=train_cfg.fused_comm)
+                                fused_comm=train_cfg.fused_comm, tp_ctx=self.tp_ctx)
         self.n_params = count_params(model_cfg)
         if init:
             self.init_weights(train_cfg.seed)
@@ -95,12 +100,12 @@ class Engine:
         gen_dev = self.device
         base = rng.key(seed, gen_dev)
         from .models import params as P
-        for name, value in P.iter_init(self.mc, seed, gen_dev):
+        for name, value in P.iter_init(self.mc, seed, gen_dev, self.mesh.tp, self.mesh.tp_index):
             self.store.load_full(name, value)
             del value
 
     def net(self, train: bool = True) -> Net:
-        return Net(self.mc, ComputeWeights(self.store, train=train))
+        return Net(self.mc, ComputeWeights(self.store, train=train), self.tp_ctx)
 
     # ---- batches
     def to_device(self, ids) -> torch.Tensor:
@@ -130,7 +135,7 @@ class Engine:
         sum_stats: Dict[str, torch.Tensor] = {}
         for i, b in enumerate(micro):
             cw = ComputeWeights(st, train=True)
-            net = Net(self.mc, cw)
+            net = Net(self.mc, cw, self.tp_ctx)
             loss, stats = loss_fn(net, b, self.step_key(step, i, N), step, lcfg)
             w = stats["mask_count"].detach() + 1e-6
             (loss * w).backward()
@@ -184,7 +189,7 @@ class Engine:
         st = self.store
         st.zero_grad()
         cw = ComputeWeights(st, train=True)
-        net = Net(self.mc, cw)
+        net = Net(self.mc, cw, self.tp_ctx)
         loss, stats = loss_fn(net, batch, key, step, lcfg)
         w = stats["mask_count"].detach() + 1e-6
         (loss * w if weight == "sum" else loss).backward()

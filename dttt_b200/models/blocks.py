@@ -33,10 +33,22 @@ def cast_like(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 class Net:
     """Stateless forward functions over a ``ComputeWeights`` view."""
 
-    def __init__(self, cfg: ModelConfig, cw):
+    def __init__(self, cfg: ModelConfig, cw, tp_ctx=None):
+        """``tp_ctx`` (``parallel.tp.TPContext``): the trunk's projections are tensor parallel.  Hidden states, fast weights and
+        losses then cover this rank's ``B / tp`` sequences, while Q / K / V, the KV windows and the attention cover all ``B``
+        sequences of the group for this rank's ``heads / tp`` heads (``parallel/tp.py``)."""
         self.cfg, self.cw = cfg, cw
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.dtype = cw.dtype
+        self.tp = tp_ctx
+        self.tp_size = 1 if tp_ctx is None else tp_ctx.size
+
+    def group_rows(self, pos: torch.Tensor) -> torch.Tensor:
+        """Positions of the ``B / tp`` local sequences -> positions for all ``B`` sequences of the tensor-parallel group.  The
+        sequences of a group share their positions (``loss_fn`` refuses per-sequence position ids under tensor parallelism)."""
+        if self.tp_size == 1:
+            return pos
+        return pos[:1].expand(pos.shape[0] * self.tp_size, *pos.shape[1:])
 
     # ---- parameter access
     def p(self, name: str, layer: Optional[int] = None) -> torch.Tensor:
@@ -65,9 +77,11 @@ class Net:
         cfg = self.cfg
         nh, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         b = (lambda n: self.p(f"{stack}.attn.{n}.bias", l)) if cfg.attention_bias else (lambda n: None)
-        q = Fn.linear(x, self.p(f"{stack}.attn.q.weight", l), b("q")).unflatten(-1, (nh, d))
-        k = Fn.linear(x, self.p(f"{stack}.attn.k.weight", l), b("k")).unflatten(-1, (nkv, d))
-        v = Fn.linear(x, self.p(f"{stack}.attn.v.weight", l), b("v")).unflatten(-1, (nkv, d))
+        q = Fn.linear(x, self.p(f"{stack}.attn.q.weight", l), b("q")).unflatten(-1, (-1, d))       # heads / tp under tensor parallelism
+        k = Fn.linear(x, self.p(f"{stack}.attn.k.weight", l), b("k")).unflatten(-1, (-1, d))
+        v = Fn.linear(x, self.p(f"{stack}.attn.v.weight", l), b("v")).unflatten(-1, (-1, d))
+        pos = self.group_rows(pos)
+        pos_q = None if pos_q is None else self.group_rows(pos_q)
         if cfg.qk_norm:
             q = Fn.rms_norm(q, self.p(f"{stack}.attn.q_norm.weight", l), cfg.rms_norm_eps)
             k = Fn.rms_norm(k, self.p(f"{stack}.attn.k_norm.weight", l), cfg.rms_norm_eps)
@@ -137,6 +151,7 @@ class Net:
         q, k, v = self.qkv("prefix", l, x, pos_k, pos_q)                       # [B, S, T, heads, d]
         kc, vc = k[:, CLEAN], v[:, CLEAN]
         k_prev, v_prev = (None, None) if kv_win is None else kv_win
+        B = q.shape[0]                                                         # all sequences of the tensor-parallel group
         nv_of = [A.valid_window_chunks(first_chunk + c, Wn, reach) for c in range(nc)]
         groups: Dict[int, List[int]] = {}
         for c, nv in enumerate(nv_of):
@@ -163,7 +178,7 @@ class Net:
                     extra = (fl(sel(kc.unflatten(1, (nc, C)))), fl(sel(vc.unflatten(1, (nc, C)))))
                 a = A.attend_window(fl(sel(qs)), fl(sel(ks)), fl(sel(vs)), k_wins[nv], v_wins[nv], nv, C,
                                     self.scale, own=own if own != "read" else "full", own_mask=own_mask, extra_own=extra)
-                a = a.unflatten(0, (B, len(cs)))
+                a = a.unflatten(0, (-1, len(cs)))
                 for j, c in enumerate(cs):
                     a_s[c] = a[:, j]
             outs.append(torch.stack(a_s, dim=1).flatten(1, 2))                  # [B, T, nh, d]

@@ -79,10 +79,14 @@ class ShardedAdamW:
         g = st.grad_shard
         if grad_scale != 1.0:
             g.mul_(1.0 / grad_scale)
-        sq = torch.zeros(len(GROUPS), dtype=torch.float32, device=g.device)
+        # squared norms per group; the slices of tensor-parallel weights add up over the TP group, whole parameters count once
+        sq2 = torch.zeros(2, len(GROUPS), dtype=torch.float32, device=g.device)
         for name, a, b, _, _ in self.segs:
-            sq[GROUPS.index(group_of(name))] += g[a:b].pow(2).sum()
-        sq = st.all_reduce_scalar(sq, groups=("fsdp",))
+            sq2[1 if st.tp_layout.get(name) is not None else 0, GROUPS.index(group_of(name))] += g[a:b].pow(2).sum()
+        sq2 = st.all_reduce_scalar(sq2, groups=("fsdp",))
+        if st.mesh.tp > 1:
+            st.all_reduce_scalar(sq2[1], groups=("tp",))
+        sq = sq2[0] + sq2[1]
         sq_host = sq.tolist()
         gnorm = math.sqrt(sum(sq_host))
         finite = math.isfinite(gnorm)

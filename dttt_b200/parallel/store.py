@@ -33,9 +33,14 @@ ALIGN = 64          # elements; keeps every parameter view 128-byte aligned in b
 
 class ParamStore:
     def __init__(self, spec: "OrderedDict[str, Tuple[Tuple[int, ...], str]]", mesh: Mesh, compute_dtype: torch.dtype,
-                 device: torch.device, trainable: bool = True, fused_comm: bool = True):
+                 device: torch.device, trainable: bool = True, fused_comm: bool = True, tp_ctx=None):
+        """``spec`` holds the shapes THIS rank stores (tensor-parallel slices when ``mesh.tp > 1``, see
+        ``models.params.tp_layout``); ``tp_ctx``: the ``parallel.tp.TPContext`` the sliced weights are used through."""
         self.spec, self.mesh, self.dtype, self.device = spec, mesh, compute_dtype, device
         self.trainable = trainable
+        self.tp_ctx = tp_ctx
+        from ..models.params import tp_layout
+        self.tp_layout = {n: tp_layout(n) for n in spec} if mesh.tp > 1 else {}
         self.fs = mesh.fsdp
         self.slots: Dict[str, Tuple[str, int, int, Tuple[int, ...]]] = {}      # name -> (space, offset, numel, shape)
         offs = {"big": 0, "small": 0}
@@ -52,7 +57,7 @@ class ParamStore:
         # memory (parallel.symm): the fused reduce-scatter / optimiser / all-gather kernels read and write the other
         # ranks' copies directly over NVLink.  Otherwise they are ordinary tensors and the collectives are NCCL / gloo.
         self.peer = None
-        self.fused = bool(fused_comm and trainable and self.fs > 1 and device.type == "cuda")
+        self.fused = bool(fused_comm and trainable and self.fs > 1 and device.type == "cuda" and mesh.tp == 1)
         if self.fused:
             from .symm import PeerBuffer
             lo_big = self.n["big"] * torch.empty(0, dtype=compute_dtype).element_size()
@@ -77,6 +82,19 @@ class ParamStore:
         self.grad_shard = torch.zeros(ns, dtype=f32, device=device) if trainable else None
 
     # ---- geometry
+    def tp_replicated_ranges(self) -> Dict[str, List[Tuple[int, int]]]:
+        """Per space, the merged ``[start, end)`` ranges of the flat buffers that hold parameters every rank of a
+        tensor-parallel group keeps whole: their gradients are partial sums over the group's sequences."""
+        out: Dict[str, List[Tuple[int, int]]] = {"big": [], "small": []}
+        for name, (space, off, n, _) in self.slots.items():
+            if self.tp_layout.get(name) is None:
+                end = -(-(off + n) // ALIGN) * ALIGN
+                if out[space] and out[space][-1][1] == off:
+                    out[space][-1] = (out[space][-1][0], end)
+                else:
+                    out[space].append((off, end))
+        return out
+
     def shard_range(self, space: str) -> Tuple[int, int]:
         r = self.mesh.fsdp_index
         return r * self.shard_n[space], (r + 1) * self.shard_n[space]
@@ -127,6 +145,10 @@ class ParamStore:
     def load_full(self, name: str, value: torch.Tensor) -> None:
         """Set parameter ``name`` from a full f32 tensor (every rank passes the same values)."""
         space, off, n, shape = self.slots[name]
+        lay = self.tp_layout.get(name)
+        if lay is not None and tuple(value.shape) != tuple(shape):
+            from ..models.params import tp_slice
+            value = tp_slice(name, value, self.mesh.tp, self.mesh.tp_index)      # a full tensor (checkpoint): keep this rank's slice
         v = value.to(device=self.device, dtype=torch.float32).reshape(-1)
         assert v.numel() == n, (name, tuple(value.shape), shape)
         self.lo[space][off:off + n].copy_(v)
@@ -141,10 +163,17 @@ class ParamStore:
         space, off, n, shape = self.slots[name]
         part = self.master_part(space, buf)
         if self.fs == 1:
-            return part[off:off + n].view(shape).clone()
-        full = torch.empty(self.n[space], dtype=torch.float32, device=self.device)
-        dist.all_gather_into_tensor(full, part.contiguous(), group=self.mesh.fsdp_group)
-        return full[off:off + n].view(shape).clone()
+            local = part[off:off + n].view(shape).clone()
+        else:
+            full = torch.empty(self.n[space], dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(full, part.contiguous(), group=self.mesh.fsdp_group)
+            local = full[off:off + n].view(shape).clone()
+        lay = self.tp_layout.get(name)
+        if lay is None:
+            return local
+        parts = [torch.empty_like(local) for _ in range(self.mesh.tp)]           # the whole tensor from the group's slices
+        dist.all_gather(parts, local, group=self.mesh.tp_group)
+        return torch.cat(parts, dim=lay[1])
 
     # ---- the step's collectives
     def zero_grad(self) -> None:
@@ -154,6 +183,10 @@ class ParamStore:
     def reduce_grads(self) -> None:
         """Sum the full gradient buffers over every data rank and leave this rank's slice in ``grad_shard``."""
         m = self.mesh
+        if m.tp > 1:
+            for space, ranges in self.tp_replicated_ranges().items():
+                for a, b in ranges:
+                    dist.all_reduce(self.grad[space][a:b], op=dist.ReduceOp.SUM, group=m.tp_group)
         if self.fused:
             # one kernel per space: every rank pulls its slice of every peer's gradient buffer over NVLink, sums,
             # and accumulates the slice's squared norm; no library collective.
@@ -187,8 +220,10 @@ class ParamStore:
             if self.fs > 1:
                 dist.all_gather_into_tensor(self.lo[space], self.lo[space][lo:hi].clone(), group=m.fsdp_group)
 
-    def all_reduce_scalar(self, x: torch.Tensor, groups=("fsdp", "dp")) -> torch.Tensor:
+    def all_reduce_scalar(self, x: torch.Tensor, groups=("fsdp", "dp", "tp")) -> torch.Tensor:
         m = self.mesh
+        if "tp" in groups and m.tp > 1:
+            dist.all_reduce(x, group=m.tp_group)
         if "fsdp" in groups and m.fsdp > 1:
             dist.all_reduce(x, group=m.fsdp_group)
         if "dp" in groups and m.dp > 1:
@@ -222,6 +257,9 @@ class ComputeWeights:
                 t.requires_grad_(True)
                 if not is_small(name):
                     t.grad_target = (self.store.grad_view(name), layer)
+            lay = self.store.tp_layout.get(name)
+            if lay is not None and not name.endswith("bias"):
+                t.tp = (lay[0], self.store.tp_ctx)
             self._leaves[key] = t
         return t
 

@@ -137,6 +137,18 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     run_dev = net.p("final_norm.weight").device
     host = torch.device("cpu")
     batch = Batch(*[None if x is None else x.to(host) for x in batch])
+    tp = net.tp_size
+    if tp > 1:
+        # the micro-batch belongs to the tensor-parallel group: this rank scores its own B / tp sequences
+        if batch.position_ids is not None or cfg.inner_task == "split":
+            raise NotImplementedError("tensor parallel: the sequences of a group must share their positions "
+                                      "(no position_ids, no split inner task)")
+        Bg = batch.input_ids.shape[0]
+        if Bg % tp:
+            raise ValueError(f"tensor parallel {tp}: the micro-batch of {Bg} sequences does not divide over the group")
+        lo_, hi_ = net.tp.index * (Bg // tp), (net.tp.index + 1) * (Bg // tp)
+        batch = Batch(*[None if x is None else x[lo_:hi_] for x in batch])
+        key = key[lo_:hi_] if key.dim() == 2 else rng.fold_in(key, 7_000_001 + net.tp.index)
     ids = batch.input_ids.long()
     dev = host
     B, T = ids.shape
@@ -337,7 +349,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         raise ValueError(f"segment_chunks {n_seg_chunks} < window_chunks {Wn}: the carried window would be short")
     n_seg = nc // n_seg_chunks
     T_seg = n_seg_chunks * C
-    nkv, d = mc.num_key_value_heads, mc.head_dim
+    nkv, d = mc.num_key_value_heads // tp, mc.head_dim                       # this rank's KV heads
     Lp = mc.prefix_len
     cdt = net.dtype
     lr_now = IN.inner_lr(step, cfg.inner_lr, cfg.inner_lr_warmup_steps)
@@ -389,7 +401,8 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
 
     # ---- carries at the sequence start
     kvp = None                                                                      # per prefix layer (k, v) tails
-    kvs = [(torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev), torch.zeros(B, Wn * C, nkv, d, dtype=cdt, device=dev))
+    Bkv = B * tp                                                                    # windows hold every sequence of the TP group
+    kvs = [(torch.zeros(Bkv, Wn * C, nkv, d, dtype=cdt, device=dev), torch.zeros(Bkv, Wn * C, nkv, d, dtype=cdt, device=dev))
            for _ in range(S)]
     if use_gdn:
         mem = torch.zeros(B, S, mc.gdn_heads, mc.gdn_head_dim, mc.gdn_head_dim, dtype=torch.float32, device=dev)

@@ -19,8 +19,9 @@ def main():
     case, out = sys.argv[1], sys.argv[2]
     rank, world, _ = init_distributed("gloo", timeout_s=int(os.environ.get("TEST_TIMEOUT_S", "60")))
     fsdp = int(os.environ.get("TEST_FSDP", "0"))
-    mesh = make_mesh(fsdp, 1, torch.device("cpu"))
-    eng = Engine(tiny_model(), tiny_train(batch_size=4, fsdp_size=fsdp), mesh, torch.device("cpu"))
+    tp = int(os.environ.get("TEST_TP", "1"))
+    mesh = make_mesh(fsdp, tp, torch.device("cpu"))
+    eng = Engine(tiny_model(), tiny_train(batch_size=4, fsdp_size=fsdp, tp_size=tp), mesh, torch.device("cpu"))
     ids = torch.randint(0, 120, (4, 32), generator=torch.Generator().manual_seed(0))
     n = 4 // mesh.batch_ranks
     mine = ids[mesh.batch_index * n:(mesh.batch_index + 1) * n]
@@ -30,6 +31,22 @@ def main():
         d = CK.save(os.path.join(out, "ck"), 2, eng, "h")
         if rank == 0:
             torch.save({"metrics": ms, "params": full, "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
+    elif case == "tp_grads":
+        # tensor parallel: the group's micro-batch is the whole `ids`; row-wise keys make the draws independent of the split
+        from dttt_b200.ttt.scan import Batch
+        from dttt_b200.utils import rng
+        keys = rng.split(rng.key(11), 4)
+        loss, w = eng.grad_of(Batch(ids), keys, 0, weight="sum")
+        tot = torch.tensor([loss * w, w], dtype=torch.float64)
+        dist.all_reduce(tot)
+        eng.store.reduce_grads()
+        grads = {k: eng.store.gather_full(k, eng.store.grad_shard) for k in eng.store.names()}
+        ms = [eng.train_step(ids, s) for s in range(2)]
+        full = {k: eng.store.gather_full(k) for k in eng.store.names()}
+        d = CK.save(os.path.join(out, "ck"), 1, eng, "h")
+        if rank == 0:
+            torch.save({"ce_sum": float(tot[0]), "count": float(tot[1]), "grads": grads, "metrics": ms, "params": full,
+                        "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
     elif case == "rank_exits":
         # rank 1 leaves between steps (no collective in flight); the others must get an error, not hang
         eng.train_step(mine, 0)

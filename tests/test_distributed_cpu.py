@@ -46,6 +46,34 @@ def test_sharded_training_matches_one_process(tmp_path, world, fsdp):
         assert torch.equal(eng.store.gather_full(k), v), k
 
 
+@pytest.mark.parametrize("world,fsdp", [(2, 1), (4, 2)])
+def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp):
+    """tp = 2: trunk projections split over the group (heads / MLP columns), sequences split for everything else.  The loss sum,
+    every parameter's gradient (slices re-assembled, whole parameters summed over the group) and the checkpoint must equal the
+    single-process ones."""
+    from dttt_b200.ttt.scan import Batch
+    from dttt_b200.utils import rng
+    r = launch(world, "tp_grads", tmp_path, {"TEST_FSDP": str(fsdp), "TEST_TP": "2"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = torch.load(tmp_path / "result.pt", weights_only=False)
+    assert res["mesh"]["tp"] == 2
+    eng = make_engine(batch_size=4)
+    ids = torch.randint(0, 120, (4, 32), generator=torch.Generator().manual_seed(0))
+    n_groups = world // 2                                         # every TP group scores the same four sequences here
+    loss, w = eng.grad_of(Batch(ids), rng.split(rng.key(11), 4), 0, weight="sum")
+    eng.store.reduce_grads()
+    assert abs(res["count"] - n_groups * w) < 1e-3 and abs(res["ce_sum"] - n_groups * loss * w) < 1e-3 * abs(loss * w)
+    for k in eng.store.names():
+        ref = n_groups * eng.store.gather_full(k, eng.store.grad_shard)
+        assert res["grads"][k].shape == ref.shape, k
+        assert torch.allclose(res["grads"][k], ref, atol=2e-5, rtol=2e-4), (k, (res["grads"][k] - ref).abs().max().item())
+    assert all(m["finite"] == 1.0 for m in res["metrics"])
+    from dttt_b200.ckpt import store as CK
+    CK.load_weights(str(tmp_path / "ck" / "step_00000001"), eng)
+    for k, v in res["params"].items():
+        assert torch.equal(eng.store.gather_full(k), v), k
+
+
 def test_a_rank_that_leaves_is_detected(tmp_path):
     # plain child processes (an elastic launcher would tear the survivors down itself)
     port = str(29900 + os.getpid() % 90)
