@@ -32,17 +32,26 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ------------------------------------------------------------------ RMSNorm
 // One warp per row; D a multiple of 8.  y = w * x * rsqrt(mean(x^2) + eps), f32 math (reference
 // src/ttt/model.py:123-134).
+template <int NC>                 // 16-byte pieces of a row per lane: the row stays in registers between the two passes
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, long long rows, int D,
                                    float eps) {
   const int lane = threadIdx.x & 31;
+  const int nvec = D / 8;
   const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
   for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+    uint4 v[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {                       // every load of the row is in flight before the first use
+      const int c = lane + 32 * j;
+      v[j] = c < nvec ? xr[c] : make_uint4(0, 0, 0, 0);
+    }
     float ss = 0.f;
-    for (int c = lane; c < D / 8; c += 32) {
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
       float f[8];
-      unpack8(xr[c], f);
+      unpack8(v[j], f);
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
     }
@@ -50,13 +59,17 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const fl
     const float r = rsqrtf(ss / D + eps);
     if (lane == 0 && rstd) rstd[row] = r;
     uint4* yr = reinterpret_cast<uint4*>(y + row * D);
-    for (int c = lane; c < D / 8; c += 32) {
-      float f[8];
-      unpack8(xr[c], f);
-      const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
-      f[0] *= r * w0.x; f[1] *= r * w0.y; f[2] *= r * w0.z; f[3] *= r * w0.w;
-      f[4] *= r * w1.x; f[5] *= r * w1.y; f[6] *= r * w1.z; f[7] *= r * w1.w;
-      yr[c] = pack8(f);
+#pragma unroll
+    for (int j = 0; j < NC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nvec) {
+        float f[8];
+        unpack8(v[j], f);
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+        f[0] *= r * w0.x; f[1] *= r * w0.y; f[2] *= r * w0.z; f[3] *= r * w0.w;
+        f[4] *= r * w1.x; f[5] *= r * w1.y; f[6] *= r * w1.z; f[7] *= r * w1.w;
+        yr[c] = pack8(f);
+      }
     }
   }
 }
@@ -404,7 +417,16 @@ extern "C" int dttt_rmsnorm_fwd(const void* x, const float* w, void* y, float* r
   const int wpb = 8;
   long long blocks = (rows + wpb - 1) / wpb;
   int grid = (int)(blocks > 148 * 32 ? 148 * 32 : (blocks < 1 ? 1 : blocks));
-  rmsnorm_fwd_kernel<<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rstd, rows, D, eps);
+  if (D > 8192) return -2;
+  const int nc = (D / 8 + 31) / 32;
+#define FWD(NC) rmsnorm_fwd_kernel<NC><<<grid, wpb * 32, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)y, rstd, rows, D, eps)
+  if (nc <= 1) FWD(1);
+  else if (nc <= 2) FWD(2);
+  else if (nc <= 4) FWD(4);
+  else if (nc <= 8) FWD(8);
+  else if (nc <= 16) FWD(16);
+  else FWD(32);
+#undef FWD
   return (int)cudaGetLastError();
 }
 

@@ -21,7 +21,8 @@ def delta_rule_chunked(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, log
                        block: int = 64) -> torch.Tensor:
     """``k [B, C, nh, dk]``, ``v [B, C, nh, dv]``, ``beta / log_alpha [B, C, nh]``, ``S0 [B, nh, dv, dk]`` -> ``S_C``."""
     from . import kernels
-    if k.is_cuda and kernels.available("gdn") and not torch.is_grad_enabled():
+    if (k.is_cuda and kernels.available("gdn") and k.shape[-1] in (64, 128) and v.shape[-1] == k.shape[-1]
+            and not (torch.is_grad_enabled() and any(t.requires_grad for t in (k, v, beta, log_alpha, S0)))):
         return kernels.gdn_chunked(k, v, beta, log_alpha, S0, block)
     B, C, nh, dk = k.shape
     L = min(block, C)
