@@ -133,6 +133,15 @@ class Engine:
         wsum = torch.zeros((), dtype=torch.float32, device=self.device)
         loss_w = torch.zeros((), dtype=torch.float32, device=self.device)
         sum_stats: Dict[str, torch.Tensor] = {}
+        # Gradient noise scale from the micro-batches (reference train.py:767-779): every micro-batch's own gradient norm is
+        # needed, so each one lands in the (zeroed) gradient buffers and is then moved into an accumulator.
+        noise = N > 1 and self.mesh.tp == 1
+        micro_sq = torch.zeros((), dtype=torch.float32, device=self.device)
+        if noise:
+            if getattr(self, "_grad_acc", None) is None:
+                self._grad_acc = {k: torch.zeros_like(v) for k, v in st.grad.items()}
+            for v in self._grad_acc.values():
+                v.zero_()
         for i, b in enumerate(micro):
             cw = ComputeWeights(st, train=True)
             net = Net(self.mc, cw, self.tp_ctx)
@@ -140,6 +149,12 @@ class Engine:
             w = stats["mask_count"].detach() + 1e-6
             (loss * w).backward()
             cw.fold_grads()
+            if noise:
+                sq = sum(g.float().pow(2).sum() for g in st.grad.values())
+                micro_sq += sq / (w * w)                       # the buffers hold w_m * grad(ce_m / n_m)
+                for k, g in st.grad.items():
+                    self._grad_acc[k] += g
+                    g.zero_()
             wsum += w
             loss_w += loss.detach().float() * w
             for k, v in stats.items():
@@ -153,9 +168,12 @@ class Engine:
                     sum_stats[k] = sum_stats.get(k, 0) + v.detach().float()
             del cw, net, loss
         # one global normaliser: micro-batches and data ranks together are one batch
-        red = torch.stack([wsum, loss_w])
+        if noise:
+            for k, g in st.grad.items():
+                g.copy_(self._grad_acc[k])
+        red = torch.stack([wsum, loss_w, micro_sq])
         red = st.all_reduce_scalar(red)
-        wsum_g, loss_g = red[0].item(), red[1].item()
+        wsum_g, loss_g, micro_sq_g = red[0].item(), red[1].item(), red[2].item()
         with prof.range("reduce_grads"):
             st.reduce_grads()
         with prof.range("optimizer"):
@@ -167,6 +185,16 @@ class Engine:
         if self.device.type == "cuda":
             _lib.check_status(self.device)
         out = {"loss": loss_g / wsum_g, **om}
+        if noise:
+            # E|g_b|^2 = |G|^2 + tr(S) / b: the per-rank micro-batches (b_s sequences) and the whole step (b_l) give both
+            R = self.mesh.batch_ranks
+            b_s = float(micro[0].input_ids.shape[0])
+            b_l = b_s * N * R
+            m_sq, f_sq = micro_sq_g / (N * R), om["grad_norm"] ** 2
+            tr_sigma = (m_sq - f_sq) / (1.0 / b_s - 1.0 / b_l)
+            signal = (b_l * f_sq - b_s * m_sq) / (b_l - b_s)
+            out["grad_norm_micro"] = math.sqrt(max(m_sq, 0.0))
+            out["grad_noise_scale"] = tr_sigma / signal if signal > 0 else float("nan")
         host = {k: float(v) for k, v in sum_stats.items()}
         for k, v in host.items():
             out[k] = v / N

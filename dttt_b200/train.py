@@ -295,6 +295,8 @@ def main(argv=None) -> int:
         t = t.to(device)
         return eng.store.all_reduce_scalar(t)
 
+    wb_holder = [None]                                           # set once the tracker is up (it starts after this definition)
+
     def run_eval(step):
         if eval_fns is None:
             return {}
@@ -304,6 +306,8 @@ def main(argv=None) -> int:
             ev.update(EV.evaluate(fns, groups, cfg, mcfg, make_batch, step, log, is_main=is_main, tag=f" t={t_fixed:g}", all_reduce=ar))
         if planted_fns is not None:
             ev.update(EV.evaluate_planted(planted_fns, groups, cfg, mcfg, make_batch, step, log, is_main=is_main))
+        if wb_holder[0] is not None:
+            wb_holder[0].log({k: v for k, v in ev.items() if isinstance(v, (int, float))}, step=step)
         return ev
 
     # ---- memory probe: one dry step, report the allocator's peak, exit
@@ -317,8 +321,22 @@ def main(argv=None) -> int:
                 f"{torch.cuda.max_memory_reserved() / 2**30:.2f} GiB per GPU (one step: forward, backward, optimiser)")
         return 0
 
+    # ---- experiment tracker (main process only, optional): continue the checkpoint's run only when this run writes into the
+    # same checkpoint directory; a branch into another directory is a new run (reference train.py:1049-1056)
+    wb = None
+    wb_id = None
+    if cfg.wandb_project and is_main:
+        try:
+            import wandb
+            same_run = bool(resume_dir) and os.path.dirname(os.path.abspath(resume_dir)) == os.path.abspath(cfg.ckpt_dir)
+            wb = wandb.init(project=cfg.wandb_project, config={**dc.asdict(cfg), **dc.asdict(mcfg)}, resume="allow",
+                            id=st.get("wandb_run_id") if same_run else None)
+            wb_id = wb.id
+            wb_holder[0] = wb
+        except Exception as e:                                   # noqa: BLE001 - not installed, offline, no credentials
+            log(f"[ttt] wandb_project={cfg.wandb_project} but the tracker is unavailable ({type(e).__name__}: {e}); logging to stdout only")
     prefetch = Prefetcher(sampler, (start_step - data_offset) * N, max(cfg.prefetch, N), mask_maker if mask_maker.active else None)
-    save_state = lambda: {"data_offset": data_offset}
+    save_state = lambda: {"data_offset": data_offset, **({"wandb_run_id": wb_id} if wb_id else {})}
     tokens_per_step = cfg.batch_size * cfg.seq_len * N
     t_last, last_log = time.time(), start_step - 1
     trace = None
@@ -370,9 +388,13 @@ def main(argv=None) -> int:
                     + (f"  mtp {m['mtp_loss']:.3f}/{m['inner_mtp']:.3f}" if cfg.mtp else "")
                     + (f"  aux x{cfg.aux_causal_weight:g}" if cfg.aux_causal_weight > 0 else "")
                     + (f"  kvb {m['inner_kvb']:.3f}" if cfg.inner_kvb_weight > 0 else "")
+                    + (f"  noise {m['grad_noise_scale']:.0f}" if "grad_noise_scale" in m else "")
                     + (f"  overflow {m['overflow']}" if m["overflow"] else "")
                     + (f"  gn[e/p/s/w/o] {m['gnorm_embed']:.2f}/{m['gnorm_prefix']:.2f}/{m['gnorm_suffix']:.2f}/"
                        f"{m['gnorm_fast_weight']:.2f}/{m['gnorm_other']:.2f}" if m["grad_norm"] > 2.0 or step < 2 else ""))
+                if wb:
+                    wb.log({**{f"train/{k}": v for k, v in m.items() if isinstance(v, (int, float))}, "train/s_per_step": dt,
+                            "train/tokens_per_s": tps}, step=step)
             saved_here = False
             if cfg.ckpt_interval and ((step + 1) % cfg.ckpt_interval == 0 or step == cfg.steps - 1):
                 d = ckpt.save(cfg.ckpt_dir, step, eng, sampler.hash, keep=cfg.keep_checkpoints, extra_state=save_state())
