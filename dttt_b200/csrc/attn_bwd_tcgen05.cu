@@ -34,12 +34,15 @@ constexpr int BQ = 128, BKEY = 128, HD = 64;
 
 struct AttnBwdParams {
   int n, Cq, Kn, nh, nkv, causal;
+  int Kn1;              // keys [0, Kn1) belong to the first K / V pair (and dK / dV), the rest to the second
   float scale;
   const float* lse;     // [n, nh, Cq]
   const float* delta;   // [n, nh, Cq]  rowsum(dO * O)
   float* dQ;            // [n, Cq, nh, 64] f32, accumulated into
-  __nv_bfloat16* dK;    // [n, Kn, nkv, 64]
+  __nv_bfloat16* dK;    // [n, Kn1, nkv, 64]
   __nv_bfloat16* dV;
+  __nv_bfloat16* dK2;   // [n, Kn - Kn1, nkv, 64]
+  __nv_bfloat16* dV2;
   int* status;
 };
 
@@ -113,6 +116,7 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
                 const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                const __grid_constant__ CUtensorMap mapK2, const __grid_constant__ CUtensorMap mapV2,
                 const __grid_constant__ CUtensorMap mapdQ, const AttnBwdParams p) {
   using L = BwdSmem;
   extern __shared__ uint8_t smem_raw[];
@@ -159,7 +163,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(acc_final, 1);
     *abort_word = 0;
     fence_mbar_init();
-    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapdO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapdQ);
+    tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapdO); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapK2); tma_prefetch_desc(&mapV2); tma_prefetch_desc(&mapdQ);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -171,8 +175,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // ---------------------------------------------------------------- TMA producer
     if (elect_one() && n_it > 0) {
       mbar_expect_tx(kv_full, 2 * L::TILE);
-      tma_load_4d_b(sK, &mapK, kv_full, 0, hk, jb * BKEY, b);
-      tma_load_4d_b(sV, &mapV, kv_full, 0, hk, jb * BKEY, b);
+      const bool second = jb * BKEY >= p.Kn1;                // this key block lies in the second K / V pair
+      const int krow = second ? jb * BKEY - p.Kn1 : jb * BKEY;
+      tma_load_4d_b(sK, second ? &mapK2 : &mapK, kv_full, 0, hk, krow, b);
+      tma_load_4d_b(sV, second ? &mapV2 : &mapV, kv_full, 0, hk, krow, b);
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
         if (!mbar_wait_bounded(&st_empty[s], ((it >> 1) & 1) ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
@@ -384,7 +390,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_ld_32x32(tmem + C_DK + lane_addr + sub * 32, rk);
         tmem_ld_wait();
         if (kj < p.Kn) {
-          const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + sub * 32;
+          const bool second = kj >= p.Kn1;
+          const int len = second ? p.Kn - p.Kn1 : p.Kn1, kl = second ? kj - p.Kn1 : kj;
+          __nv_bfloat16* outK = second ? p.dK2 : p.dK;
+          __nv_bfloat16* outV = second ? p.dV2 : p.dV;
+          const long long o = (((long long)b * len + kl) * p.nkv + hk) * HD + sub * 32;
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v, k;
@@ -395,19 +405,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
               vb[q] = __floats2bfloat162_rn(__uint_as_float(rv[i + 2 * q]), __uint_as_float(rv[i + 2 * q + 1]));
               kb[q] = __floats2bfloat162_rn(__uint_as_float(rk[i + 2 * q]), __uint_as_float(rk[i + 2 * q + 1]));
             }
-            *reinterpret_cast<uint4*>(p.dV + o + i) = v;
-            *reinterpret_cast<uint4*>(p.dK + o + i) = k;
+            *reinterpret_cast<uint4*>(outV + o + i) = v;
+            *reinterpret_cast<uint4*>(outK + o + i) = k;
           }
         }
       }
     } else if (n_it == 0 && kj < p.Kn) {
       // no query sees this key block: its gradients are zero
-      const long long o = (((long long)b * p.Kn + kj) * p.nkv + hk) * HD + sub * 32;
+      const bool second = kj >= p.Kn1;
+      const int len = second ? p.Kn - p.Kn1 : p.Kn1, kl = second ? kj - p.Kn1 : kj;
+      const long long o = (((long long)b * len + kl) * p.nkv + hk) * HD + sub * 32;
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
-        *reinterpret_cast<uint4*>(p.dV + o + i) = z;
-        *reinterpret_cast<uint4*>(p.dK + o + i) = z;
+        *reinterpret_cast<uint4*>((second ? p.dV2 : p.dV) + o + i) = z;
+        *reinterpret_cast<uint4*>((second ? p.dK2 : p.dK) + o + i) = z;
       }
     }
   }
@@ -447,11 +459,12 @@ static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int he
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads) {
+static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads, long long batch_stride = 0) {
   EncodeTiledFnB enc = bwd_encode_fn();
   if (!enc) return -1;
+  if (batch_stride <= 0) batch_stride = (long long)rows * heads * HD;
   cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
-  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)heads * HD * 2, (cuuint64_t)rows * heads * HD * 2};
+  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)heads * HD * 2, (cuuint64_t)batch_stride * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -464,33 +477,45 @@ static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int he
 
 using namespace dttt;
 
-// Q, O, dO [n, Cq, nh, 64]; K, V, dK, dV [n, Kn, nkv, 64] (bf16, contiguous); lse [n, nh, Cq] f32 from the forward;
-// delta [n, nh, Cq] f32 scratch (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).
-extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* O, const void* dO, const float* lse,
-                             float* delta, float* dQ, void* dK, void* dV, int n, int Cq, int Kn, int nh, int nkv, int d,
-                             float scale, int causal, int* status, cudaStream_t stream) {
+// Q, O, dO [n, Cq, nh, 64] (bf16, contiguous); keys / values as one or two pairs like dttt_attn_fwd (K2 == null: one pair):
+// K / V [n, Kn1, nkv, 64] with `k_bs` / `v_bs` elements between sequences, K2 / V2 [n, Kn2, nkv, 64]; dK / dV [n, Kn1, nkv, 64]
+// and dK2 / dV2 [n, Kn2, nkv, 64] contiguous outputs; lse [n, nh, Cq] f32 from the forward; delta [n, nh, Cq] f32 scratch
+// (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).
+extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* K2, const void* V2, const void* O, const void* dO,
+                             const float* lse, float* delta, float* dQ, void* dK, void* dV, void* dK2, void* dV2, int n, int Cq,
+                             int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs, long long k2_bs,
+                             long long v2_bs, float scale, int causal, int* status, cudaStream_t stream) {
+  const int Kn = Kn1 + (K2 ? Kn2 : 0);
   if (d != HD || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
   if (causal && Kn < Cq) return -3;
+  if (K2 && Kn1 % BKEY) return -4;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
-  CUtensorMap mq, mdo, mk, mv, mdq;
+  CUtensorMap mq, mdo, mk, mv, mk2, mv2, mdq;
   int r;
   if ((r = make_map4f(&mdq, dQ, n, Cq, nh))) return 500 + r;
   if ((r = make_map4b(&mq, Q, n, Cq, nh))) return 100 + r;
   if ((r = make_map4b(&mdo, dO, n, Cq, nh))) return 200 + r;
-  if ((r = make_map4b(&mk, K, n, Kn, nkv))) return 300 + r;
-  if ((r = make_map4b(&mv, V, n, Kn, nkv))) return 400 + r;
+  if ((r = make_map4b(&mk, K, n, Kn1, nkv, k_bs))) return 300 + r;
+  if ((r = make_map4b(&mv, V, n, Kn1, nkv, v_bs))) return 400 + r;
+  if (K2) {
+    if ((r = make_map4b(&mk2, K2, n, Kn2, nkv, k2_bs))) return 600 + r;
+    if ((r = make_map4b(&mv2, V2, n, Kn2, nkv, v2_bs))) return 700 + r;
+  } else {
+    mk2 = mk; mv2 = mv;
+  }
   const long long rows = (long long)n * Cq * nh;
   attn_bwd_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, rows, Cq, nh);
   AttnBwdParams p;
-  p.n = n; p.Cq = Cq; p.Kn = Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
   p.lse = lse; p.delta = delta; p.dQ = dQ;
-  p.dK = reinterpret_cast<__nv_bfloat16*>(dK); p.dV = reinterpret_cast<__nv_bfloat16*>(dV); p.status = status;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dK); p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
+  p.dK2 = reinterpret_cast<__nv_bfloat16*>(dK2); p.dV2 = reinterpret_cast<__nv_bfloat16*>(dV2); p.status = status;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
   dim3 grid((Kn + BKEY - 1) / BKEY, nkv, n);
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mdq, p);
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -27,6 +27,7 @@ constexpr int AK = 128;   // keys per block
 
 struct AttnParams {
   int n, Cq, Kn, nh, nkv, causal;
+  int Kn1;              // keys [0, Kn1) come from the first K / V pair, [Kn1, Kn) from the second (Kn1 a multiple of 128, or Kn)
   float scale;
   __nv_bfloat16* O;
   float* lse;
@@ -303,7 +304,8 @@ struct Attn2Smem {
 template <int D>
 __global__ void __launch_bounds__(320, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                 const __grid_constant__ CUtensorMap mapV, const AttnParams p) {
+                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapK2,
+                 const __grid_constant__ CUtensorMap mapV2, const AttnParams p) {
   using L = Attn2Smem<D>;
   constexpr int DB = D / 64;
   extern __shared__ uint8_t smem_raw[];
@@ -344,6 +346,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     *abort_word = 0;
     fence_mbar_init();
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapK2); tma_prefetch_desc(&mapV2);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
@@ -369,8 +372,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         mbar_expect_tx(&kv_full[s], L::KV_BYTES);
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
-          tma_load_4d(sK + db * (AK * 128), &mapK, &kv_full[s], db * 64, hk, j * AK, b);
-          tma_load_4d(sV + db * (AK * 128), &mapV, &kv_full[s], db * 64, hk, j * AK, b);
+          // the window (first pair) and the chunk's own keys (second pair) are separate tensors: no concatenation pass
+          const bool second = j * AK >= p.Kn1;
+          const int krow = second ? j * AK - p.Kn1 : j * AK;
+          tma_load_4d(sK + db * (AK * 128), second ? &mapK2 : &mapK, &kv_full[s], db * 64, hk, krow, b);
+          tma_load_4d(sV + db * (AK * 128), second ? &mapV2 : &mapV, &kv_full[s], db * 64, hk, krow, b);
         }
       }
     }
@@ -549,11 +555,12 @@ static EncodeTiledFn4 attn_encode_fn() {
 }
 
 // [n, rows, heads, d] bf16 with d contiguous; box = 64 d x 1 head x 128 rows x 1
-static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int heads, int d) {
+static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int heads, int d, long long batch_stride = 0) {
   EncodeTiledFn4 enc = attn_encode_fn();
   if (!enc) return -1;
+  if (batch_stride <= 0) batch_stride = (long long)rows * heads * d;      // elements between sequences (a slice of a longer window has more)
   cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
-  cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)rows * heads * d * 2};
+  cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)batch_stride * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -566,31 +573,42 @@ static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int hea
 
 using namespace dttt;
 
-// Q [n, Cq, nh, d], K / V [n, Kn, nkv, d], O [n, Cq, nh, d] (bf16, contiguous), lse [n, nh, Cq] f32 or null.  d in {64, 128}.
-// variant 0: two query tiles per CTA, P in tensor memory (the default); 1: one tile per CTA, P through shared memory.
-extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, void* O, float* lse, int n, int Cq, int Kn, int nh,
-                             int nkv, int d, float scale, int causal, int variant, int* status, cudaStream_t stream) {
+// Q [n, Cq, nh, d], O like Q (bf16, contiguous), lse [n, nh, Cq] f32 or null, d in {64, 128}.  Keys and values may come
+// as two pairs: K / V [n, Kn1, nkv, d] followed by K2 / V2 [n, Kn2, nkv, d] (rows contiguous, `*_bs` = elements between
+// sequences, so a slice of a longer window needs no copy); K2 == null means one pair of Kn1 keys.  With two pairs Kn1 must be
+// a multiple of 128 and the two-tile variant (0) is used.
+extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, const void* K2, const void* V2, void* O, float* lse, int n,
+                             int Cq, int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs, long long k2_bs,
+                             long long v2_bs, float scale, int causal, int variant, int* status, cudaStream_t stream) {
+  const int Kn = Kn1 + (K2 ? Kn2 : 0);
   if ((d != 64 && d != 128) || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
   if (causal && Kn < Cq) return -3;
+  if (K2 && (Kn1 % AK || variant != 0)) return -4;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mk2, mv2;
   int r;
   if ((r = make_map4(&mq, Q, n, Cq, nh, d))) return 100 + r;
-  if ((r = make_map4(&mk, K, n, Kn, nkv, d))) return 200 + r;
-  if ((r = make_map4(&mv, V, n, Kn, nkv, d))) return 300 + r;
+  if ((r = make_map4(&mk, K, n, Kn1, nkv, d, k_bs))) return 200 + r;
+  if ((r = make_map4(&mv, V, n, Kn1, nkv, d, v_bs))) return 300 + r;
+  if (K2) {
+    if ((r = make_map4(&mk2, K2, n, Kn2, nkv, d, k2_bs))) return 400 + r;
+    if ((r = make_map4(&mv2, V2, n, Kn2, nkv, d, v2_bs))) return 500 + r;
+  } else {
+    mk2 = mk; mv2 = mv;
+  }
   AttnParams p;
-  p.n = n; p.Cq = Cq; p.Kn = Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
   p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
   if (variant == 0) {
     dim3 grid2((Cq + 2 * AQ - 1) / (2 * AQ), nh, n);
     static bool a64 = false, a128 = false;
     if (d == 64) {
       if (!a64) { cudaFuncSetAttribute(attn_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<64>::TOTAL); a64 = true; }
-      attn_fwd2_kernel<64><<<grid2, 320, Attn2Smem<64>::TOTAL, stream>>>(mq, mk, mv, p);
+      attn_fwd2_kernel<64><<<grid2, 320, Attn2Smem<64>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
     } else {
       if (!a128) { cudaFuncSetAttribute(attn_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<128>::TOTAL); a128 = true; }
-      attn_fwd2_kernel<128><<<grid2, 320, Attn2Smem<128>::TOTAL, stream>>>(mq, mk, mv, p);
+      attn_fwd2_kernel<128><<<grid2, 320, Attn2Smem<128>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
     }
     cudaError_t e2 = cudaGetLastError();
     return e2 == cudaSuccess ? 0 : 1000 + (int)e2;

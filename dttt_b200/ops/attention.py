@@ -178,6 +178,11 @@ def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_w
     """
     WC = k_win.shape[1]
     kw, vw = k_win[:, WC - n_valid * chunk:], v_win[:, WC - n_valid * chunk:]
+    if (extra_own is None and n_valid > 0 and use_kernels(q) and (own_mask is None and own in ("full", "causal"))
+            and _two_segment_ok(q, kw, k_own)):
+        # window and own keys stay separate tensors: the kernels read (and, backward, write) both pairs directly
+        return staged((_fast_fwd2, _fast_bwd2, _ref_for_staged2), (q, kw, vw, k_own.to(kw.dtype), v_own.to(vw.dtype)),
+                      (scale, own == "causal"))
     parts_k = [kw] + ([extra_own[0].to(k_own.dtype)] if extra_own is not None else []) + [k_own]
     parts_v = [vw] + ([extra_own[1].to(v_own.dtype)] if extra_own is not None else []) + [v_own]
     K = torch.cat(parts_k, dim=1) if len(parts_k) > 1 or n_valid else k_own
@@ -229,6 +234,28 @@ def _ref_for_staged(q, K, V, scale, causal):
     p = torch.softmax(s, dim=-1).to(q.dtype)
     o = mm(p, vg)
     return o.view(n, nkv, rep, C, d).permute(0, 3, 1, 2, 4).reshape(n, C, nh, d)
+
+
+def _two_segment_ok(q, kw, k_own) -> bool:
+    from . import kernels
+    return (q.is_cuda and kernels.available("attention") and kernels.available("attention_bwd") and kernels.attention_bwd_supported(q, kw)
+            and kw.shape[1] % 128 == 0 and kernels.ATTN_VARIANT == 0)
+
+
+def _ref_for_staged2(q, kw, vw, ko, vo, scale, causal):
+    return _ref_for_staged(q, torch.cat([kw, ko], 1), torch.cat([vw, vo], 1), scale, causal)
+
+
+def _fast_fwd2(q, kw, vw, ko, vo, scale, causal):
+    from . import kernels
+    o, lse = kernels.attention_fwd(q, kw, vw, scale, causal, k2=ko, v2=vo)
+    return o, (o, lse)
+
+
+def _fast_bwd2(g, tensors, saved, needs, scale, causal):
+    from . import kernels
+    q, kw, vw, ko, vo = tensors
+    return kernels.attention_bwd(g, q, kw, vw, saved[0], saved[1], scale, causal, k2=ko, v2=vo)
 
 
 def _fast_fwd(q, K, V, scale, causal):

@@ -254,23 +254,40 @@ def seq_lincomb(a, g, alpha, beta):
 
 
 # =============================================================================== attention family
-_lib.register("dttt_attn_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp])
+_lib.register("dttt_attn_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _f, _i, _i, _vp, _vp])
 ATTN_VARIANT = int(os.environ.get("DTTT_ATTN_VARIANT", "0"))
 _SYMBOL.update(attention="dttt_attn_fwd")
 
 
-def attention_fwd(q, k, v, scale, causal, variant=None):
+def _kv_rows(t):
+    """A K / V tensor ``[n, rows, heads, d]`` usable without a copy: rows, heads and d contiguous, any stride between
+    sequences (a slice of a longer window), 16-byte aligned."""
+    n, rows, heads, d = t.shape
+    if t.stride(3) != 1 or t.stride(2) != d or t.stride(1) != heads * d or t.data_ptr() % 16 or (n > 1 and t.stride(0) % 8):
+        t = t.contiguous()
+    return t, (t.stride(0) if n > 1 else rows * heads * d)
+
+
+def attention_fwd(q, k, v, scale, causal, variant=None, k2=None, v2=None):
     """Flash attention forward on the tcgen05 kernel.  ``q [n, Cq, nh, d]``, ``k / v [n, Kn, nkv, d]`` bf16, every key
-    valid, ``causal`` aligned to the end of the key axis.  Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
+    valid, ``causal`` aligned to the end of the key axis.  ``k2 / v2 [n, Kn2, nkv, d]``: more keys AFTER ``k / v`` (the chunk's
+    own keys after the window's), read from their own tensors instead of a concatenation (``Kn`` a multiple of 128).
+    Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
     n, Cq, nh, d = q.shape
     Kn, nkv = k.shape[1], k.shape[2]
     assert q.dtype == torch.bfloat16 and d in (64, 128), (q.dtype, d)
-    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    var = ATTN_VARIANT if variant is None else int(variant)
+    if k2 is not None and (Kn % 128 or var != 0 or Kn == 0):
+        k, v, k2, v2 = torch.cat([k, k2], 1), torch.cat([v, v2], 1), None, None
+        Kn = k.shape[1]
+    qc = q.contiguous()
+    (kc, kbs), (vc, vbs) = _kv_rows(k), _kv_rows(v)
+    (k2c, k2bs), (v2c, v2bs) = (_kv_rows(k2), _kv_rows(v2)) if k2 is not None else ((None, 0), (None, 0))
     o = torch.empty_like(qc)
     lse = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
     st = _lib.status_tensor(q.device)
-    _check(_lib.lib().dttt_attn_fwd(_p(qc), _p(kc), _p(vc), _p(o), _p(lse), n, Cq, Kn, nh, nkv, d, float(scale), 1 if causal else 0,
-                                    ATTN_VARIANT if variant is None else int(variant), _p(st), _stream()), "attn_fwd")
+    _check(_lib.lib().dttt_attn_fwd(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(o), _p(lse), n, Cq, Kn, 0 if k2 is None else k2.shape[1],
+                                    nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale), 1 if causal else 0, var, _p(st), _stream()), "attn_fwd")
     return o, lse
 
 
@@ -327,7 +344,7 @@ def linear_ce_dlogits(h, Eb, targets_i32, coef, lse, col0):
     return D
 
 
-_lib.register("dttt_attn_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp])
+_lib.register("dttt_attn_bwd", _i, [_vp] * 14 + [_i] * 7 + [_ll] * 4 + [_f, _i, _vp, _vp])
 _SYMBOL.update(attention_bwd="dttt_attn_bwd")
 
 
@@ -335,21 +352,32 @@ def attention_bwd_supported(q, k) -> bool:
     return attention_supported(q, k) and q.shape[-1] == 64
 
 
-def attention_bwd(g, q, k, v, o, lse, scale, causal):
-    """First-order backward of ``attention_fwd`` on the tcgen05 kernel: ``(dq, dk, dv)``.  ``dq`` is accumulated in f32
-    by the kernel (one ``[128, 64]`` tile per key block and query tile) and cast once at the end."""
+def attention_bwd(g, q, k, v, o, lse, scale, causal, k2=None, v2=None):
+    """First-order backward of ``attention_fwd`` on the tcgen05 kernel: ``(dq, dk, dv)`` or, with a second key / value pair,
+    ``(dq, dk, dv, dk2, dv2)``.  ``dq`` is accumulated in f32 by the kernel (one bulk reduction per key block and query tile)
+    and cast once at the end."""
     n, Cq, nh, d = q.shape
     Kn, nkv = k.shape[1], k.shape[2]
-    qc, kc, vc, oc, gc = q.contiguous(), k.contiguous(), v.contiguous(), o.contiguous(), g.contiguous()
+    two = k2 is not None and Kn % 128 == 0 and Kn > 0
+    if k2 is not None and not two:
+        dq, dk, dv = attention_bwd(g, q, torch.cat([k, k2], 1), torch.cat([v, v2], 1), o, lse, scale, causal)
+        return dq, dk[:, :Kn], dv[:, :Kn], dk[:, Kn:], dv[:, Kn:]
+    qc, oc, gc = q.contiguous(), o.contiguous(), g.contiguous()
+    (kc, kbs), (vc, vbs) = _kv_rows(k), _kv_rows(v)
+    (k2c, k2bs), (v2c, v2bs) = (_kv_rows(k2), _kv_rows(v2)) if two else ((None, 0), (None, 0))
     dq32 = torch.zeros(n, Cq, nh, d, dtype=torch.float32, device=q.device)
     delta = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
-    dk, dv = torch.empty_like(kc), torch.empty_like(vc)
+    mk = lambda t: torch.empty(t.shape, dtype=t.dtype, device=t.device)
+    dk, dv = mk(k), mk(v)
+    dk2, dv2 = (mk(k2), mk(v2)) if two else (None, None)
     st = _lib.status_tensor(q.device)
-    _check(_lib.lib().dttt_attn_bwd(_p(qc), _p(kc), _p(vc), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv), n, Cq, Kn,
-                                    nh, nkv, d, float(scale), 1 if causal else 0, _p(st), _stream()), "attn_bwd")
+    _check(_lib.lib().dttt_attn_bwd(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv),
+                                    _p(dk2), _p(dv2), n, Cq, Kn, k2.shape[1] if two else 0, nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale),
+                                    1 if causal else 0, _p(st), _stream()), "attn_bwd")
     global LAUNCHES
     LAUNCHES += 1                                   # the delta kernel
-    return dq32.to(q.dtype), dk, dv
+    dq = dq32.to(q.dtype)
+    return (dq, dk, dv, dk2, dv2) if two else (dq, dk, dv)
 
 
 # =============================================================================== embedding / objective family

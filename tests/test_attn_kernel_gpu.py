@@ -97,3 +97,30 @@ def test_attn_bwd(n, Cq, Kn, nh, nkv, causal):
     assert rel(dv, dvr) < 2e-2, ("dv", rel(dv, dvr))
     assert rel(dk, dkr) < 2e-2, ("dk", rel(dk, dkr))
     assert rel(dq, dqr) < 2e-2, ("dq", rel(dq, dqr))
+
+
+@pytest.mark.parametrize("n,Cq,Kw,nh,nkv,causal", [(2, 256, 512, 4, 2, True), (2, 256, 512, 4, 2, False), (1, 1024, 2048, 8, 2, True), (3, 128, 128, 2, 1, True)])
+def test_two_segment_keys_equal_the_concatenation(n, Cq, Kw, nh, nkv, causal):
+    """Window keys (a strided slice of a longer window buffer) and own keys passed as separate tensors: forward and backward
+    must equal the single-tensor call on their concatenation."""
+    from dttt_b200.ops import _lib, kernels
+    torch.manual_seed(6)
+    d = 64
+    q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    win_k = torch.randn(n, Kw + 256, nkv, d, device="cuda", dtype=torch.bfloat16)
+    win_v = torch.randn(n, Kw + 256, nkv, d, device="cuda", dtype=torch.bfloat16)
+    kw, vw = win_k[:, 256:], win_v[:, 256:]                                   # not contiguous across sequences
+    ko = torch.randn(n, Cq, nkv, d, device="cuda", dtype=torch.bfloat16)
+    vo = torch.randn(n, Cq, nkv, d, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    o2, lse2 = kernels.attention_fwd(q, kw, vw, scale, causal, k2=ko, v2=vo)
+    K, V = torch.cat([kw, ko], 1), torch.cat([vw, vo], 1)
+    o1, lse1 = kernels.attention_fwd(q, K, V, scale, causal)
+    assert torch.equal(o1, o2) and torch.equal(lse1, lse2)
+    dq2, dkw, dvw, dko, dvo = kernels.attention_bwd(g, q, kw, vw, o2, lse2, scale, causal, k2=ko, v2=vo)
+    dq1, dk1, dv1 = kernels.attention_bwd(g, q, K, V, o1, lse1, scale, causal)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    assert torch.equal(torch.cat([dkw, dko], 1), dk1) and torch.equal(torch.cat([dvw, dvo], 1), dv1)
+    assert (dq2.float() - dq1.float()).abs().max().item() < 2e-2 * dq1.float().abs().max().item()      # bulk reductions add in any order
