@@ -42,11 +42,27 @@ def lib() -> ctypes.CDLL:
         with _lock:
             if _lib is None:
                 path = _build.LIBPATH
-                if not os.path.exists(path):
+                # With a compiler at hand the build is re-checked on every first use (unchanged sources cost a few hashes), so a
+                # library older than the sources -- whose entry points may no longer match the Python wrappers -- is never loaded.
+                # Concurrent ranks of one node serialise on a lock file.
+                if _build.nvcc_path() is not None:
+                    path = _locked_build()
+                elif not os.path.exists(path):
                     path = _build.build()
                 _lib = ctypes.CDLL(path)
                 _declare(_lib)
     return _lib
+
+
+def _locked_build() -> str:
+    import fcntl
+    os.makedirs(os.path.dirname(_build.LIBPATH), exist_ok=True)
+    with open(_build.LIBPATH + ".lock", "w") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            return _build.build()
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
 
 
 def _declare(l: ctypes.CDLL) -> None:

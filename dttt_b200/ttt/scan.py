@@ -429,7 +429,18 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     if cfg.mtp:
         tok2_c, wgt2_c, tm2_c = OBJ.to_chunks(tgt_mtp, C), OBJ.to_chunks(w_mtp, C), OBJ.to_chunks(m_mtp, C)
 
-    for g in range(n_seg):
+    def run_segment(g, kvp, kvs, W, mem):
+        """Prefix layers and the chunk scan of segment ``g`` from the carries ``(kvp, kvs, W | mem)``.  Returns the new carries and
+        the segment's sums: ``sums [6]`` (ce, count, ce2, count2, distill mass, aux), inner stats, plan CE, per-sequence CE / count,
+        per-chunk CE / count ``[ncs]`` and, with ``per_token``, the per-token arrays ``[ncs, B, C]``."""
+        zero = torch.zeros((), dtype=torch.float32, device=dev)
+        acc = dict(ce_sum=zero, mask_count=zero, ce2_sum=zero, mask2_count=zero, distill_mass=zero, aux=zero)
+        inner_stats = IN.zero_stats(dev)
+        plan_ce = torch.zeros(2, device=dev)
+        ce_chunk, mask_chunk = [None] * n_seg_chunks, [None] * n_seg_chunks
+        ce_seq = torch.zeros(B, device=dev)
+        mask_seq = torch.zeros(B, device=dev)
+        ce_tok, mask_tok = [None] * n_seg_chunks, [None] * n_seg_chunks
         sl = slice(g * T_seg, (g + 1) * T_seg)
         first = eff(g * n_seg_chunks)
         if n_rr and g * n_seg_chunks == n_rr:
@@ -504,9 +515,65 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
             acc["distill_mass"] = acc["distill_mass"] + dmass_c
             inner_stats = inner_stats + st_c.detach()
             plan_ce = plan_ce + plan_c.detach()
-            ce_chunk[c], mask_chunk[c] = ce_sum_c.detach(), mask_count_c.detach()
+            ce_chunk[j], mask_chunk[j] = ce_sum_c.detach(), mask_count_c.detach()
             ce_seq, mask_seq = ce_seq + ce_seq_c.detach(), mask_seq + mask_seq_c.detach()
-            ce_tok[c], mask_tok[c] = ce_tok_c, mask_tok_c
+            ce_tok[j], mask_tok[j] = ce_tok_c, mask_tok_c
+        as_f = lambda x: x.float() if torch.is_tensor(x) else torch.tensor(float(x), device=dev)
+        sums = torch.stack([as_f(acc[k]).reshape(()) for k in ("ce_sum", "mask_count", "ce2_sum", "mask2_count", "distill_mass", "aux")])
+        tok = (torch.stack(ce_tok), torch.stack(mask_tok)) if cfg.per_token else None
+        return kvp, kvs, W, mem, (sums, inner_stats, plan_ce, ce_seq, mask_seq, torch.stack(ce_chunk), torch.stack(mask_chunk)), tok
+
+
+    # Segments: with more than one segment under recompute regions, a segment is itself a region (nested around the per-layer
+    # and per-chunk ones): the backward keeps one set of carries per segment and re-runs one segment at a time, so memory
+    # does not grow with the number of chunks (reference chunk_scan.py:679-779, the outer scan over checkpointed segments).
+    nest = use_regions and n_seg > 1
+    zero = torch.zeros((), dtype=torch.float32, device=dev)
+    acc = dict(ce_sum=zero, mask_count=zero, ce2_sum=zero, mask2_count=zero, distill_mass=zero, aux=zero)
+    for g in range(n_seg):
+        if not nest:
+            kvp, kvs, W, mem, outs_g, tok_g = run_segment(g, kvp, kvs, W, mem)
+        else:
+            has_kvp = kvp is not None
+            flat_in = ([t for pair in kvp for t in pair] if has_kvp else []) + [t for pair in kvs for t in pair] \
+                + ([mem] if use_gdn else ([] if cfg.no_write else IN.flat(W)))
+
+            def seg_fn(*ts, _g=g, _has_kvp=has_kvp):
+                o = 0
+                kvp_i = None
+                if _has_kvp:
+                    kvp_i = [(ts[2 * i], ts[2 * i + 1]) for i in range(Lp)]; o += 2 * Lp
+                kvs_i = [(ts[o + 2 * i], ts[o + 2 * i + 1]) for i in range(S)]; o += 2 * S
+                mem_i, W_i = mem, W
+                if use_gdn:
+                    mem_i = ts[o]
+                elif not cfg.no_write:
+                    W_i = IN.unflat(ts[o:])
+                kvp_o, kvs_o, W_o, mem_o, outs_o, tok_o = run_segment(_g, kvp_i, kvs_i, W_i, mem_i)
+                flat_out = [t for pair in kvp_o for t in pair] + [t for pair in kvs_o for t in pair] \
+                    + ([mem_o] if use_gdn else ([] if cfg.no_write else IN.flat(W_o))) + list(outs_o) + (list(tok_o) if tok_o is not None else [])
+                return tuple(flat_out)
+            res = region(seg_fn, tuple(flat_in), True, "segment.bwd")
+            o = 0
+            kvp = [(res[2 * i], res[2 * i + 1]) for i in range(Lp)]; o += 2 * Lp
+            kvs = [(res[o + 2 * i], res[o + 2 * i + 1]) for i in range(S)]; o += 2 * S
+            if use_gdn:
+                mem = res[o]; o += 1
+            elif not cfg.no_write:
+                W = IN.unflat(res[o:o + 3 * F_]); o += 3 * F_
+            outs_g = res[o:o + 7]; o += 7
+            tok_g = (res[o], res[o + 1]) if cfg.per_token else None
+        sums_g, st_g, plan_g, ce_seq_g, mask_seq_g, ce_chunk_g, mask_chunk_g = outs_g
+        for i, k in enumerate(("ce_sum", "mask_count", "ce2_sum", "mask2_count", "distill_mass", "aux")):
+            acc[k] = acc[k] + sums_g[i]
+        inner_stats = inner_stats + st_g.detach()
+        plan_ce = plan_ce + plan_g.detach()
+        ce_seq, mask_seq = ce_seq + ce_seq_g.detach(), mask_seq + mask_seq_g.detach()
+        for j in range(n_seg_chunks):
+            c = g * n_seg_chunks + j
+            ce_chunk[c], mask_chunk[c] = ce_chunk_g[j].detach(), mask_chunk_g[j].detach()
+            if tok_g is not None:
+                ce_tok[c], mask_tok[c] = tok_g[0][j], tok_g[1][j]
         if cfg.truncate_fast_weight and not use_gdn and not cfg.no_write:
             W = [tuple(t.detach() for t in w) for w in W]
 
