@@ -237,4 +237,46 @@ class Engine:
     @torch.no_grad()
     def eval_step(self, batch: Batch, key: torch.Tensor, step: int, lcfg: LossConfig):
         net = self.net(train=False)
-        return loss_fn(net, batch, key, step, lcfg)
+        loss, stats = loss_fn(net, batch, key, step, lcfg)
+        if self.mesh.tp > 1:
+            loss, stats = self._merge_over_tp(loss, stats)
+        return loss, stats
+
+    def _merge_over_tp(self, loss: torch.Tensor, stats: Dict[str, torch.Tensor]):
+        """Under tensor parallelism every rank scored its own sequences of the group's batch: put the per-sequence arrays back
+        in batch order, add the counts, and average the rest by scored tokens, so callers see the group's batch."""
+        import torch.distributed as dist
+        g, tp = self.mesh.tp_group, self.mesh.tp
+        w = stats["mask_count"].detach().float() + 1e-6
+        wsum = w.clone()
+        dist.all_reduce(wsum, group=g)
+
+        def cat(x):
+            parts = [torch.empty_like(x) for _ in range(tp)]
+            dist.all_gather(parts, x.contiguous(), group=g)
+            return torch.cat(parts, 0)
+
+        def wmean(x, wl, wt):
+            y = x.detach().float() * wl
+            dist.all_reduce(y, group=g)
+            return y / wt
+        out = {}
+        mbc = stats.get("mask_by_chunk")
+        mbc_sum = None
+        if mbc is not None:
+            mbc_sum = mbc.detach().float().clone()
+            dist.all_reduce(mbc_sum, group=g)
+        for k, v in stats.items():
+            if k in ("loss_by_seq", "mask_by_seq", "ce_by_token", "mask_by_token"):
+                out[k] = cat(v)
+            elif k in ("mask_count", "mtp_mask_count", "mask_by_chunk"):
+                y = v.detach().float().clone()
+                dist.all_reduce(y, group=g)
+                out[k] = y
+            elif k == "loss_by_chunk" and mbc is not None:
+                out[k] = wmean(v, mbc.detach().float() + 1e-6, mbc_sum + tp * 1e-6)
+            elif torch.is_tensor(v) and v.is_floating_point():
+                out[k] = wmean(v, w, wsum)
+            else:
+                out[k] = v
+        return wmean(loss, w, wsum), out

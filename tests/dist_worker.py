@@ -41,11 +41,14 @@ def main():
         dist.all_reduce(tot)
         eng.store.reduce_grads()
         grads = {k: eng.store.gather_full(k, eng.store.grad_shard) for k in eng.store.names()}
+        import dataclasses as dc
+        ev_loss, ev = eng.eval_step(Batch(ids), keys, 0, dc.replace(eng.lcfg, per_sequence=True))
         ms = [eng.train_step(ids, s) for s in range(2)]
         full = {k: eng.store.gather_full(k) for k in eng.store.names()}
         d = CK.save(os.path.join(out, "ck"), 1, eng, "h")
         if rank == 0:
             torch.save({"ce_sum": float(tot[0]), "count": float(tot[1]), "grads": grads, "metrics": ms, "params": full,
+                        "ev_loss": float(ev_loss), "ev_by_seq": ev["loss_by_seq"], "ev_count": float(ev["mask_count"]),
                         "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
     elif case == "rank_exits":
         # rank 1 leaves between steps (no collective in flight); the others must get an error, not hang

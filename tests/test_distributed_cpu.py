@@ -68,6 +68,11 @@ def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp):
         assert res["grads"][k].shape == ref.shape, k
         assert torch.allclose(res["grads"][k], ref, atol=2e-5, rtol=2e-4), (k, (res["grads"][k] - ref).abs().max().item())
     assert all(m["finite"] == 1.0 for m in res["metrics"])
+    # evaluation under tensor parallelism reports the group's whole batch, sequences in order
+    import dataclasses as dc
+    ev_loss, ev = make_engine(batch_size=4).eval_step(Batch(ids), rng.split(rng.key(11), 4), 0, dc.replace(eng.lcfg, per_sequence=True))
+    assert abs(res["ev_loss"] - float(ev_loss)) < 1e-5 and abs(res["ev_count"] - float(ev["mask_count"])) < 1e-3
+    assert torch.allclose(res["ev_by_seq"], ev["loss_by_seq"], atol=1e-5)
     from dttt_b200.ckpt import store as CK
     CK.load_weights(str(tmp_path / "ck" / "step_00000001"), eng)
     for k, v in res["params"].items():
