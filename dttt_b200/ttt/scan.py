@@ -34,6 +34,12 @@ from . import objective as OBJ
 from .regions import region
 
 
+# From this many segments on a segment is a recompute region of its own.  Below it the per-chunk carries of the whole
+# sequence (0.9 GB per chunk and sequence at 1B) still fit beside the working set and the extra forward pass (about 15 % of a
+# step) is not worth paying; from 64 chunks (128k tokens of 1024-token chunks in segments of 8) they no longer do.
+NEST_SEGMENTS_FROM = 8
+
+
 class Batch(NamedTuple):
     input_ids: torch.Tensor                          # [B, T]
     loss_mask: Optional[torch.Tensor] = None         # [B, T] bool
@@ -527,7 +533,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     # Segments: with more than one segment under recompute regions, a segment is itself a region (nested around the per-layer
     # and per-chunk ones): the backward keeps one set of carries per segment and re-runs one segment at a time, so memory
     # does not grow with the number of chunks (reference chunk_scan.py:679-779, the outer scan over checkpointed segments).
-    nest = use_regions and n_seg > 1
+    nest = use_regions and n_seg >= NEST_SEGMENTS_FROM
     zero = torch.zeros((), dtype=torch.float32, device=dev)
     acc = dict(ce_sum=zero, mask_count=zero, ce2_sum=zero, mask2_count=zero, distill_mass=zero, aux=zero)
     for g in range(n_seg):

@@ -24,6 +24,17 @@ def test_remat_and_segments_do_not_change_loss_or_grads(task, shift):
     assert all(v.abs().sum() > 0 for k, v in g0.items()), [k for k, v in g0.items() if v.abs().sum() == 0]
 
 
+def test_nested_segment_regions_do_not_change_loss_or_grads(monkeypatch):
+    from dttt_b200.ttt import scan
+    eng = make_engine()
+    lc = loss_config(eng.tc)
+    l0, g0, _ = loss_and_grads(eng, IDS, dc.replace(lc, remat=False))
+    monkeypatch.setattr(scan, "NEST_SEGMENTS_FROM", 2)                  # 4 chunks in segments of 2: every segment its own region
+    for variant in (dc.replace(lc, segment_chunks=2), dc.replace(lc, segment_chunks=2, truncate_fast_weight=False, per_token=True)):
+        l1, g1, _ = loss_and_grads(eng, IDS, variant)
+        assert abs(l0 - l1) < 1e-6 and max_diff(g0, g1) < 1e-6
+
+
 def test_second_order_is_alive_and_first_order_differs():
     eng = make_engine()
     lc = loss_config(eng.tc)
