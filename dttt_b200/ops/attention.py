@@ -181,7 +181,7 @@ def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_w
     if (extra_own is None and n_valid > 0 and use_kernels(q) and (own_mask is None and own in ("full", "causal"))
             and _two_segment_ok(q, kw, k_own)):
         # window and own keys stay separate tensors: the kernels read (and, backward, write) both pairs directly
-        return staged((_fast_fwd2, _fast_bwd2, _ref_for_staged2), (q, kw, vw, k_own.to(kw.dtype), v_own.to(vw.dtype)),
+        return staged((_fast_fwd2, _fast_bwd2, _ref_for_staged2, _diff_bwd2), (q, kw, vw, k_own.to(kw.dtype), v_own.to(vw.dtype)),
                       (scale, own == "causal"))
     parts_k = [kw] + ([extra_own[0].to(k_own.dtype)] if extra_own is not None else []) + [k_own]
     parts_v = [vw] + ([extra_own[1].to(v_own.dtype)] if extra_own is not None else []) + [v_own]
@@ -192,13 +192,15 @@ def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_w
     simple = own_mask is None or (own == "causal" and extra_own is None)
     if use_kernels(q) and simple:
         causal = own_mask is not None
-        spec = (_fast_fwd, _fast_bwd, _ref_for_staged)
+        spec = (_fast_fwd, _fast_bwd, _ref_for_staged, _diff_bwd)
         return staged(spec, (q, K, V), (scale, causal))
     return ref.attend(q, K, V, None, scale, own_mask)
 
 
 # staged execution: library/hand-written forward + first-order backward, reference for the second order
 _BIAS = {}
+# the recorded backward runs the flash backward kernel with a hand-written derivative (False: differentiate the reference statement)
+SECOND_ORDER_KERNEL = True
 
 
 def _causal_bias(C: int, Kn: int, device) -> torch.Tensor:
@@ -256,6 +258,24 @@ def _fast_bwd2(g, tensors, saved, needs, scale, causal):
     from . import kernels
     q, kw, vw, ko, vo = tensors
     return kernels.attention_bwd(g, q, kw, vw, saved[0], saved[1], scale, causal, k2=ko, v2=vo)
+
+
+def _diff_bwd2(g, tensors, saved, needs, scale, causal):
+    """The backward as an operation with a hand-written derivative (``ops.attn_second``), or ``None`` to decline."""
+    from . import attn_second
+    q, kw, vw, ko, vo = tensors
+    if not SECOND_ORDER_KERNEL or not saved or not attn_second.supported(q, kw.shape[1] + ko.shape[1]):
+        return None
+    return attn_second.attention_bwd_diff(g, q, kw, vw, ko, vo, saved[0], saved[1], scale, causal)
+
+
+def _diff_bwd(g, tensors, saved, needs, scale, causal):
+    from . import attn_second, kernels
+    q, K, V = tensors
+    if (not SECOND_ORDER_KERNEL or not saved or not kernels.available("attention_bwd") or not kernels.attention_bwd_supported(q, K)
+            or not attn_second.supported(q, K.shape[1])):
+        return None
+    return attn_second.attention_bwd_diff(g, q, K, V, None, None, saved[0], saved[1], scale, causal)
 
 
 def _fast_fwd(q, K, V, scale, causal):

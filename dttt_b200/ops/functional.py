@@ -34,12 +34,14 @@ def use_kernels(*tensors: torch.Tensor) -> bool:
 
 class _Staged(torch.autograd.Function):
     """forward: ``fast_fwd(*tensors)`` -> (out, saved...); backward: ``fast_bwd`` when no graph is being
-    recorded, else the VJP of ``ref_fn`` taken with ``create_graph=True``."""
+    recorded; else the optional fourth entry of the spec, a backward that is itself a differentiable
+    operation (it may decline by returning ``None``), else the VJP of ``ref_fn`` taken with
+    ``create_graph=True``."""
 
     @staticmethod
     def forward(ctx, spec, n_tensors, *args):
         tensors, consts = args[:n_tensors], args[n_tensors:]
-        fast_fwd, fast_bwd, ref_fn = spec
+        fast_fwd = spec[0]
         out, saved = fast_fwd(*tensors, *consts)
         ctx.spec, ctx.consts, ctx.n = spec, consts, n_tensors
         ctx.n_saved = len(saved)
@@ -48,11 +50,19 @@ class _Staged(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        fast_fwd, fast_bwd, ref_fn = ctx.spec
+        fast_bwd, ref_fn = ctx.spec[1], ctx.spec[2]
+        diff_bwd = ctx.spec[3] if len(ctx.spec) > 3 else None
         tensors = ctx.saved_tensors[:ctx.n]
         saved = ctx.saved_tensors[ctx.n:]
         needs = ctx.needs_input_grad[2:2 + ctx.n]
-        if torch.is_grad_enabled():
+        full = None
+        if torch.is_grad_enabled() and diff_bwd is not None:
+            res = diff_bwd(g, tensors, saved, needs, *ctx.consts)
+            if res is not None:
+                full = [t if nd else None for t, nd in zip(res, needs)]
+        if full is not None:
+            pass
+        elif torch.is_grad_enabled():
             with torch.enable_grad():
                 ins = [t if t.requires_grad else t.detach().requires_grad_(nd) for t, nd in zip(tensors, needs)]
                 out = ref_fn(*ins, *ctx.consts)

@@ -380,6 +380,26 @@ def attention_bwd(g, q, k, v, o, lse, scale, causal, k2=None, v2=None):
     return (dq, dk, dv, dk2, dv2) if two else (dq, dk, dv)
 
 
+# =============================================================================== second-order attention (row stage)
+_lib.register("dttt_attn_bwd2_rows", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _f, _vp])
+_SYMBOL.update(attention_bwd2="dttt_attn_bwd2_rows")
+ATTN_BWD2_MAX_KEYS = 10240
+
+
+def attention_bwd2_rows(S, dP, gdS, X, lse, delta, chunk, causal, scale):
+    """Row stage of the derivative of the attention backward: f32 ``S, dP, gdS, X [rows, Kn]`` (unscaled scores, ``dO V^T``,
+    unscaled ``gQ K^T + Q gK^T``, ``dO gV^T``) and ``lse, delta [rows]`` -> bf16 ``P, scale dS, gdP, scale gS [rows, Kn]``.
+    Row ``r`` is query position ``r % chunk`` of its chunk."""
+    Kn = S.shape[-1]
+    rows = S.numel() // Kn
+    outs = [torch.empty(S.shape, dtype=torch.bfloat16, device=S.device) for _ in range(4)]
+    for t in (S, dP, gdS, X, lse, delta):
+        assert t.is_contiguous() and t.dtype == torch.float32
+    _check(_lib.lib().dttt_attn_bwd2_rows(_p(S), _p(dP), _p(gdS), _p(X), _p(lse), _p(delta), *[_p(t) for t in outs], rows, Kn, int(chunk),
+                                          1 if causal else 0, float(scale), _stream()), "attn_bwd2_rows")
+    return outs
+
+
 # =============================================================================== embedding / objective family
 _lib.register("dttt_embed_gather", _i, [_vp, _vp, _vp, _ll, _i, _vp])
 _lib.register("dttt_embed_scatter_f32", _i, [_vp, _vp, _vp, _ll, _i, _vp])

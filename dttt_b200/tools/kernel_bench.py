@@ -146,6 +146,59 @@ def bench_attn(a, out):
         out(resb)
 
 
+def bench_attn2(a, out):
+    """The derivative of the attention backward (``ops.attn_second``): the row kernel alone against the copy bandwidth, and the
+    whole second-order call (4 + 7 tensor-core products around it) against autograd differentiating the staged statement."""
+    from dttt_b200.ops import attention, attn_second, kernels
+    n, Cq, Kn, nh, nkv, d = a.seqs, a.cq, a.kn, a.heads, a.kv_heads, a.head_dim
+    scale = d ** -0.5
+    mk = lambda *s: torch.randn(*s, device="cuda", dtype=torch.bfloat16)
+    q, k, v, g = mk(n, Cq, nh, d), mk(n, Kn, nkv, d), mk(n, Kn, nkv, d), mk(n, Cq, nh, d)
+    cq, ck, cv = mk(n, Cq, nh, d), mk(n, Kn, nkv, d), mk(n, Kn, nkv, d)
+    o, lse = kernels.attention_fwd(q, k, v, scale, a.causal)
+    hbm, flops, src = peaks()
+    rows = n * nh * Cq
+    S, dP, gdS, X = (torch.randn(rows, Kn, device="cuda") for _ in range(4))
+    lse_r, delta = torch.full((rows,), 8.0, device="cuda"), torch.zeros(rows, device="cuda")
+    ms = timeit(lambda: kernels.attention_bwd2_rows(S, dP, gdS, X, lse_r, delta, Cq, a.causal, scale), a.iters, a.once)
+    nbytes = rows * Kn * 24.0
+    out({"kernel": "attn_bwd2_rows", "rows": rows, "Kn": Kn, "causal": a.causal, "ms": ms, "gbs": nbytes / ms / 1e6,
+         "frac_of_copy_bw": nbytes / (ms * 1e-3) / hbm, "note": "4 f32 reads + 4 bf16 writes per score", "peaks": src})
+    del S, dP, gdS, X
+    if a.compare and not a.once:                      # the products around the row kernel, one of each kind
+        from dttt_b200.ops.gemm import gemm_raw
+        B, R = n * nkv, (nh // nkv) * Cq
+        qg, kg = mk(B, R, d), mk(B, Kn, d)
+        q2, k2 = mk(B, R, 2 * d), mk(B, Kn, 2 * d)
+        Pm = mk(B, R, Kn)
+        acc_r, acc_k = torch.zeros(B, R, d, device="cuda"), torch.zeros(B, Kn, d, device="cuda")
+        for name, fn, nb in (("scores f32 = q k^T", lambda: gemm_raw(qg, kg, False, True, torch.float32), B * R * Kn * 4.0),
+                             ("scores f32, inner 128", lambda: gemm_raw(q2, k2, False, True, torch.float32), B * R * Kn * 4.0),
+                             ("row side: P @ k (f32 accumulate)", lambda: gemm_raw(Pm, kg, False, False, torch.float32, out=acc_r, accumulate=True), B * R * Kn * 2.0),
+                             ("key side: P^T @ q (f32 accumulate)", lambda: gemm_raw(Pm, qg, True, False, torch.float32, out=acc_k, accumulate=True), B * R * Kn * 2.0)):
+            t = timeit(fn, a.iters)
+            out({"kernel": "attn_second_order product: " + name, "batch": B, "rows": R, "Kn": Kn, "ms": t, "gbs": nb / t / 1e6,
+                 "frac_of_copy_bw": nb / (t * 1e-3) / hbm, "peaks": src})
+        del Pm
+    ms2 = timeit(lambda: attn_second.second_order(cq, ck, cv, g, q, k, v, o, lse, scale, a.causal), a.iters, a.once)
+    pairs = Cq * Kn
+    fl = 2.0 * n * nh * d * pairs * 12                                   # 5 score-shaped + 7 output products, dense
+    res = {"kernel": "attn_second_order (GEMMs + row kernel)", "seqs": n, "Cq": Cq, "Kn": Kn, "heads": nh, "kv_heads": nkv, "head_dim": d,
+           "causal": a.causal, "ms": ms2, "tflops_dense": fl / ms2 / 1e9, "min_bytes_ms": rows * Kn * 54.0 / hbm * 1e3, "peaks": src}
+    if a.compare and not a.once:
+        def by_autograd():
+            ins = [t.detach().requires_grad_(True) for t in (q, k, v)]
+            gg = g.detach().requires_grad_(True)
+            oo = attention._ref_for_staged(*ins, scale, a.causal)
+            first = torch.autograd.grad(oo, ins, gg, create_graph=True)
+            L = sum((c.float() * f.float()).sum() for c, f in zip((cq, ck, cv), first))
+            return torch.autograd.grad(L, ins + [gg])
+        mr = timeit(by_autograd, max(3, a.iters // 3))
+        res.update(ms_autograd_of_statement=mr, vs_autograd=mr / ms2,
+                   note="the autograd figure includes the statement's forward and first backward, which the kernel path replaces by the flash kernels")
+    out(res)
+
+
 def bench_ce(a, out):
     """Linear + cross-entropy: the forward (GEMM with the per-tile softmax-partials epilogue + combine) and one vocabulary
     block of the backward's dlogits GEMM, against the unfused statement (f32 logits GEMM + torch logsumexp)."""
@@ -178,7 +231,7 @@ def bench_ce(a, out):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.kernel_bench")
-    ap.add_argument("cmd", choices=["gemm", "attn", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
+    ap.add_argument("cmd", choices=["gemm", "attn", "attn2", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
     ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--vocab", type=int, default=128256); ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
@@ -199,6 +252,8 @@ def main(argv=None):
         bench_gemm(a, out)
     elif a.cmd == "attn":
         bench_attn(a, out)
+    elif a.cmd == "attn2":
+        bench_attn2(a, out)
     elif a.cmd == "ce":
         a.rows = 2048 if a.rows == 49152 else a.rows
         a.k = 2048 if a.k == 8192 else a.k

@@ -25,6 +25,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kernels", action="store_true")
     ap.add_argument("--trace", default="")
     ap.add_argument("--shapes", action="store_true", help="also group the framework ops by input shapes")
+    ap.add_argument("--top", type=int, default=60, help="rows of the by-shape table")
     a = ap.parse_args(argv)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -70,7 +71,7 @@ def main(argv=None) -> int:
         if a.shapes:
             print("device time by op and input shapes:")
             ks = p.key_averages(group_by_input_shape=True)
-            for e in sorted(ks, key=lambda e: -e.self_device_time_total)[:60]:
+            for e in sorted(ks, key=lambda e: -e.self_device_time_total)[:a.top]:
                 if e.key.startswith(("aten::", "_")):
                     print(f"  {e.key[:28]:28s} n={e.count:5d} {e.self_device_time_total / 1e3:8.1f} ms  {str(e.input_shapes)[:150]}")
         if a.trace:
