@@ -15,9 +15,12 @@ and for cotangents ``(gQ, gK, gV)`` of ``(dQ, dK, dV)``
     grad dO = P gV + gdP V               grad V = gdP^T dO
     grad Q  = scale (gS K + dS gK)       grad K = scale (gS^T Q + dS^T gQ)
 
-On the GPU the four score-shaped products and the seven output products run on the tcgen05 GEMM, batched over
-(sequence, KV head) with the query heads of a group folded into the rows, and everything between them is ONE kernel
-(``csrc/attn_bwd2_rows.cu``) that reads each score row once.  ``second_order`` is also stated in plain PyTorch
+On the GPU the score stage (the four score-shaped products, the row sums, the four bf16 operand matrices
+``P, scale dS, gdP, scale gS``) is one tcgen05 kernel that keeps the scores in tensor memory
+(``csrc/attn_bwd2_tcgen05.cu``; head dimension 64, chunk a multiple of 128, keys a multiple of 64); other shapes
+form the score products with the tensor-core GEMM in f32 and run ``csrc/attn_bwd2_rows.cu`` over them.  The seven
+output products run on the tcgen05 GEMM, batched over (sequence, KV head) with the query heads of a group folded
+into the rows.  ``second_order`` is also stated in plain PyTorch
 (f32) for CPU tensors; the tests compare both against autograd differentiating the reference statement twice.
 """
 from __future__ import annotations
@@ -26,6 +29,10 @@ from typing import Optional, Sequence, Tuple
 
 import torch
 from torch.autograd.function import once_differentiable
+
+
+# the score stage runs on the tcgen05 kernel where its shape limits hold (False: f32 score GEMMs + the row kernel)
+FUSED_SCORES = True
 
 
 def _rows(t: torch.Tensor, nkv: int) -> torch.Tensor:
@@ -89,7 +96,8 @@ def second_order(gQ: Optional[torch.Tensor], gK: Optional[torch.Tensor], gV: Opt
     gQ = torch.zeros_like(q) if gQ is None else gQ
     gK = torch.zeros_like(K) if gK is None else gK
     gV = torch.zeros_like(V) if gV is None else gV
-    delta = (dO.float() * o.float()).sum(-1).permute(0, 2, 1).reshape(n * nkv, G * C).contiguous()
+    delta_h = (dO.float() * o.float()).sum(-1).permute(0, 2, 1).contiguous()                  # [n, nh, C]
+    delta = delta_h.reshape(n * nkv, G * C)
     lse_r = lse.reshape(n * nkv, G * C).contiguous().float()
     if q.is_cuda:
         from . import kernels
@@ -98,12 +106,17 @@ def second_order(gQ: Optional[torch.Tensor], gK: Optional[torch.Tensor], gV: Opt
         qg, dOg, gQg = (_rows(t.to(bf), nkv).contiguous() for t in (q, dO, gQ))
         kg, vg, gKg, gVg = (_keys(t.to(bf)).contiguous() for t in (K, V, gK, gV))
         f32 = torch.float32
-        S = gemm_raw(qg, kg, False, True, f32)
-        dP = gemm_raw(dOg, vg, False, True, f32)
-        gdS = gemm_raw(torch.cat([gQg, qg], -1), torch.cat([kg, gKg], -1), False, True, f32)
-        X = gemm_raw(dOg, gVg, False, True, f32)
-        P, dS, gdP, gS = kernels.attention_bwd2_rows(S, dP, gdS, X, lse_r, delta, C, causal, scale)
-        del S, dP, gdS, X
+        if FUSED_SCORES and kernels.available("attention_bwd2_scores") and kernels.attention_bwd2_scores_supported(q, K):
+            # scores in tensor memory, never in global memory
+            P, dS, gdP, gS = kernels.attention_bwd2_scores(q, dO.to(bf), gQ.to(bf), K, V.to(bf), gK.to(bf), gV.to(bf),
+                                                           lse.float(), delta_h, scale, causal)
+        else:
+            S = gemm_raw(qg, kg, False, True, f32)
+            dP = gemm_raw(dOg, vg, False, True, f32)
+            gdS = gemm_raw(torch.cat([gQg, qg], -1), torch.cat([kg, gKg], -1), False, True, f32)
+            X = gemm_raw(dOg, gVg, False, True, f32)
+            P, dS, gdP, gS = kernels.attention_bwd2_rows(S, dP, gdS, X, lse_r, delta, C, causal, scale)
+            del S, dP, gdS, X
         g_dO = gemm_raw(P, gVg, False, False, f32)
         gemm_raw(gdP, vg, False, False, f32, out=g_dO, accumulate=True)
         g_V = gemm_raw(gdP, dOg, True, False)

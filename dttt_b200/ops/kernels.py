@@ -400,6 +400,31 @@ def attention_bwd2_rows(S, dP, gdS, X, lse, delta, chunk, causal, scale):
     return outs
 
 
+_lib.register("dttt_attn_bwd2_scores", _i, [_vp] * 13 + [_i, _i, _i, _i, _i, _f, _i, _vp, _vp])
+_SYMBOL.update(attention_bwd2_scores="dttt_attn_bwd2_scores")
+
+
+def attention_bwd2_scores_supported(q, K) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 64 and q.shape[1] % 128 == 0 and K.shape[1] % 64 == 0
+            and q.shape[2] % K.shape[2] == 0)
+
+
+def attention_bwd2_scores(q, dO, gQ, K, V, gK, gV, lse, delta, scale, causal):
+    """Score stage of the derivative of the attention backward on the tcgen05 kernel (``csrc/attn_bwd2_tcgen05.cu``):
+    ``q, dO, gQ [n, C, nh, 64]``, ``K, V, gK, gV [n, Kn, nkv, 64]`` bf16, ``lse, delta [n, nh, C]`` f32 ->
+    bf16 ``P, scale dS, gdP, scale gS`` as ``[n * nkv, G * C, Kn]`` (head ``h = kv * G + g``, row ``g * C + c``)."""
+    n, C, nh, d = q.shape
+    Kn, nkv = K.shape[1], K.shape[2]
+    ins = [t.contiguous() for t in (q, dO, gQ, K, V, gK, gV)]
+    lse, delta = lse.contiguous(), delta.contiguous()
+    assert lse.dtype == torch.float32 and delta.dtype == torch.float32 and all(t.dtype == torch.bfloat16 for t in ins)
+    outs = [torch.empty(n * nkv, (nh // nkv) * C, Kn, dtype=torch.bfloat16, device=q.device) for _ in range(4)]
+    st = _lib.status_tensor(q.device)
+    _check(_lib.lib().dttt_attn_bwd2_scores(*[_p(t) for t in ins], _p(lse), _p(delta), *[_p(t) for t in outs], n, C, Kn, nh, nkv,
+                                            float(scale), 1 if causal else 0, _p(st), _stream()), "attn_bwd2_scores")
+    return outs
+
+
 # =============================================================================== embedding / objective family
 _lib.register("dttt_embed_gather", _i, [_vp, _vp, _vp, _ll, _i, _vp])
 _lib.register("dttt_embed_scatter_f32", _i, [_vp, _vp, _vp, _ll, _i, _vp])

@@ -180,6 +180,13 @@ def bench_attn2(a, out):
             out({"kernel": "attn_second_order product: " + name, "batch": B, "rows": R, "Kn": Kn, "ms": t, "gbs": nb / t / 1e6,
                  "frac_of_copy_bw": nb / (t * 1e-3) / hbm, "peaks": src})
         del Pm
+    if kernels.available("attention_bwd2_scores") and kernels.attention_bwd2_scores_supported(q, k):
+        dl = torch.zeros(n, nh, Cq, device="cuda")
+        ms = timeit(lambda: kernels.attention_bwd2_scores(q, g, cq, k, v, ck, cv, lse, dl, scale, a.causal), a.iters, a.once)
+        fl5 = 2.0 * n * nh * d * Cq * Kn * 5 * 2                          # five products, two sweeps
+        out({"kernel": "attn_bwd2_scores_tcgen05", "seqs": n, "Cq": Cq, "Kn": Kn, "heads": nh, "causal": a.causal, "ms": ms,
+             "tflops": fl5 / ms / 1e9, "write_gbs": rows * Kn * 8.0 / ms / 1e6, "frac_of_copy_bw": rows * Kn * 8.0 / (ms * 1e-3) / hbm,
+             "note": "replaces the four f32 score products and the row kernel; 8 bytes written per score", "peaks": src})
     ms2 = timeit(lambda: attn_second.second_order(cq, ck, cv, g, q, k, v, o, lse, scale, a.causal), a.iters, a.once)
     pairs = Cq * Kn
     fl = 2.0 * n * nh * d * pairs * 12                                   # 5 score-shaped + 7 output products, dense

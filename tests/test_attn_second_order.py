@@ -104,9 +104,41 @@ def test_row_kernel_matches_the_row_statement(rows, Kn, C, causal):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("n,C,Kn,nh,nkv,causal", [(1, 128, 384, 4, 2, True), (2, 256, 256, 8, 2, True), (1, 128, 640, 4, 1, False), (1, 256, 1088, 2, 1, True)])
+def test_score_kernel_matches_the_row_statement(n, C, Kn, nh, nkv, causal):
+    """The tcgen05 score stage against the f64 row statement applied to f64 score products."""
+    from dttt_b200.ops import _lib, kernels
+    assert kernels.available("attention_bwd2_scores"), "the second-order score kernel is not in the loaded library"
+    d = 64
+    dev = torch.device("cuda", 0)
+    scale = 1.0 / math.sqrt(d)
+    q, K, V, dO, cots = _case(n, C, Kn, nh, nkv, d, causal, dtype=torch.float32, seed=5)
+    bf = lambda t: t.to(dev).to(torch.bfloat16)
+    q, K, V, dO = bf(q), bf(K), bf(V), bf(dO)
+    gQ, gK, gV = (bf(c) for c in cots)
+    up = lambda t: t.double().cpu()
+    o, lse = _statement(up(q), up(K), up(V), scale, causal)
+    delta = (up(dO) * o).sum(-1).permute(0, 2, 1).contiguous()                        # [n, nh, C]
+    got = kernels.attention_bwd2_scores(q, dO, gQ, K, V, gK, gV, lse.float().to(dev), delta.float().to(dev), scale, causal)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    T = lambda t: t.transpose(-1, -2)
+    qg, dOg, gQg = (attn_second._rows(up(t), nkv) for t in (q, dO, gQ))
+    kg, vg, gKg, gVg = (attn_second._keys(up(t)) for t in (K, V, gK, gV))
+    G = nh // nkv
+    want = attn_second._rows_torch(qg @ T(kg), dOg @ T(vg), gQg @ T(kg) + qg @ T(gKg), dOg @ T(gVg), lse.reshape(n * nkv, G * C),
+                                   delta.reshape(n * nkv, G * C), C, causal, scale)
+    for name, w, gt in zip(("P", "dS", "gdP", "gS"), want, got):
+        assert gt.shape == w.shape, name
+        assert _rel(gt, w) < 6e-3, (name, _rel(gt, w))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("n,C,Kn,nh,nkv,causal", [(1, 128, 384, 4, 2, True), (2, 256, 256, 8, 2, True), (1, 128, 640, 4, 1, False)])
-def test_second_order_on_the_gpu_matches_f64_autograd(n, C, Kn, nh, nkv, causal):
+def test_second_order_on_the_gpu_matches_f64_autograd(n, C, Kn, nh, nkv, causal, fused, monkeypatch):
     from dttt_b200.ops import _lib
+    monkeypatch.setattr(attn_second, "FUSED_SCORES", fused)
     d = 64
     dev = torch.device("cuda", 0)
     scale = 1.0 / math.sqrt(d)
