@@ -130,7 +130,87 @@ def _ce_bwd(g, tensors, saved, needs, block, target=None):
     return (g_h.to(h.dtype) if need_h else None, g_E.to(E.dtype) if g_E is not None else None, None, None)
 
 
-_SPEC = (_ce_fwd, _ce_bwd, _ce_ref)
+# ---- the backward as a differentiable operation (recorded inner pass)
+SECOND_ORDER_KERNEL = True
+
+
+def second_order(c, g, h, E, targets, weights, logZ):
+    """Derivative of ``g_h = g w (p E - E_y)`` (the cross-entropy backward w.r.t. ``h``) contracted with the cotangent
+    ``c [N, H]``: returns ``(grad g, grad h [N, H] f32, r, d, grad w)`` where E's gradient is ``r^T h + d^T c``
+    (left to the caller, who may accumulate it in place).  With ``u = c E^T`` and ``ubar = rowsum(p o u)``:
+    ``r = gw p o (u - ubar)``, ``d = gw (p - onehot)``, ``grad h = r E``, ``grad g = sum_i w_i (ubar_i - u_iy)``."""
+    gw = g.float() * weights.float()
+    tl = targets.long()
+    if h.is_cuda:
+        from . import kernels
+        Eb = E if E.dtype == torch.bfloat16 else E.to(torch.bfloat16)
+        hb, cb = h.to(torch.bfloat16), c.to(torch.bfloat16)
+        z = _gemm.gemm_raw(hb, Eb, False, True, torch.float32)
+        u = _gemm.gemm_raw(cb, Eb, False, True, torch.float32)
+        ubar = kernels.ce_bwd2_rowdot(z, u, logZ)
+        r, d = kernels.ce_bwd2_make(z, u, logZ, ubar, gw, targets)
+        del z, u
+        g_h = _gemm.gemm_raw(r, Eb, False, False, torch.float32)
+    else:
+        z = h.float() @ E.float().t()
+        u = c.float() @ E.float().t()
+        p = torch.exp(z - logZ[:, None])
+        ubar = (p * u).sum(-1)
+        r = gw[:, None] * p * (u - ubar[:, None])
+        d = gw[:, None] * p
+        d[torch.arange(d.shape[0]), tl] -= gw
+        g_h = r @ E.float()
+    u_y = (c.float() * E[tl].float()).sum(-1)
+    diff = ubar - u_y
+    return (weights.float() * diff).sum(), g_h, r, d, g.float() * diff
+
+
+class _CEBwd(torch.autograd.Function):
+    """``(g, h, E, targets, weights, logZ) -> g_h`` by the streaming first-order backward; differentiable once more by
+    ``second_order``.  ``logZ`` is a cache of the forward, not an independent input."""
+
+    @staticmethod
+    def forward(ctx, g, h, E, targets, weights, logZ, block, target):
+        ctx.save_for_backward(g, h, E, targets, weights, logZ)
+        ctx.target = target
+        return _ce_bwd(g, (h, E, targets, weights), (logZ,), (True, False, False, False), block, target)[0]
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, c):
+        g, h, E, targets, weights, logZ = ctx.saved_tensors
+        g_g, g_h, r, d, g_w = second_order(c, g, h, E, targets, weights, logZ)
+        g_E = None
+        if ctx.needs_input_grad[2]:
+            if h.is_cuda:
+                hb, cb = h.to(torch.bfloat16), c.to(torch.bfloat16)
+                if ctx.target is not None:
+                    gfull, layer = ctx.target
+                    gbuf = gfull if layer is None else gfull[layer]
+                    _gemm.gemm_raw(r, hb, True, False, torch.float32, out=gbuf, accumulate=True)
+                    _gemm.gemm_raw(d, cb, True, False, torch.float32, out=gbuf, accumulate=True)
+                else:
+                    acc = _gemm.gemm_raw(r, hb, True, False, torch.float32)
+                    _gemm.gemm_raw(d, cb, True, False, torch.float32, out=acc, accumulate=True)
+                    g_E = acc.to(E.dtype)
+            else:
+                g_E = (r.t() @ h.float() + d.t() @ c.float()).to(E.dtype)
+        return (g_g if ctx.needs_input_grad[0] else None, g_h.to(h.dtype) if ctx.needs_input_grad[1] else None, g_E, None,
+                g_w.to(weights.dtype) if ctx.needs_input_grad[4] else None, None, None, None)
+
+
+def _ce_diff_bwd(g, tensors, saved, needs, block, target=None):
+    """The recorded backward of the inner loss (only ``h``'s gradient is wanted there), or ``None`` to decline."""
+    h, E, targets, weights = tensors
+    if not SECOND_ORDER_KERNEL or not needs[0] or (needs[1] and not _INNER_BACKWARD[0]) or not _fused(h, E) or E.shape[0] % 4:
+        return None
+    from . import kernels
+    if not kernels.available("linear_ce_bwd2"):
+        return None
+    return (_CEBwd.apply(g, h, E, targets, weights, saved[0], block, target), None, None, None)
+
+
+_SPEC = (_ce_fwd, _ce_bwd, _ce_ref, _ce_diff_bwd)
 
 
 def weighted_ce(h: torch.Tensor, E: torch.Tensor, targets: torch.Tensor, weights: torch.Tensor, block: int = 8192) -> torch.Tensor:

@@ -425,6 +425,32 @@ def attention_bwd2_scores(q, dO, gQ, K, V, gK, gV, lse, delta, scale, causal):
     return outs
 
 
+# =============================================================================== second-order linear + cross-entropy (row kernels)
+_lib.register("dttt_ce_bwd2_rowdot", _i, [_vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
+_lib.register("dttt_ce_bwd2_make", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _ll, _vp])
+_SYMBOL.update(linear_ce_bwd2="dttt_ce_bwd2_rowdot")
+
+
+def ce_bwd2_rowdot(z, u, lse):
+    """``ubar[i] = sum_v exp(z[i, v] - lse[i]) u[i, v]`` for f32 ``z, u [N, W]`` (``W`` a multiple of 4)."""
+    N, W = z.shape
+    assert z.dtype == torch.float32 and u.dtype == torch.float32 and z.stride() == u.stride() and z.stride(1) == 1
+    out = torch.empty(N, dtype=torch.float32, device=z.device)
+    _check(_lib.lib().dttt_ce_bwd2_rowdot(_p(z), _p(u), _p(lse.contiguous()), _p(out), N, W, z.stride(0), _stream()), "ce_bwd2_rowdot")
+    return out
+
+
+def ce_bwd2_make(z, u, lse, ubar, gw, targets):
+    """``r = gw p (u - ubar)``, ``d = gw (p - onehot(targets))`` with ``p = exp(z - lse)``: bf16 ``[N, W]`` each."""
+    N, W = z.shape
+    r = torch.empty(N, W, dtype=torch.bfloat16, device=z.device)
+    d = torch.empty(N, W, dtype=torch.bfloat16, device=z.device)
+    assert z.is_contiguous() and u.is_contiguous()
+    _check(_lib.lib().dttt_ce_bwd2_make(_p(z), _p(u), _p(lse.contiguous()), _p(ubar), _p(gw.contiguous()), _p(targets.to(torch.int32).contiguous()),
+                                        _p(r), _p(d), N, W, W, _stream()), "ce_bwd2_make")
+    return r, d
+
+
 # =============================================================================== embedding / objective family
 _lib.register("dttt_embed_gather", _i, [_vp, _vp, _vp, _ll, _i, _vp])
 _lib.register("dttt_embed_scatter_f32", _i, [_vp, _vp, _vp, _ll, _i, _vp])
