@@ -119,7 +119,68 @@ def _rms_bwd(g, tensors, saved, needs, eps):
     return dx, (dw.to(w.dtype) if dw is not None else None)
 
 
-_RMS_SPEC = (_rms_fwd, _rms_bwd, _ref.rms_norm)
+# ---- the RMSNorm backward as a differentiable operation (recorded passes)
+_lib.register("dttt_rmsnorm_bwd2", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
+_lib.register("dttt_swiglu_bwd2", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp])
+_SYMBOL.update(elementwise_bwd2="dttt_rmsnorm_bwd2")
+SECOND_ORDER_ELEMENTWISE = True
+
+
+def rms_norm_bwd2(c, e, g, x, w, rstd):
+    """Derivative of the RMSNorm backward ``(g, x, w) -> (dx, dw)`` contracted with the cotangents ``c`` (of ``dx``) and ``e``
+    (of ``dw``, may be ``None``): ``(grad g, grad x, grad w)``."""
+    D = x.shape[-1]
+    rows = x.numel() // D
+    wf = w.detach().float().contiguous()
+    if not x.is_cuda:
+        x32, g32, c32, r = x.float().reshape(rows, D), g.float().reshape(rows, D), c.float().reshape(rows, D), rstd.reshape(rows, 1)
+        xh, u = x32 * r, wf * g32
+        al, be, ga = (c32 * xh).mean(-1, keepdim=True), (u * xh).mean(-1, keepdim=True), (c32 * u).mean(-1, keepdim=True)
+        t = r * (c32 - xh * al)
+        gg = wf * t
+        gx = r * r * ((3 * al * be - ga) * xh - be * c32 - al * u)
+        if e is not None:
+            v = e.float() * g32
+            gg = gg + e.float() * xh
+            gx = gx + r * (v - xh * (v * xh).mean(-1, keepdim=True))
+        return gg.to(g.dtype).view(g.shape), gx.to(x.dtype).view(x.shape), (g32 * t).sum(0).to(w.dtype)
+    xc, gc, cc = x.contiguous(), g.contiguous(), c.contiguous()
+    gg, gx = torch.empty_like(gc), torch.empty_like(xc)
+    gwt = torch.zeros(D, dtype=torch.float32, device=x.device)
+    ef = None if e is None else e.detach().float().contiguous()
+    _check(_lib.lib().dttt_rmsnorm_bwd2(_p(xc), _p(wf), _p(gc), _p(rstd), _p(cc), _p(ef), _p(gg), _p(gx), _p(gwt), rows, D, _stream()),
+           "rmsnorm_bwd2")
+    return gg, gx, gwt.to(w.dtype)
+
+
+class _RmsBwd(torch.autograd.Function):
+    """``(g, x, w, rstd) -> (dx, dw)`` on the backward kernel; differentiable once more by ``rms_norm_bwd2``.  ``rstd`` is a
+    cache of the forward, not an independent input."""
+
+    @staticmethod
+    def forward(ctx, g, x, w, rstd, eps):
+        ctx.save_for_backward(g, x, w, rstd)
+        dx, dw = _rms_bwd(g, (x, w), (rstd,), (True, True), eps)
+        return dx, dw
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, c, e):
+        g, x, w, rstd = ctx.saved_tensors
+        if c is None:
+            c = torch.zeros_like(x)
+        gg, gx, gw = rms_norm_bwd2(c.to(x.dtype), e, g.to(x.dtype), x, w, rstd)
+        return gg.to(g.dtype), gx, gw, None, None
+
+
+def _rms_diff_bwd(g, tensors, saved, needs, eps):
+    x, w = tensors
+    if not SECOND_ORDER_ELEMENTWISE or x.dtype != torch.bfloat16 or (x.is_cuda and not available("elementwise_bwd2")):
+        return None
+    return _RmsBwd.apply(g, x, w, saved[0], eps)
+
+
+_RMS_SPEC = (_rms_fwd, _rms_bwd, _ref.rms_norm, _rms_diff_bwd)
 
 
 def rms_norm(x, w, eps):
@@ -190,7 +251,47 @@ def _swiglu_bwd(dy, tensors, saved, needs):
     return dg, du
 
 
-_SWIGLU_SPEC = (_swiglu_fwd, _swiglu_bwd, lambda g, u: _ref.glu(g, u, "silu"))
+def swiglu_bwd2(cg, cu, dy, g, u):
+    """Derivative of the SwiGLU backward ``(dy, g, u) -> (dg, du)`` contracted with ``(cg, cu)``: ``(grad dy, grad g, grad u)``."""
+    if not g.is_cuda:
+        g32, u32, d32, a, b = g.float(), u.float(), dy.float(), cg.float(), cu.float()
+        s = torch.sigmoid(g32)
+        silu = g32 * s
+        s1 = s * (1 + g32 * (1 - s))
+        s2 = s * (1 - s) * (2 + g32 * (1 - 2 * s))
+        return ((a * u32 * s1 + b * silu).to(dy.dtype), (d32 * (a * u32 * s2 + b * s1)).to(g.dtype), (a * d32 * s1).to(u.dtype))
+    gc, uc, dc, ac, bc = (t.contiguous() for t in (g, u, dy, cg, cu))
+    og, ou, od = torch.empty_like(gc), torch.empty_like(uc), torch.empty_like(dc)
+    _check(_lib.lib().dttt_swiglu_bwd2(_p(gc), _p(uc), _p(dc), _p(ac), _p(bc), _p(og), _p(ou), _p(od), gc.numel(), _stream()), "swiglu_bwd2")
+    return od, og, ou
+
+
+class _SwigluBwd(torch.autograd.Function):
+    """``(dy, g, u) -> (dg, du)`` on the backward kernel; differentiable once more by ``swiglu_bwd2``."""
+
+    @staticmethod
+    def forward(ctx, dy, g, u):
+        ctx.save_for_backward(dy, g, u)
+        return _swiglu_bwd(dy, (g, u), (), (True, True))
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, cg, cu):
+        dy, g, u = ctx.saved_tensors
+        cg = torch.zeros_like(g) if cg is None else cg.to(g.dtype)
+        cu = torch.zeros_like(u) if cu is None else cu.to(u.dtype)
+        return swiglu_bwd2(cg, cu, dy.to(g.dtype), g, u)
+
+
+def _swiglu_diff_bwd(dy, tensors, saved, needs):
+    g, u = tensors
+    if (not SECOND_ORDER_ELEMENTWISE or g.dtype != torch.bfloat16 or u.dtype != torch.bfloat16 or dy.dtype != torch.bfloat16
+            or (g.is_cuda and not available("elementwise_bwd2"))):
+        return None
+    return _SwigluBwd.apply(dy, g, u)
+
+
+_SWIGLU_SPEC = (_swiglu_fwd, _swiglu_bwd, lambda g, u: _ref.glu(g, u, "silu"), _swiglu_diff_bwd)
 
 
 def swiglu(g, u):
