@@ -214,9 +214,20 @@ def _rope_ref(x, pos, inv_freq):
     return _ref.apply_rope(x, emb.cos(), emb.sin())
 
 
-_ROPE_SPEC = (lambda x, pos, inv: (_rope_run(x, pos, inv, 1.0), ()),
-              lambda g, tensors, saved, needs, pos, inv: (_rope_run(g, pos, inv, -1.0),),
-              _rope_ref)
+class _Rope(torch.autograd.Function):
+    """The rotation is linear in ``x`` and its transpose is the rotation by the opposite angle, so the backward is the same
+    operation with the sign flipped: differentiable to any order on the kernel."""
+
+    @staticmethod
+    def forward(ctx, x, pos, inv_freq, sign):
+        ctx.pos, ctx.inv, ctx.sign = pos, inv_freq, sign
+        return _rope_run(x, pos, inv_freq, sign)
+
+    @staticmethod
+    def backward(ctx, g):
+        if torch.is_grad_enabled():
+            return _Rope.apply(g, ctx.pos, ctx.inv, -ctx.sign), None, None, None
+        return _rope_run(g, ctx.pos, ctx.inv, -ctx.sign), None, None, None
 
 
 def rope(x, pos, inv_freq):
@@ -225,7 +236,7 @@ def rope(x, pos, inv_freq):
     if x.shape[-1] % 16:
         return _rope_ref(x, pos, inv_freq)
     if torch.is_grad_enabled() and x.requires_grad:
-        return staged(_ROPE_SPEC, (x,), (pos, inv_freq))
+        return _Rope.apply(x, pos, inv_freq, 1.0)
     return _rope_run(x, pos, inv_freq, 1.0)
 
 

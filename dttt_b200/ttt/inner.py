@@ -122,13 +122,13 @@ def inner_objective(W: FastW, model, h_inner: torch.Tensor, tokens: torch.Tensor
                     feat_mode: str = "off", feat_weight: float = 1.0, extras: Optional[InnerExtras] = None,
                     distill_weight: float = 1.0, mtp_weight: float = 1.0, soft_only: bool = False,
                     surprise_gamma: float = 0.0, kvb_weight: float = 0.0, kvb_src=None, score_from: int = 0,
-                    own_mask=None):
+                    own_mask=None, W_cast: Optional[FastW] = None):
     """Sum over sequences of the per-sequence inner objective, and its terms ``[5]`` (batch-summed
     ``ce, feat, distill, mtp, kvb``).  ``h_inner [B, C, H]`` (or ``[B, V, C, H]`` for V views, averaged),
     ``tokens / inner_mask [B, C]`` (``[B, V, C]``).  Each term is a weighted mean over its own slots of
     one sequence; see the reference docstring (inner_loop.py:201-230) for the terms."""
     net = model
-    Wc = cast_fast(W, net.dtype)
+    Wc = W_cast if W_cast is not None else cast_fast(W, net.dtype)       # ``W_cast``: the compute-dtype copies, made by the caller
     lm_w = net.lm_weight()
     has_temp = net.cw.has("inner_temp_log")
 
@@ -313,6 +313,11 @@ def inner_grad(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid, f
     extras = kw.get("extras")
     soft_first_order = extras is not None and extras.soft_ids is not None and not distill_meta
     Wl = flat(W)
+    kw = dict(kw)
+    W_cast = kw.pop("W_cast", None)
+    # The objective sees W only through its compute-dtype copy, so the gradient is taken w.r.t. that copy (same values as
+    # the gradient w.r.t. W, without the cast's backward and, under the meta-gradient, that backward's derivative).
+    via_cast = (GRAD_VIA_CAST[0] and Wl[0].dtype != model.dtype and not soft_first_order and not kw.get("kvb_weight", 0.0))
     if not create_graph:
         # a first-order write: nothing outside this call may see the graph built here
         h_inner = h_inner.detach()
@@ -327,10 +332,19 @@ def inner_grad(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid, f
         kw2 = dict(kw)
         if soft_first_order:
             kw2["distill_weight"] = 0.0
+        wrt = Wl
+        if via_cast:
+            if not create_graph:
+                src = flat(W_cast) if W_cast is not None else flat(cast_fast(unflat(Wl), model.dtype))
+                wrt = [c.detach().requires_grad_(True) for c in src]
+            else:
+                wrt = flat(W_cast) if W_cast is not None and all(c.requires_grad for c in flat(W_cast)) \
+                    else flat(cast_fast(unflat(Wl), model.dtype))
+            kw2["W_cast"] = unflat(wrt)
         obj, terms = inner_objective(unflat(Wl), model, h_inner, tokens, inner_mask, kv, pos, n_valid, fused_block,
                                      tok_w=tok_w, **kw2)
         with Fn.inner_backward():
-            g = torch.autograd.grad(obj, Wl, create_graph=create_graph)
+            g = torch.autograd.grad(obj, wrt, create_graph=create_graph)
         if soft_first_order:
             Wd = [w.detach().requires_grad_(True) for w in Wl]
             obj2, terms2 = inner_objective(unflat(Wd), model, h_inner, tokens, inner_mask, kv, pos, n_valid, fused_block,
@@ -344,6 +358,9 @@ def inner_grad(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid, f
         g = [x.detach() for x in g]
     return list(g), terms
 
+
+# The inner gradient is taken w.r.t. the compute-dtype copies of the fast weights (False: w.r.t. the f32 weights themselves).
+GRAD_VIA_CAST = [True]
 
 # The plain step as one autograd node with fused kernels (False: the chain of differentiable torch ops; "force": also
 # for CPU tensors, where the node's pieces are torch statements -- used by the tests).
@@ -411,7 +428,6 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
     """The step of gradient ``g``: ``(W', pre-clip norm [B])`` (reference inner_loop.py:435-481)."""
     net = model
     Wl = flat(W)
-    g = [x.float() for x in g]
     plain = (rule == "sgd" and unit_mask is None and frac >= 1.0 and scale is None
              and not net.cw.has("inner_precond.0.gate.weight") and not net.cw.has("inner_gate.weight")
              and not net.cw.has("inner_decay_logit"))
@@ -421,8 +437,9 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
         if net.cw.has("inner_step_log"):
             eta = eta * torch.exp(net.p("inner_step_log").float())
         if FUSED_PLAIN_STEP[0] and (Wl[0].is_cuda or FUSED_PLAIN_STEP[0] == "force"):
-            out = _PlainStep.apply(float(clip), eta, len(Wl), *Wl, *g)
+            out = _PlainStep.apply(float(clip), eta, len(Wl), *Wl, *g)           # the kernels read bf16 or f32 gradients
             return unflat(list(out[:-1])), out[-1]
+        g = [x.float() for x in g]
         norm = seq_norm(g)
         s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
         B = Wl[0].shape[0]
@@ -433,6 +450,7 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
                 p, d = Wl[3 * f + j], g[3 * f + j]
                 new.append(torch.addcmul(p, coef[:, f].view(B, 1, 1), d, value=-1.0))
         return unflat(new), norm
+    g = [x.float() for x in g]
     if unit_mask is not None:
         g = mask_units(g, unit_mask)
     u = direction(g, rule)
@@ -527,14 +545,15 @@ def fast_unit_mask(inter: int, frac: float, device=None) -> torch.Tensor:
 
 def write_chunk(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid: int, lr: float, clip: float,
                 fused_block: int, rule: str, h_clean, pos_q, own: str, wc: WriteConfig, *, create_graph: bool,
-                W0: Optional[FastW] = None, kvb_src=None):
+                W0: Optional[FastW] = None, kvb_src=None, W_cast: Optional[FastW] = None):
     """The causal write of one chunk under ``wc`` (reference inner_loop.py:588-719); a plain ``wc`` is one
-    ``inner_update``.  Shared by training and decoding."""
+    ``inner_update``.  Shared by training and decoding.  ``W_cast``: the caller's compute-dtype copies of ``W``
+    (differentiable functions of it), reused by the plain write instead of casting again."""
     net = model
     base = dict(rule=rule, h_clean=h_clean, own=own, create_graph=create_graph)
     if wc.plain:
         return inner_update(W, net, h_inner, tokens, inner_mask, kv, pos, n_valid, lr, clip, fused_block,
-                            pos_q=pos_q, **base)
+                            pos_q=pos_q, W_cast=W_cast, **base)
     if net.cw.has("inner_gate.weight") or net.cw.has("inner_decay_logit"):
         raise ValueError("the write schemes are defined for the plain step: no write gate / learned decay")
     ks_all = kvb_src if wc.kvb_weight > 0 else None

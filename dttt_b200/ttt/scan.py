@@ -723,7 +723,8 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
                                        pos_q=None if cfg.inner_task == "mask" else k["p_q"], own=own_inner,
                                        feat_tgt=feat_tgt, feat_mode=cfg.inner_feat, feat_weight=cfg.inner_feat_weight,
                                        frac=cfg.inner_update_frac, extras=extras, distill_weight=distill_w,
-                                       mtp_weight=cfg.inner_mtp_weight, distill_meta=cfg.distill_meta)
+                                       mtp_weight=cfg.inner_mtp_weight, distill_meta=cfg.distill_meta,
+                                       W_cast=Wc if w is W else None)
             if cfg.write_plan:
                 k_c = k["k_c"]
                 W1, st = plain_step(W)

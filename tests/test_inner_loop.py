@@ -111,3 +111,25 @@ def test_fused_plain_step_node_matches_autograd(clip):
     assert abs(L_r.item() - L_f.item()) < 1e-4
     for a, b in zip(gr, gf):
         assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+
+
+def test_inner_gradient_taken_through_the_compute_dtype_copies_is_the_same_gradient():
+    """bf16 compute, f32 fast weights: differentiating the inner loss w.r.t. the bf16 copies (the default) and w.r.t. the f32
+    weights gives the same write and the same meta-gradient (the cast's backward only changes the dtype)."""
+    from util import loss_and_grads, tiny_train
+    from dttt_b200.ttt import inner
+    ids = torch.randint(0, 120, (2, 32), generator=torch.Generator().manual_seed(3))
+    res = {}
+    for flag in (True, False):
+        inner.GRAD_VIA_CAST[0] = flag
+        try:
+            eng = make_engine(tc=tiny_train(compute_dtype="bfloat16"))
+            res[flag] = loss_and_grads(eng, ids, loss_config(eng.tc))
+        finally:
+            inner.GRAD_VIA_CAST[0] = True
+    assert abs(res[True][0] - res[False][0]) < 1e-6
+    for k in res[True][1]:
+        a, b = res[True][1][k], res[False][1][k]
+        # bf16 rounding noise only: the shared copy sums its three uses' gradients in bf16 before the cast back
+        assert (a - b).abs().max().item() <= 5e-2 * (b.abs().max().item() + 1e-8), k
+        assert (a - b).norm().item() <= 2e-2 * (b.norm().item() + 1e-8), k

@@ -100,6 +100,12 @@ def test_rope(d, heads):
     yr = ref.apply_rope(x32, cos, sin)
     (dxr,) = torch.autograd.grad(yr, x32, g.float())
     assert _rel(y, yr) < 1e-2 and _rel(dx, dxr) < 1e-2
+    # the backward is itself differentiable (the rotation by the opposite angle): d<c, dx(g)>/dg = rope(c)
+    g2 = g.clone().requires_grad_(True)
+    (dx2,) = torch.autograd.grad(y, x, g2, create_graph=True)
+    c = torch.randn_like(dx2)
+    (gg,) = torch.autograd.grad(dx2, g2, c)
+    assert _rel(gg, ref.apply_rope(c.float(), cos, sin)) < 1e-2
 
 
 def test_swiglu():
