@@ -113,6 +113,8 @@ def main() -> int:
     ap.add_argument("--fsdp", type=int, default=0)
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--keep-prefix-layers", type=int, default=-1, help="prefix layers whose activations stay resident (-1: the config's)")
+    ap.add_argument("--keep-suffix-chunks", type=int, default=-1, help="chunk steps per segment whose graph stays resident (-1: the config's)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -144,7 +146,9 @@ def main() -> int:
     T = spec["seq_len"]
     tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
                      seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
-                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **spec["extra"])
+                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp,
+                     **dict(spec["extra"], **({"keep_prefix_layers": args.keep_prefix_layers} if args.keep_prefix_layers >= 0 else {}),
+                            **({"keep_suffix_chunks": args.keep_suffix_chunks} if args.keep_suffix_chunks >= 0 else {})))
     eng = Engine(mc, tc, mesh, dev)
 
     # synthetic data: distinct tokens for every step, on pinned host memory
@@ -197,7 +201,7 @@ def main() -> int:
         "config": {"model": f"1B TTT ({args.config}): " + spec["model"], "global_batch": per_gpu * mesh.batch_ranks, "seq_len": T,
                    "parallelism": f"dp{mesh.dp}xfsdp{mesh.fsdp}xtp{mesh.tp}", "micro_batch_per_gpu": micro, "grad_accum": accum,
                    "l2": "per-step working set (3 GB bf16 weights + activations) >> 126 MB L2; no explicit flush",
-                   "params": eng.n_params},
+                   "params": eng.n_params, "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
         "clocks": ck, "gpu_launches": launches, "final_loss": last.get("main_loss") if last else None,
     }
     if ms_e2e is not None:

@@ -49,7 +49,8 @@ def loss_config(cfg: TrainConfig) -> LossConfig:
         outer_t=cfg.outer_t, outer_shift=cfg.outer_shift, inner_lr=cfg.inner_lr, inner_clip=cfg.inner_clip,
         inner_lr_warmup_steps=cfg.inner_lr_warmup_steps, inner_mask_range=tuple(cfg.inner_mask_range),
         inner_mask_ratio=cfg.inner_mask_ratio, second_order=cfg.second_order, remat_levels=cfg.remat_levels,
-        remat_prefix=cfg.remat_prefix, prefix_remat_levels=cfg.prefix_remat_levels, segment_chunks=cfg.segment_chunks,
+        remat_prefix=cfg.remat_prefix, prefix_remat_levels=cfg.prefix_remat_levels, keep_prefix_layers=cfg.keep_prefix_layers, keep_suffix_chunks=cfg.keep_suffix_chunks,
+        segment_chunks=cfg.segment_chunks,
         truncate_fast_weight=cfg.truncate_fast_weight, inner_views=cfg.inner_views, inner_view_mode=cfg.inner_view_mode,
         inner_views_sequential=cfg.inner_views_sequential, inner_cart=cfg.inner_cart, inner_mask_span=cfg.inner_mask_span,
         inner_update=cfg.inner_update, no_write=cfg.no_write, inner_task=cfg.inner_task,

@@ -66,6 +66,8 @@ class LossConfig:
     remat_levels: int = 1
     remat_prefix: bool = False
     prefix_remat_levels: int = 1
+    keep_prefix_layers: int = 0           # the first k prefix layers are not recompute regions: their activations stay resident
+    keep_suffix_chunks: int = 0           # likewise the first k chunk steps of every segment (their recorded graph stays resident)
     segment_chunks: int = 0
     truncate_fast_weight: bool = False
     inner_views: int = 1
@@ -464,7 +466,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
                 return hh, tail[0], tail[1]
             ins = (h,) + (tuple(win) if win is not None else ())
             with prof.range("prefix_layer.fwd"):
-                h, tk, tv = region(layer_fn, ins, use_regions, "prefix_layer.bwd")
+                h, tk, tv = region(layer_fn, ins, use_regions and l >= cfg.keep_prefix_layers, "prefix_layer.bwd")
             kvp_next.append((tk, tv))
         kvp = kvp_next if n_seg > 1 else None
         hch = h.unflatten(2, (n_seg_chunks, C))                                     # [B, NS, ncs, C, H]
@@ -505,7 +507,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
                 return _suffix_step(net, cfg, kv_l, memv, ho_, hc_, hi_, ht_, hv_, _k, W0, sp_flags, lr_now, distill_w,
                                     create_graph, own_inner, clean_own, read_own, clean_prime, s_S, s_T, B, C, S, use_gdn)
             with prof.range("suffix_step.fwd"):
-                outs = region(step_fn, tuple(dyn), use_regions, "suffix_step.bwd")
+                outs = region(step_fn, tuple(dyn), use_regions and j >= cfg.keep_suffix_chunks, "suffix_step.bwd")
             kvs = [(outs[2 * i], outs[2 * i + 1]) for i in range(S)]
             o = n_kv
             if use_gdn:

@@ -17,7 +17,9 @@ def test_remat_and_segments_do_not_change_loss_or_grads(task, shift):
     eng = make_engine(inner_task=task, outer_shift=shift)
     lc = loss_config(eng.tc)
     l0, g0, _ = loss_and_grads(eng, IDS, dc.replace(lc, remat=False))
-    for variant in (dc.replace(lc, remat=True), dc.replace(lc, segment_chunks=2), dc.replace(lc, segment_chunks=2, remat=False),
+    for variant in (dc.replace(lc, remat=True), dc.replace(lc, remat=True, keep_prefix_layers=1, keep_suffix_chunks=2), dc.replace(lc, segment_chunks=2),
+                    dc.replace(lc, segment_chunks=2, keep_suffix_chunks=1),
+                    dc.replace(lc, segment_chunks=2, remat=False),
                     dc.replace(lc, fused_ce_block=48)):
         l1, g1, _ = loss_and_grads(eng, IDS, variant)
         assert abs(l0 - l1) < 1e-6 and max_diff(g0, g1) < 1e-6
