@@ -47,13 +47,14 @@ def test_shipped_run_configs_load(name):
 
 
 def test_reference_run_configs_load_unchanged():
-    ref = "/root/reference/runs"
-    if not os.path.isdir(ref):
-        pytest.skip("reference tree not mounted")
+    tree = os.environ.get("DTTT_REFERENCE_TREE", "")          # a checkout of the reference, when one is at hand
+    ref = os.path.join(tree, "runs")
+    if not tree or not os.path.isdir(ref):
+        pytest.skip("no reference checkout named by DTTT_REFERENCE_TREE")
     for f in os.listdir(ref):
         load_run_config(os.path.join(ref, f))
-    ModelConfig.load("/root/reference/configs/1b_e2e")
-    ModelConfig.load("/root/reference/configs/tiny_smoke")
+    ModelConfig.load(os.path.join(tree, "configs/1b_e2e"))
+    ModelConfig.load(os.path.join(tree, "configs/tiny_smoke"))
 
 
 def test_model_validation_and_derived():
