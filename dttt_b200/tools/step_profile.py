@@ -26,6 +26,8 @@ def main(argv=None) -> int:
     ap.add_argument("--trace", default="")
     ap.add_argument("--shapes", action="store_true", help="also group the framework ops by input shapes")
     ap.add_argument("--top", type=int, default=60, help="rows of the by-shape table")
+    ap.add_argument("--keep-prefix-layers", type=int, default=0)
+    ap.add_argument("--keep-suffix-chunks", type=int, default=0)
     a = ap.parse_args(argv)
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     sys.path.insert(0, root)
@@ -36,7 +38,8 @@ def main(argv=None) -> int:
 
     dev = torch.device("cuda", 0)
     mc = ModelConfig.load(a.config if os.path.isabs(a.config) else os.path.join(root, a.config))
-    tc = TrainConfig(seq_len=a.seq_len, batch_size=a.batch, steps=10000, seed=0, inner_task="causal", outer_shift=True)
+    tc = TrainConfig(seq_len=a.seq_len, batch_size=a.batch, steps=10000, seed=0, inner_task="causal", outer_shift=True,
+                     keep_prefix_layers=a.keep_prefix_layers, keep_suffix_chunks=a.keep_suffix_chunks)
     eng = Engine(mc, tc, device=dev)
     ids = torch.randint(0, min(mc.vocab_size, 128000), (a.batch, a.seq_len))
     for s in range(2):
