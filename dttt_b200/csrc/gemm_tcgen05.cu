@@ -23,6 +23,7 @@
 #include <unordered_map>
 #include <cstring>
 #include <cstdio>
+#include <cstdlib>
 
 namespace dttt {
 
@@ -509,6 +510,219 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
   }
 }
 
+// ------------------------------------------------------------------ 256 x 256 tiles
+// The same GEMM with TWO 128-row halves per tile that share every B tile: one stage holds A (2 x 16 KB) and B (32 KB), the issuer
+// feeds both accumulators (TMEM columns [0, 256) and [256, 512)) from it, so a CTA pulls 64 bytes per tensor-pipe cycle from L2
+// instead of 96 and three stages cover 3072 cycles of load latency instead of 2048.  The price: the accumulators are not
+// double-buffered across tiles (all 512 columns belong to the current tile), so the epilogue (eight warps) is exposed; the
+// launcher uses this form where the tiles are many and K is long (weight gradients over all tokens, down projections).
+// Plain store epilogue only.
+struct Smem256 {
+  static constexpr int A_BYTES = 2 * BM * BK * 2;
+  static constexpr int B_BYTES = 256 * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 3;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+};
+
+__global__ void __launch_bounds__(320, 1)
+gemm256_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmParams p) {
+  using L = Smem256;
+  constexpr int BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + L::STAGES * L::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty = full + L::STAGES;
+  uint64_t* acc_full = empty + L::STAGES;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int kblocks = (p.K + BK - 1) / BK;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 256);
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&mapA);
+    tma_prefetch_desc(&mapB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(tile, p, b, tm, tn);
+        const int m0 = tm * 2 * BM, n0 = tn * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t ph = (it / L::STAGES) & 1;
+          if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sA = smem + s * L::STAGE_BYTES;
+          uint8_t* sB = sA + L::A_BYTES;
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!p.a_mn_major) {
+            tma_load_3d(sA, &mapA, &full[s], k0, m0, b);                       // box {64 k, 128 rows}, once per half
+            tma_load_3d(sA + BM * BK * 2, &mapA, &full[s], k0, m0 + BM, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2 * BM / 64; ++j)                              // box {64 m, 64 k-rows}
+              tma_load_3d(sA + j * (BK * 128), &mapA, &full[s], m0 + j * 64, k0, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(sB, &mapB, &full[s], k0, n0, b);                       // box {64 k, 256 rows}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sB + j * (BK * 128), &mapB, &full[s], n0 + j * 64, k0, b);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn_major, p.b_mn_major);
+      const uint32_t a_lbo = p.a_mn_major ? BK * 128 : 16, b_lbo = p.b_mn_major ? BK * 128 : 16;
+      const uint32_t a_kstep = p.a_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t b_kstep = p.b_mn_major ? UMMA_K * 128 : UMMA_K * 2;
+      const uint32_t a_half = p.a_mn_major ? 2 * (BK * 128) : BM * BK * 2;      // bytes between the two 128-row halves of A
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        if (!mbar_wait_bounded(acc_empty, (local_tile & 1) ^ 1, abort_word, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % L::STAGES;
+          const uint32_t ph = (it / L::STAGES) & 1;
+          if (!mbar_wait_bounded(&full[s], ph, abort_word, p.status, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sB = sA + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t bd = make_smem_desc(sB + k * b_kstep, b_lbo, 1024);
+            umma_f16(tmem_base, make_smem_desc(sA + k * a_kstep, a_lbo, 1024), bd, idesc, (kb | k) ? 1u : 0u);
+            umma_f16(tmem_base + BN, make_smem_desc(sA + a_half + k * a_kstep, a_lbo, 1024), bd, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(acc_full);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9: half = (warp - 2) / 4)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t local_tile = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local_tile) {
+      int b, tm, tn;
+      tile_coords(tile, p, b, tm, tn);
+      int got = 1;
+      if (lane == 0) got = mbar_wait_bounded(acc_full, local_tile & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) break;
+      tc_fence_after();
+      const int row = tm * 2 * BM + half * BM + quarter * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + half * BN + ((uint32_t)(quarter * 32) << 16);
+      const bool row_ok = row < p.M;
+      const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row_ok && col < p.N) {
+          const bool full_chunk = (col + 32 <= p.N);
+          if (p.c_is_f32) {
+            float* out = reinterpret_cast<float*>(p.C) + row_off + col;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                if (p.accumulate) {
+                  const float4 o = *reinterpret_cast<float4*>(out + j);
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *reinterpret_cast<float4*>(out + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += out[j];
+                out[j] = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.C) + row_off + col;
+            if (full_chunk && ((reinterpret_cast<uintptr_t>(out) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float f[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) f[q] = __uint_as_float(r[j + q]) * p.alpha;
+                if (p.accumulate) {
+                  const uint4 o = *reinterpret_cast<uint4*>(out + j);
+                  const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    const float2 of = __bfloat1622float2(ob[q]);
+                    f[2 * q] += of.x; f[2 * q + 1] += of.y;
+                  }
+                }
+                uint4 v;
+                __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) vb[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+                *reinterpret_cast<uint4*>(out + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]) * p.alpha;
+                if (p.accumulate) v += __bfloat162float(out[j]);
+                out[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acc_empty);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -580,6 +794,38 @@ static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const G
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
 
+static int launch_gemm256(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm256_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem256::TOTAL);
+    attr_set = true;
+  }
+  long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
+  int grid = (int)(tiles < g_num_sms ? tiles : g_num_sms);
+  gemm256_bf16_kernel<<<grid, 320, Smem256::TOTAL, stream>>>(mapA, mapB, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+// 256 x 256 tiles pay where the grid still fills the SMs about as well as 128 x 256 tiles do (wave quantisation) and the
+// exposed epilogue is short against the main loop.  DTTT_GEMM_TILE256=0 switches the form off, =1 forces it wherever it is legal.
+static int g_tile256_mode = -2;            // -2: read the environment on first use; -1: automatic; 0: off; 1: wherever legal
+static bool use_256_rows(int M, int N, int K, int batch, int max_ctas) {
+  if (g_tile256_mode == -2) {
+    const char* e = getenv("DTTT_GEMM_TILE256");
+    g_tile256_mode = e ? atoi(e) : -1;
+  }
+  const int mode = g_tile256_mode;
+  if (mode == 0 || max_ctas > 0) return false;
+  if (mode == 1) return true;
+  if (K < 8192) return false;               // measured: +2 % at K = 8192, +12 % at K = 49152, -6 % at K = 2048 (the exposed epilogue)
+  const long long sms = g_num_sms > 0 ? g_num_sms : 148;
+  auto eff = [&](long long tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
+  const long long tn = (N + 255) / 256;
+  const long long t128 = (long long)batch * ((M + 127) / 128) * tn, t256 = (long long)batch * ((M + 255) / 256) * tn;
+  return eff(t256) * 1.12 >= eff(t128);
+}
+
 // Combine the per-tile (max, sum exp) partials of EPI_CE_PARTIAL into lse[row] and nll[row] = lse - target logit.
 __global__ void ce_combine_kernel(const float2* __restrict__ part, long long part_stride, int tiles_n, int M,
                                   const float* __restrict__ tgt_logit, float* __restrict__ lse, float* __restrict__ nll) {
@@ -613,6 +859,9 @@ __global__ void ce_combine_kernel(const float2* __restrict__ part, long long par
 
 using namespace dttt;
 
+// Tile form of dttt_gemm_bf16 for N > 128: -1 automatic (the default), 0 always 128 x 256, 1 256 x 256 wherever legal.
+extern "C" void dttt_gemm_tile256(int mode) { g_tile256_mode = mode; }
+
 // C[b] (+)= alpha * A[b] x B[b].
 //   a_mn_major = 0: A stored [M, K] (row stride lda);  1: A stored [K, M] (row stride lda).
 //   b_mn_major = 0: B stored [N, K] (row stride ldb);  1: B stored [K, N] (row stride ldb).
@@ -645,6 +894,10 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   p.C = C; p.status = status;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + bn - 1) / bn;
+  if (bn == 256 && use_256_rows(M, N, K, batch, max_ctas)) {
+    p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
+    return launch_gemm256(mapA, mapB, p, stream);
+  }
   if (bn == 256) return launch_gemm<256, EPI_STORE>(mapA, mapB, p, max_ctas, stream);
   return launch_gemm<128, EPI_STORE>(mapA, mapB, p, max_ctas, stream);
 }

@@ -112,6 +112,16 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
     return out
 
 
+def set_tile_form(mode: int) -> None:
+    """Tile form of the plain GEMM when N > 128: ``-1`` chosen per shape (the default), ``0`` always 128 x 256 tiles with
+    double-buffered accumulators, ``1`` 256 x 256 tiles (two row halves sharing every B tile) wherever legal."""
+    from ctypes import c_int
+    l = _lib.lib()
+    l.dttt_gemm_tile256.argtypes = [c_int]
+    l.dttt_gemm_tile256.restype = None
+    l.dttt_gemm_tile256(int(mode))
+
+
 def _torch_mm(a, b, ta, tb, out_dtype):
     x = a.transpose(-1, -2) if ta else a
     y = b.transpose(-1, -2) if tb else b

@@ -82,6 +82,28 @@ def bench_gemm(a, out):
     out(res)
 
 
+def bench_gemm_forms(a, out):
+    """The model's large plain GEMM shapes under both tile forms (128 x 256 with double-buffered accumulators, 256 x 256 with two
+    row halves per B tile), one line per shape."""
+    from dttt_b200.ops import gemm
+    _, flops, src = peaks()
+    shapes = [(49152, 8192, 2048, 1, 0, 0), (49152, 2048, 8192, 1, 0, 0), (49152, 2048, 2048, 1, 0, 0), (2048, 8192, 2048, 1, 0, 0),
+              (2048, 128256, 2048, 1, 0, 1), (2048, 8192, 49152, 1, 1, 0), (1024, 8192, 2048, 2, 0, 0), (8192, 8192, 8192, 1, 0, 0)]
+    for M, N, K, B, ta, tb in shapes:
+        lead = (B,) if B > 1 else ()
+        x = torch.randn(*lead, *((K, M) if ta else (M, K)), device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(*lead, *((N, K) if tb else (K, N)), device="cuda", dtype=torch.bfloat16)
+        res = {"kernel": "gemm tile forms", "M": M, "N": N, "K": K, "batch": B, "ta": ta, "tb": tb, "peaks": src}
+        for form, name in ((0, "ms_128x256"), (1, "ms_256x256")):
+            gemm.set_tile_form(form)
+            ms = timeit(lambda: gemm.gemm_raw(x, w, bool(ta), bool(tb)), a.iters)
+            res[name] = ms
+            res[name.replace("ms_", "tflops_")] = 2.0 * M * N * K * B / ms / 1e9
+        gemm.set_tile_form(-1)
+        res["speedup_256"] = res["ms_128x256"] / res["ms_256x256"]
+        out(res)
+
+
 def bench_elementwise(a, out):
     from dttt_b200.ops import kernels
     R, D = a.rows, a.dim
@@ -238,7 +260,7 @@ def bench_ce(a, out):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.kernel_bench")
-    ap.add_argument("cmd", choices=["gemm", "attn", "attn2", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
+    ap.add_argument("cmd", choices=["gemm", "gemm_forms", "attn", "attn2", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
     ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--vocab", type=int, default=128256); ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
@@ -248,8 +270,12 @@ def main(argv=None):
     ap.add_argument("--rows", type=int, default=49152); ap.add_argument("--dim", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10); ap.add_argument("--once", action="store_true")
     ap.add_argument("--out", default="")
+    ap.add_argument("--tile-form", type=int, default=-1, help="plain GEMM tile form: -1 per shape, 0 128 x 256, 1 256 x 256")
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
+    if a.tile_form != -1:
+        from dttt_b200.ops import gemm as _g
+        _g.set_tile_form(a.tile_form)
     lines = []
 
     def out(d):
@@ -259,6 +285,8 @@ def main(argv=None):
         bench_gemm(a, out)
     elif a.cmd == "attn":
         bench_attn(a, out)
+    elif a.cmd == "gemm_forms":
+        bench_gemm_forms(a, out)
     elif a.cmd == "attn2":
         bench_attn2(a, out)
     elif a.cmd == "ce":

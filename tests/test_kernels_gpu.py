@@ -30,6 +30,29 @@ def test_gemm_layouts(M, N, K, ta, tb, batch):
     assert _rel(c, ref) < 1e-2
 
 
+@pytest.mark.parametrize("M,N,K,ta,tb,batch", [(512, 512, 256, 0, 0, 1), (300, 520, 200, 0, 1, 1), (384, 512, 256, 1, 0, 3),
+                                              (640, 264, 512, 1, 1, 1), (2048, 2048, 1024, 0, 0, 2), (130, 272, 1032, 0, 1, 1),
+                                              (4096, 1024, 2048, 1, 0, 1)])
+def test_gemm_256_row_tiles(M, N, K, ta, tb, batch):
+    """The 256 x 256 tile form (two row halves sharing every B tile) forced on, all four layouts, ragged edges, f32 accumulate."""
+    from dttt_b200.ops import gemm
+    torch.manual_seed(1)
+    lead = (batch,) if batch > 1 else ()
+    a = torch.randn(*lead, *((K, M) if ta else (M, K)), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(*lead, *((N, K) if tb else (K, N)), device="cuda", dtype=torch.bfloat16)
+    ref = (a.transpose(-1, -2) if ta else a).float() @ (b.transpose(-1, -2) if tb else b).float()
+    gemm.set_tile_form(1)
+    try:
+        c = gemm.gemm_raw(a, b, bool(ta), bool(tb))
+        acc = torch.ones(*lead, M, N, device="cuda", dtype=torch.float32)
+        gemm.gemm_raw(a, b, bool(ta), bool(tb), torch.float32, out=acc, accumulate=True, alpha=0.5)
+        gemm.gemm_raw(a, b, bool(ta), bool(tb), torch.float32, out=acc, accumulate=True, alpha=0.5)
+    finally:
+        gemm.set_tile_form(-1)
+    assert _rel(c, ref) < 1e-2
+    assert _rel(acc - 1.0, ref) < 1e-2
+
+
 def test_gemm_f32_accumulate_and_views():
     from dttt_b200.ops import gemm
     torch.manual_seed(1)
