@@ -96,13 +96,24 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const fl
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + row * D);
     const float r = rstd[row];
+    // rows of up to 2048 elements stay in registers between the reduction and the output (every load in flight at once)
+    constexpr bool CACHE = MAXC <= 8;
+    uint4 vx[CACHE ? MAXC : 1], vg[CACHE ? MAXC : 1];
+    if constexpr (CACHE) {
+#pragma unroll
+      for (int j = 0; j < MAXC; ++j) {
+        const int c = lane + 32 * j;
+        vx[j] = c < nchunk ? xr[c] : make_uint4(0, 0, 0, 0);
+        vg[j] = c < nchunk ? gr[c] : make_uint4(0, 0, 0, 0);
+      }
+    }
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXC; ++j) {
       const int c = lane + 32 * j;
       if (c < nchunk) {
         float fx[8], fg[8];
-        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        unpack8(CACHE ? vx[j] : xr[c], fx); unpack8(CACHE ? vg[j] : gr[c], fg);
         const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
         const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
@@ -120,7 +131,7 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const fl
       const int c = lane + 32 * j;
       if (c < nchunk) {
         float fx[8], fg[8], o[8];
-        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        unpack8(CACHE ? vx[j] : xr[c], fx); unpack8(CACHE ? vg[j] : gr[c], fg);
         const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
         const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
