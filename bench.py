@@ -27,6 +27,8 @@ import sys
 import threading
 import time
 
+# the 8k configuration with every graph resident peaks at 129 GiB (DTTT_BENCH_MIN_FREE_GIB overrides the threshold)
+RESIDENT_MIN_FREE_GIB = float(os.environ.get("DTTT_BENCH_MIN_FREE_GIB", "150"))
 BASELINE_TOK_S_PER_DEVICE = 4500.0        # reference, GH200, 2 sequences/device (docs/launch.md:73)
 
 CONFIGS = {
@@ -147,11 +149,19 @@ def main() -> int:
     micro = min(args.micro or spec["micro"], per_gpu)
     accum = per_gpu // micro
     T = spec["seq_len"]
+    extra = dict(spec["extra"], **({"keep_prefix_layers": args.keep_prefix_layers} if args.keep_prefix_layers >= 0 else {}),
+                 **({"keep_suffix_chunks": args.keep_suffix_chunks} if args.keep_suffix_chunks >= 0 else {}))
+    # resident graphs need the whole part: with less than RESIDENT_MIN_FREE_GIB free on any rank the regions recompute instead
+    free = torch.tensor([torch.cuda.mem_get_info(dev)[0] / 2 ** 30], device=dev)
+    if world > 1:
+        dist.all_reduce(free, op=dist.ReduceOp.MIN)
+    note = None
+    if (extra.get("keep_prefix_layers") or extra.get("keep_suffix_chunks")) and free.item() < RESIDENT_MIN_FREE_GIB:
+        extra.update(keep_prefix_layers=0, keep_suffix_chunks=0)
+        note = f"{free.item():.0f} GiB free: recompute regions instead of resident graphs"
     tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
                      seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
-                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp,
-                     **dict(spec["extra"], **({"keep_prefix_layers": args.keep_prefix_layers} if args.keep_prefix_layers >= 0 else {}),
-                            **({"keep_suffix_chunks": args.keep_suffix_chunks} if args.keep_suffix_chunks >= 0 else {})))
+                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **extra)
     eng = Engine(mc, tc, mesh, dev)
 
     # synthetic data: distinct tokens for every step, on pinned host memory
@@ -165,8 +175,31 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for s in range(W):
-        m = eng.train_step(host[s].to(dev, non_blocking=True), s)
+    oom = False
+    try:
+        for s in range(W):
+            m = eng.train_step(host[s].to(dev, non_blocking=True), s)
+    except torch.OutOfMemoryError:
+        if world > 1 or not (extra.get("keep_prefix_layers") or extra.get("keep_suffix_chunks")):
+            raise
+        oom = True
+    if oom:
+        # a single GPU that cannot hold the resident graphs after all: start over with recompute regions
+        # (outside the handler, so that the failed step's frames and their tensors are gone)
+        import gc
+        del eng
+        m = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        extra.update(keep_prefix_layers=0, keep_suffix_chunks=0)
+        note = "out of memory with resident graphs: recompute regions instead"
+        tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
+                         seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
+                         outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **extra)
+        eng = Engine(mc, tc, mesh, dev)
+        torch.cuda.reset_peak_memory_stats()
+        for s in range(W):
+            m = eng.train_step(host[s].to(dev, non_blocking=True), s)
     launches0 = gemm.LAUNCHES + kernels.LAUNCHES
 
     def timed(first_step: int, e2e: bool):
@@ -204,7 +237,9 @@ def main() -> int:
         "config": {"model": f"1B TTT ({args.config}): " + spec["model"], "global_batch": per_gpu * mesh.batch_ranks, "seq_len": T,
                    "parallelism": f"dp{mesh.dp}xfsdp{mesh.fsdp}xtp{mesh.tp}", "micro_batch_per_gpu": micro, "grad_accum": accum,
                    "l2": "per-step working set (3 GB bf16 weights + activations) >> 126 MB L2; no explicit flush",
-                   "params": eng.n_params, "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
+                   "params": eng.n_params, "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+                   "keep_prefix_layers": extra.get("keep_prefix_layers", 0), "keep_suffix_chunks": extra.get("keep_suffix_chunks", 0),
+                   **({"note": note} if note else {})},
         "clocks": ck, "gpu_launches": launches, "final_loss": last.get("main_loss") if last else None,
     }
     if ms_e2e is not None:
