@@ -136,3 +136,15 @@ def test_round_compare_sections(runs, tmp_path, capsys):
     assert round_compare.main(["--step", str(step), f"A={runs['A']}", f"B={runs['B']}", "--pairs", "B-A"]) == 0
     out = capsys.readouterr().out
     assert "## 8K" in out and "B - A" in out and "## bound" in out and "memory's part" in out
+
+
+def test_memory_model_counts_kept_graphs_and_the_recomputation_they_save():
+    from dttt_b200.tools import memory_model as mm
+    c = mm._cfg(os.path.join(ROOT, "configs/b200_1b_8k"))
+    base = mm.report(c, 8192, 2, 1, 1)
+    kept = mm.report(c, 8192, 2, 1, 1, keep_prefix_layers=12, keep_suffix_chunks=8)
+    assert base["kept_graphs_gib"] == 0 and base["hardware_gflop_per_token"] > base["model_gflop_per_token"]
+    assert abs(kept["hardware_gflop_per_token"] - kept["model_gflop_per_token"]) < 1e-9          # nothing is recomputed
+    assert 55 < kept["kept_graphs_gib"] < 80                                                      # measured: 70.7 GiB for two sequences
+    half = mm.report(c, 8192, 2, 1, 1, keep_prefix_layers=6, keep_suffix_chunks=4)
+    assert base["hardware_gflop_per_token"] > half["hardware_gflop_per_token"] > kept["hardware_gflop_per_token"]
