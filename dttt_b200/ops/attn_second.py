@@ -25,7 +25,7 @@ into the rows.  ``second_order`` is also stated in plain PyTorch
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Tuple
 
 import torch
 from torch.autograd.function import once_differentiable

@@ -15,7 +15,7 @@ teacher distribution (``:151-213``) and the streaming ``topk_logprobs`` (``:224-
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Tuple
 
 import torch
 

@@ -16,7 +16,7 @@ three executions:
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 

@@ -14,7 +14,6 @@ per-sequence gradients and one backward pass serves the whole batch.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import List, NamedTuple, Optional, Sequence, Tuple
 

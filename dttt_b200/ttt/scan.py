@@ -19,7 +19,7 @@ without a graph, and its backward re-runs it with the graph (the inner step then
 from __future__ import annotations
 
 import dataclasses as dc
-from typing import Dict, List, NamedTuple, Optional, Tuple
+from typing import NamedTuple, Optional, Tuple
 
 import torch
 
