@@ -78,10 +78,19 @@ def _rows_torch(S, dP, gdS, X, lse, delta, chunk, causal, scale):
     return p, dS * scale, gdP, gS * scale
 
 
-def supported(q: torch.Tensor, Kn: int) -> bool:
+def _fused_ok(q: torch.Tensor, Kn: int) -> bool:
     from . import kernels
-    return (q.is_cuda and kernels.available("attention_bwd2") and q.dtype == torch.bfloat16 and Kn % 4 == 0
-            and Kn <= kernels.ATTN_BWD2_MAX_KEYS and q.shape[-1] % 8 == 0)
+    return (FUSED_SCORES and kernels.available("attention_bwd2_scores") and q.shape[-1] == 64 and q.shape[1] % 128 == 0
+            and Kn % 64 == 0)
+
+
+def supported(q: torch.Tensor, Kn: int) -> bool:
+    """Whether ``second_order`` has a kernel path for this call: the tcgen05 score stage (any number of keys), or the row kernel
+    over f32 score products (up to ``kernels.ATTN_BWD2_MAX_KEYS`` keys, a multiple of 4)."""
+    from . import kernels
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] % 8 == 0):
+        return False
+    return _fused_ok(q, Kn) or (kernels.available("attention_bwd2") and Kn % 4 == 0 and Kn <= kernels.ATTN_BWD2_MAX_KEYS)
 
 
 def second_order(gQ: Optional[torch.Tensor], gK: Optional[torch.Tensor], gV: Optional[torch.Tensor], dO: torch.Tensor,
@@ -106,7 +115,7 @@ def second_order(gQ: Optional[torch.Tensor], gK: Optional[torch.Tensor], gV: Opt
         qg, dOg, gQg = (_rows(t.to(bf), nkv).contiguous() for t in (q, dO, gQ))
         kg, vg, gKg, gVg = (_keys(t.to(bf)).contiguous() for t in (K, V, gK, gV))
         f32 = torch.float32
-        if FUSED_SCORES and kernels.available("attention_bwd2_scores") and kernels.attention_bwd2_scores_supported(q, K):
+        if _fused_ok(q, Kn) and kernels.attention_bwd2_scores_supported(q, K):
             # scores in tensor memory, never in global memory
             P, dS, gdP, gS = kernels.attention_bwd2_scores(q, dO.to(bf), gQ.to(bf), K, V.to(bf), gK.to(bf), gV.to(bf),
                                                            lse.float(), delta_h, scale, causal)
