@@ -148,3 +148,38 @@ def test_memory_model_counts_kept_graphs_and_the_recomputation_they_save():
     assert 55 < kept["kept_graphs_gib"] < 80                                                      # measured: 70.7 GiB for two sequences
     half = mm.report(c, 8192, 2, 1, 1, keep_prefix_layers=6, keep_suffix_chunks=4)
     assert base["hardware_gflop_per_token"] > half["hardware_gflop_per_token"] > kept["hardware_gflop_per_token"]
+
+
+def test_common_pile_fetch_is_resumable_against_a_fake_hub(tmp_path):
+    """Plan -> missing -> fetch -> manifest with a stand-in hub: a second pass fetches only what is missing or has the wrong size."""
+    import types
+    from dttt_b200.tools.data import download_common_pile as dl
+    files = {"a/000.json.gz": 10, "a/001.json.gz": 20, "README.md": 5, "a/002.json.gz": 30}
+    api = types.SimpleNamespace(dataset_info=lambda repo, files_metadata: types.SimpleNamespace(
+        sha="f" * 40, siblings=[types.SimpleNamespace(rfilename=k, size=v) for k, v in files.items()]))
+    plan = dl.plan_source(api, "books", 0)
+    assert plan.repo == "common-pile/books_filtered" and [s.path for s in plan.shards] == sorted(k for k in files if k.endswith(".gz"))
+    assert plan.nbytes == 60 and len(dl.plan_source(api, "books", 2).shards) == 2
+    calls = []
+
+    def download(repo_id, repo_type, revision, filename, local_dir):
+        calls.append(filename)
+        if filename.endswith("001.json.gz") and calls.count(filename) == 1:
+            raise OSError("connection reset")
+        path = os.path.join(local_dir, filename)
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "wb") as fh:
+            fh.write(b"x" * files[filename])
+
+    root = str(tmp_path)
+    failed = dl.fetch(plan, dl.missing_shards(plan, root), root, 2, download)
+    assert len(failed) == 1 and "001" in failed[0]
+    assert [s.path for s in dl.missing_shards(plan, root)] == ["a/001.json.gz"]
+    with open(os.path.join(root, "books", "a/000.json.gz"), "wb") as fh:        # a truncated file counts as missing
+        fh.write(b"x")
+    todo = dl.missing_shards(plan, root)
+    assert [s.path for s in todo] == ["a/000.json.gz", "a/001.json.gz"]
+    assert dl.fetch(plan, todo, root, 2, download) == [] and dl.missing_shards(plan, root) == []
+    man = os.path.join(root, "manifest.json")
+    dl.write_manifest(man, {"books": {"revision": plan.revision}})
+    assert dl.read_manifest(man)["books"]["revision"] == "f" * 40 and dl.read_manifest(os.path.join(root, "none.json")) == {}
