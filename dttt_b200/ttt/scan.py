@@ -31,6 +31,7 @@ from ..ops import reference as ref
 from ..utils import prof, rng
 from . import inner as IN
 from . import objective as OBJ
+from . import validate as VAL
 from .regions import region
 
 
@@ -135,10 +136,11 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     """Batch loss and diagnostics.  ``key``: ``[2]`` (training) or row-wise ``[B, 2]`` (evaluation)."""
     mc = net.cfg
     use_gdn = mc.memory == "gdn"
+    asked_of_gdn = dict(inner_from_outer=cfg.inner_from_outer, write_off=cfg.write_off, distill=cfg.distill, mtp=cfg.mtp,
+                        inner_feat=cfg.inner_feat != "off")
     if use_gdn:
-        if cfg.inner_from_outer or cfg.write_off or cfg.distill or cfg.mtp or cfg.inner_feat != "off":
-            raise ValueError("memory gdn: no inner stream (inner_from_outer / write_off / distill / mtp / inner_feat do not apply)")
-        cfg = dc.replace(cfg, no_write=True)
+        cfg = dc.replace(cfg, no_write=True)                 # the GDN state is written by its own recurrence, not by a gradient step
+    VAL.check_options(cfg, mc, net.cw.has, use_gdn, asked_of_gdn)
     # Everything up to the first model call (noising, weights, inner masks, positions) is integer / small-float
     # work on [B, T] arrays: it runs on the host, where the token ids come from, and is moved to the device in
     # one go; the device queue never waits on it.
@@ -203,35 +205,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     x_t, t, t_mask, w_raw, m_outer, weight = noisy_view(key_mask)
     tgt_outer = _pad_left_shift(ids, 1) if cfg.outer_shift else ids
     VO = cfg.outer_views
-    if VO < 1:
-        raise ValueError("outer_views >= 1")
-    if VO > 1 and (cfg.distill or cfg.mtp or cfg.reread_chunks or cfg.inner_from_outer or cfg.per_sequence
-                   or cfg.per_token or mc.read_block):
-        raise ValueError("outer_views > 1 is a training option: not with distill / mtp / reread_chunks / inner_from_outer / "
-                         "per-sequence or per-token scores / read_block")
     extra_views = [noisy_view(fold(key_mask, v)) for v in range(1, VO)]
-    if (cfg.mtp or cfg.distill) and (cfg.no_write or cfg.inner_from_outer or cfg.inner_task == "split" or cfg.inner_views != 1):
-        raise ValueError("distill / mtp need a single-view mask or causal write (not no_write / inner_from_outer / split)")
-    if cfg.write_off and (cfg.no_write or cfg.inner_from_outer or cfg.distill or cfg.mtp or cfg.inner_views != 1
-                          or cfg.inner_feat != "off"):
-        raise ValueError("write_off keeps one plain inner stream (not no_write / inner_from_outer / distill / mtp / views / feat)")
-    if cfg.aux_causal_weight > 0 and (cfg.no_write or cfg.inner_from_outer):
-        raise ValueError("aux_causal_weight needs an inner stream (not no_write / inner_from_outer)")
-    if cfg.write_plan and (not cfg.write.plain or cfg.inner_task != "causal" or cfg.inner_views != 1 or cfg.no_write
-                           or cfg.write_off or cfg.inner_from_outer or cfg.reread_chunks or min(cfg.write_plan) < 0):
-        raise ValueError("write_plan needs the plain causal write (one view, a write, no re-read) and steps >= 0")
-    if not cfg.write.plain:
-        cfg.write.check(C)
-        if (cfg.inner_task != "causal" or cfg.inner_views != 1 or cfg.no_write or cfg.inner_from_outer or cfg.write_off
-                or cfg.distill or cfg.mtp or cfg.inner_feat != "off" or cfg.inner_update_frac < 1.0):
-            raise ValueError("the write schemes need the plain causal write (inner_task causal, one view, a write; "
-                             "not with write_off / distill / mtp / inner_feat / inner_update_frac)")
-        if cfg.write.kvb_weight > 0 and not net.cw.has("inner_kvb_value.weight"):
-            raise ValueError("inner_kvb_weight needs a model with inner_kvb_head")
-    if cfg.self_prior > 0 and (use_gdn or cfg.no_write or cfg.write_off or cfg.inner_from_outer or cfg.write_plan
-                               or cfg.reread_chunks or cfg.inner_views != 1):
-        raise ValueError("self_prior reads a chunk after its own write: it needs a write (TTT, one view, no write plan / "
-                         "re-read)")
     base_key = key if key.dim() == 1 else key[0]
     reach = mc.reach
     if cfg.window_drop > 0:
@@ -241,10 +215,6 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     if cfg.self_prior > 0:
         sp_flags = (rng.uniform(fold(key, 8), ()) if key.dim() == 2 else rng.uniform(fold(key, 8), (B,))) < cfg.self_prior
     if cfg.mtp:
-        if not cfg.outer_shift or cfg.inner_task != "causal":
-            raise ValueError("mtp needs outer_shift and the causal write")
-        if not net.cw.has("mtp_head.weight"):
-            raise ValueError("mtp needs a model with mtp_head")
         tgt_mtp = _pad_left_shift(ids, 2)
         m_mtp = _pad_left_shift(t_mask, 2)
         w_mtp = _pad_left_shift(w_raw, 2) * m_mtp.float()
@@ -255,10 +225,6 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     T0, nc0, n_rr = T, nc, cfg.reread_chunks
     host_mask, host_perm = batch.inner_mask, batch.inner_perm
     if n_rr:
-        if cfg.segment_chunks <= 0 or n_rr % cfg.segment_chunks:
-            raise ValueError("reread_chunks needs segment_chunks > 0 dividing it (the window reset is a segment boundary)")
-        if cfg.distill:
-            raise ValueError("reread_chunks with distill is not supported")
         nC = n_rr * C
         dup = lambda a: torch.cat([a[:, :nC], a], dim=1)
         zero = lambda a: torch.cat([torch.zeros_like(a[:, :nC]), a], dim=1)
@@ -318,10 +284,6 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         slot = torch.arange(C, device=dev)
         inner_mask_c = ((slot >= max(K - 1, 0)) & (slot <= C - 2))[None, None].expand(nc, B, C)
     if cfg.inner_feat != "off":
-        if cfg.no_write or cfg.inner_from_outer:
-            raise ValueError("inner_feat needs the inner stream (not no_write / inner_from_outer)")
-        if not net.cw.has("inner_feat_head.weight"):
-            raise ValueError("inner_feat needs a model with inner_feat_head")
         i = torch.arange(C, device=dev)
         if cfg.inner_task == "mask":
             tgt_idx_c = i[None, None].expand(nc, B, C)
@@ -350,11 +312,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         mtp_tgt_c = mtp_mask_c = None
 
     # ---- segments
-    n_seg_chunks = cfg.segment_chunks or nc
-    if nc % n_seg_chunks:
-        raise ValueError(f"{nc} chunks not a multiple of segment_chunks {n_seg_chunks}")
-    if n_seg_chunks < Wn and n_seg_chunks < nc:
-        raise ValueError(f"segment_chunks {n_seg_chunks} < window_chunks {Wn}: the carried window would be short")
+    n_seg_chunks = VAL.check_geometry(T, mc, cfg.segment_chunks, nc)
     n_seg = nc // n_seg_chunks
     T_seg = n_seg_chunks * C
     nkv, d = mc.num_key_value_heads // tp, mc.head_dim                       # this rank's KV heads
@@ -366,8 +324,6 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         distill_w = cfg.distill_weight * min(1.0, step / cfg.distill_warmup_steps)
     clean_prime = (not cfg.write.plain) and cfg.write.kvb_weight > 0 and cfg.write.kvb_value == "clean"
     rb = mc.read_block
-    if rb and cfg.distill:
-        raise ValueError("read_block: no distillation teacher stream")
     clean_own = "full" if not rb else f"block:{rb}"
     read_own = None if not rb else A.read_mask_matrix(C, rb, dev)
     lm_w_of = net.lm_weight

@@ -43,3 +43,32 @@ def test_write_plan_spec():
     assert evalsuite.parse_write_plan("1:3, 2:0", 4) == (1, 3, 0, 1)
     with pytest.raises(ValueError):
         evalsuite.parse_write_plan("4:2", 4)
+
+
+def test_refused_option_combinations():
+    """``ttt.validate``: the table of combinations the objective refuses, and a few that it accepts."""
+    import dataclasses as dc
+    from util import loss_config, make_engine, tiny_model
+    from dttt_b200.ttt import validate as VAL
+    eng = make_engine()
+    lc, mc = loss_config(eng.tc), eng.mc
+    has_all, has_none = (lambda name: True), (lambda name: False)
+    VAL.check_options(lc, mc, has_none)                                                     # the default objective is fine
+    VAL.check_options(dc.replace(lc, mtp=True, outer_shift=True, inner_task="causal"), mc, has_all)
+    refused = [dc.replace(lc, outer_views=0), dc.replace(lc, outer_views=2, per_token=True),
+               dc.replace(lc, distill=True, no_write=True), dc.replace(lc, write_off=True, inner_views=2),
+               dc.replace(lc, aux_causal_weight=0.5, no_write=True), dc.replace(lc, write_plan=(1, 2, 1, 1), inner_task="mask"),
+               dc.replace(lc, write_plan=(1, -1, 1, 1)), dc.replace(lc, self_prior=0.1, no_write=True),
+               dc.replace(lc, mtp=True, outer_shift=False), dc.replace(lc, reread_chunks=2, segment_chunks=0),
+               dc.replace(lc, reread_chunks=3, segment_chunks=2), dc.replace(lc, inner_feat="cos", no_write=True)]
+    for bad in refused:
+        with pytest.raises(ValueError):
+            VAL.check_options(bad, mc, has_all)
+    with pytest.raises(ValueError):                                                         # a head the model was not built with
+        VAL.check_options(dc.replace(lc, mtp=True, outer_shift=True, inner_task="causal"), mc, has_none)
+    with pytest.raises(ValueError):
+        VAL.check_options(dc.replace(lc, no_write=True), mc, has_all, use_gdn=True, gdn_requested={"distill": True})
+    assert VAL.check_geometry(64, mc, 0, 8) == 8 and VAL.check_geometry(64, mc, 4, 8) == 4
+    for args in ((60, mc, 0, 7), (64, mc, 3, 8), (64, tiny_model(window_chunks=3), 2, 8)):
+        with pytest.raises(ValueError):
+            VAL.check_geometry(*args)
