@@ -64,6 +64,35 @@ def loss_config(cfg: TrainConfig) -> LossConfig:
         attn_chunk_batch=cfg.attn_chunk_batch, compute_dtype=cfg.compute_dtype)
 
 
+def resolve_keep(tc: TrainConfig, mc: ModelConfig, free_bytes: float, seqs_per_pass: int) -> TrainConfig:
+    """``keep_prefix_layers`` / ``keep_suffix_chunks`` below zero mean "as many as fit": fill them in from the memory model
+    (``tools.memory_model``) and the bytes free on the device after the parameters are in place.  What must stay free besides
+    the kept graphs: the region inputs, the transients of the pass in flight (about 19 GB per 16k tokens for the 1B model,
+    scaled by width) and a safety margin.  Chunk steps are kept before prefix layers (they save more time per byte: a kept
+    chunk step also drops its unrecorded first pass)."""
+    if tc.keep_prefix_layers >= 0 and tc.keep_suffix_chunks >= 0:
+        return tc
+    import dataclasses as dc
+    from .tools import memory_model as MM
+    c = dc.asdict(mc)
+    c.setdefault("ttt_intermediate_size", None)
+    seq_len, n_prefix = tc.seq_len, mc.num_hidden_layers - mc.suffix_len
+    per_segment = tc.segment_chunks or max(1, seq_len // mc.chunk_size)
+    tokens = seqs_per_pass * seq_len
+    carried = MM.carry_bytes(c)
+    regions = seqs_per_pass * (n_prefix * 3 * seq_len * mc.hidden_size * 2 + (seq_len // mc.chunk_size) * (carried["fast_weight"] + carried["kv"]))
+    transients = 19e9 * tokens / 16384 * (mc.hidden_size / 2048)
+    budget = free_bytes - regions - transients - 15e9
+    kept = lambda layers, chunks: seqs_per_pass * MM.kept_bytes(c, seq_len, layers, chunks, tc.segment_chunks)
+    chunks = tc.keep_suffix_chunks
+    if chunks < 0:
+        chunks = max((k for k in range(per_segment + 1) if kept(0, k) <= budget), default=0)
+    layers = tc.keep_prefix_layers
+    if layers < 0:
+        layers = max((k for k in range(n_prefix + 1) if kept(k, chunks) <= budget), default=0)
+    return tc.replace(keep_prefix_layers=layers, keep_suffix_chunks=chunks)
+
+
 def torch_dtype(name: str) -> torch.dtype:
     return {"bfloat16": torch.bfloat16, "float32": torch.float32}[name]
 
@@ -92,6 +121,16 @@ class Engine:
             self.opt = ShardedAdamW(self.store, c.lr, c.end_lr, c.warmup_steps, c.decay_start, c.decay_end, c.weight_decay,
                                     c.grad_clip, c.adam_b1, c.adam_b2, no_decay_pattern=c.no_decay_pattern,
                                     fast_weight_lr_scale=c.fast_weight_lr_scale)
+        if train_cfg.keep_prefix_layers < 0 or train_cfg.keep_suffix_chunks < 0:
+            free = float(torch.cuda.mem_get_info(self.device)[0]) if self.device.type == "cuda" else 0.0
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                # every rank must resolve the same numbers: under tensor parallelism a rank that recomputes a region issues
+                # collectives its peers would not
+                t = torch.tensor([free], dtype=torch.float64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                free = float(t.item())
+            train_cfg = self.tc = resolve_keep(train_cfg, model_cfg, free, max(1, train_cfg.batch_size // self.mesh.batch_ranks))
         self.lcfg = loss_config(train_cfg)
         self.key = rng.key(train_cfg.seed)
         self.overflow = 0

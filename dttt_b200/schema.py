@@ -270,8 +270,8 @@ class TrainConfig:
     remat_levels: int = 1
     remat_prefix: bool = False
     prefix_remat_levels: int = 1
-    keep_prefix_layers: int = 0             # this many prefix layers keep their activations instead of recomputing (180 GB parts)
-    keep_suffix_chunks: int = 0             # this many chunk steps per segment keep their graph instead of running twice
+    keep_prefix_layers: int = 0             # this many prefix layers keep their activations instead of recomputing (180 GB parts); < 0: as many as fit
+    keep_suffix_chunks: int = 0             # this many chunk steps per segment keep their graph instead of running twice; < 0: as many as fit
     segment_chunks: int = 0
     truncate_fast_weight: bool = False
     inner_views: int = 1

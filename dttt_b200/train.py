@@ -72,6 +72,7 @@ class Trainer:
         self.log(f"[ttt] {self.eng.n_params / 1e9:.3f}B params")
         self.restart = RS.restore(cfg, self.eng, self.log)
         self._open_data()
+        self.cfg = cfg = self.eng.tc                              # "as many as fit" knobs are numbers from here on
         self.lc_base = loss_config(cfg)
         self.lc_train = dc.replace(self.lc_base, time_reweighting="none") if cfg.train_recall else self.lc_base
         self.evals = self._build_evals()

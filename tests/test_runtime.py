@@ -72,3 +72,22 @@ def test_refused_option_combinations():
     for args in ((60, mc, 0, 7), (64, mc, 3, 8), (64, tiny_model(window_chunks=3), 2, 8)):
         with pytest.raises(ValueError):
             VAL.check_geometry(*args)
+
+
+def test_keep_knobs_below_zero_are_filled_in_from_the_memory_model():
+    from dttt_b200.engine import resolve_keep
+    from dttt_b200.schema import ModelConfig, TrainConfig
+    from util import ROOT
+    mc = ModelConfig.load(os.path.join(ROOT, "configs/b200_1b_8k"))
+    tc = TrainConfig(model_config="configs/b200_1b_8k", seq_len=8192, batch_size=2, keep_prefix_layers=-1, keep_suffix_chunks=-1)
+    roomy = resolve_keep(tc, mc, 154e9, 2)                     # a B200 after the parameters: everything fits (measured: 129 GB peak)
+    assert (roomy.keep_prefix_layers, roomy.keep_suffix_chunks) == (12, 8)
+    tight = resolve_keep(tc, mc, 90e9, 2)
+    assert tight.keep_suffix_chunks == 8 and 0 <= tight.keep_prefix_layers < 12
+    none = resolve_keep(tc, mc, 40e9, 2)
+    assert (none.keep_prefix_layers, none.keep_suffix_chunks) == (0, 0)
+    four = resolve_keep(tc, mc, 154e9, 4)                      # four sequences per pass: only part of it fits
+    assert four.keep_suffix_chunks + four.keep_prefix_layers < 20 and four.keep_suffix_chunks >= 1
+    fixed = resolve_keep(tc.replace(keep_suffix_chunks=3), mc, 154e9, 2)
+    assert fixed.keep_suffix_chunks == 3 and fixed.keep_prefix_layers == 12
+    assert resolve_keep(tc.replace(keep_prefix_layers=0, keep_suffix_chunks=0), mc, 0.0, 2).keep_prefix_layers == 0
