@@ -69,3 +69,45 @@ def test_self_prior_zero_is_the_plain_scan_and_a_half_changes_the_meta_gradient(
     assert all(torch.isfinite(v).all() for v in g_half.values()) and torch.isfinite(torch.tensor(l_half))
     l_one, g_one, _ = loss_and_grads(eng, ids, dc.replace(lc, self_prior=1.0))
     assert abs(l_one - l0) > 1e-7 and max_diff(g_one, g0) > 1e-7
+
+
+def _loss_and_stats(eng, lc, ids, step=3):
+    net = Net(eng.mc, ComputeWeights(eng.store))
+    with torch.no_grad():
+        loss, stats = loss_fn(net, Batch(ids), rng.key(5), step, lc)
+    return float(loss), {k: v.clone() for k, v in stats.items()}
+
+
+def test_write_off_keeps_the_inner_loss_but_never_moves_w_and_the_auxiliary_weight_adds_it():
+    """The auxiliary-loss control (the reference's tests/test_aux_causal.py): ``write_off`` runs the inner stream for its
+    cross-entropy only; ``aux_causal_weight`` adds that cross-entropy to the outer objective."""
+    eng = make_engine(inner_task="causal", outer_shift=True)
+    lc = loss_config(eng.tc)
+    ids = torch.randint(1, 120, (2, 32), generator=torch.Generator().manual_seed(3))
+    l_on, s_on = _loss_and_stats(eng, lc, ids)
+    l_off, s_off = _loss_and_stats(eng, dc.replace(lc, write_off=True), ids)
+    assert float(s_on["ttt_delta_norm"]) > 0 and float(s_off["ttt_delta_norm"]) == 0.0
+    assert float(s_off["inner_loss"]) > 0 and torch.isfinite(s_off["inner_loss"])
+    l_none, s_none = _loss_and_stats(eng, dc.replace(lc, no_write=True), ids)
+    assert abs(l_off - l_none) < 1e-6                                          # reading W_0 either way
+    for w in (0.5, 2.0):
+        l_aux, s_aux = _loss_and_stats(eng, dc.replace(lc, write_off=True, aux_causal_weight=w), ids)
+        assert abs((l_aux - l_off) - w * float(s_aux["inner_loss"])) < 1e-5, (w, l_aux, l_off, float(s_aux["inner_loss"]))
+        assert abs(float(s_aux["main_loss"]) - l_off) < 1e-6
+
+
+def test_the_shifted_outer_loss_scores_the_masked_targets_from_slot_one_on():
+    """With ``outer_shift`` slot i predicts token i + 1: the first token of a sequence is never a target, so the scored count is
+    the number of masked tokens after position 0 (the reference's tests/test_outer_shift.py, invariant 3)."""
+    eng = make_engine(inner_task="causal", outer_shift=True, time_reweighting="none")
+    lc = dc.replace(loss_config(eng.tc), per_token=True, per_sequence=True)
+    ids = torch.randint(1, 120, (3, 32), generator=torch.Generator().manual_seed(4))
+    keys = torch.stack([rng.fold_in(rng.key(9), j) for j in range(3)])
+    net = Net(eng.mc, ComputeWeights(eng.store))
+    with torch.no_grad():
+        loss, st = loss_fn(net, Batch(ids), keys, 0, lc)
+    scored = st["mask_by_token"] > 0.5
+    assert torch.isfinite(loss) and float(st["mask_count"]) == float(scored.sum())
+    assert torch.allclose(st["mask_by_seq"], scored.sum(1).float())
+    assert not bool(scored[:, 0].any())                                        # per-token arrays are indexed by the TARGET token
+    assert bool(scored[:, 1:].any())
