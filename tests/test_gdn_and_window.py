@@ -111,3 +111,20 @@ def test_the_shifted_outer_loss_scores_the_masked_targets_from_slot_one_on():
     assert torch.allclose(st["mask_by_seq"], scored.sum(1).float())
     assert not bool(scored[:, 0].any())                                        # per-token arrays are indexed by the TARGET token
     assert bool(scored[:, 1:].any())
+
+
+def test_the_reread_layout_scores_the_same_tail_under_the_same_masks():
+    """Re-read evaluation (the reference's tests/test_reread.py): the first n chunks run twice with the window restarted at the
+    second pass and only the tail is scored; its outer masks are exactly those of the single pass, so the benefit of re-reading is a
+    paired difference."""
+    eng = make_engine(mc=tiny_model(window_chunks=2), seq_len=64)
+    lc = dc.replace(loss_config(eng.tc), segment_chunks=2, score_from_chunk=2)
+    ids = torch.randint(1, 120, (2, 64), generator=torch.Generator().manual_seed(0))
+    keys = torch.stack([rng.fold_in(rng.key(9), j) for j in range(2)])
+    net = Net(eng.mc, ComputeWeights(eng.store))
+    with torch.no_grad():
+        single, s1 = loss_fn(net, Batch(ids), keys, 3, lc)
+        again, s2 = loss_fn(net, Batch(ids), keys, 3, dc.replace(lc, reread_chunks=2))
+    assert torch.equal(s1["mask_by_chunk"], s2["mask_by_chunk"]) and float(s1["mask_by_chunk"][0]) == 0.0
+    assert float(s1["mask_count"]) == float(s2["mask_count"])
+    assert torch.isfinite(again) and float(again) != float(single)             # the memory has seen the first chunks twice
