@@ -180,3 +180,39 @@ def test_init_from_tolerates_new_heads_and_narrows_a_wider_fast_weight(tmp_path)
     assert np.allclose(narrow.store.gather_full("fast_weight.gate.weight").numpy()[0], g[0][:, keep[0]])
     with pytest.raises(ValueError, match="narrower"):
         CK.load_weights(CK.save(str(tmp_path / "ck2"), 0, narrow, "h"), make_engine(mc=tiny_model(ttt_intermediate_size=96)))
+
+
+def test_prepare_tokenises_parquet_into_a_stream_once(tmp_path):
+    """Raw parquet -> ``tokens.u32`` + ``meta.json`` with the shipped tokenizer: one EOS after every document, the directory is
+    named by a hash of (files, tokenizer, options) so a second call does nothing, short documents are dropped on request, and
+    the grouped form keeps the rows of a group adjacent and in order (a group is kept or dropped as a whole)."""
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    from util import ROOT
+    tokenizer = os.path.join(ROOT, "configs/1b_e2e")
+    docs = [f"Document number {i}. " + "The quick brown fox jumps over the lazy dog. " * (i % 5 + 1) for i in range(23)]
+    raw = str(tmp_path / "raw.parquet")
+    pq.write_table(pa.table({"text": docs}), raw, row_group_size=10)
+    out = prep.prepare("toy", [raw], "text", tokenizer, str(tmp_path / "tok"), workers=2)
+    meta = json.load(open(os.path.join(out, "meta.json")))
+    stream = np.fromfile(os.path.join(out, "tokens.u32"), dtype="<u4")
+    eos = meta["tokenizer"]["eos_token_id"]
+    assert meta["num_docs"] == 23 and meta["num_tokens"] == len(stream) and int((stream == eos).sum()) == 23 and stream[-1] == eos
+    lengths = prep.doc_lengths(out)
+    assert len(lengths) == 23 and int(lengths.sum()) == len(stream) and (np.diff(lengths[:5]) > 0).all()
+    assert prep.prepare("toy", [raw], "text", tokenizer, str(tmp_path / "tok"), workers=2) == out          # already prepared
+    longer = prep.prepare("toy", [raw], "text", tokenizer, str(tmp_path / "tok"), min_doc_tokens=40, workers=2)
+    assert longer != out and json.load(open(os.path.join(longer, "meta.json")))["num_docs"] == int((lengths - 1 >= 40).sum())
+    counts = prep.unigram_counts([out], 128256)
+    assert counts.sum() == len(stream) and counts[eos] == 23
+    pages = pa.table({"book": ["b", "a", "b", "a", "a"], "page": ["2", "1", "1", "3", "2"],
+                      "text": ["b two.", "a one.", "b one.", "a three.", "a two."]})
+    grouped_raw = str(tmp_path / "pages.parquet")
+    pq.write_table(pages, grouped_raw)
+    grouped = prep.prepare_grouped("books", [grouped_raw], "text", "book", "page", tokenizer, str(tmp_path / "tok"), 0, workers=1)
+    gmeta = json.load(open(os.path.join(grouped, "meta.json")))
+    assert gmeta["num_groups"] == 2 and gmeta["num_docs"] == 5 and len(prep.doc_lengths(grouped)) == 5      # pages stay documents
+    from transformers import PreTrainedTokenizerFast
+    tok = PreTrainedTokenizerFast.from_pretrained(tokenizer)
+    text = tok.decode([int(t) for t in np.fromfile(os.path.join(grouped, "tokens.u32"), dtype="<u4") if t != eos])
+    assert text.replace(" ", "") == "aone.atwo.athree.bone.btwo."                                           # groups and pages in order
