@@ -163,7 +163,8 @@ def load_weights(d: str, engine, log=print) -> None:
     """Weights only, into the engine's sharded store (every rank reads the file)."""
     mc: ModelConfig = engine.mc
     saved = _saved_config(d)
-    saved_spec = param_spec(ModelConfig(**{k: v for k, v in saved.items()})) if saved is not None else engine.spec
+    # through the schema loader: a file written by the reference or by an older run may still carry retired keys at their "off" value
+    saved_spec = param_spec(ModelConfig.load(os.path.join(d, "model_config.json"))) if saved is not None else engine.spec
     missing = [n for n in engine.spec if n not in saved_spec]
     for n in missing:
         field = n.split(".")[0]
@@ -195,7 +196,10 @@ def load_weights(d: str, engine, log=print) -> None:
 
 
 def load_opt(d: str, engine) -> None:
-    """Optimiser state into the engine's shards (same model structure required)."""
+    """Optimiser state into the engine's shards (same model structure required).  The file holds whole tensors (``save``
+    re-assembles tensor-parallel slices), so under tensor parallelism every moment is cut to this rank's slice first, exactly
+    as ``ParamStore.load_full`` cuts the weights."""
+    from ..models.params import tp_slice
     st, opt = engine.store, engine.opt
     names = list(st.names())
     it = NS.read_records(os.path.join(d, "opt.eqx"))
@@ -204,7 +208,12 @@ def load_opt(d: str, engine) -> None:
         for name in names:
             arr = next(it)
             space, off, n, shape = st.slots[name]
-            v = torch.from_numpy(np.ascontiguousarray(arr.astype(np.float32))).reshape(-1)
+            full = torch.from_numpy(np.ascontiguousarray(arr.astype(np.float32)))
+            if st.tp_layout.get(name) is not None and tuple(full.shape) != tuple(shape):
+                full = tp_slice(name, full, engine.mesh.tp, engine.mesh.tp_index)
+            v = full.reshape(-1)
+            if v.numel() != n:
+                raise ValueError(f"checkpoint {d}: optimiser leaf of {name} has {v.numel()} elements, this rank stores {n}")
             lo, hi = st.shard_range(space)
             a, b = max(off, lo), min(off + n, hi)
             if a < b:

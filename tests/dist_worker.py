@@ -50,6 +50,24 @@ def main():
             torch.save({"ce_sum": float(tot[0]), "count": float(tot[1]), "grads": grads, "metrics": ms, "params": full,
                         "ev_loss": float(ev_loss), "ev_by_seq": ev["loss_by_seq"], "ev_count": float(ev["mask_count"]),
                         "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
+    elif case == "tp_resume":
+        # two steps, save, two more; a fresh engine of the same mesh restored from the checkpoint must take the same two steps
+        for s in range(2):
+            eng.train_step(ids, s)
+        d = CK.save(os.path.join(out, "ck"), 2, eng, "h")
+        moments = {k: (eng.store.gather_full(k, eng.opt.m), eng.store.gather_full(k, eng.opt.v)) for k in eng.store.names()}
+        for s in range(2, 4):
+            eng.train_step(ids, s)
+        cont = {k: eng.store.gather_full(k) for k in eng.store.names()}
+        eng2 = Engine(tiny_model(), tiny_train(batch_size=4, fsdp_size=fsdp, tp_size=tp), mesh, torch.device("cpu"))
+        CK.load_weights(d, eng2)
+        CK.load_opt(d, eng2)
+        eng2.store.sync_compute()
+        for s in range(2, 4):
+            eng2.train_step(ids, s)
+        resumed = {k: eng2.store.gather_full(k) for k in eng2.store.names()}
+        if rank == 0:
+            torch.save({"cont": cont, "resumed": resumed, "moments": moments, "mesh": mesh.shape()}, os.path.join(out, "result.pt"))
     elif case == "rank_exits":
         # rank 1 leaves between steps (no collective in flight); the others must get an error, not hang
         eng.train_step(mine, 0)

@@ -79,6 +79,30 @@ def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp):
         assert torch.equal(eng.store.gather_full(k), v), k
 
 
+def test_tensor_parallel_resume_restores_the_optimiser_slices(tmp_path):
+    """tp = 2: a checkpoint holds whole tensors; restoring it must hand every rank ITS slice of the Adam moments (column
+    slices of Q / K / V / gate / up, row slices of o / down), so that the resumed run takes bit-identical steps, and a
+    single-process engine must read back the same whole moments."""
+    r = launch(2, "tp_resume", tmp_path, {"TEST_FSDP": "1", "TEST_TP": "2"})
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    res = torch.load(tmp_path / "result.pt", weights_only=False)
+    assert res["mesh"]["tp"] == 2
+    for k, v in res["cont"].items():
+        assert torch.equal(res["resumed"][k], v), k
+    from dttt_b200.ckpt import store as CK
+    eng = make_engine(batch_size=4)
+    d = str(tmp_path / "ck" / "step_00000002")
+    CK.load_weights(d, eng)
+    CK.load_opt(d, eng)
+    assert eng.opt.count == 2
+    moved = 0
+    for k, (m, v) in res["moments"].items():
+        assert torch.equal(eng.store.gather_full(k, eng.opt.m), m), k
+        assert torch.equal(eng.store.gather_full(k, eng.opt.v), v), k
+        moved += int(m.abs().sum() > 0)
+    assert moved > 10
+
+
 def test_a_rank_that_leaves_is_detected(tmp_path):
     # plain child processes (an elastic launcher would tear the survivors down itself)
     port = str(29900 + os.getpid() % 90)
