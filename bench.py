@@ -89,20 +89,130 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def _reference_root():
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+
+
 def reference_arm(args) -> int:
-    """The reference is a JAX / Equinox / Optax program; none of the three is installed in this image and no
-    index is reachable, so the reference arm cannot run."""
-    why = "reference needs jax 0.11 + equinox + optax (not in the image or the offline wheelhouse); import jax fails"
-    try:
-        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref"))
-        import jax  # noqa: F401
-        import equinox  # noqa: F401
-        import optax  # noqa: F401
-        why = "jax present but the reference arm is not wired for this image"
-    except Exception:
-        pass
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+    """The unmodified reference (``baseline/_ref``, a JAX / Equinox / Optax program) through its own entry point,
+    ``python -m ttt.train --config <run.json>``, on Zipf token streams written in its on-disk format and the run
+    configuration of the same benchmark; tokens/s from its own log lines.  The reference is one SPMD process over all
+    local devices, so rank 0 of a torchrun launch drives it and the other ranks only wait.  Prints ``unavailable`` when the
+    reference or one of its dependencies cannot be imported in this image."""
+    rank = int(os.environ.get("RANK", "0"))
+    root = _reference_root()
+    why = None
+    if not os.path.isdir(os.path.join(root, "ttt")):
+        why = ("reference not installed: pip install of /root/reference needs the hatchling build backend, which is neither in "
+               "the image nor in the offline wheelhouse; baseline/_ref is empty")
+    else:
+        import importlib.util
+        missing = [m for m in ("jax", "equinox", "optax", "jaxtyping") if importlib.util.find_spec(m) is None]
+        if missing:
+            why = f"reference needs {', '.join(missing)} (not in the image or the offline wheelhouse)"
+    if why is None and importlib.util.find_spec("jax") is None:
+        why = "reference needs jax 0.11 + equinox + optax (not in the image or the offline wheelhouse); import jax fails"
+    if why is not None:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    if rank != 0:
+        return 0
+    import re
+    import tempfile
+    import numpy as np
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, here)
+    from dttt_b200.data.synth import write_stream, zipf_tokens
+    from dttt_b200.schema import ModelConfig
+    spec = CONFIGS[args.config]
+    mc = ModelConfig.load(os.path.join(here, spec["model"]))
+    W, K = max(3, args.warmup), max(1, args.steps)
+    per_gpu = args.seqs_per_gpu or spec["seqs_per_gpu"]
+    micro = min(args.micro or spec["micro"], per_gpu)
+    T = spec["seq_len"]
+    work = tempfile.mkdtemp(prefix="dttt_ref_")
+    toks = zipf_tokens((W + K + 2) * per_gpu * args.gpus * T + T, mc.vocab_size, seed=1234, eos=mc.eos_token_id,
+                       mean_doc=spec["mean_doc"], exclude=(mc.mask_token_id, mc.pad_token_id, mc.bos_token_id or -1))
+    write_stream(os.path.join(work, "tokens", "zipf"), toks, mc.eos_token_id, vocab=mc.vocab_size)
+    run = dict(model_config=os.path.join(here, spec["model"]), data_root=os.path.join(work, "tokens"), sources="zipf=zipf:1.0",
+               seq_len=T, batch_size=micro * args.gpus, grad_accum=per_gpu // micro, steps=W + K, seed=0, lr=1e-3, end_lr=1e-4,
+               warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal", outer_shift=True, second_order=True,
+               fsdp_size=args.gpus, ckpt_dir=os.path.join(work, "ckpt"), ckpt_interval=10 ** 9, log_interval=1, eval_interval=0,
+               **{k: v for k, v in spec["extra"].items() if not k.startswith("keep_")})
+    cfg_path = os.path.join(work, "run.json")
+    with open(cfg_path, "w") as fh:
+        json.dump(run, fh)
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    r = subprocess.run([sys.executable, "-u", "-m", "ttt.train", "--config", cfg_path], env=env, capture_output=True, text=True, cwd=work)
+    rows = re.findall(r"\[\s*(\d+)\]\s+loss\s+([0-9.eE+-]+).*?([0-9.]+)s/step", r.stdout)
+    timed = [float(dt) for step, _, dt in rows if int(step) >= W]
+    if r.returncode != 0 or not timed:
+        print(json.dumps({"impl": "reference", "unavailable": "reference run failed: " + (r.stderr or r.stdout)[-300:].replace("\n", " ")}))
+        return 0
+    sec = float(np.mean(timed))
+    tokens = per_gpu * args.gpus * T
+    print(json.dumps({"impl": "reference", "metric": "train tokens/s (whole job)", "value": tokens / sec, "unit": "tokens/s",
+                      "n_gpus": args.gpus, "steps": len(timed), "warmup": W, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                      "scaling": "weak", "dtype": "bf16", "data": "synthetic Zipf(1.1) tokens in the reference's stream format; random-init weights",
+                      "timing": "the reference's own wall-clock s/step log lines (its step blocks on the metrics)",
+                      "config": {"model": spec["model"], "global_batch": per_gpu * args.gpus, "seq_len": T, "parallelism": f"fsdp{args.gpus}"},
+                      "final_loss": float(rows[-1][1])}))
+    return 0
+
+
+def held_out_loss(eng, mc, spec, seqs: int, T: int) -> float:
+    """Unweighted masked-token cross-entropy of the current weights on one fixed held-out batch (the same tokens, noise
+    levels and masks on every rank and for every mesh): what a 1-GPU run, an FSDP run and a tensor-parallel run of the same
+    global batch can be compared on.  Fixed noise levels stratified over the batch, row-wise keys, no time re-weighting."""
+    import dataclasses as dc
+    import numpy as np
+    import torch
+    from dttt_b200.data.synth import zipf_tokens
+    from dttt_b200.ttt.scan import Batch
+    from dttt_b200.utils import rng
+    seqs = max(seqs, eng.mesh.tp)
+    toks = zipf_tokens(seqs * T, mc.vocab_size, seed=99_991, eos=mc.eos_token_id, mean_doc=spec["mean_doc"],
+                       exclude=(mc.mask_token_id, mc.pad_token_id, mc.bos_token_id or -1))
+    ids = torch.from_numpy(toks.astype(np.int64)).view(seqs, T)
+    t = (torch.arange(seqs, dtype=torch.float32) + 0.5) / seqs
+    lcfg = dc.replace(eng.lcfg, time_reweighting="none", self_prior=0.0, window_drop=0.0)
+    loss, _ = eng.eval_step(Batch(ids, outer_t=t), rng.split(rng.key(4242), seqs), 0, lcfg)
+    return float(loss)
+
+
+def cpu_baseline(args, spec, mc, mesh, W: int, K: int) -> int:
+    """The small CPU configuration (2 layers, d_model 128, 4 heads of 32, SwiGLU 512, window 128, chunk 64, the last layer's
+    MLP a fast weight, vocabulary 1024): fp32, AdamW lr 1e-3, batch 2 x 512 Zipf tokens, timed with the wall clock."""
+    import numpy as np
+    import torch
+    from dttt_b200.data.synth import zipf_tokens
+    from dttt_b200.engine import Engine
+    from dttt_b200.schema import TrainConfig
+    T, B = spec["seq_len"], spec["seqs_per_gpu"]
+    tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=B, grad_accum=1, steps=W + K, seed=0, lr=1e-3, end_lr=1e-3,
+                     warmup_steps=0, inner_lr_warmup_steps=0, inner_task="causal", outer_shift=True, second_order=True,
+                     compute_dtype="float32", **spec["extra"])
+    eng = Engine(mc, tc, mesh, torch.device("cpu"))
+    toks = zipf_tokens((W + K) * B * T, mc.vocab_size, seed=0, eos=mc.eos_token_id, mean_doc=spec["mean_doc"],
+                       exclude=(mc.mask_token_id, mc.pad_token_id))
+    ids = torch.from_numpy(toks.astype(np.int64)).view(W + K, B, T)
+    losses = []
+    for s in range(W):
+        losses.append(eng.train_step(ids[s], s)["main_loss"])
+    t0 = time.perf_counter()
+    for s in range(W, W + K):
+        losses.append(eng.train_step(ids[s], s)["main_loss"])
+    sec = time.perf_counter() - t0
+    print(json.dumps({"metric": "train tokens/s (whole job)", "value": B * T * K / sec, "unit": "tokens/s", "n_gpus": 0, "device": "cpu",
+                      "steps": K, "warmup": W, "ms_per_step": sec / K * 1e3, "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "fp32", "data": "synthetic Zipf(1.1) tokens, EOS at geometric boundaries (mean 200); random-init weights",
+                      "config": {"model": "tiny (CPU baseline): " + spec["model"], "global_batch": B, "seq_len": T, "parallelism": "cpu",
+                                 "timing": "wall clock (no device)", "threads": torch.get_num_threads()},
+                      "gpu_launches": 0, "first_loss": losses[0], "final_loss": losses[-1],
+                      "eval_loss": held_out_loss(eng, mc, spec, B, T)}))
     return 0
 
 
@@ -140,9 +250,13 @@ def main() -> int:
     rank, world, local = init_distributed()
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
     spec = CONFIGS[args.config]
+    on_gpu = torch.cuda.is_available()
+    if not on_gpu and args.config != "tiny":
+        raise SystemExit("no CUDA device: only --config tiny (the CPU baseline configuration, fp32) runs without one")
+    if on_gpu:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local) if on_gpu else torch.device("cpu")
     mesh = make_mesh(args.fsdp, args.tp, dev)
     mc = ModelConfig.load(os.path.join(here, spec["model"]))
     per_gpu = args.seqs_per_gpu or spec["seqs_per_gpu"]
@@ -152,13 +266,15 @@ def main() -> int:
     extra = dict(spec["extra"], **({"keep_prefix_layers": args.keep_prefix_layers} if args.keep_prefix_layers >= 0 else {}),
                  **({"keep_suffix_chunks": args.keep_suffix_chunks} if args.keep_suffix_chunks >= 0 else {}))
     # resident graphs need the whole part: with less than RESIDENT_MIN_FREE_GIB free on any rank the regions recompute instead
-    free = torch.tensor([torch.cuda.mem_get_info(dev)[0] / 2 ** 30], device=dev)
+    free = torch.tensor([torch.cuda.mem_get_info(dev)[0] / 2 ** 30 if on_gpu else 0.0], device=dev)
     if world > 1:
         dist.all_reduce(free, op=dist.ReduceOp.MIN)
     note = None
     if (extra.get("keep_prefix_layers") or extra.get("keep_suffix_chunks")) and free.item() < RESIDENT_MIN_FREE_GIB:
         extra.update(keep_prefix_layers=0, keep_suffix_chunks=0)
         note = f"{free.item():.0f} GiB free: recompute regions instead of resident graphs"
+    if not on_gpu:
+        return cpu_baseline(args, spec, mc, mesh, W, K)
     tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
                      seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
                      outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **extra)
@@ -241,6 +357,7 @@ def main() -> int:
                    "keep_prefix_layers": extra.get("keep_prefix_layers", 0), "keep_suffix_chunks": extra.get("keep_suffix_chunks", 0),
                    **({"note": note} if note else {})},
         "clocks": ck, "gpu_launches": launches, "final_loss": last.get("main_loss") if last else None,
+        "eval_loss": held_out_loss(eng, mc, spec, micro, T),
     }
     if ms_e2e is not None:
         out["e2e"] = {"value": tokens_per_step * K / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / K,

@@ -756,38 +756,64 @@ static int make_map(CUtensorMap* map, const void* ptr, long long inner, long lon
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-static int g_num_sms = 0;
+// Per-device launch state: a kernel's shared-memory attribute and the SM count belong to a device, and one process may
+// drive several (a C host without one-process-per-GPU).  Guarded by a mutex; indexed by the CUDA device ordinal.
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  int num_sms = 0;
+  unsigned long long attr_mask = 0;        // bit i: kernel form i has its dynamic shared-memory attribute set on this device
+};
+static DeviceState g_dev[kMaxDevices];
+static std::mutex g_dev_mutex;
 
-static int bind_thread_context() {
-  // The tensor-map encoder is a driver call and needs a current context in the calling thread.  Autograd
-  // runs backward passes on its own threads, where no runtime call may have bound the primary context yet:
-  // bind it once per thread.
-  static thread_local bool ctx_bound = false;
-  if (!ctx_bound) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaSetDevice(dev);
-    cudaFree(0);
-    ctx_bound = true;
-  }
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
+static int num_sms() {
+  const int dev = current_device();
+  if (dev < 0) return 148;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (g_dev[dev].num_sms == 0) cudaDeviceGetAttribute(&g_dev[dev].num_sms, cudaDevAttrMultiProcessorCount, dev);
+  return g_dev[dev].num_sms > 0 ? g_dev[dev].num_sms : 148;
+}
+
+// Run `set` once per (device, kernel form).
+template <class F>
+static void once_per_device(int form, F set) {
+  const int dev = current_device();
+  if (dev < 0) { set(); return; }
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!(g_dev[dev].attr_mask >> form & 1ull)) { set(); g_dev[dev].attr_mask |= 1ull << form; }
+}
+
+// The tensor-map encoder is a driver call and needs a current context in the calling thread.  Autograd runs backward
+// passes on its own threads, where no runtime call may have bound the primary context yet: bind it once per thread and
+// device.  `may_allocate = false` (the allocation-free entry point) binds with cudaSetDevice alone, which initialises the
+// primary context since CUDA 12 without touching the allocator.
+static int bind_thread_context(bool may_allocate = true) {
+  static thread_local int bound_dev = -1;
+  const int dev = current_device();
+  if (dev < 0) return -1;
+  if (bound_dev != dev) {
+    if (cudaSetDevice(dev) != cudaSuccess) return -1;
+    if (may_allocate) cudaFree(0);
+    bound_dev = dev;
   }
   return 0;
 }
 
 template <int BN, int MODE>
 static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, int max_ctas, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
+  once_per_device((BN == 256 ? 0 : 8) + MODE, [] {
     cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL);
-    attr_set = true;
-  }
+  });
+  const int sms = num_sms();
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
-  int cap = (max_ctas > 0 && max_ctas < g_num_sms) ? max_ctas : g_num_sms;
+  int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   int grid = (int)(tiles < cap ? tiles : cap);
   gemm_bf16_kernel<BN, MODE><<<grid, MODE == EPI_AG ? 320 : 192, MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
@@ -795,13 +821,10 @@ static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const G
 }
 
 static int launch_gemm256(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm256_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem256::TOTAL);
-    attr_set = true;
-  }
+  once_per_device(16, [] { cudaFuncSetAttribute(gemm256_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem256::TOTAL); });
+  const int sms = num_sms();
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
-  int grid = (int)(tiles < g_num_sms ? tiles : g_num_sms);
+  int grid = (int)(tiles < sms ? tiles : sms);
   gemm256_bf16_kernel<<<grid, 320, Smem256::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
@@ -819,7 +842,7 @@ static bool use_256_rows(int M, int N, int K, int batch, int max_ctas) {
   if (mode == 0 || max_ctas > 0) return false;
   if (mode == 1) return true;
   if (K < 8192) return false;               // measured: +2 % at K = 8192, +12 % at K = 49152, -6 % at K = 2048 (the exposed epilogue)
-  const long long sms = g_num_sms > 0 ? g_num_sms : 148;
+  const long long sms = num_sms();
   auto eff = [&](long long tiles) { return (double)tiles / (double)(((tiles + sms - 1) / sms) * sms); };
   const long long tn = (N + 255) / 256;
   const long long t128 = (long long)batch * ((M + 127) / 128) * tn, t256 = (long long)batch * ((M + 255) / 256) * tn;
@@ -908,13 +931,14 @@ extern "C" long long dttt_linear_ce_scratch_elems(int rows, int classes) {
   return stride * ((classes + 255) / 256);
 }
 
-// Shared by the entry points that differ only in where the scratch comes from.
+// Shared by the entry points that differ only in where the scratch comes from.  `may_allocate = false`: the calling
+// thread's context is bound without any allocator call (the allocation-free entry point).
 int dttt_linear_ce_fwd_impl(const void* h, const void* E, const int* targets, int rows, int classes, int K, long long ldh,
                             long long ldE, void* scratch, float* tgt_logit, float* lse, float* nll, int* status,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, bool may_allocate = true) {
   if (rows <= 0 || classes <= 0 || K <= 0) return 0;
   if ((ldh % 8) || (ldE % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(E) & 15)) return -2;
-  bind_thread_context();
+  if (bind_thread_context(may_allocate)) return -3;
   CUtensorMap mapA, mapB;
   int r;
   if ((r = make_map(&mapA, h, K, rows, 1, ldh, 0, BM))) return 100 + r;
@@ -1079,7 +1103,8 @@ extern "C" int dttt_gemm_rs_bf16(const void* A, const void* B, void* const* peer
   p.m_rotate = self * (p.rows_per_rank / BM);
   p.done_counter = done_counter;
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
-  const int grid = (int)(tiles < g_num_sms ? tiles : g_num_sms);
+  const int sms = num_sms();
+  const int grid = (int)(tiles < sms ? tiles : sms);
   {
     std::lock_guard<std::mutex> lock(g_done_mutex);
     p.done_target = (g_done_count[done_counter] += grid);
@@ -1111,27 +1136,19 @@ extern "C" int dttt_tp_slot_reduce(const void* slots, const int* landed_flags, i
 static __device__ __align__(256) float2 g_linear_ce_scratch[DTTT_LINEAR_CE_STATIC_MAX_ELEMS];
 
 namespace {
-constexpr int kMaxDevices = 64;
-float2* g_scratch_addr[kMaxDevices] = {nullptr};
+float2* g_scratch_addr[dttt::kMaxDevices] = {nullptr};
 std::mutex g_scratch_mutex;
 
 // Device address of the array on the current device.  The array's name is a host-side handle, not a device
-// pointer: the address comes from cudaGetSymbolAddress, once per device.
+// pointer: the address comes from cudaGetSymbolAddress, once per device, with that device current.
 int static_scratch(float2** out) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
-  // The tensor-map encoder is a driver call: the device's primary context has to be current in the calling thread.
-  static thread_local int bound_dev = -1;
-  if (bound_dev != dev) {
-    if (cudaSetDevice(dev) != cudaSuccess) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
-    bound_dev = dev;
-  }
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= dttt::kMaxDevices) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_addr[dev]) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_linear_ce_scratch) != cudaSuccess || !ptr) return DTTT_LINEAR_CE_STATIC_SETUP_FAILED;
     g_scratch_addr[dev] = reinterpret_cast<float2*>(ptr);
-    if (g_num_sms == 0) cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   }
   *out = g_scratch_addr[dev];
   return 0;
@@ -1147,6 +1164,7 @@ extern "C" const char* dttt_linear_ce_static_strerror(int code) {
     case DTTT_LINEAR_CE_STATIC_SETUP_FAILED:
       return "dttt_linear_ce_fwd_static: could not resolve the device address of the scratch array on the current device";
     case -2: return "dttt_linear_ce_fwd_static: operands must be 16-byte aligned with row strides that are multiples of 8 elements";
+    case -3: return "dttt_linear_ce_fwd_static: no usable current CUDA device in the calling thread";
     default: return "dttt_linear_ce_fwd_static: launch failed (tensor-map encoding or kernel launch error)";
   }
 }
@@ -1156,22 +1174,9 @@ extern "C" int dttt_linear_ce_fwd_static(const void* h, const void* E, const int
                                          cudaStream_t stream) {
   if (rows <= 0 || classes <= 0 || K <= 0) return 0;
   if (dttt_linear_ce_scratch_elems(rows, classes) > DTTT_LINEAR_CE_STATIC_MAX_ELEMS) return DTTT_LINEAR_CE_STATIC_TOO_LARGE;
-  if ((ldh % 8) || (ldE % 8) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(E) & 15)) return -2;
   float2* scratch = nullptr;
-  int r = static_scratch(&scratch);
+  const int r = static_scratch(&scratch);
   if (r) return r;
-  CUtensorMap mapA, mapB;
-  if ((r = make_map(&mapA, h, K, rows, 1, ldh, 0, BM))) return 100 + r;
-  if ((r = make_map(&mapB, E, K, classes, 1, ldE, 0, 256))) return 200 + r;
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  p.M = rows; p.N = classes; p.K = K; p.batch = 1; p.alpha = 1.f; p.status = status;
-  p.tiles_m = (rows + BM - 1) / BM;
-  p.tiles_n = (classes + 255) / 256;
-  p.targets = targets; p.part = scratch; p.tgt_logit = tgt_logit;
-  p.part_stride = (long long)p.tiles_m * BM;
-  if ((r = launch_gemm<256, EPI_CE_PARTIAL>(mapA, mapB, p, 0, stream))) return r;
-  ce_combine_kernel<<<(rows + 31) / 32, dim3(32, 8), 0, stream>>>(scratch, p.part_stride, p.tiles_n, rows, tgt_logit, lse, nll);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : 2000 + (int)e;
+  // the one body both entry points run; told not to touch the allocator while binding the thread's context
+  return dttt_linear_ce_fwd_impl(h, E, targets, rows, classes, K, ldh, ldE, scratch, tgt_logit, lse, nll, status, stream, false);
 }

@@ -18,7 +18,8 @@
 // launched; dttt_linear_ce_static_strerror() gives the message.
 //
 // Set-up: the first call on a device (with that device current) resolves the array's device address, sets the
-// kernel's shared-memory attribute and loads the kernels; make that first call before any stream capture begins.
+// kernel's shared-memory attribute for that device and loads the kernels; make that first call before any stream
+// capture begins.  The state is kept per device, so one process may call this on several devices in turn.
 // Sharing: every call on a device uses the same array.  Nothing in it has to start at zero (each entry that is read
 // was written earlier by the same call), but two calls in flight at once -- on different streams, or from different
 // threads without ordering between their streams -- race on it and give wrong results.  Calls on one stream are safe.

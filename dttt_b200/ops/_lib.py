@@ -112,3 +112,20 @@ def check_status(device=None, reset: bool = True) -> None:
 
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
+
+
+register("dttt_wait_selftest", ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p])
+
+
+def wait_selftest(flag: torch.Tensor, target: int, limit_ms: float = 2.0) -> torch.Tensor:
+    """Launch the bounded-wait self-test: a kernel that waits at most ``limit_ms`` for ``flag[0] >= target`` and, when the
+    wait runs out, records the self-test code in the status word (``check_status`` then raises).  Returns a one-element
+    int32 tensor that receives the microseconds waited."""
+    waited = torch.zeros(1, dtype=torch.int32, device=flag.device)
+    st = status_tensor(flag.device)
+    rc = lib().dttt_wait_selftest(ctypes.c_void_p(flag.data_ptr()), int(target), int(limit_ms * 1e6), ctypes.c_void_p(st.data_ptr()),
+                                  ctypes.c_void_p(waited.data_ptr()), ctypes.c_void_p(stream_ptr()))
+    if rc != 0:
+        raise KernelError(f"dttt_wait_selftest launch failed rc={rc}")
+    return waited

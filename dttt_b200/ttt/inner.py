@@ -111,6 +111,20 @@ def seq_norm(ts: Sequence[torch.Tensor]) -> torch.Tensor:
     return torch.sqrt(sq + 1e-8)
 
 
+_FRAC_MASKS = {}
+
+
+def _update_frac_mask(i: int, shape, frac: float, device) -> torch.Tensor:
+    """The bool mask of leaf ``i`` kept by ``inner_update_frac``: ``uniform(key(7919 + i), shape) < frac`` on the threefry
+    generator, cached (it does not depend on the step or the data)."""
+    k = (i, shape, frac, str(device))
+    m = _FRAC_MASKS.get(k)
+    if m is None:
+        from ..utils import rng as _rng
+        m = _FRAC_MASKS[k] = _rng.bernoulli(_rng.key(7919 + i), frac, shape).to(device)
+    return m
+
+
 def _bcast(v: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
     return v.reshape(v.shape + (1,) * (t.dim() - v.dim()))
 
@@ -464,10 +478,8 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
                 out.append(u[3 * f + j] * torch.exp(a)[None, :, None] * torch.exp(b)[None, None, :])
         u = out
     if frac < 1.0:
-        masks = []
-        for i, x in enumerate(u):
-            gen = torch.Generator(device="cpu").manual_seed(7919 + i)
-            masks.append((torch.rand(x.shape[1:], generator=gen) < frac).to(x.device, x.dtype))
+        # fixed write dimensions, one draw per leaf from the counter generator (reference inner_loop.py: bernoulli(PRNGKey(7919 + i)))
+        masks = [_update_frac_mask(i, tuple(x.shape[1:]), float(frac), x.device).to(x.dtype) for i, x in enumerate(u)]
         um = [x * m for x, m in zip(u, masks)]
         ratio = seq_norm(u) / seq_norm(um)
         u = [x * _bcast(ratio, x) for x in um]

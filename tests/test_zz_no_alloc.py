@@ -38,11 +38,16 @@ def test_static_scratch_matches_ordinary_entry_point_twice():
         nll = torch.empty(N, device="cuda")
         torch.cuda.synchronize()
         before = torch.cuda.memory_stats().get("allocation.all.allocated", 0)
+        free_before = torch.cuda.mem_get_info()[0]
         rc = f(h.data_ptr(), E.data_ptr(), y.data_ptr(), N, V, K, h.stride(0), E.stride(0), tgt.data_ptr(), lse.data_ptr(),
                nll.data_ptr(), st.data_ptr(), stream)
         assert rc == 0, strerror(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_stats().get("allocation.all.allocated", 0) == before      # nothing went through torch's allocator
+        if call == 1:
+            # ... and nothing went to the driver behind its back either: once the first call has loaded the kernels, a call
+            # leaves the device's free memory where it was (a raw cudaMalloc / cudaFree inside the library would move it)
+            assert torch.cuda.mem_get_info()[0] == free_before
         _lib.check_status()
         lse_ref, nll_ref = kernels.linear_ce_fwd(h, E, y)
         torch.cuda.synchronize()
