@@ -216,3 +216,21 @@ def test_prepare_tokenises_parquet_into_a_stream_once(tmp_path):
     tok = PreTrainedTokenizerFast.from_pretrained(tokenizer)
     text = tok.decode([int(t) for t in np.fromfile(os.path.join(grouped, "tokens.u32"), dtype="<u4") if t != eos])
     assert text.replace(" ", "") == "aone.atwo.athree.bone.btwo."                                           # groups and pages in order
+
+
+def test_host_targets_match_recorded_vectors():
+    """The ranking terms, the 3-gram hash and the shuffle seeding are a contract shared with the reference
+    (src/ttt/inner_masks.py): the same tokens must give the same targets.  Vectors recorded from the loop-per-chunk statement."""
+    toks = np.random.default_rng(7).integers(0, 40, 64)
+    toks[5] = 39; toks[30] = 39; toks[40:44] = 38
+    uni = np.random.default_rng(8).integers(1, 500, 40).astype(np.int64)
+    m = inner_mask_rule(toks, "docaware", 16, 39, 38, uni, 0.5, 0.1, 3)
+    assert "".join("1" if x else "0" for x in m) == "1110101010100001111010110101000000110110000011111110001011101000"
+    p = split_perm(toks, "docaware", 16, 39, 38, 0.5, uni, 0.1, 3)
+    assert p.tolist() == [3, 5, 7, 9, 11, 12, 13, 14, 1, 2, 6, 0, 4, 10, 15, 8, 19, 21, 24, 26, 28, 29, 30, 31, 18, 22, 25, 20, 23, 17,
+                          16, 27, 32, 33, 36, 39, 40, 41, 42, 43, 37, 44, 47, 34, 46, 45, 35, 38, 51, 52, 53, 55, 59, 61, 62, 63, 54, 56,
+                          57, 49, 50, 60, 58, 48]
+    # a chunk of pads has no ranked target: the split order takes its targets from the end of the context
+    pads = np.full(16, 38)
+    q = split_perm(pads, "rare", 16, 39, 38, 0.5, uni, 0.1, 0)
+    assert sorted(q.tolist()) == list(range(16)) and q[:8].tolist() == list(range(8))
