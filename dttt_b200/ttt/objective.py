@@ -33,17 +33,16 @@ def q_sample(key: torch.Tensor, ids: torch.Tensor, loss_mask: Optional[torch.Ten
     Returns ``(x_t [B,T], t [B], t_mask [B,T])``."""
     B, T = ids.shape
     dev = ids.device
-    key = key.to(dev)
-    if key.dim() == 2:
-        ks = rng.split(key, 2)                      # [B, 2, 2]
+    # keys are derived where the key lives; the per-token draw happens on the tokens' device
+    ks = rng.split(key, 2)
+    if key.dim() == 2:                              # row-wise keys [B, 2]
         if t is None:
             t = rng.uniform(ks[:, 0], ())
-        u = rng.uniform(ks[:, 1], (T,))
+        u = rng.uniform(ks[:, 1].to(dev), (T,))
     else:
-        ks = rng.split(key, 2)
         if t is None:
             t = rng.uniform(ks[0], (B,))
-        u = rng.uniform(ks[1], (B, T))
+        u = rng.uniform(ks[1].to(dev), (B, T))
     t = t.to(dev).float()
     t_mask = u < t[:, None]
     if loss_mask is not None:
@@ -93,28 +92,27 @@ def inner_masks(keys: torch.Tensor, chunks: torch.Tensor, ratio: float, ratio_ra
     lo, hi = float(ratio_range[0]), float(ratio_range[1])
     C = chunks.shape[-1]
     dev = chunks.device
-    keys = keys.to(dev)
     not_pad = chunks != pad_token_id
     mask_tok = torch.full_like(chunks, mask_token_id)
     if view_mode == "strata":
         ks = rng.split(keys, 3)
         u = rng.uniform(ks[..., 0, :], ())
         order = torch.argsort(rng.uniform(ks[..., 1, :], (views,)), dim=-1).float()
-        r = lo + (hi - lo) * (order + u[..., None]) / views                    # [..., V]
+        r = (lo + (hi - lo) * (order + u[..., None]) / views).to(dev)           # [..., V]
         if span > 0:
             vk = rng.split(ks[..., 2, :], views)
-            ms = span_mask(vk, C, r, span)
+            ms = span_mask(vk.to(dev), C, r, span)
         else:
-            ms = rng.uniform(ks[..., 2, :], (views, C)) < r[..., None]
+            ms = rng.uniform(ks[..., 2, :].to(dev), (views, C)) < r[..., None]
         ms = ms & not_pad[..., None, :]
         return torch.where(ms, mask_tok[..., None, :], chunks[..., None, :]), ms
     if ratio is not None and ratio >= 0:
         r = torch.full(keys.shape[:-1], float(ratio), device=dev)
-        k_draw = keys
+        k_draw = keys.to(dev)
     else:
         ks = rng.split(keys, 2)
-        r = rng.uniform(ks[..., 0, :], (), lo, hi)
-        k_draw = ks[..., 1, :]
+        r = rng.uniform(ks[..., 0, :], (), lo, hi).to(dev)
+        k_draw = ks[..., 1, :].to(dev)
     if span > 0:
         m = span_mask(k_draw, C, r, span) & not_pad
     else:

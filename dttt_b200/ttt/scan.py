@@ -32,6 +32,7 @@ from ..utils import prof, rng
 from . import inner as IN
 from . import objective as OBJ
 from . import validate as VAL
+from .plan import StreamPlan
 from .regions import region
 
 
@@ -141,12 +142,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     if use_gdn:
         cfg = dc.replace(cfg, no_write=True)                 # the GDN state is written by its own recurrence, not by a gradient step
     VAL.check_options(cfg, mc, net.cw.has, use_gdn, asked_of_gdn)
-    # Everything up to the first model call (noising, weights, inner masks, positions) is integer / small-float
-    # work on [B, T] arrays: it runs on the host, where the token ids come from, and is moved to the device in
-    # one go; the device queue never waits on it.
     run_dev = net.p("final_norm.weight").device
-    host = torch.device("cpu")
-    batch = Batch(*[None if x is None else x.to(host) for x in batch])
     tp = net.tp_size
     if tp > 1:
         # the micro-batch belongs to the tensor-parallel group: this rank scores its own B / tp sequences
@@ -159,160 +155,25 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         lo_, hi_ = net.tp.index * (Bg // tp), (net.tp.index + 1) * (Bg // tp)
         batch = Batch(*[None if x is None else x[lo_:hi_] for x in batch])
         key = key[lo_:hi_] if key.dim() == 2 else rng.fold_in(key, 7_000_001 + net.tp.index)
-    ids = batch.input_ids.long()
-    dev = host
-    B, T = ids.shape
-    C, Wn, S, F_ = mc.chunk_size, mc.window_chunks, mc.suffix_len, mc.fast_len
-    if T % C:
-        raise ValueError(f"seq_len {T} not a multiple of chunk_size {C}")
-    nc = T // C
-    pos = torch.arange(T, device=dev)[None].expand(B, T) if batch.position_ids is None else batch.position_ids.long()
-    key = key.to(dev)
     train_graph = torch.is_grad_enabled()
     use_regions = cfg.remat and train_graph
 
-    # ---- keys (the split order is a contract, reference chunk_scan.py:229-237)
-    if key.dim() == 2:
-        ks3 = rng.split(key, 3)
-        key_mask, key_inner = ks3[:, 1], ks3[:, 2]
-        inner_keys = rng.split(key_inner, nc).transpose(0, 1)                       # [nc, B, 2]
-    else:
-        ks3 = rng.split(key, 3)
-        key_mask, key_inner = ks3[1], ks3[2]
-        inner_keys = rng.split(key_inner, nc * B).reshape(nc, B, 2)
-    fold = lambda k, v: rng.fold_in(k, v)
-
-    # ---- outer objective
-    loss_mask = batch.loss_mask
-    if cfg.score_from_chunk:
-        scored = (torch.arange(T, device=dev) >= cfg.score_from_chunk * C)[None]
-        loss_mask = scored.expand(B, T) if loss_mask is None else (loss_mask.bool() & scored)
-    t_in = batch.outer_t
-    if cfg.outer_t >= 0:
-        t_in = torch.full((B,), cfg.outer_t, dtype=torch.float32, device=dev)
-    kernel = ref.cart_kernel(cfg.cart_p, cfg.cart_window, dev) if (cfg.time_reweighting == "cart" or cfg.inner_cart) else None
-
-    def noisy_view(k):
-        x_t, t, t_mask = OBJ.q_sample(k, ids, loss_mask, mc.mask_token_id, t=t_in)
-        w_raw = OBJ.time_weights(cfg.time_reweighting, t, t_mask, kernel)
-        if cfg.outer_shift:
-            m_outer = _pad_left_shift(t_mask, 1)
-            weight = _pad_left_shift(w_raw, 1) * m_outer.float()
-        else:
-            m_outer, weight = t_mask, w_raw * t_mask.float()
-        return x_t, t, t_mask, w_raw, m_outer, weight
-
-    x_t, t, t_mask, w_raw, m_outer, weight = noisy_view(key_mask)
-    tgt_outer = _pad_left_shift(ids, 1) if cfg.outer_shift else ids
-    VO = cfg.outer_views
-    extra_views = [noisy_view(fold(key_mask, v)) for v in range(1, VO)]
-    base_key = key if key.dim() == 1 else key[0]
-    reach = mc.reach
-    if cfg.window_drop > 0:
-        drop = bool(rng.uniform(fold(base_key, 7), ()) < cfg.window_drop) and step < cfg.window_drop_until
-        reach = 0 if drop else (Wn if mc.reach is None else mc.reach)
-    sp_flags = None
-    if cfg.self_prior > 0:
-        sp_flags = (rng.uniform(fold(key, 8), ()) if key.dim() == 2 else rng.uniform(fold(key, 8), (B,))) < cfg.self_prior
-    if cfg.mtp:
-        tgt_mtp = _pad_left_shift(ids, 2)
-        m_mtp = _pad_left_shift(t_mask, 2)
-        w_mtp = _pad_left_shift(w_raw, 2) * m_mtp.float()
-    else:
-        tgt_mtp = m_mtp = w_mtp = None
-
-    # ---- re-read layout (evaluation; reference chunk_scan.py:340-372)
-    T0, nc0, n_rr = T, nc, cfg.reread_chunks
-    host_mask, host_perm = batch.inner_mask, batch.inner_perm
-    if n_rr:
-        nC = n_rr * C
-        dup = lambda a: torch.cat([a[:, :nC], a], dim=1)
-        zero = lambda a: torch.cat([torch.zeros_like(a[:, :nC]), a], dim=1)
-        x_t = torch.cat([ids[:, :nC], x_t], dim=1)
-        ids, pos, m_outer, weight, tgt_outer = dup(ids), dup(pos), zero(m_outer), zero(weight), dup(tgt_outer)
-        if cfg.mtp:
-            tgt_mtp, m_mtp, w_mtp = dup(tgt_mtp), zero(m_mtp), zero(w_mtp)
-        if host_mask is not None:
-            host_mask = dup(host_mask)
-        if host_perm is not None:
-            host_perm = torch.cat([host_perm[:, :nC], host_perm + nC], dim=1)
-        kf = fold(key_inner, 1)
-        rr_inner = rng.split(kf, n_rr).transpose(0, 1) if key_inner.dim() == 2 else rng.split(kf, n_rr * B).reshape(n_rr, B, 2)
-        inner_keys = torch.cat([rr_inner, inner_keys], dim=0)
-        T, nc = T + nC, nc + n_rr
-    eff = (lambda c: c - n_rr * (c >= n_rr)) if n_rr else (lambda c: c)
-    plan = (tuple(cfg.write_plan) + (1,) * nc)[:nc] if cfg.write_plan else None
-
-    # ---- the inner (write) task: what stream C sees and predicts (reference chunk_scan.py:375-427)
-    ids_c = OBJ.to_chunks(ids, C)                                                 # [nc, B, C]
-    pos_c = OBJ.to_chunks(pos, C)
-    own_inner = "full"
-    pos_in_c, pos_q_c, perm_c = pos_c, None, None
-    V = cfg.inner_views
-    if cfg.inner_task == "mask":
-        if host_mask is not None:
-            if V != 1:
-                raise ValueError("host-side inner masks support one view")
-            inner_mask_c = OBJ.to_chunks(host_mask.bool(), C)
-            x_inner_c = torch.where(inner_mask_c, torch.full_like(ids_c, mc.mask_token_id), ids_c)
-        else:
-            x_inner_c, inner_mask_c = OBJ.inner_masks(inner_keys, ids_c, cfg.inner_mask_ratio, cfg.inner_mask_range,
-                                                      mc.mask_token_id, mc.pad_token_id, V, cfg.inner_mask_span,
-                                                      cfg.inner_view_mode)             # [nc, B, (V,) C]
-        target_c = ids_c
-        if cfg.inner_cart:
-            shp = inner_mask_c.shape
-            flat_m = inner_mask_c.reshape(-1, C)
-            inner_mask_c = (OBJ.cart_weights(1.0 - flat_m.float(), kernel) * flat_m.float()).reshape(shp)
-    else:
-        if V != 1:
-            raise ValueError("causal / split inner tasks are single-view")
-        if cfg.inner_task == "split":
-            if host_perm is None:
-                raise ValueError("inner_task split needs Batch.inner_perm (host-side, data.masks.split_perm)")
-            perm_c = OBJ.to_chunks(host_perm.long(), C)
-            K = int(round(cfg.inner_context_frac * C))
-            own_inner = f"split:{K}"
-        else:
-            perm_c = torch.arange(T, device=dev).reshape(nc, 1, C).expand(nc, B, C)
-            K = 0
-            own_inner = "causal"
-        x_inner_c = torch.gather(ids[None].expand(nc, B, T), 2, perm_c)
-        pos_in_c = torch.gather(pos[None].expand(nc, B, T), 2, perm_c)
-        target_c = torch.cat([x_inner_c[:, :, 1:], x_inner_c[:, :, -1:]], dim=2)
-        pos_q_c = torch.cat([pos_in_c[:, :, 1:], pos_in_c[:, :, -1:]], dim=2)
-        slot = torch.arange(C, device=dev)
-        inner_mask_c = ((slot >= max(K - 1, 0)) & (slot <= C - 2))[None, None].expand(nc, B, C)
-    if cfg.inner_feat != "off":
-        i = torch.arange(C, device=dev)
-        if cfg.inner_task == "mask":
-            tgt_idx_c = i[None, None].expand(nc, B, C)
-        elif cfg.inner_task == "causal":
-            tgt_idx_c = torch.clamp(i + 1, max=C - 1)[None, None].expand(nc, B, C)
-        else:
-            local = perm_c - (torch.arange(nc, device=dev) * C)[:, None, None]
-            tgt_idx_c = torch.cat([local[:, :, 1:], local[:, :, -1:]], dim=2)
-    else:
-        tgt_idx_c = None
-
-    # ---- the distillation teacher stream (reference chunk_scan.py:437-452)
-    if cfg.distill:
-        kT = fold(key_inner, 2)
-        keys_T = rng.split(kT, nc).transpose(0, 1) if key_inner.dim() == 2 else rng.split(kT, nc * B).reshape(nc, B, 2)
-        x_teacher_c, m_teacher_c = OBJ.inner_masks(keys_T, ids_c, -1.0, cfg.distill_t_range, mc.mask_token_id, mc.pad_token_id)
-    else:
-        x_teacher_c = m_teacher_c = None
+    # ---- what the batch asks of the model: streams, positions, targets, masks, weights (ttt.plan), built on the run device
+    plan = StreamPlan.build(batch, key, step, cfg, mc, run_dev)
+    dev = run_dev
+    B, T, nc, T0, n_rr = plan.B, plan.T, plan.nc, plan.T_data, plan.reread
+    C, Wn, S, F_ = mc.chunk_size, mc.window_chunks, mc.suffix_len, mc.fast_len
+    V, VO = cfg.inner_views, cfg.outer_views
+    reach, sp_flags, read_own, own_inner = plan.reach, plan.self_prior_rows, plan.read_mask, plan.inner_own
+    ids_streams, pos_k_streams, pos_q_streams, owns = plan.streams, plan.pos_k, plan.pos_q, plan.owns
+    NS, n_inner, n_teacher = plan.NS, plan.n_inner, plan.n_teacher
+    has_inner = n_inner > 0
+    eff = plan.data_chunk
     s_S = 1 if cfg.inner_task == "causal" else 0
     s_T = 1 if cfg.outer_shift else 0
-    if cfg.mtp:
-        slot = torch.arange(C, device=dev)
-        mtp_tgt_c = torch.cat([x_inner_c[:, :, 2:], x_inner_c[:, :, -2:]], dim=2)
-        mtp_mask_c = (slot <= C - 3)[None, None].expand(nc, B, C).float()
-    else:
-        mtp_tgt_c = mtp_mask_c = None
 
     # ---- segments
-    n_seg_chunks = VAL.check_geometry(T, mc, cfg.segment_chunks, nc)
+    n_seg_chunks = plan.segment_chunks
     n_seg = nc // n_seg_chunks
     T_seg = n_seg_chunks * C
     nkv, d = mc.num_key_value_heads // tp, mc.head_dim                       # this rank's KV heads
@@ -325,43 +186,7 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     clean_prime = (not cfg.write.plain) and cfg.write.kvb_weight > 0 and cfg.write.kvb_value == "clean"
     rb = mc.read_block
     clean_own = "full" if not rb else f"block:{rb}"
-    read_own = None if not rb else A.read_mask_matrix(C, rb, dev)
-    lm_w_of = net.lm_weight
-    fb = cfg.fused_ce_block
     create_graph = train_graph and cfg.second_order
-
-    # ---- streams of the prefix: [outer, clean, inner views..., teacher, extra outer views...]
-    has_inner = not (cfg.no_write or cfg.inner_from_outer)
-    x_inner = None
-    if has_inner:
-        x_inner = [OBJ.from_chunks(x_inner_c)] if V == 1 else [OBJ.from_chunks(x_inner_c[:, :, v]) for v in range(V)]
-    streams = [x_t, ids] + (x_inner or []) + ([OBJ.from_chunks(x_teacher_c)] if cfg.distill else []) + [v[0] for v in extra_views]
-    ids_streams = torch.stack(streams, dim=1)                                       # [B, NS, T]
-    NS = ids_streams.shape[1]
-    n_inner = V if has_inner else 0
-    n_teacher = 1 if cfg.distill else 0
-    owns = ["full", "full"] + [own_inner] * n_inner + ["full"] * (n_teacher + VO - 1)
-    p_q_outer_full = pos + 1 if cfg.outer_shift else pos
-    if not cfg.outer_shift and (cfg.inner_task == "mask" or not has_inner):
-        pos_k_streams = pos[:, None].expand(B, NS, T)
-        pos_q_streams = None
-    else:
-        p_in = OBJ.from_chunks(pos_in_c) if cfg.inner_task != "mask" else pos
-        p_q = OBJ.from_chunks(pos_q_c) if (pos_q_c is not None and cfg.inner_task != "mask") else pos
-        pk = [pos, pos] + [p_in] * n_inner + [pos] * (n_teacher + VO - 1)
-        pq = [p_q_outer_full, pos] + [p_q] * n_inner + [p_q_outer_full] * (n_teacher + VO - 1)
-        pos_k_streams, pos_q_streams = torch.stack(pk, 1), torch.stack(pq, 1)
-
-    # ---- host -> device, once
-    dev = run_dev
-    D = lambda x: None if x is None else x.to(dev, non_blocking=True)
-    ids_streams, pos_k_streams, pos_q_streams, pos_c = D(ids_streams), D(pos_k_streams), D(pos_q_streams), D(pos_c)
-    inner_mask_c, target_c, pos_in_c, pos_q_c, tgt_idx_c = D(inner_mask_c), D(target_c), D(pos_in_c), D(pos_q_c), D(tgt_idx_c)
-    m_teacher_c, mtp_tgt_c, mtp_mask_c, sp_flags, read_own = D(m_teacher_c), D(mtp_tgt_c), D(mtp_mask_c), D(sp_flags), D(read_own)
-    weight, m_outer, tgt_outer = D(weight), D(m_outer), D(tgt_outer)
-    extra_views = [tuple(D(x) for x in v) for v in extra_views]
-    if cfg.mtp:
-        tgt_mtp, w_mtp, m_mtp = D(tgt_mtp), D(w_mtp), D(m_mtp)
 
     # ---- carries at the sequence start
     kvp = None                                                                      # per prefix layer (k, v) tails
@@ -386,12 +211,6 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
     ce_seq = torch.zeros(B, device=dev)
     mask_seq = torch.zeros(B, device=dev)
     ce_tok, mask_tok = [None] * nc, [None] * nc
-
-    views_w_c = [OBJ.to_chunks(v[5], C) for v in extra_views]
-    views_m_c = [OBJ.to_chunks(v[4], C) for v in extra_views]
-    weight_c, m_outer_c, tgt_outer_c = OBJ.to_chunks(weight, C), OBJ.to_chunks(m_outer, C), OBJ.to_chunks(tgt_outer, C)
-    if cfg.mtp:
-        tok2_c, wgt2_c, tm2_c = OBJ.to_chunks(tgt_mtp, C), OBJ.to_chunks(w_mtp, C), OBJ.to_chunks(m_mtp, C)
 
     def run_segment(g, kvp, kvs, W, mem):
         """Prefix layers and the chunk scan of segment ``g`` from the carries ``(kvp, kvs, W | mem)``.  Returns the new carries and
@@ -430,21 +249,14 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
         # ---- suffix: chunk by chunk
         for j in range(n_seg_chunks):
             c = g * n_seg_chunks + j
-            nv = A.valid_window_chunks(eff(c), Wn, reach)
             ho, hc = hch[:, OUTER, j], hch[:, CLEAN, j]
             hi = None
             if has_inner:
                 hi = hch[:, INNER, j] if V == 1 else hch[:, INNER:INNER + V, j]
             ht = hch[:, INNER + n_inner, j] if cfg.distill else None
             hv = [hch[:, NS - VO + 1 + k, j] for k in range(VO - 1)]
-            p = pos_c[c]
-            consts = dict(
-                c=c, nv=nv, p=p, tok=tgt_outer_c[c], wgt=weight_c[c], tm=m_outer_c[c], im=inner_mask_c[c] if has_inner or cfg.inner_from_outer else None,
-                tgt=target_c[c], p_in=pos_in_c[c], p_q=None if pos_q_c is None else pos_q_c[c],
-                ti=None if tgt_idx_c is None else tgt_idx_c[c], mt=None if m_teacher_c is None else m_teacher_c[c],
-                tok2=tok2_c[c] if cfg.mtp else None, wgt2=wgt2_c[c] if cfg.mtp else None, tm2=tm2_c[c] if cfg.mtp else None,
-                mtp_t=None if mtp_tgt_c is None else mtp_tgt_c[c], mtp_m=None if mtp_mask_c is None else mtp_mask_c[c],
-                wv=[w[c] for w in views_w_c], tmv=[m[c] for m in views_m_c], k_c=None if plan is None else plan[c])
+            consts = plan.at(c)
+            nv = consts["nv"]
 
             n_kv = 2 * S
             mem_flat = [mem] if use_gdn else ([] if cfg.no_write else IN.flat(W))

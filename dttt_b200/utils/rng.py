@@ -90,6 +90,14 @@ def _to_unit(b: torch.Tensor) -> torch.Tensor:
 def uniform(k: torch.Tensor, shape: Sequence[int] = (), lo: float = 0.0, hi: float = 1.0) -> torch.Tensor:
     """float32 uniform on ``[lo, hi)``; ``k [..., 2]`` -> ``[..., *shape]``."""
     n = int(math.prod(shape)) if len(shape) else 1
+    if k.is_cuda and n * max(1, k.numel() // 2) >= 1024 and k.numel() // 2 <= 65535:
+        # bulk draws on a GPU: one launch of the counter-RNG kernel (same bits as the statement below)
+        from ..ops import kernels
+        if kernels.available("mask_rng"):
+            u = kernels.threefry_uniform(k.reshape(-1, 2), n).reshape(tuple(k.shape[:-1]) + tuple(shape))
+            if lo != 0.0 or hi != 1.0:
+                u = torch.clamp_min(u * (hi - lo) + lo, lo)
+            return u
     if n <= _CHUNK or k.dim() > 1:
         u = _to_unit(bits(k, shape))
     else:
