@@ -24,13 +24,10 @@ from typing import NamedTuple, Optional, Tuple
 import torch
 
 from ..models.blocks import CLEAN, INNER, OUTER, Net
-from ..ops import attention as A
 from ..ops import ce as CE
 from ..ops import functional as Fn
-from ..ops import reference as ref
 from ..utils import prof, rng
 from . import inner as IN
-from . import objective as OBJ
 from . import validate as VAL
 from .plan import StreamPlan
 from .regions import region
@@ -110,11 +107,6 @@ class LossConfig:
     attn_chunk_batch: int = 2
     compute_dtype: str = "bfloat16"
     remat: bool = True                    # False: keep every activation (small models, tests)
-
-
-def _pad_left_shift(x: torch.Tensor, k: int) -> torch.Tensor:
-    """``y[:, i] = x[:, i + k]``, zero beyond the end (``jnp.pad(x[:, k:], ((0,0),(0,k)))``)."""
-    return torch.cat([x[:, k:], torch.zeros_like(x[:, :k])], dim=1)
 
 
 def shift_slots(x: torch.Tensor, k: int):
