@@ -154,109 +154,160 @@ class DecodeOpts:
     priority: str = "logp"            # logp | margin | entropy
 
 
+# ---- confidence unmasking of one block (reference generate.py:227-355: LLaDA-style, with the options of ``DecodeOpts``)
+def _rank_of(priority: torch.Tensor) -> torch.Tensor:
+    """Position of every slot when its row is sorted by descending priority (earlier slot first among equals)."""
+    return torch.argsort(torch.argsort(-priority, dim=-1, stable=True), dim=-1)
+
+
+def _gumbel(key: torch.Tensor, shape, device) -> torch.Tensor:
+    u = rng.uniform(key.to("cpu"), shape).to(device).clamp_(1e-20, 1 - 1e-7)
+    return -torch.log(-torch.log(u))
+
+
+# how sure a slot's proposal is, from the log-probabilities over the vocabulary and the log-probability of the proposed token
+_PRIORITY = {
+    "logp": lambda logp, chosen: chosen,
+    "margin": lambda logp, chosen: (lambda top: top[..., 0].exp() - top[..., 1].exp())(logp.topk(2, -1).values),
+    "entropy": lambda logp, chosen: (logp.exp() * torch.where(torch.isfinite(logp), logp, torch.zeros_like(logp))).sum(-1),
+}
+
+
+class _KeyChain:
+    """One fresh key per request: ``(carry, out) = split(carry)``."""
+
+    def __init__(self, key: torch.Tensor):
+        self.carry = key
+
+    def take(self) -> torch.Tensor:
+        self.carry, out = rng.split(self.carry, 2).unbind(0)
+        return out
+
+
+class BlockUnmasker:
+    """The state of one block while it is being decoded: the tokens committed so far, the log-probability each was
+    committed with, and the read-only context (positions, caches, previous block's tail logit)."""
+
+    def __init__(self, net: Net, ids, known, pos, state: DecodeState, key, temperature: float, outer_shift: bool, prev_tail_logit,
+                 opts: DecodeOpts):
+        self.net, self.pos, self.state, self.opts = net, pos, state, opts
+        self.temperature, self.outer_shift, self.prev_tail = temperature, outer_shift, prev_tail_logit
+        self.ids, self.known, self.given = ids, known, known.clone()
+        self.B, self.C = ids.shape
+        self.dev, self.mask_id, self.V = ids.device, net.cfg.mask_token_id, net.cfg.vocab_size
+        self.pos_q = pos + 1 if outer_shift else None
+        self.blank = torch.full_like(ids, self.mask_id)
+        self.committed_logp = torch.zeros(self.B, self.C, device=self.dev)
+        self.keys = _KeyChain(key)
+
+    def masked_input(self, visible: torch.Tensor) -> torch.Tensor:
+        return torch.where(visible, self.ids, self.blank)
+
+    def propose(self, visible: torch.Tensor, key: torch.Tensor, own_kv=None):
+        """A token for every slot given the ``visible`` ones: ``(tokens, their log-probability, their priority)``."""
+        o = self.opts
+        x = self.masked_input(visible)
+        logits = block_forward(self.net, x, self.pos, self.state, pos_q=self.pos_q, own_kv=own_kv)[0]
+        logits[..., self.mask_id] = float("-inf")
+        if self.outer_shift:                                        # slot i is predicted at slot i - 1; slot 0 by the previous block's tail
+            lead = self.prev_tail.clone() if self.prev_tail is not None else torch.zeros(self.B, self.V, device=self.dev)
+            lead[..., self.mask_id] = float("-inf")
+            logits = torch.cat([lead[:, None], logits[:, :-1]], 1)
+        if o.presence_penalty > 0:
+            seen = torch.zeros(self.B, self.V, device=self.dev).scatter_(1, x, 1.0)
+            seen[:, self.mask_id] = 0
+            logits = logits - o.presence_penalty * seen[:, None]
+        logp = torch.log_softmax(logits, -1)
+        if self.temperature > 0:
+            tokens = (logits / self.temperature + _gumbel(key, (self.B, self.C, self.V), self.dev)).argmax(-1)
+        else:
+            tokens = logits.argmax(-1)
+        chosen = logp.gather(-1, tokens[..., None])[..., 0]
+        return tokens, chosen, _PRIORITY[o.priority](logp, chosen)
+
+    def pick(self, priority: torch.Tensor, key: torch.Tensor, quota: torch.Tensor, allowed=None) -> torch.Tensor:
+        """The ``quota [B]`` open (and allowed) slots of highest priority; with ``order = random`` the priority is a draw."""
+        if self.opts.order == "random":
+            priority = rng.uniform(rng.fold_in(key, 1).to("cpu"), (self.B, self.C)).to(self.dev)
+        shut = self.known if allowed is None else (self.known | ~allowed)
+        priority = torch.where(shut, torch.full_like(priority, float("-inf")), priority)
+        return (_rank_of(priority) < quota[:, None]) & ~shut
+
+    def commit(self, where: torch.Tensor, tokens: torch.Tensor, logp: torch.Tensor) -> None:
+        self.ids = torch.where(where, tokens, self.ids)
+        self.committed_logp = torch.where(where, logp, self.committed_logp)
+        self.known = self.known | where
+
+    # ---- schedules
+    def sweep(self, n_steps: int, allowed=None, own_kv=None) -> None:
+        """Fill the open (allowed) slots in ``n_steps`` rounds, an equal share of what is left per round."""
+        for i in range(n_steps):
+            key = self.keys.take()
+            tokens, logp, priority = self.propose(self.known, key, own_kv)
+            open_ = ~self.known if allowed is None else (~self.known & allowed)
+            quota = torch.ceil(open_.sum(-1).float() / (n_steps - i)).long()
+            self.commit(self.pick(priority, key, quota, allowed), tokens, logp)
+
+    def until_confident(self, threshold: float) -> None:
+        """Each round commits every slot whose proposal reaches ``threshold`` probability, and at least the best one."""
+        one = torch.ones(self.B, dtype=torch.long, device=self.dev)
+        rounds = 0
+        while (~self.known).any() and rounds < self.C:
+            key = self.keys.take()
+            tokens, logp, priority = self.propose(self.known, key)
+            sure = (logp >= float(np.log(threshold))) & ~self.known
+            self.commit(sure | self.pick(priority, key, one), tokens, logp)
+            rounds += 1
+
+    def revise(self, rounds: int, k: int) -> None:
+        """Re-predict, ``rounds`` times, the ``k`` generated slots that were committed least surely (Gumbel-perturbed)."""
+        for _ in range(rounds):
+            k_pick, k_draw = self.keys.take(), self.keys.take()
+            doubt = torch.where(self.given, torch.full_like(self.committed_logp, float("-inf")),
+                                -self.committed_logp + _gumbel(k_pick, (self.B, self.C), self.dev))
+            again = (_rank_of(doubt) < k) & ~self.given
+            tokens, logp, _ = self.propose(~again, k_draw)
+            self.ids = torch.where(again, tokens, self.ids)
+            self.committed_logp = torch.where(again, logp, self.committed_logp)
+
+
+def _check_decode_opts(opts: DecodeOpts, C: int, read_block: int, outer_shift: bool) -> None:
+    if opts.order not in ("confidence", "random") or opts.priority not in _PRIORITY:
+        raise ValueError(f"DecodeOpts order {opts.order!r} / priority {opts.priority!r}")
+    if opts.subblock < 0 or (opts.subblock and (C % opts.subblock or opts.threshold > 0)):
+        raise ValueError(f"DecodeOpts.subblock {opts.subblock}: a divisor of the block size {C}, without threshold")
+    if read_block and (opts.threshold > 0 or opts.remask_loop > 0 or opts.subblock not in (0, read_block) or not outer_shift):
+        raise ValueError(f"read_block {read_block}: its groups are decoded in order, with the outer shift")
+
+
 @torch.no_grad()
 def decode_block(net: Net, ids, known, pos, state: DecodeState, key, steps: int, temperature: float = 0.0, outer_shift: bool = False,
                  prev_tail_logit=None, opts: DecodeOpts = DecodeOpts()):
     """Unmask one block: ``ids [B, C]`` carry the known tokens, ``known [B, C]`` marks them.  Returns ``(ids, tail logit)``."""
     cfg = net.cfg
-    C, V = cfg.chunk_size, cfg.vocab_size
-    B = ids.shape[0]
-    dev = ids.device
-    if opts.order not in ("confidence", "random") or opts.priority not in ("logp", "margin", "entropy"):
-        raise ValueError(f"DecodeOpts order {opts.order!r} / priority {opts.priority!r}")
-    if opts.subblock < 0 or (opts.subblock and (C % opts.subblock or opts.threshold > 0)):
-        raise ValueError(f"DecodeOpts.subblock {opts.subblock}: a divisor of the block size {C}, without threshold")
-    rb = cfg.read_block
-    if rb and (opts.threshold > 0 or opts.remask_loop > 0 or opts.subblock not in (0, rb) or not outer_shift):
-        raise ValueError(f"read_block {rb}: its groups are decoded in order, with the outer shift")
-    prompt = known.clone()
-    pos_q = pos + 1 if outer_shift else None
-    mask_tok = torch.full_like(ids, cfg.mask_token_id)
-    state_key = [key]
-
-    def next_key():
-        ks = rng.split(state_key[0], 2)
-        state_key[0] = ks[0]
-        return ks[1]
-
-    def predict(ids, known, k, own=None):
-        x = torch.where(known, ids, mask_tok)
-        logits = block_forward(net, x, pos, state, pos_q=pos_q, own_kv=own)[0]
-        logits[..., cfg.mask_token_id] = float("-inf")
-        if outer_shift:
-            p0 = prev_tail_logit.clone() if prev_tail_logit is not None else torch.zeros(B, V, device=dev)
-            p0[..., cfg.mask_token_id] = float("-inf")
-            logits = torch.cat([p0[:, None], logits[:, :-1]], 1)
-        if opts.presence_penalty > 0:
-            present = torch.zeros(B, V, device=dev).scatter_(1, x, 1.0)
-            present[:, cfg.mask_token_id] = 0
-            logits = logits - opts.presence_penalty * present[:, None]
-        logp = torch.log_softmax(logits, -1)
-        if temperature > 0:
-            u = rng.uniform(k.to("cpu"), (B, C, V)).to(dev).clamp_(1e-20, 1 - 1e-7)
-            sampled = (logits / temperature - torch.log(-torch.log(u))).argmax(-1)
-        else:
-            sampled = logits.argmax(-1)
-        conf = logp.gather(-1, sampled[..., None])[..., 0]
-        if opts.priority == "logp":
-            score = conf
-        elif opts.priority == "margin":
-            top2 = logp.topk(2, -1).values
-            score = top2[..., 0].exp() - top2[..., 1].exp()
-        else:
-            score = (logp.exp() * torch.where(torch.isfinite(logp), logp, torch.zeros_like(logp))).sum(-1)
-        return sampled, conf, score
-
-    def select(known, score, k, n_commit, allowed=None):
-        prio = score if opts.order == "confidence" else rng.uniform(rng.fold_in(k, 1).to("cpu"), (B, C)).to(dev)
-        closed = known if allowed is None else (known | ~allowed)
-        prio = torch.where(closed, torch.full_like(prio, float("-inf")), prio)
-        rank = torch.argsort(torch.argsort(-prio, dim=-1, stable=True), dim=-1)
-        return (rank < n_commit[:, None]) & ~closed
-
-    def run(n_steps, ids, known, conf_at, allowed=None, own=None):
-        for i in range(n_steps):
-            k = next_key()
-            sampled, conf, score = predict(ids, known, k, own)
-            open_ = ~known if allowed is None else (~known & allowed)
-            n_commit = torch.ceil(open_.sum(-1).float() / (n_steps - i)).long()
-            commit = select(known, score, k, n_commit, allowed)
-            ids, known, conf_at = torch.where(commit, sampled, ids), known | commit, torch.where(commit, conf, conf_at)
-        return ids, known, conf_at
-
-    conf_at = torch.zeros(B, C, device=dev)
-    tok = torch.arange(C, device=dev)
+    C, rb = cfg.chunk_size, cfg.read_block
+    _check_decode_opts(opts, C, rb, outer_shift)
+    work = BlockUnmasker(net, ids, known, pos, state, key, temperature, outer_shift, prev_tail_logit, opts)
+    slot = torch.arange(C, device=ids.device)
+    whole_rows = lambda m: m[None].expand(work.B, C)
     if opts.threshold > 0:
-        it = 0
-        while (~known).any() and it < C:
-            k = next_key()
-            sampled, conf, score = predict(ids, known, k)
-            top = select(known, score, k, torch.ones(B, dtype=torch.long, device=dev))
-            commit = ((conf >= float(np.log(opts.threshold))) & ~known) | top
-            ids, known, conf_at, it = torch.where(commit, sampled, ids), known | commit, torch.where(commit, conf, conf_at), it + 1
+        work.until_confident(opts.threshold)
     elif rb:
-        steps_g = max(1, -(-steps * rb // C))
+        # group g holds the slots predicted from sub-block g of the clean stream (shifted by one); its own clean keys are refreshed first
+        per_group = max(1, -(-steps * rb // C))
         for g in range(C // rb):
-            allowed = ((tok >= g * rb + 1) & (tok <= (g + 1) * rb)) | ((tok == 0) & (g == 0))
-            own = clean_forward(net, torch.where(known, ids, mask_tok), pos, state)[2]
-            ids, known, conf_at = run(steps_g, ids, known, conf_at, allowed[None].expand(B, C), own)
+            members = ((slot >= g * rb + 1) & (slot <= (g + 1) * rb)) | ((slot == 0) & (g == 0))
+            own = clean_forward(net, work.masked_input(work.known), pos, state)[2]
+            work.sweep(per_group, whole_rows(members), own)
     elif opts.subblock:
-        b = opts.subblock
-        steps_g = max(1, -(-steps * b // C))
-        for g in range(C // b):
-            ids, known, conf_at = run(steps_g, ids, known, conf_at, ((tok // b) == g)[None].expand(B, C))
+        per_group = max(1, -(-steps * opts.subblock // C))
+        for g in range(C // opts.subblock):
+            work.sweep(per_group, whole_rows((slot // opts.subblock) == g))
     else:
-        ids, known, conf_at = run(steps, ids, known, conf_at)
-    for _ in range(opts.remask_loop):
-        kp, ks = next_key(), next_key()
-        gumbel = -torch.log(-torch.log(rng.uniform(kp.to("cpu"), (B, C)).to(dev).clamp_(1e-20, 1 - 1e-7)))
-        prio = torch.where(prompt, torch.full_like(conf_at, float("-inf")), -conf_at + gumbel)
-        rank = torch.argsort(torch.argsort(-prio, dim=-1, stable=True), dim=-1)
-        again = (rank < opts.remask_k) & ~prompt
-        sampled, conf, _ = predict(ids, ~again, ks)
-        ids, conf_at = torch.where(again, sampled, ids), torch.where(again, conf, conf_at)
-    tail = block_tail(net, ids, pos, state) if outer_shift else torch.zeros(B, V, device=dev)
-    return ids, tail
+        work.sweep(steps)
+    work.revise(opts.remask_loop, opts.remask_k)
+    tail = block_tail(net, work.ids, pos, state) if outer_shift else torch.zeros(work.B, cfg.vocab_size, device=ids.device)
+    return work.ids, tail
 
 
 @torch.no_grad()

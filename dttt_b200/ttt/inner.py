@@ -55,23 +55,33 @@ class WriteConfig:
     def plain(self) -> bool:
         return self == WriteConfig()
 
+    def problems(self, chunk: int) -> List[str]:
+        """Every rule this combination of write options breaks (empty: fine).  One rule per line: the range of a single
+        option first, then which schemes exclude one another."""
+        sub, fast, many = self.subchunks > 1, self.fast_frac > 0, self.steps > 1
+        table = [
+            (self.subchunks < 1 or chunk % max(self.subchunks, 1) != 0, f"inner_subchunks = {self.subchunks} does not divide the chunk of {chunk} tokens"),
+            (not 0.0 < self.subchunk_scale <= 1.0, f"inner_subchunk_scale = {self.subchunk_scale} is outside (0, 1]"),
+            (self.surprise_gamma < 0, "inner_surprise_gamma is negative"),
+            (self.kvb_weight < 0, "inner_kvb_weight is negative"),
+            (self.kvb_value not in ("self", "clean"), f"inner_kvb_value = {self.kvb_value!r} is neither 'self' nor 'clean'"),
+            (not 0.0 <= self.fast_frac < 1.0, f"inner_fast_frac = {self.fast_frac} is outside [0, 1)"),
+            (not 0.0 <= self.fast_decay <= 1.0, f"inner_fast_decay = {self.fast_decay} is outside [0, 1]"),
+            (self.fast_lr_scale < 0, "inner_fast_lr_scale is negative"),
+            (self.steps < 1, "inner_write_steps is below 1"),
+            (self.norm_alpha < 0, "inner_norm_alpha is negative"),
+            (self.norm_cap < 1.0, "inner_norm_cap is below 1"),
+            (fast and self.subchunks < 2, "inner_fast_frac splits the units by time scale and the fast ones are written per sub-chunk: set inner_subchunks >= 2"),
+            (many and (sub or fast), "inner_write_steps > 1 repeats the whole-chunk step: not together with sub-chunks or fast units"),
+            (self.normalised and (sub or fast or many), "the normalised step (inner_norm_alpha > 0) is one whole-chunk step: not together with "
+                                                        "sub-chunks, fast units or repeated steps"),
+        ]
+        return [why for broken, why in table if broken]
+
     def check(self, chunk: int) -> None:
-        if self.subchunks < 1 or chunk % self.subchunks:
-            raise ValueError(f"inner_subchunks {self.subchunks} must divide the chunk size {chunk}")
-        if not 0.0 < self.subchunk_scale <= 1.0 or self.surprise_gamma < 0 or self.kvb_weight < 0:
-            raise ValueError("inner_subchunk_scale in (0, 1], inner_surprise_gamma >= 0, inner_kvb_weight >= 0")
-        if self.kvb_value not in ("self", "clean"):
-            raise ValueError(f"inner_kvb_value {self.kvb_value!r} (self | clean)")
-        if not 0.0 <= self.fast_frac < 1.0 or not 0.0 <= self.fast_decay <= 1.0 or self.fast_lr_scale < 0:
-            raise ValueError("inner_fast_frac in [0, 1), inner_fast_decay in [0, 1], inner_fast_lr_scale >= 0")
-        if self.fast_frac > 0 and self.subchunks < 2:
-            raise ValueError("inner_fast_frac needs inner_subchunks >= 2 (the fast units are written per sub-chunk)")
-        if self.steps < 1 or (self.steps > 1 and (self.subchunks > 1 or self.fast_frac > 0)):
-            raise ValueError("inner_write_steps >= 1, and > 1 only with whole-chunk steps (no sub-chunks / fast units)")
-        if self.norm_alpha < 0 or self.norm_cap < 1.0 or (self.normalised and (
-                self.subchunks > 1 or self.fast_frac > 0 or self.steps > 1)):
-            raise ValueError("inner_norm_alpha >= 0, inner_norm_cap >= 1, and the normalised step alone, as one "
-                             "whole-chunk step")
+        found = self.problems(chunk)
+        if found:
+            raise ValueError("write options: " + "; ".join(found))
 
 
 class InnerExtras(NamedTuple):
