@@ -1,11 +1,12 @@
-"""Reproduction check between two evaluations of the same weights (two ``eval_<step>.npz`` / ``eval_<step>_planted.npz``
-files written on different machines or builds).
+"""Did two builds (or two machines) evaluate the same weights to the same numbers?
 
     python -m dttt_b200.tools.compare_eval A/eval_4000.npz B/eval_4000.npz
 
-First whether both scored the same sequences (sources, document ids and lengths, tokens beyond the window), then for
-every per-sequence array they share: both means, the mean difference, quantiles of ``|B - A|`` and the correlation;
-for the losses also the mean difference per source.  Role of the reference's ``tools/compare_eval.py:1-48``.
+Works on the ``eval_<step>.npz`` / ``eval_<step>_planted.npz`` files a run writes.  Step one decides whether the two files are
+about the same items at all: the identity arrays (sources, document ids and lengths, tokens beyond the window) must be
+equal element for element.  Step two is one agreement table (``evalstats.agreement``) over every per-sequence array both
+files hold, and, when the items pair up, the per-source shift of the losses with the write on and off.  Same purpose as
+the reference's ``tools/compare_eval.py``.
 """
 from __future__ import annotations
 
@@ -16,31 +17,37 @@ import numpy as np
 from . import evalstats as S
 
 IDENTITY = ("sources", "doc_ids", "doc_lens", "beyond")
+BY_SOURCE = ("loss_1.0", "loss_0.0")
+
+
+def same_items(a, b) -> dict:
+    """Identity array -> whether both files hold it with equal contents (arrays neither file has are left out)."""
+    held = [k for k in IDENTITY if k in a or k in b]
+    return {k: k in a and k in b and a[k].shape == b[k].shape and bool((a[k] == b[k]).all()) for k in held}
+
+
+def comparable(a, b):
+    """Names of the 1-D arrays of equal, non-zero length that both files share (identity arrays excluded)."""
+    for k in sorted(set(a).intersection(b).difference(IDENTITY)):
+        if np.ndim(a[k]) == 1 and np.shape(a[k]) == np.shape(b[k]) and len(a[k]):
+            yield k
 
 
 def compare(a, b, out=print) -> bool:
-    paired = True
-    for k in IDENTITY:
-        if k in a or k in b:
-            same = k in a and k in b and a[k].shape == b[k].shape and bool(np.all(a[k] == b[k]))
-            paired &= same
-            out(f"  {k:10s} {'identical' if same else 'DIFFERENT'}")
+    verdicts = same_items(a, b)
+    for k, ok in verdicts.items():
+        out(f"  {k:10s} {'identical' if ok else 'DIFFERENT'}")
+    paired = all(verdicts.values())
     if not paired:
         out("  the files did not score the same sequences: what follows is not a paired comparison")
-    out(f"  {'array':16s} {'mean A':>10s} {'mean B':>10s} {'B - A':>10s} {'|d| p50':>10s} {'p99':>10s} {'max':>10s} {'corr':>8s}")
-    for k in sorted((set(a) & set(b)) - set(IDENTITY)):
-        x, y = np.asarray(a[k], np.float64), np.asarray(b[k], np.float64)
-        if x.ndim != 1 or x.shape != y.shape or not len(x):
-            continue
-        d = np.abs(y - x)
-        corr = np.corrcoef(x, y)[0, 1] if x.std() > 0 and y.std() > 0 else float("nan")
-        out(f"  {k:16s} {x.mean():10.5f} {y.mean():10.5f} {(y - x).mean():+10.5f} {np.median(d):10.5f} {np.quantile(d, 0.99):10.5f} "
-            f"{d.max():10.5f} {corr:8.4f}")
+    table = S.text_table({k: S.agreement(a[k], b[k]) for k in comparable(a, b)}, first="array")
+    for line in table.splitlines():
+        out("  " + line)
     if paired and "sources" in a:
         src = a["sources"].astype(str)
-        for k in ("loss_1.0", "loss_0.0"):
-            if k in a and k in b:
-                out(f"  {k} B - A by source: " + " | ".join(f"{s} {(b[k][src == s] - a[k][src == s]).mean():+.5f}" for s in dict.fromkeys(src)))
+        for k in (k for k in BY_SOURCE if k in a and k in b):
+            shift = {s: float((np.asarray(b[k])[src == s] - np.asarray(a[k])[src == s]).mean()) for s in dict.fromkeys(src)}
+            out(f"  {k} B - A by source: " + " | ".join(f"{s} {v:+.5f}" for s, v in shift.items()))
     return paired
 
 

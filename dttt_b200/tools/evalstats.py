@@ -132,3 +132,26 @@ def find_file(run_dir: str, rel: str) -> Optional[str]:
         if os.path.exists(p):
             return p
     return None
+
+
+# ------------------------------------------------------------------------------------------------ paired agreement tables
+def agreement(x, y) -> Dict[str, float]:
+    """How two measurements of the same items agree: both means, the mean shift, quantiles of the absolute difference and
+    the correlation (NaN when either side is constant)."""
+    x, y = np.asarray(x, np.float64), np.asarray(y, np.float64)
+    gap = np.abs(y - x)
+    varies = x.std() > 0 and y.std() > 0
+    return {"mean A": x.mean(), "mean B": y.mean(), "B - A": (y - x).mean(), "|d| p50": np.median(gap), "|d| p99": np.quantile(gap, 0.99),
+            "|d| max": gap.max(), "corr": np.corrcoef(x, y)[0, 1] if varies else float("nan")}
+
+
+def text_table(rows: Dict[str, Dict[str, float]], first: str = "", digits: int = 5, signed=("B - A",)) -> str:
+    """Rows of named numbers as an aligned text table; ``rows`` maps a label to ``{column: value}`` (same columns each)."""
+    if not rows:
+        return ""
+    cols = list(next(iter(rows.values())))
+    wide = max([len(first)] + [len(k) for k in rows]) + 2
+    cell = lambda c, v: f"{v:+.{digits}f}" if c in signed else f"{v:.{digits}f}"
+    lines = [first.ljust(wide) + "".join(c.rjust(digits + 8) for c in cols)]
+    lines += [label.ljust(wide) + "".join(cell(c, r[c]).rjust(digits + 8) for c in cols) for label, r in rows.items()]
+    return "\n".join(lines)
