@@ -17,10 +17,35 @@ from __future__ import annotations
 import torch
 
 
+class _ChunkKernel(torch.autograd.Function):
+    """The chunk update on the blocked CUDA kernel (``csrc/gdn_chunked.cu``): the forward keeps only its inputs, the backward
+    re-creates the block states and runs the reverse sweep."""
+
+    @staticmethod
+    def forward(ctx, k, v, beta, log_alpha, S0):
+        from . import kernels
+        ctx.save_for_backward(k, v, beta, log_alpha, S0)
+        return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gS):
+        from . import kernels
+        k, v, beta, log_alpha, S0 = ctx.saved_tensors
+        dk, dv, db, dla, dS0 = kernels.gdn_chunk_bwd(k, v, beta, log_alpha, S0, gS)
+        return dk.to(k.dtype), dv.to(v.dtype), db.to(beta.dtype), dla.to(log_alpha.dtype), dS0.to(S0.dtype)
+
+
 def delta_rule_chunked(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, log_alpha: torch.Tensor, S0: torch.Tensor,
                        block: int = 64) -> torch.Tensor:
-    """``k [B, C, nh, dk]``, ``v [B, C, nh, dv]``, ``beta / log_alpha [B, C, nh]``, ``S0 [B, nh, dv, dk]`` -> ``S_C``."""
+    """``k [B, C, nh, dk]``, ``v [B, C, nh, dv]``, ``beta / log_alpha [B, C, nh]``, ``S0 [B, nh, dv, dk]`` -> ``S_C``.
+    On a GPU (head dimension 64 / 128, blocks of 64) both directions run on the blocked kernel; elsewhere the same block
+    algebra is stated in PyTorch below and differentiated by autograd."""
     from . import kernels
+    if kernels.gdn_chunk_supported(k, v, min(block, k.shape[1])):
+        if torch.is_grad_enabled() and any(t.requires_grad for t in (k, v, beta, log_alpha, S0)):
+            return _ChunkKernel.apply(k, v, beta, log_alpha, S0)
+        return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
     if (k.is_cuda and kernels.available("gdn") and k.shape[-1] in (64, 128) and v.shape[-1] == k.shape[-1]
             and not (torch.is_grad_enabled() and any(t.requires_grad for t in (k, v, beta, log_alpha, S0)))):
         return kernels.gdn_chunked(k, v, beta, log_alpha, S0, block)

@@ -631,3 +631,52 @@ def gdn_chunked(k, v, beta, log_alpha, S0, block=64):
     _check(_lib.lib().dttt_gdn_update(_p(f(k)), _p(f(v)), _p(f(beta)), _p(f(log_alpha)), _p(f(S0)), _p(out), B, C, nh, D, _stream()),
            "gdn_update")
     return out
+
+
+# ---- the blocked (WY) form: forward with optional block-state checkpoints, and the backward
+_lib.register("dttt_gdn_chunk_state_elems", _ll, [_i, _i, _i, _i])
+_lib.register("dttt_gdn_chunk_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp])
+_lib.register("dttt_gdn_chunk_bwd", _i, [_vp] * 11 + [_i, _i, _i, _i, _vp])
+_SYMBOL.update(gdn_chunk="dttt_gdn_chunk_bwd")
+GDN_SLICE_ROWS = 32
+
+
+def gdn_chunk_supported(k, v, block: int) -> bool:
+    return (k.is_cuda and block == 64 and k.shape[1] % 64 == 0 and k.shape[-1] in (64, 128) and v.shape[-1] == k.shape[-1]
+            and available("gdn_chunk"))
+
+
+def _f32c(t):
+    return t if (t.dtype == torch.float32 and t.is_contiguous()) else t.float().contiguous()
+
+
+def gdn_chunk_fwd(k, v, beta, log_alpha, S0, states=None):
+    """State after one chunk of the gated delta rule in the blocked form (f32): ``k / v [B, C, nh, D]``, ``beta / log_alpha
+    [B, C, nh]``, ``S0 [B, nh, D, D]``.  ``states`` (``[B, nh, C / 64, D, D]`` f32): also record the state at every block start."""
+    B, C, nh, D = k.shape
+    k, v, beta, log_alpha, S0 = (_f32c(t) for t in (k, v, beta, log_alpha, S0))
+    out = torch.empty(B, nh, D, D, dtype=torch.float32, device=k.device)
+    _check(_lib.lib().dttt_gdn_chunk_fwd(_p(k), _p(v), _p(beta), _p(log_alpha), _p(S0), _p(out), _p(states), B, C, nh, D, _stream()),
+           "gdn_chunk_fwd")
+    return out
+
+
+def gdn_chunk_bwd(k, v, beta, log_alpha, S0, gS):
+    """Gradients of ``gdn_chunk_fwd`` w.r.t. ``(k, v, beta, log_alpha, S0)`` given ``gS = dL / dS_out``.  One forward sweep
+    re-creates the block states, one reverse sweep produces the gradients; what the value-row slices of a head share is summed
+    here over the slices."""
+    B, C, nh, D = k.shape
+    k, v, beta, log_alpha, S0, gS = (_f32c(t) for t in (k, v, beta, log_alpha, S0, gS))
+    dev = k.device
+    states = torch.empty(B, nh, C // 64, D, D, dtype=torch.float32, device=dev)
+    _check(_lib.lib().dttt_gdn_chunk_fwd(_p(k), _p(v), _p(beta), _p(log_alpha), _p(S0), _p(None), _p(states), B, C, nh, D, _stream()),
+           "gdn_chunk_fwd(states)")
+    ns = D // GDN_SLICE_ROWS
+    dk = torch.empty(ns, B, C, nh, D, dtype=torch.float32, device=dev)
+    dv = torch.empty(B, C, nh, D, dtype=torch.float32, device=dev)
+    db = torch.empty(ns, B, C, nh, dtype=torch.float32, device=dev)
+    dla = torch.empty(ns, B, C, nh, dtype=torch.float32, device=dev)
+    dS0 = torch.empty(B, nh, D, D, dtype=torch.float32, device=dev)
+    _check(_lib.lib().dttt_gdn_chunk_bwd(_p(k), _p(v), _p(beta), _p(log_alpha), _p(states), _p(gS), _p(dk), _p(dv), _p(db), _p(dla), _p(dS0),
+                                         B, C, nh, D, _stream()), "gdn_chunk_bwd")
+    return dk.sum(0), dv, db.sum(0), dla.sum(0), dS0
