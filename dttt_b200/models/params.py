@@ -141,7 +141,10 @@ def iter_init(cfg: ModelConfig, seed: int, device="cpu", tp: int = 1, tp_index: 
     device, the process count or how the tree is later sharded.  Normal leaves have std
     ``initializer_range`` (reference model.py:137-148), norm weights are 1, gates / biases 0, the GDN
     decay is initialised long (reference gdn.py:74-88)."""
-    base = trng.key(seed, device)
+    # keys are derived on the host (a few integers each); only the bulk draws run on `device`, where a GPU uses the
+    # counter-RNG kernel (same bits as the host statement)
+    base = trng.key(seed)
+    on = lambda key: key.to(device)
     for idx, (name, (shape, kind)) in enumerate(param_spec(cfg).items()):
         k = trng.fold_in(base, idx + 1)
         if kind == "ones":
@@ -150,9 +153,9 @@ def iter_init(cfg: ModelConfig, seed: int, device="cpu", tp: int = 1, tp_index: 
             t = torch.zeros(shape)
         elif kind == "normal":
             if len(shape) >= 3:        # stacked: one key per layer, so slicing the stack leaves values unchanged
-                t = torch.stack([trng.normal(trng.fold_in(k, l), shape[1:]) for l in range(shape[0])]) * cfg.initializer_range
+                t = torch.stack([trng.normal(on(trng.fold_in(k, l)), shape[1:]) for l in range(shape[0])]) * cfg.initializer_range
             else:
-                t = trng.normal(k, shape) * cfg.initializer_range
+                t = trng.normal(on(k), shape) * cfg.initializer_range
         elif kind == "gdn_dt":
             u = trng.uniform(k, shape, math.log(1e-4), math.log(1e-2))
             dt0 = torch.exp(u)
