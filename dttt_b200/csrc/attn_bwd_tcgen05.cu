@@ -24,17 +24,28 @@
 //               final dK / dV stores
 // TMEM columns: S^T / P^T [0,128)  dP^T / dS^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448).
 // Every wait is bounded (ptx_sm100.cuh); on a timeout the roles leave through the common exit and TMEM is freed.
+//
+// Which queries a key block meets is a LIST of work items built when the CTA starts: (sequence, query tile) pairs that see
+// at least one key of the block under the own-chunk pattern (attn_common.cuh).  In the plain form the list holds the query
+// tiles of the block's own sequence.  In the segment form a block of the clean stream's [previous window | segment] buffer
+// is met by every stream's chunks that have it in their window and by the clean stream's own chunk, so the gradient of a
+// clean key is accumulated once, in tensor memory, over all of them (no per-window partial gradients to add up afterwards).
 #include "ptx_sm100.cuh"
+#include "attn_common.cuh"
 
 #include <mutex>
+#include <cstring>
 
 namespace dttt {
 
 constexpr int BQ = 128, BKEY = 128, HD = 64;
+constexpr int MAX_ITEMS = 512;
 
 struct AttnBwdParams {
   int n, Cq, Kn, nh, nkv, causal;
   int Kn1;              // keys [0, Kn1) belong to the first K / V pair (and dK / dV), the rest to the second
+  int mask_mode, mask_param;
+  SegSpec sg;           // segment form: dK / dV mirror the clean buffer [B, (W + chunks) C, nkv, 64], dK2 / dV2 the streams' own keys
   float scale;
   const float* lse;     // [n, nh, Cq]
   const float* delta;   // [n, nh, Cq]  rowsum(dO * O)
@@ -128,7 +139,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   float* sDQ = reinterpret_cast<float*>(sDS + 2 * L::DS_BYTES);    // [128 queries][64] f32, the step's dQ tile
   float* sLSE = sDQ + 128 * HD;                              // [2][128], premultiplied by log2(e)
   float* sDel = sLSE + 2 * 128;                              // [2][128], premultiplied by scale
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sDel + 2 * 128));
+  int* sE1 = reinterpret_cast<int*>(sDel + 2 * 128);         // [2][128] per query column: last key of the prefix interval
+  int* sS2 = sE1 + 2 * 128;                                  // [2][128] second interval
+  int* sE2 = sS2 + 2 * 128;
+  int2* items = reinterpret_cast<int2*>(sE2 + 2 * 128);      // .x = sequence, .y = query tile * 2 + needs-mask
+  uint64_t* bars = reinterpret_cast<uint64_t*>(items + MAX_ITEMS);
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;                              // [2]
   uint64_t* st_empty = st_full + 2;                          // [2]
@@ -139,16 +154,75 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t* acc_final = dq_empty + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_final + 1);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_items_slot = const_cast<int*>(abort_word) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int rep = p.nh / p.nkv;
-  const int off = p.Kn - p.Cq;
   const int nqt = (p.Cq + BQ - 1) / BQ;
-  int qt_start = 0;
-  if (p.causal) { const int lo = jb * BKEY - off; qt_start = lo > 0 ? lo / BQ : 0; }
-  const int nq_it = max(0, nqt - qt_start);
-  const int n_it = rep * nq_it;
+  // ---- which key block this CTA owns: tensor pair (first / second), sequence and row inside that tensor
+  bool second;
+  int kseq, krow, klen;        // klen: rows of that tensor per sequence (for the output offset)
+  if (!p.sg.on) {
+    if (jb * BKEY >= p.Kn) return;
+    second = jb * BKEY >= p.Kn1;
+    kseq = b;
+    krow = second ? jb * BKEY - p.Kn1 : jb * BKEY;
+    klen = second ? p.Kn - p.Kn1 : p.Kn1;
+  } else {
+    // z = (sequence, stream): the clean stream's CTAs walk the clean buffer, the others their own keys
+    const int bb = b / p.sg.streams, st = b % p.sg.streams;
+    second = st != 1;
+    klen = second ? p.sg.chunks * p.Cq : (p.sg.W + p.sg.chunks) * p.Cq;
+    if (jb * BKEY >= klen) return;
+    krow = jb * BKEY;
+    kseq = second ? b : bb;                                  // own keys are [B * streams, chunks * C]; the clean buffer [B, ...]
+  }
+  // ---- the work items (one thread; a few hundred cheap tests at most)
+  if (threadIdx.x == 0) {
+    int n = 0;
+    auto consider = [&](int v, const SeqGeom& G, int kpos0) {
+      // key block = positions [kpos0, kpos0 + 127] of sequence v's key axis
+      for (int qt = 0; qt < nqt; ++qt) {
+        const int i0 = qt * BQ, i1 = min(i0 + BQ - 1, p.Cq - 1);
+        const RowMask a = row_mask(G.mode, G.param, i0, G.Kn, p.Cq), z = row_mask(G.mode, G.param, i1, G.Kn, p.Cq);
+        const bool any = (kpos0 <= z.e1) || (kpos0 + BKEY - 1 >= a.s2 && kpos0 <= z.e2);
+        if (!any) continue;
+        const bool all = (kpos0 + BKEY - 1 <= a.e1) || (kpos0 >= z.s2 && kpos0 + BKEY - 1 <= a.e2);
+        const bool ragged = kpos0 + BKEY > G.Kn;
+        if (n < MAX_ITEMS) items[n] = make_int2(v, qt * 2 + ((all && !ragged) ? 0 : 1));
+        ++n;
+      }
+    };
+    if (!p.sg.on) {
+      const SeqGeom G = seq_geom(p.sg, b, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
+      consider(b, G, jb * BKEY);
+    } else {
+      const int bb = b / p.sg.streams, st = b % p.sg.streams;
+      const int per_b = p.sg.streams * p.sg.chunks;
+      if (second) {
+        const int c = krow / p.Cq;
+        const int v = bb * per_b + st * p.sg.chunks + c;
+        const SeqGeom G = seq_geom(p.sg, v, p.Cq, 0, 0, 0, 0);
+        consider(v, G, G.Kn - p.Cq + (krow - c * p.Cq));
+      } else {
+        // a block of the clean buffer: row krow = chunk (krow / C - W) of the segment (negative: the previous segment's window)
+        const int kc = krow / p.Cq - p.sg.W;
+        for (int c = max(kc, 0); c < min(kc + p.sg.W + 1, p.sg.chunks); ++c)
+          for (int s2 = 0; s2 < p.sg.streams; ++s2) {
+            const int v = bb * per_b + s2 * p.sg.chunks + c;
+            const SeqGeom G = seq_geom(p.sg, v, p.Cq, 0, 0, 0, 0);
+            const int kpos0 = krow - G.row0;
+            // the stream reads this buffer up to its window (nv chunks), the clean stream (and a reading stream) one chunk further
+            const int reach_rows = G.nv * p.Cq + ((s2 == 1 || G.mode == MASK_READ) ? p.Cq : 0);
+            if (kpos0 < 0 || kpos0 >= reach_rows) continue;
+            consider(v, G, kpos0);
+          }
+      }
+    }
+    *n_items_slot = n;
+  }
+  // (published by the __syncthreads below)
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
 
@@ -170,23 +244,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  int nq_it = *n_items_slot;
+  if (nq_it > MAX_ITEMS) {                                   // the launcher sizes the list; never expected
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ERR_WORK_LIST);
+    nq_it = 0;
+  }
+  const int n_it = rep * nq_it;                              // heads of the group outermost, work items inside
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one() && n_it > 0) {
       mbar_expect_tx(kv_full, 2 * L::TILE);
-      const bool second = jb * BKEY >= p.Kn1;                // this key block lies in the second K / V pair
-      const int krow = second ? jb * BKEY - p.Kn1 : jb * BKEY;
-      tma_load_4d_b(sK, second ? &mapK2 : &mapK, kv_full, 0, hk, krow, b);
-      tma_load_4d_b(sV, second ? &mapV2 : &mapV, kv_full, 0, hk, krow, b);
+      tma_load_4d_b(sK, second ? &mapK2 : &mapK, kv_full, 0, hk, krow, kseq);
+      tma_load_4d_b(sV, second ? &mapV2 : &mapV, kv_full, 0, hk, krow, kseq);
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
         if (!mbar_wait_bounded(&st_empty[s], ((it >> 1) & 1) ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
-        const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+        const int2 item = items[it % nq_it];
+        const int h = hk * rep + it / nq_it, qt = item.y >> 1;
         uint8_t* sQ = sST + s * 2 * L::TILE;
         mbar_expect_tx(&st_full[s], 2 * L::TILE);
-        tma_load_4d_b(sQ, &mapQ, &st_full[s], 0, h, qt * BQ, b);
-        tma_load_4d_b(sQ + L::TILE, &mapdO, &st_full[s], 0, h, qt * BQ, b);
+        tma_load_4d_b(sQ, &mapQ, &st_full[s], 0, h, qt * BQ, item.x);
+        tma_load_4d_b(sQ + L::TILE, &mapdO, &st_full[s], 0, h, qt * BQ, item.x);
       }
     }
     __syncwarp();
@@ -256,18 +335,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int sub = w >> 2;                                  // which 32 of a half's 64 query columns
     const int tid = threadIdx.x - 64;                        // 0..255
     const int kr = quarter * 32 + lane;                      // key row within the block == TMEM lane
-    const int kj = jb * BKEY + kr;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr float LOG2E = 1.4426950408889634f;
-    const bool key_ok = kj < p.Kn;
     bool ok = n_it > 0;
-    auto load_aux = [&](int it, float& val) {
-      const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
+    // position of this CTA's first key row on the key axis of work item `item` (the pattern is stated on that axis)
+    auto key_pos0 = [&](const SeqGeom& G) -> int {
+      if (!p.sg.on) return jb * BKEY;
+      return second ? G.Kn - p.Cq + (krow % p.Cq) : krow - G.row0;
+    };
+    auto load_aux = [&](int it, float& val, int& e1, int& s2, int& e2) {
+      const int2 item = items[it % nq_it];
+      const int h = hk * rep + it / nq_it, qt = item.y >> 1;
       const int qi = qt * BQ + (tid & 127);
-      const long long base = ((long long)b * p.nh + h) * p.Cq;
-      if (tid < 128) val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
-      else val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
+      const long long base = ((long long)item.x * p.nh + h) * p.Cq;
+      if (tid < 128) {
+        val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
+        // the keys query qi sees, as positions RELATIVE to this block's first row; rows past the sequence see nothing
+        const SeqGeom G = seq_geom(p.sg, item.x, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
+        const int k0 = key_pos0(G);
+        const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
+        e1 = rm.e1 - k0; s2 = rm.s2 - k0; e2 = rm.e2 - k0;
+      } else {
+        val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
+      }
     };
     // add the dQ tile of step `it` (lanes = queries) into global memory: the eight warps copy it from TMEM into a
     // shared-memory tile and one thread issues a single bulk tensor reduction (f32 add) for the whole 128 x 64 tile;
@@ -294,25 +385,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       fence_async_proxy();
       asm volatile("bar.sync 2, 256;" ::: "memory");
       if (tid == 0) {
-        const int h = hk * rep + it / nq_it, qt = qt_start + it % nq_it;
-        tma_reduce_add_4d(&mapdQ, sDQ, 0, h, qt * BQ, b);
-        tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, 32, h, qt * BQ, b);
+        const int2 item = items[it % nq_it];
+        const int h = hk * rep + it / nq_it, qt = item.y >> 1;
+        tma_reduce_add_4d(&mapdQ, sDQ, 0, h, qt * BQ, item.x);
+        tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, 32, h, qt * BQ, item.x);
         bulk_commit();
       }
       return true;
     };
     if (ok) {
       float v0;
-      load_aux(0, v0);
-      if (tid < 128) sLSE[tid] = v0; else sDel[tid - 128] = v0;
+      int a0 = 0, a1 = 0, a2 = 0;
+      load_aux(0, v0, a0, a1, a2);
+      if (tid < 128) { sLSE[tid] = v0; sE1[tid] = a0; sS2[tid] = a1; sE2[tid] = a2; } else sDel[tid - 128] = v0;
     }
     for (int it = 0; it < n_it && ok; ++it) {
       float vnext = 0.f;
-      if (it + 1 < n_it) load_aux(it + 1, vnext);
-      const int qt = qt_start + it % nq_it;
+      int n1 = 0, n2 = 0, n3 = 0;
+      if (it + 1 < n_it) load_aux(it + 1, vnext, n1, n2, n3);
       const float* lse2 = sLSE + (it & 1) * 128;
       const float* del = sDel + (it & 1) * 128;
-      const bool need_mask = p.causal && (jb * BKEY + BKEY - 1 > qt * BQ + off);
+      const int* e1s = sE1 + (it & 1) * 128;
+      const int* s2s = sS2 + (it & 1) * 128;
+      const int* e2s = sE2 + (it & 1) * 128;
+      const bool need_mask = (items[it % nq_it].y & 1) != 0;
       uint8_t* ds_tile = sDS + (it & 1) * L::DS_BYTES;
 #pragma unroll 1
       for (int hf = 0; hf < 2 && ok; ++hf) {
@@ -338,7 +434,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
-              if (!key_ok || (need_mask && kj > qt * BQ + c0 + i + u + off)) pe = 0.f;
+              if (need_mask) {
+                const int q = c0 + i + u;                    // query column; visible: kr <= e1 or s2 <= kr <= e2 (block-relative)
+                if (kr > e1s[q] && (kr < s2s[q] || kr > e2s[q])) pe = 0.f;
+              }
               pv[u] = pe;
               dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
             }
@@ -373,7 +472,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       if (!ok) break;
       // next step's LSE / D into the other buffer (its last readers passed barrier 1 of this step)
       if (it + 1 < n_it) {
-        if (tid < 128) sLSE[((it + 1) & 1) * 128 + tid] = vnext; else sDel[((it + 1) & 1) * 128 + tid - 128] = vnext;
+        const int nx = ((it + 1) & 1) * 128;
+        if (tid < 128) { sLSE[nx + tid] = vnext; sE1[nx + tid] = n1; sS2[nx + tid] = n2; sE2[nx + tid] = n3; } else sDel[nx + tid - 128] = vnext;
       }
     }
     if (ok) ok = reduce_dq(n_it - 1);
@@ -389,12 +489,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_ld_32x32(tmem + C_DV + lane_addr + sub * 32, rv);
         tmem_ld_32x32(tmem + C_DK + lane_addr + sub * 32, rk);
         tmem_ld_wait();
-        if (kj < p.Kn) {
-          const bool second = kj >= p.Kn1;
-          const int len = second ? p.Kn - p.Kn1 : p.Kn1, kl = second ? kj - p.Kn1 : kj;
+        if (krow + kr < klen) {
           __nv_bfloat16* outK = second ? p.dK2 : p.dK;
           __nv_bfloat16* outV = second ? p.dV2 : p.dV;
-          const long long o = (((long long)b * len + kl) * p.nkv + hk) * HD + sub * 32;
+          const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * 32;
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 v, k;
@@ -410,11 +508,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
       }
-    } else if (n_it == 0 && kj < p.Kn) {
+    } else if (n_it == 0 && krow + kr < klen) {
       // no query sees this key block: its gradients are zero
-      const bool second = kj >= p.Kn1;
-      const int len = second ? p.Kn - p.Kn1 : p.Kn1, kl = second ? kj - p.Kn1 : kj;
-      const long long o = (((long long)b * len + kl) * p.nkv + hk) * HD + sub * 32;
+      const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * 32;
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int i = 0; i < 32; i += 8) {
@@ -477,18 +573,36 @@ static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int he
 
 using namespace dttt;
 
+namespace dttt {
+static int launch_bwd(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const CUtensorMap& mk2, const CUtensorMap& mv2, const CUtensorMap& mdq, const AttnBwdParams& p,
+                      const void* O, const void* dO, float* delta, long long q_rows, cudaStream_t stream) {
+  attn_bwd_delta_kernel<<<(unsigned)((q_rows * 8 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, q_rows, p.Cq, p.nh);
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
+  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+}  // namespace dttt
+
 // Q, O, dO [n, Cq, nh, 64] (bf16, contiguous); keys / values as one or two pairs like dttt_attn_fwd (K2 == null: one pair):
 // K / V [n, Kn1, nkv, 64] with `k_bs` / `v_bs` elements between sequences, K2 / V2 [n, Kn2, nkv, 64]; dK / dV [n, Kn1, nkv, 64]
 // and dK2 / dV2 [n, Kn2, nkv, 64] contiguous outputs; lse [n, nh, Cq] f32 from the forward; delta [n, nh, Cq] f32 scratch
-// (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).
-extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* K2, const void* V2, const void* O, const void* dO,
-                             const float* lse, float* delta, float* dQ, void* dK, void* dV, void* dK2, void* dV2, int n, int Cq,
-                             int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs, long long k2_bs,
-                             long long v2_bs, float scale, int causal, int* status, cudaStream_t stream) {
+// (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).  mode / param: the own-chunk pattern as in
+// dttt_attn_fwd_masked (Cq a multiple of 128 for modes 2-4).
+extern "C" int dttt_attn_bwd_masked(const void* Q, const void* K, const void* V, const void* K2, const void* V2, const void* O,
+                                    const void* dO, const float* lse, float* delta, float* dQ, void* dK, void* dV, void* dK2, void* dV2,
+                                    int n, int Cq, int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs,
+                                    long long k2_bs, long long v2_bs, float scale, int mode, int param, int* status,
+                                    cudaStream_t stream) {
   const int Kn = Kn1 + (K2 ? Kn2 : 0);
-  if (d != HD || nh % nkv || n <= 0 || Cq <= 0 || Kn <= 0) return -2;
-  if (causal && Kn < Cq) return -3;
+  if (d != HD || nh % nkv || n <= 0 || Cq <= 0 || Kn < Cq || mode < 0 || mode > MASK_READ) return -2;
+  if (mode >= MASK_SPLIT && (Cq % BKEY || param <= 0 || param > Cq)) return -3;
+  if (mode == MASK_READ && Kn < 2 * Cq) return -3;
   if (K2 && Kn1 % BKEY) return -4;
+  if ((Cq + BQ - 1) / BQ > MAX_ITEMS) return -5;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
   CUtensorMap mq, mdo, mk, mv, mk2, mv2, mdq;
@@ -496,26 +610,72 @@ extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const 
   if ((r = make_map4f(&mdq, dQ, n, Cq, nh))) return 500 + r;
   if ((r = make_map4b(&mq, Q, n, Cq, nh))) return 100 + r;
   if ((r = make_map4b(&mdo, dO, n, Cq, nh))) return 200 + r;
-  if ((r = make_map4b(&mk, K, n, Kn1, nkv, k_bs))) return 300 + r;
-  if ((r = make_map4b(&mv, V, n, Kn1, nkv, v_bs))) return 400 + r;
+  if (Kn1 > 0) {
+    if ((r = make_map4b(&mk, K, n, Kn1, nkv, k_bs))) return 300 + r;
+    if ((r = make_map4b(&mv, V, n, Kn1, nkv, v_bs))) return 400 + r;
+  }
   if (K2) {
     if ((r = make_map4b(&mk2, K2, n, Kn2, nkv, k2_bs))) return 600 + r;
     if ((r = make_map4b(&mv2, V2, n, Kn2, nkv, v2_bs))) return 700 + r;
+    if (Kn1 == 0) { mk = mk2; mv = mv2; }
   } else {
     mk2 = mk; mv2 = mv;
   }
-  const long long rows = (long long)n * Cq * nh;
-  attn_bwd_delta_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, rows, Cq, nh);
   AttnBwdParams p;
-  p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
+  memset(&p, 0, sizeof(p));
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = mode == MASK_CAUSAL; p.scale = scale;
+  p.mask_mode = mode; p.mask_param = param;
   p.lse = lse; p.delta = delta; p.dQ = dQ;
   p.dK = reinterpret_cast<__nv_bfloat16*>(dK); p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
   p.dK2 = reinterpret_cast<__nv_bfloat16*>(dK2); p.dV2 = reinterpret_cast<__nv_bfloat16*>(dV2); p.status = status;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
   dim3 grid((Kn + BKEY - 1) / BKEY, nkv, n);
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
-  cudaError_t e = cudaGetLastError();
-  return e == cudaSuccess ? 0 : 1000 + (int)e;
+  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * Cq * nh, stream);
+}
+
+extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* K2, const void* V2, const void* O, const void* dO,
+                             const float* lse, float* delta, float* dQ, void* dK, void* dV, void* dK2, void* dV2, int n, int Cq,
+                             int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs, long long k2_bs,
+                             long long v2_bs, float scale, int causal, int* status, cudaStream_t stream) {
+  return dttt_attn_bwd_masked(Q, K, V, K2, V2, O, dO, lse, delta, dQ, dK, dV, dK2, dV2, n, Cq, Kn1, Kn2, nh, nkv, d, k_bs, v_bs, k2_bs,
+                              v2_bs, scale, causal ? MASK_CAUSAL : MASK_FULL, 0, status, stream);
+}
+
+// Backward of dttt_attn_fwd_segment.  Q, O, dO [B, streams, chunks * C, nh, 64]; Kc / Vc the clean buffer [B, (W + chunks) C, nkv, 64]
+// (`kc_bs` / `vc_bs` elements between sequences); Ko / Vo [B, streams, chunks * C, nkv, 64]; lse, delta [B * streams * chunks, nh, C];
+// dQ f32 like Q, zero on entry.  Outputs: dKc / dVc [B, (W + chunks) C, nkv, 64] contiguous (the gradient of every clean key from
+// every chunk that had it in its window AND from the clean stream's own chunk, summed on chip); dKo / dVo [B, streams, chunks * C,
+// nkv, 64] for the other streams' own keys (the clean stream's slot is not written: its own keys are rows of the clean buffer).
+// The clean stream is stream 1.
+extern "C" int dttt_attn_bwd_segment(const void* Q, const void* Kc, const void* Vc, const void* Ko, const void* Vo, const void* O,
+                                     const void* dO, const float* lse, float* delta, float* dQ, void* dKc, void* dVc, void* dKo, void* dVo,
+                                     int B, int streams, int chunks, int C, int W, int first, int reach, int nh, int nkv, int d,
+                                     long long kc_bs, long long vc_bs, const int* modes, const int* params, float scale, int* status,
+                                     cudaStream_t stream) {
+  if (d != HD || nh % nkv || B <= 0 || streams < 2 || streams > MAX_STREAMS || chunks <= 0 || C % BKEY || W < 0) return -2;
+  if (streams * (W + 1) * (C / BQ) > MAX_ITEMS) return -5;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
+  const int n = B * streams * chunks;
+  CUtensorMap mq, mdo, mk, mv, mk2, mv2, mdq;
+  int r;
+  if ((r = make_map4f(&mdq, dQ, n, C, nh))) return 500 + r;
+  if ((r = make_map4b(&mq, Q, n, C, nh))) return 100 + r;
+  if ((r = make_map4b(&mdo, dO, n, C, nh))) return 200 + r;
+  if ((r = make_map4b(&mk, Kc, B, (W + chunks) * C, nkv, kc_bs))) return 300 + r;
+  if ((r = make_map4b(&mv, Vc, B, (W + chunks) * C, nkv, vc_bs))) return 400 + r;
+  if ((r = make_map4b(&mk2, Ko, B * streams, chunks * C, nkv))) return 600 + r;
+  if ((r = make_map4b(&mv2, Vo, B * streams, chunks * C, nkv))) return 700 + r;
+  AttnBwdParams p;
+  memset(&p, 0, sizeof(p));
+  p.n = n; p.Cq = C; p.nh = nh; p.nkv = nkv; p.scale = scale;
+  p.sg.on = 1; p.sg.streams = streams; p.sg.chunks = chunks; p.sg.first = first; p.sg.W = W; p.sg.reach = reach;
+  for (int s = 0; s < streams; ++s) {
+    if (modes[s] < 0 || modes[s] >= MASK_READ || (modes[s] >= MASK_SPLIT && (params[s] <= 0 || params[s] > C))) return -3;
+    p.sg.mode[s] = modes[s]; p.sg.param[s] = params[s];
+  }
+  p.lse = lse; p.delta = delta; p.dQ = dQ;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dKc); p.dV = reinterpret_cast<__nv_bfloat16*>(dVc);
+  p.dK2 = reinterpret_cast<__nv_bfloat16*>(dKo); p.dV2 = reinterpret_cast<__nv_bfloat16*>(dVo); p.status = status;
+  dim3 grid((W + chunks) * C / BKEY, nkv, B * streams);
+  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * C * nh, stream);
 }

@@ -17,8 +17,10 @@
 // S(j+1) is issued before the softmax of block j finishes, so the tensor pipe and the exponentials overlap.
 // Every wait is bounded (ptx_sm100.cuh): on a timeout the roles leave through the common exit and TMEM is freed.
 #include "ptx_sm100.cuh"
+#include "attn_common.cuh"
 
 #include <mutex>
+#include <cstring>
 
 namespace dttt {
 
@@ -32,7 +34,13 @@ struct AttnParams {
   __nv_bfloat16* O;
   float* lse;
   int* status;
+  int mask_mode, mask_param;      // own-chunk pattern (two-tile kernel); `causal` is MASK_CAUSAL for the one-tile kernel
+  SegSpec sg;                     // segment form (attn_common.cuh)
 };
+
+__device__ __forceinline__ SeqGeom seq_geom(const AttnParams& p, int v) {
+  return seq_geom(p.sg, v, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
+}
 
 template <int D>
 struct AttnSmem {
@@ -326,16 +334,32 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   const int qt = gridDim.x - 1 - blockIdx.x;                // longest (latest) query tiles first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.nh / p.nkv);
-  const int q0 = qt * 2 * AQ;
-  const int off = p.Kn - p.Cq;
-  int nb[2];
+  const SeqGeom G = seq_geom(p, b);
+  // The sub-block read leaves a gap in a row's keys and the two tiles of a CTA would walk different block lists:
+  // it runs one tile per CTA.  Every other pattern is a prefix of the key axis per row.
+  const bool single = G.mode == MASK_READ;
+  const int q0 = single ? qt * AQ : qt * 2 * AQ;
+  int nb[2], n1[2];
+  int gap_from = 0, gap_to = 0;                             // second block range of the single-tile form: [gap_to, ...) follows n1
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    int last_key = p.Kn - 1;
-    if (p.causal) last_key = min(last_key, q0 + t * AQ + AQ - 1 + off);
-    nb[t] = (q0 + t * AQ < p.Cq) ? last_key / AK + 1 : 0;
+    const int i0 = q0 + t * AQ, i1 = min(i0 + AQ - 1, p.Cq - 1);
+    nb[t] = n1[t] = 0;
+    if (i0 < p.Cq && !(single && t == 1)) {
+      const RowMask last = row_mask(G.mode, G.param, i1, G.Kn, p.Cq);
+      n1[t] = last.e1 >= 0 ? last.e1 / AK + 1 : 0;
+      nb[t] = n1[t];
+      if (single) {
+        const RowMask first = row_mask(G.mode, G.param, i0, G.Kn, p.Cq);
+        gap_from = n1[t];
+        gap_to = max(first.s2 / AK, n1[t]);
+        nb[t] = n1[t] + (last.e2 / AK - gap_to + 1);
+      }
+    }
   }
   const int nbmax = max(nb[0], nb[1]);
+  // entry jj of the block list -> key block
+  auto blk = [&](int jj) { return (single && jj >= gap_from) ? gap_to + (jj - gap_from) : jj; };
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t O_COL = 256;
 
@@ -357,12 +381,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
-      mbar_expect_tx(q_full, L::Q_BYTES);
+      mbar_expect_tx(q_full, (nb[1] > 0 ? 2 : 1) * (L::Q_BYTES / 2));
 #pragma unroll
       for (int t = 0; t < 2; ++t)
 #pragma unroll
         for (int db = 0; db < DB; ++db)
-          tma_load_4d(sQ + t * (AQ * D * 2) + db * (AQ * 128), &mapQ, q_full, db * 64, h, q0 + t * AQ, b);
+          if (nb[t] > 0 || t == 0) tma_load_4d(sQ + t * (AQ * D * 2) + db * (AQ * 128), &mapQ, q_full, db * 64, h, q0 + t * AQ, b);
       for (int j = 0; j < nbmax; ++j) {
         const int s = j % L::STAGES;
         const uint32_t ph = (j / L::STAGES) & 1;
@@ -373,10 +397,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
           // the window (first pair) and the chunk's own keys (second pair) are separate tensors: no concatenation pass
-          const bool second = j * AK >= p.Kn1;
-          const int krow = second ? j * AK - p.Kn1 : j * AK;
-          tma_load_4d(sK + db * (AK * 128), second ? &mapK2 : &mapK, &kv_full[s], db * 64, hk, krow, b);
-          tma_load_4d(sV + db * (AK * 128), second ? &mapV2 : &mapV, &kv_full[s], db * 64, hk, krow, b);
+          const int k0 = blk(j) * AK;
+          const bool second = k0 >= G.Kn1;
+          const int krow = second ? k0 - G.Kn1 : G.row0 + k0;
+          const int kbat = second ? b : G.kb;
+          tma_load_4d(sK + db * (AK * 128), second ? &mapK2 : &mapK, &kv_full[s], db * 64, hk, krow, kbat);
+          tma_load_4d(sV + db * (AK * 128), second ? &mapV2 : &mapV, &kv_full[s], db * 64, hk, krow, kbat);
         }
       }
     }
@@ -437,7 +463,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const uint32_t s_addr = tmem + t * 128 + lane_addr;
     const uint32_t o_addr = tmem + O_COL + t * D + lane_addr;
     const float sl2 = p.scale * 1.4426950408889634f;
-    const int limit = p.causal ? (qi + off) : (p.Kn - 1);
+    const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
     float m = -1e30f, l = 0.f;
     bool ok = true;
     const int nbt = nb[t];
@@ -453,12 +479,14 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sr[64]));
       tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sr[96]));
       tmem_ld_wait();
-      const int kbase = j * AK;
-      if ((kbase + AK - 1 > limit) || (kbase + AK > p.Kn)) {
-        const int lim = min(limit, p.Kn - 1) - kbase;        // last visible column of this block for this row
+      const int kbase = blk(j) * AK;
+      const bool whole = (kbase + AK - 1 <= rm.e1) || (kbase >= rm.s2 && kbase + AK - 1 <= rm.e2);
+      if (!whole) {
+        // columns of this block the row sees: [0, hi1] (prefix interval) and [lo2, hi2] (second interval)
+        const int hi1 = rm.e1 - kbase, lo2 = rm.s2 - kbase, hi2 = rm.e2 - kbase;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (i > lim) sr[i] = __float_as_uint(-1e30f);
+          if (i > hi1 && (i < lo2 || i > hi2)) sr[i] = __float_as_uint(MASKED);
       }
       float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
 #pragma unroll
@@ -598,8 +626,10 @@ extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, const 
     mk2 = mk; mv2 = mv;
   }
   AttnParams p;
+  memset(&p, 0, sizeof(p));
   p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = causal; p.scale = scale;
   p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
+  p.mask_mode = causal ? MASK_CAUSAL : MASK_FULL;
   if (variant == 0) {
     dim3 grid2((Cq + 2 * AQ - 1) / (2 * AQ), nh, n);
     static bool a64 = false, a128 = false;
@@ -624,4 +654,94 @@ extern "C" int dttt_attn_fwd(const void* Q, const void* K, const void* V, const 
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+namespace dttt {
+template <int D>
+static int launch_fwd2(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mk2,
+                       const CUtensorMap& mv2, const AttnParams& p, cudaStream_t stream) {
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(attn_fwd2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<D>::TOTAL); attr = true; }
+  attn_fwd2_kernel<D><<<grid, 320, Attn2Smem<D>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+}  // namespace dttt
+
+// The forward with an own-chunk pattern: mode 0 full, 1 causal, 2 split (param = context length), 3 block (param = sub-block),
+// 4 sub-block read (param = sub-block; the keys are [window | clean own chunk | own chunk], Kn1 counts the first two).  Cq must be
+// a multiple of 128 for modes 2-4.  Arguments otherwise as dttt_attn_fwd with two key / value pairs.
+extern "C" int dttt_attn_fwd_masked(const void* Q, const void* K, const void* V, const void* K2, const void* V2, void* O, float* lse, int n,
+                                    int Cq, int Kn1, int Kn2, int nh, int nkv, int d, long long k_bs, long long v_bs, long long k2_bs,
+                                    long long v2_bs, float scale, int mode, int param, int* status, cudaStream_t stream) {
+  const int Kn = Kn1 + (K2 ? Kn2 : 0);
+  if ((d != 64 && d != 128) || nh % nkv || n <= 0 || Cq <= 0 || Kn < Cq || mode < 0 || mode > MASK_READ) return -2;
+  if (mode >= MASK_SPLIT && (Cq % AK || param <= 0 || param > Cq)) return -3;
+  if (mode == MASK_READ && Kn < 2 * Cq) return -3;
+  if (K2 && Kn1 % AK) return -4;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
+  CUtensorMap mq, mk, mv, mk2, mv2;
+  int r;
+  if ((r = make_map4(&mq, Q, n, Cq, nh, d))) return 100 + r;
+  if (Kn1 > 0) {
+    if ((r = make_map4(&mk, K, n, Kn1, nkv, d, k_bs))) return 200 + r;
+    if ((r = make_map4(&mv, V, n, Kn1, nkv, d, v_bs))) return 300 + r;
+  }
+  if (K2) {
+    if ((r = make_map4(&mk2, K2, n, Kn2, nkv, d, k2_bs))) return 400 + r;
+    if ((r = make_map4(&mv2, V2, n, Kn2, nkv, d, v2_bs))) return 500 + r;
+    if (Kn1 == 0) { mk = mk2; mv = mv2; }
+  } else {
+    mk2 = mk; mv2 = mv;
+  }
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.n = n; p.Cq = Cq; p.Kn = Kn; p.Kn1 = K2 ? Kn1 : Kn; p.nh = nh; p.nkv = nkv; p.causal = mode == MASK_CAUSAL; p.scale = scale;
+  p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
+  p.mask_mode = mode; p.mask_param = param;
+  const int tiles = mode == MASK_READ ? (Cq + AQ - 1) / AQ : (Cq + 2 * AQ - 1) / (2 * AQ);
+  dim3 grid(tiles, nh, n);
+  return d == 64 ? launch_fwd2<64>(grid, mq, mk, mv, mk2, mv2, p, stream) : launch_fwd2<128>(grid, mq, mk, mv, mk2, mv2, p, stream);
+}
+
+// Segment form: every chunk of every stream of a [B, streams, chunks * C] segment in ONE launch, the clean windows read in place.
+//   Q, O          [B, streams, chunks * C, nh, d]   (contiguous)       lse [B * streams * chunks, nh, C]
+//   Kc, Vc        the clean stream's keys / values with the window of the previous segment in front: [B, (W + chunks) * C, nkv, d],
+//                 `kc_bs` / `vc_bs` elements between sequences
+//   Ko, Vo        every stream's own keys / values [B, streams, chunks * C, nkv, d] (contiguous)
+//   first         index within the sequence of the segment's first chunk; reach < 0: no limit on the window
+//   modes, params per stream own-chunk pattern (as dttt_attn_fwd_masked; a stream in read mode finds the clean own chunk right
+//                 behind its window in Kc / Vc)
+extern "C" int dttt_attn_fwd_segment(const void* Q, const void* Kc, const void* Vc, const void* Ko, const void* Vo, void* O, float* lse,
+                                     int B, int streams, int chunks, int C, int W, int first, int reach, int nh, int nkv, int d,
+                                     long long kc_bs, long long vc_bs, const int* modes, const int* params, float scale, int* status,
+                                     cudaStream_t stream) {
+  if ((d != 64 && d != 128) || nh % nkv || B <= 0 || streams <= 0 || streams > MAX_STREAMS || chunks <= 0 || C % AK || W < 0) return -2;
+  static thread_local bool ctx_bound = false;
+  if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
+  const int n = B * streams * chunks;
+  CUtensorMap mq, mk, mv, mk2, mv2;
+  int r;
+  if ((r = make_map4(&mq, Q, n, C, nh, d))) return 100 + r;
+  if ((r = make_map4(&mk, Kc, B, (W + chunks) * C, nkv, d, kc_bs))) return 200 + r;
+  if ((r = make_map4(&mv, Vc, B, (W + chunks) * C, nkv, d, vc_bs))) return 300 + r;
+  if ((r = make_map4(&mk2, Ko, n, C, nkv, d))) return 400 + r;
+  if ((r = make_map4(&mv2, Vo, n, C, nkv, d))) return 500 + r;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.n = n; p.Cq = C; p.nh = nh; p.nkv = nkv; p.scale = scale;
+  p.O = reinterpret_cast<__nv_bfloat16*>(O); p.lse = lse; p.status = status;
+  p.sg.on = 1; p.sg.streams = streams; p.sg.chunks = chunks; p.sg.first = first; p.sg.W = W; p.sg.reach = reach;
+  bool any_read = false;
+  for (int s = 0; s < streams; ++s) {
+    p.sg.mode[s] = modes[s]; p.sg.param[s] = params[s];
+    if (modes[s] < 0 || modes[s] > MASK_READ || (modes[s] >= MASK_SPLIT && (params[s] <= 0 || params[s] > C))) return -3;
+    any_read |= modes[s] == MASK_READ;
+  }
+  // one tile per CTA when a stream uses the read pattern (its CTAs walk a block list with a gap); the others then simply run
+  // their second tile as a CTA of its own
+  if (any_read) return -5;
+  dim3 grid((C + 2 * AQ - 1) / (2 * AQ), nh, n);
+  return d == 64 ? launch_fwd2<64>(grid, mq, mk, mv, mk2, mv2, p, stream) : launch_fwd2<128>(grid, mq, mk, mv, mk2, mv2, p, stream);
 }

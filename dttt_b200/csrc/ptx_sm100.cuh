@@ -27,7 +27,8 @@ enum : int {
   ERR_WAIT_TMEM_EMPTY = 4, // MMA issuer waited for an accumulator that was never drained
   ERR_WAIT_PEER = 5,       // a peer-rank flag was never raised
   ERR_WAIT_DRAIN = 6,      // in-flight copies did not land while unwinding
-  ERR_TEST_FLAG = 7        // the self-test wait on a flag nobody sets (expected to time out)
+  ERR_TEST_FLAG = 7,       // the self-test wait on a flag nobody sets (expected to time out)
+  ERR_WORK_LIST = 8        // a kernel's work list did not fit the space its launcher gave it
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

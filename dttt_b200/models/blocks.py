@@ -149,6 +149,12 @@ class Net:
         nc = T // C
         x = self.norm("prefix.attn_norm.weight", l, h)
         q, k, v = self.qkv("prefix", l, x, pos_k, pos_q)                       # [B, S, T, heads, d]
+        if not read_block and A.segment_attention_ok(q, C, Wn, owns):
+            # one launch for all chunks and streams; the clean windows are read in place (ops.attention._SegmentAttention)
+            a_seg, k_tail, v_tail = A.segment_attention(q, k, v, kv_win, C, Wn, first_chunk, reach, owns, self.scale)
+            h = h + Fn.linear(a_seg.flatten(-2), self.p("prefix.attn.o.weight", l))
+            h = h + self.mlp("prefix", l, self.norm("prefix.mlp_norm.weight", l, h))
+            return h, (k_tail, v_tail)
         kc, vc = k[:, CLEAN], v[:, CLEAN]
         k_prev, v_prev = (None, None) if kv_win is None else kv_win
         B = q.shape[0]                                                         # all sequences of the tensor-parallel group

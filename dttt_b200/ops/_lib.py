@@ -24,7 +24,8 @@ _status: dict[int, torch.Tensor] = {}
 ERR_NAMES = {0: "ok", 1: "wait for a TMA stage (full barrier) timed out", 2: "wait for a free stage (empty barrier) timed out",
              3: "wait for an accumulator (tmem full) timed out", 4: "wait for a drained accumulator (tmem empty) timed out",
              5: "wait for a peer rank's flag timed out", 6: "draining in-flight copies timed out",
-             7: "self-test flag wait timed out (expected in the bounded-wait test)"}
+             7: "self-test flag wait timed out (expected in the bounded-wait test)",
+             8: "a kernel's work list overflowed the space its launcher reserved"}
 
 
 class KernelError(RuntimeError):

@@ -17,7 +17,6 @@ from functools import lru_cache
 from typing import Optional, Tuple
 
 import torch
-import torch.nn.functional as F
 
 from . import reference as ref
 from .functional import staged, use_kernels
@@ -146,19 +145,6 @@ def read_mask_matrix(chunk: int, block: int, device=None) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------ general attention
-def _sdpa_fast(q, k, v, scale, causal_lower_right: bool):
-    """q [n, C, nh, d], k/v [n, K, nkv, d], every key valid; full pattern or causal aligned to the end of
-    the key axis (query i sees keys j <= i + K - C)."""
-    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
-    if causal_lower_right and k.shape[1] != q.shape[1]:
-        from torch.nn.attention.bias import causal_lower_right as clr
-        o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=clr(q.shape[1], k.shape[1]), scale=scale,
-                                           enable_gqa=True)
-    else:
-        o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=causal_lower_right, scale=scale, enable_gqa=True)
-    return o.transpose(1, 2)
-
-
 def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, key_valid: Optional[torch.Tensor], scale: float,
            own_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Exact masked attention, any order of differentiation (``ops.reference.attend``)."""
@@ -178,23 +164,123 @@ def attend_window(q: torch.Tensor, k_own: torch.Tensor, v_own: torch.Tensor, k_w
     """
     WC = k_win.shape[1]
     kw, vw = k_win[:, WC - n_valid * chunk:], v_win[:, WC - n_valid * chunk:]
-    if (extra_own is None and n_valid > 0 and use_kernels(q) and (own_mask is None and own in ("full", "causal"))
-            and _two_segment_ok(q, kw, k_own)):
-        # window and own keys stay separate tensors: the kernels read (and, backward, write) both pairs directly
-        return staged((_fast_fwd2, _fast_bwd2, _ref_for_staged2, _diff_bwd2), (q, kw, vw, k_own.to(kw.dtype), v_own.to(vw.dtype)),
-                      (scale, own == "causal"))
+    named = own_mask is None or extra_own is not None      # the pattern is one the kernels know by name
+    pattern = own
+    if extra_own is not None:
+        # sub-block read: [window | clean own keys | noisy own keys]; its [C, 2C] mask is the "read" pattern of the model's read_block
+        if own_mask is None or own_mask.shape[-1] != 2 * q.shape[1]:
+            named = False
+        else:
+            pattern = f"read:{_read_block_of(own_mask)}"
+    if named and use_kernels(q) and _pattern_ok(q, kw, k_own, pattern):
+        if extra_own is not None:
+            kw = torch.cat([kw, extra_own[0].to(kw.dtype)], dim=1)
+            vw = torch.cat([vw, extra_own[1].to(vw.dtype)], dim=1)
+        if kw.shape[1] > 0 and _two_segment_ok(q, kw, k_own):
+            # window and own keys stay separate tensors: the kernels read (and, backward, write) both pairs directly
+            return staged((_fast_fwd2, _fast_bwd2, _ref_for_staged2, _diff_bwd2), (q, kw, vw, k_own.to(kw.dtype), v_own.to(vw.dtype)),
+                          (scale, pattern))
+        K = torch.cat([kw, k_own.to(kw.dtype)], dim=1) if kw.shape[1] else k_own
+        V = torch.cat([vw, v_own.to(vw.dtype)], dim=1) if vw.shape[1] else v_own
+        return staged((_fast_fwd, _fast_bwd, _ref_for_staged, _diff_bwd), (q, K, V), (scale, pattern))
     parts_k = [kw] + ([extra_own[0].to(k_own.dtype)] if extra_own is not None else []) + [k_own]
     parts_v = [vw] + ([extra_own[1].to(v_own.dtype)] if extra_own is not None else []) + [v_own]
     K = torch.cat(parts_k, dim=1) if len(parts_k) > 1 or n_valid else k_own
     V = torch.cat(parts_v, dim=1) if len(parts_v) > 1 or n_valid else v_own
     if own_mask is None and own != "full":
         own_mask = own_mask_matrix(q.shape[1], own, q.device)
-    simple = own_mask is None or (own == "causal" and extra_own is None)
-    if use_kernels(q) and simple:
-        causal = own_mask is not None
-        spec = (_fast_fwd, _fast_bwd, _ref_for_staged, _diff_bwd)
-        return staged(spec, (q, K, V), (scale, causal))
+    if use_kernels(q) and own_mask is None:
+        return staged((_fast_fwd, _fast_bwd, _ref_for_staged, _diff_bwd), (q, K, V), (scale, "full"))
     return ref.attend(q, K, V, None, scale, own_mask)
+
+
+def _read_block_of(read_mask: torch.Tensor) -> int:
+    """Sub-block length of a ``read_mask_matrix``: the number of own (second-half) keys the first query sees."""
+    C = read_mask.shape[0]
+    key = (C, read_mask.data_ptr())
+    b = _READ_BLOCKS.get(key)
+    if b is None:
+        b = _READ_BLOCKS[key] = int(read_mask[0, C:].sum().item())
+    return b
+
+
+_READ_BLOCKS = {}
+
+
+def _pattern_ok(q, kw, k_own, pattern: str) -> bool:
+    """Can the kernels run this pattern on these shapes?  ``full`` / ``causal`` always (any chunk length); the others need
+    chunks that are multiples of 128 and, for the backward, head dimension 64."""
+    from . import kernels
+    if not (kernels.available("attention") and kernels.attention_supported(q, k_own)):
+        return False
+    mode, _ = kernels.parse_pattern(pattern)
+    if mode <= 1:
+        return True
+    return q.is_cuda and q.shape[1] % 128 == 0 and kw.shape[1] % 128 == 0 and kernels.available("attention_segment")
+
+
+def _own_part_mask(pattern: str, C: int, device) -> Optional[torch.Tensor]:
+    """The bool mask of a named pattern over the own-chunk keys: ``[C, C]``, for ``read`` ``[C, 2 C]`` (clean own keys first)."""
+    name, _, arg = pattern.partition(":")
+    if name == "full":
+        return None
+    return read_mask_matrix(C, int(arg), device) if name == "read" else own_mask_matrix(C, pattern, device)
+
+
+# ------------------------------------------------------------------ a whole segment of the prefix in one launch
+CLEAN_STREAM = 1
+
+
+class _SegmentAttention(torch.autograd.Function):
+    """Every chunk of every stream of one prefix layer's segment: one forward launch, one backward launch (plus the small
+    ``delta`` kernel).  The clean stream's keys and values are laid out once as ``[previous window | segment]``; every chunk
+    reads its window from that buffer in place, and the backward accumulates the gradient of a clean key over all the windows
+    that held it on chip.  First order only (the prefix is never inside the inner step's recorded backward)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, k_prev, v_prev, C, W, first, reach, patterns, scale):
+        from . import kernels
+        B, S, T = q.shape[:3]
+        WC = W * C
+
+        def lay_out(own, prev):
+            buf = own.new_empty((B, WC + T) + tuple(own.shape[3:]))
+            if WC:
+                if prev is None:
+                    buf[:, :WC].zero_()
+                else:
+                    buf[:, :WC].copy_(prev)
+            buf[:, WC:].copy_(own[:, CLEAN_STREAM])
+            return buf
+        kc, vc = lay_out(k, k_prev), lay_out(v, v_prev)
+        o, lse = kernels.attention_fwd_segment(q, kc, vc, k, v, C, W, first, reach, patterns, scale)
+        ctx.save_for_backward(q, k, v, kc, vc, o, lse)
+        ctx.meta = (C, W, first, reach, tuple(patterns), scale, k_prev is not None)
+        return o, kc[:, T:].clone(), vc[:, T:].clone()
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, go, g_tail_k, g_tail_v):
+        from . import kernels
+        q, k, v, kc, vc, o, lse = ctx.saved_tensors
+        C, W, first, reach, patterns, scale, has_prev = ctx.meta
+        dq, dk, dv, dk_prev, dv_prev = kernels.attention_bwd_segment(go, q, kc, vc, k, v, o, lse, C, W, first, reach, patterns, scale,
+                                                                     g_tail_k, g_tail_v)
+        return dq, dk, dv, (dk_prev if has_prev else None), (dv_prev if has_prev else None), None, None, None, None, None, None
+
+
+def segment_attention_ok(q: torch.Tensor, C: int, W: int, patterns) -> bool:
+    from . import kernels
+    S = q.shape[1]
+    return (use_kernels(q) and q.is_cuda and C % 128 == 0 and S >= 2 and S <= 8 and S * (W + 1) * (C // 128) <= 512
+            and kernels.attention_segment_supported(q, W, patterns))
+
+
+def segment_attention(q, k, v, kv_prev, C: int, W: int, first: int, reach, patterns, scale: float):
+    """``q [B, S, T, nh, d]``, ``k / v [B, S, T, nkv, d]`` (stream 1 is the clean one), ``kv_prev``: the clean keys / values of the
+    ``W`` chunks before the segment (None at the sequence start) -> ``(o [B, S, T, nh, d], k_tail, v_tail [B, W C, nkv, d])``."""
+    kp, vp = (None, None) if kv_prev is None else kv_prev
+    return _SegmentAttention.apply(q, k, v, kp, vp, C, W, first, reach, tuple(patterns), scale)
 
 
 # staged execution: library/hand-written forward + first-order backward, reference for the second order
@@ -216,13 +302,13 @@ def _causal_bias(C: int, Kn: int, device) -> torch.Tensor:
     return b
 
 
-def _ref_for_staged(q, K, V, scale, causal):
+def _ref_for_staged(q, K, V, scale, pattern):
     """The differentiable-to-any-order statement used when a backward is recorded.  On the GPU the two
     products run on the tensor-core GEMM (batched over sequence x KV head, the query heads of a group folded
     into the rows), scores and softmax in f32 as in the reference (attention.py:181-201)."""
-    if not use_kernels(q):
-        om = own_mask_matrix(q.shape[1], "causal", q.device) if causal else None
-        return ref.attend(q, K, V, None, scale, om)
+    causal = pattern == "causal"
+    if not use_kernels(q) or pattern not in ("full", "causal"):
+        return ref.attend(q, K, V, None, scale, _own_part_mask(pattern, q.shape[1], q.device))
     from .gemm import mm
     n, C, nh, d = q.shape
     Kn, nkv = K.shape[1], K.shape[2]
@@ -244,56 +330,59 @@ def _two_segment_ok(q, kw, k_own) -> bool:
             and kw.shape[1] % 128 == 0 and kernels.ATTN_VARIANT == 0)
 
 
-def _ref_for_staged2(q, kw, vw, ko, vo, scale, causal):
-    return _ref_for_staged(q, torch.cat([kw, ko], 1), torch.cat([vw, vo], 1), scale, causal)
+def _ref_for_staged2(q, kw, vw, ko, vo, scale, pattern):
+    return _ref_for_staged(q, torch.cat([kw, ko], 1), torch.cat([vw, vo], 1), scale, pattern)
 
 
-def _fast_fwd2(q, kw, vw, ko, vo, scale, causal):
+def _fast_fwd2(q, kw, vw, ko, vo, scale, pattern):
     from . import kernels
-    o, lse = kernels.attention_fwd(q, kw, vw, scale, causal, k2=ko, v2=vo)
+    o, lse = kernels.attention_fwd(q, kw, vw, scale, pattern, k2=ko, v2=vo)
     return o, (o, lse)
 
 
-def _fast_bwd2(g, tensors, saved, needs, scale, causal):
+def _fast_bwd2(g, tensors, saved, needs, scale, pattern):
     from . import kernels
     q, kw, vw, ko, vo = tensors
-    return kernels.attention_bwd(g, q, kw, vw, saved[0], saved[1], scale, causal, k2=ko, v2=vo)
+    return kernels.attention_bwd(g, q, kw, vw, saved[0], saved[1], scale, pattern, k2=ko, v2=vo)
 
 
-def _diff_bwd2(g, tensors, saved, needs, scale, causal):
-    """The backward as an operation with a hand-written derivative (``ops.attn_second``), or ``None`` to decline."""
+def _diff_bwd2(g, tensors, saved, needs, scale, pattern):
+    """The backward as an operation with a hand-written derivative (``ops.attn_second``), or ``None`` to decline (then the
+    statement is differentiated; the hand-written derivative covers the full and causal patterns)."""
     from . import attn_second
     q, kw, vw, ko, vo = tensors
-    if not SECOND_ORDER_KERNEL or not saved or not attn_second.supported(q, kw.shape[1] + ko.shape[1]):
+    if (pattern not in ("full", "causal") or not SECOND_ORDER_KERNEL or not saved
+            or not attn_second.supported(q, kw.shape[1] + ko.shape[1])):
         return None
-    return attn_second.attention_bwd_diff(g, q, kw, vw, ko, vo, saved[0], saved[1], scale, causal)
+    return attn_second.attention_bwd_diff(g, q, kw, vw, ko, vo, saved[0], saved[1], scale, pattern == "causal")
 
 
-def _diff_bwd(g, tensors, saved, needs, scale, causal):
+def _diff_bwd(g, tensors, saved, needs, scale, pattern):
     from . import attn_second, kernels
     q, K, V = tensors
-    if (not SECOND_ORDER_KERNEL or not saved or not kernels.available("attention_bwd") or not kernels.attention_bwd_supported(q, K)
-            or not attn_second.supported(q, K.shape[1])):
+    if (pattern not in ("full", "causal") or not SECOND_ORDER_KERNEL or not saved or not kernels.available("attention_bwd")
+            or not kernels.attention_bwd_supported(q, K) or not attn_second.supported(q, K.shape[1])):
         return None
-    return attn_second.attention_bwd_diff(g, q, K, V, None, None, saved[0], saved[1], scale, causal)
+    return attn_second.attention_bwd_diff(g, q, K, V, None, None, saved[0], saved[1], scale, pattern == "causal")
 
 
-def _fast_fwd(q, K, V, scale, causal):
+def _fast_fwd(q, K, V, scale, pattern):
     from . import kernels
     if kernels.available("attention") and kernels.attention_supported(q, K):
-        o, lse = kernels.attention_fwd(q, K, V, scale, causal)
+        o, lse = kernels.attention_fwd(q, K, V, scale, pattern)
         return o, (o, lse)
     with torch.no_grad():
-        o = _sdpa_fast(q, K, V, scale, causal) if q.is_cuda else _ref_for_staged(q, K, V, scale, causal)
+        o = _ref_for_staged(q, K, V, scale, pattern)
     return o, ()
 
 
-def _fast_bwd(g, tensors, saved, needs, scale, causal):
+def _fast_bwd(g, tensors, saved, needs, scale, pattern):
     from . import kernels
     q, K, V = tensors
     if saved and kernels.available("attention_bwd") and kernels.attention_bwd_supported(q, K):
-        return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, causal)
+        return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, pattern)
+    # shapes the backward kernel does not cover (head dimension 128 today): differentiate the tensor-core statement
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))
-        o = _sdpa_fast(qq, kk, vv, scale, causal) if q.is_cuda else _ref_for_staged(qq, kk, vv, scale, causal)
+        o = _ref_for_staged(qq, kk, vv, scale, pattern)
         return torch.autograd.grad(o, (qq, kk, vv), g)

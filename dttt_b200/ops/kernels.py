@@ -380,14 +380,31 @@ def _kv_rows(t):
     return t, (t.stride(0) if n > 1 else rows * heads * d)
 
 
+MASK_MODES = {"full": 0, "causal": 1, "split": 2, "block": 3, "read": 4}
+_lib.register("dttt_attn_fwd_masked", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _ll, _ll, _ll, _ll, _f, _i, _i, _vp, _vp])
+_lib.register("dttt_attn_fwd_segment", _i, [_vp] * 7 + [_i] * 10 + [_ll, _ll, _vp, _vp, _f, _vp, _vp])
+
+
+def parse_pattern(own) -> tuple:
+    """``"full" | "causal" | "split:K" | "block:b" | "read:b"`` (or a ``causal`` bool) -> ``(mode, param)`` of the kernels."""
+    if isinstance(own, bool):
+        return (1, 0) if own else (0, 0)
+    if isinstance(own, tuple):
+        return own
+    name, _, arg = own.partition(":")
+    return MASK_MODES[name], int(arg) if arg else 0
+
+
 def attention_fwd(q, k, v, scale, causal, variant=None, k2=None, v2=None):
     """Flash attention forward on the tcgen05 kernel.  ``q [n, Cq, nh, d]``, ``k / v [n, Kn, nkv, d]`` bf16, every key
-    valid, ``causal`` aligned to the end of the key axis.  ``k2 / v2 [n, Kn2, nkv, d]``: more keys AFTER ``k / v`` (the chunk's
-    own keys after the window's), read from their own tensors instead of a concatenation (``Kn`` a multiple of 128).
-    Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
+    valid.  ``causal``: a bool (causal aligned to the end of the key axis) or an own-chunk pattern ``"full" | "causal" |
+    "split:K" | "block:b" | "read:b"`` over the last ``Cq`` keys (``read``: over the last ``2 Cq``, clean own keys first).
+    ``k2 / v2 [n, Kn2, nkv, d]``: more keys AFTER ``k / v`` (the chunk's own keys after the window's), read from their own tensors
+    instead of a concatenation (``Kn`` a multiple of 128).  Returns ``o`` like ``q`` and ``lse [n, nh, Cq]`` (f32)."""
     n, Cq, nh, d = q.shape
     Kn, nkv = k.shape[1], k.shape[2]
     assert q.dtype == torch.bfloat16 and d in (64, 128), (q.dtype, d)
+    mode, param = parse_pattern(causal)
     var = ATTN_VARIANT if variant is None else int(variant)
     if k2 is not None and (Kn % 128 or var != 0 or Kn == 0):
         k, v, k2, v2 = torch.cat([k, k2], 1), torch.cat([v, v2], 1), None, None
@@ -398,8 +415,42 @@ def attention_fwd(q, k, v, scale, causal, variant=None, k2=None, v2=None):
     o = torch.empty_like(qc)
     lse = torch.empty(n, nh, Cq, dtype=torch.float32, device=q.device)
     st = _lib.status_tensor(q.device)
+    if mode >= 2:
+        _check(_lib.lib().dttt_attn_fwd_masked(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(o), _p(lse), n, Cq, Kn, 0 if k2 is None else k2.shape[1],
+                                               nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale), mode, param, _p(st), _stream()), "attn_fwd_masked")
+        return o, lse
     _check(_lib.lib().dttt_attn_fwd(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(o), _p(lse), n, Cq, Kn, 0 if k2 is None else k2.shape[1],
-                                    nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale), 1 if causal else 0, var, _p(st), _stream()), "attn_fwd")
+                                    nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale), mode, var, _p(st), _stream()), "attn_fwd")
+    return o, lse
+
+
+def _int_array(vals):
+    return (ctypes.c_int * len(vals))(*[int(x) for x in vals])
+
+
+def attention_segment_supported(q, W: int, patterns) -> bool:
+    """``q [B, S, T, nh, d]``: the one-launch segment form covers head dimension 64, chunks that are multiples of 128 tokens,
+    every pattern but the sub-block read, and work lists of at most 512 (stream, chunk, tile) entries per key block."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 64 and available("attention_segment")
+            and all(parse_pattern(p)[0] < 4 for p in patterns))
+
+
+def attention_fwd_segment(q, kc, vc, ko, vo, C: int, W: int, first: int, reach, patterns, scale: float):
+    """Every chunk of every stream of a segment in one launch.  ``q [B, S, T, nh, d]``; ``kc / vc [B, (W + T / C) C, nkv, d]``: the
+    clean stream's keys / values with the previous segment's window in front; ``ko / vo [B, S, T, nkv, d]``: every stream's own
+    keys / values.  Returns ``o`` like ``q`` and ``lse [B * S * T / C, nh, C]``."""
+    B, S, T, nh, d = q.shape
+    nkv = kc.shape[2]
+    chunks = T // C
+    qc, koc, voc = q.contiguous(), ko.contiguous(), vo.contiguous()
+    (kcc, kbs), (vcc, vbs) = _kv_rows(kc), _kv_rows(vc)
+    o = torch.empty_like(qc)
+    lse = torch.empty(B * S * chunks, nh, C, dtype=torch.float32, device=q.device)
+    modes, params = zip(*[parse_pattern(p) for p in patterns])
+    st = _lib.status_tensor(q.device)
+    _check(_lib.lib().dttt_attn_fwd_segment(_p(qc), _p(kcc), _p(vcc), _p(koc), _p(voc), _p(o), _p(lse), B, S, chunks, C, W, int(first),
+                                            -1 if reach is None else int(reach), nh, nkv, d, kbs, vbs, _int_array(modes), _int_array(params),
+                                            float(scale), _p(st), _stream()), "attn_fwd_segment")
     return o, lse
 
 
@@ -457,7 +508,9 @@ def linear_ce_dlogits(h, Eb, targets_i32, coef, lse, col0):
 
 
 _lib.register("dttt_attn_bwd", _i, [_vp] * 14 + [_i] * 7 + [_ll] * 4 + [_f, _i, _vp, _vp])
-_SYMBOL.update(attention_bwd="dttt_attn_bwd")
+_lib.register("dttt_attn_bwd_masked", _i, [_vp] * 14 + [_i] * 7 + [_ll] * 4 + [_f, _i, _i, _vp, _vp])
+_lib.register("dttt_attn_bwd_segment", _i, [_vp] * 14 + [_i] * 10 + [_ll, _ll, _vp, _vp, _f, _vp, _vp])
+_SYMBOL.update(attention_bwd="dttt_attn_bwd", attention_segment="dttt_attn_bwd_segment")
 
 
 def attention_bwd_supported(q, k) -> bool:
@@ -466,13 +519,14 @@ def attention_bwd_supported(q, k) -> bool:
 
 def attention_bwd(g, q, k, v, o, lse, scale, causal, k2=None, v2=None):
     """First-order backward of ``attention_fwd`` on the tcgen05 kernel: ``(dq, dk, dv)`` or, with a second key / value pair,
-    ``(dq, dk, dv, dk2, dv2)``.  ``dq`` is accumulated in f32 by the kernel (one bulk reduction per key block and query tile)
-    and cast once at the end."""
+    ``(dq, dk, dv, dk2, dv2)``.  ``causal``: a bool or an own-chunk pattern as in ``attention_fwd``.  ``dq`` is accumulated in
+    f32 by the kernel (one bulk reduction per key block and query tile) and cast once at the end."""
     n, Cq, nh, d = q.shape
     Kn, nkv = k.shape[1], k.shape[2]
+    mode, param = parse_pattern(causal)
     two = k2 is not None and Kn % 128 == 0 and Kn > 0
     if k2 is not None and not two:
-        dq, dk, dv = attention_bwd(g, q, torch.cat([k, k2], 1), torch.cat([v, v2], 1), o, lse, scale, causal)
+        dq, dk, dv = attention_bwd(g, q, torch.cat([k, k2], 1), torch.cat([v, v2], 1), o, lse, scale, (mode, param))
         return dq, dk[:, :Kn], dv[:, :Kn], dk[:, Kn:], dv[:, Kn:]
     qc, oc, gc = q.contiguous(), o.contiguous(), g.contiguous()
     (kc, kbs), (vc, vbs) = _kv_rows(k), _kv_rows(v)
@@ -483,13 +537,45 @@ def attention_bwd(g, q, k, v, o, lse, scale, causal, k2=None, v2=None):
     dk, dv = mk(k), mk(v)
     dk2, dv2 = (mk(k2), mk(v2)) if two else (None, None)
     st = _lib.status_tensor(q.device)
-    _check(_lib.lib().dttt_attn_bwd(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv),
-                                    _p(dk2), _p(dv2), n, Cq, Kn, k2.shape[1] if two else 0, nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale),
-                                    1 if causal else 0, _p(st), _stream()), "attn_bwd")
+    _check(_lib.lib().dttt_attn_bwd_masked(_p(qc), _p(kc), _p(vc), _p(k2c), _p(v2c), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dk), _p(dv),
+                                           _p(dk2), _p(dv2), n, Cq, Kn, k2.shape[1] if two else 0, nh, nkv, d, kbs, vbs, k2bs, v2bs, float(scale),
+                                           mode, param, _p(st), _stream()), "attn_bwd")
     global LAUNCHES
     LAUNCHES += 1                                   # the delta kernel
     dq = dq32.to(q.dtype)
     return (dq, dk, dv, dk2, dv2) if two else (dq, dk, dv)
+
+
+def attention_bwd_segment(g, q, kc, vc, ko, vo, o, lse, C: int, W: int, first: int, reach, patterns, scale: float,
+                          g_tail_k=None, g_tail_v=None):
+    """Backward of ``attention_fwd_segment``: ``(dq [B, S, T, nh, d], dk, dv [B, S, T, nkv, d], dk_prev, dv_prev [B, W C, nkv, d])``.
+    The clean stream's ``dk / dv`` (stream 1) hold the gradient of its keys from every window that held them and from its own
+    chunks, summed on chip; ``dk_prev / dv_prev`` is the part that falls on the previous segment's window."""
+    B, S, T, nh, d = q.shape
+    nkv = kc.shape[2]
+    chunks = T // C
+    qc, oc, gc, koc, voc = q.contiguous(), o.contiguous(), g.contiguous(), ko.contiguous(), vo.contiguous()
+    (kcc, kbs), (vcc, vbs) = _kv_rows(kc), _kv_rows(vc)
+    dq32 = torch.zeros(B, S, T, nh, d, dtype=torch.float32, device=q.device)
+    delta = torch.empty(B * S * chunks, nh, C, dtype=torch.float32, device=q.device)
+    dkc = torch.empty(B, (W + chunks) * C, nkv, d, dtype=q.dtype, device=q.device)
+    dvc = torch.empty_like(dkc)
+    dko = torch.empty(B, S, T, nkv, d, dtype=q.dtype, device=q.device)
+    dvo = torch.empty_like(dko)
+    modes, params = zip(*[parse_pattern(p) for p in patterns])
+    st = _lib.status_tensor(q.device)
+    _check(_lib.lib().dttt_attn_bwd_segment(_p(qc), _p(kcc), _p(vcc), _p(koc), _p(voc), _p(oc), _p(gc), _p(lse), _p(delta), _p(dq32), _p(dkc), _p(dvc),
+                                            _p(dko), _p(dvo), B, S, chunks, C, W, int(first), -1 if reach is None else int(reach), nh, nkv, d,
+                                            kbs, vbs, _int_array(modes), _int_array(params), float(scale), _p(st), _stream()), "attn_bwd_segment")
+    global LAUNCHES
+    LAUNCHES += 1
+    if g_tail_k is not None:                        # what the next segment's windows sent back to this buffer's last W chunks
+        dkc[:, T:].add_(g_tail_k)
+        dvc[:, T:].add_(g_tail_v)
+    # the clean stream (index 1) has its own keys inside the clean buffer: move that part of the gradient to its slot
+    dko[:, 1].copy_(dkc[:, W * C:])
+    dvo[:, 1].copy_(dvc[:, W * C:])
+    return dq32.to(q.dtype), dko, dvo, dkc[:, :W * C], dvc[:, :W * C]
 
 
 # =============================================================================== second-order attention (row stage)
