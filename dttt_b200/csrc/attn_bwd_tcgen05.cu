@@ -63,7 +63,9 @@ struct BwdSmem {
   static constexpr int STAGES = 2;
   static constexpr int AUX = 2 * 2 * 128 * 4;               // LSE and D, two buffers
   static constexpr int DQ_BYTES = 128 * HD * 4;                // f32 dQ tile staged for the bulk reduction
-  static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + 2 * DS_BYTES + DQ_BYTES + AUX + 1024 + 1024;
+  static constexpr int MASK = 2 * 3 * 128 * 4;              // per query column: e1, s2, e2 (two buffers)
+  static constexpr int ITEMS = MAX_ITEMS * 8;               // work items: (sequence, query tile | needs mask)
+  static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + 2 * DS_BYTES + DQ_BYTES + AUX + MASK + ITEMS + 1024 + 1024;
 };
 
 __device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
@@ -144,6 +146,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   int* sE2 = sS2 + 2 * 128;
   int2* items = reinterpret_cast<int2*>(sE2 + 2 * 128);      // .x = sequence, .y = query tile * 2 + needs-mask
   uint64_t* bars = reinterpret_cast<uint64_t*>(items + MAX_ITEMS);
+  // everything carved above plus the barrier block must fit what the launcher asks for (1024 bytes of alignment slack included)
+  static_assert(2 * L::TILE + L::STAGES * 2 * L::TILE + 2 * L::DS_BYTES + L::DQ_BYTES + L::AUX + L::MASK + L::ITEMS + 256 + 1024 <= L::TOTAL,
+                "shared-memory layout exceeds BwdSmem::TOTAL");
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;                              // [2]
   uint64_t* st_empty = st_full + 2;                          // [2]

@@ -28,6 +28,11 @@ LAUNCHES = 0                  # kernel launches issued by this module (bench acc
 # staged backward) on CPU bf16 tensors with every device kernel replaced by its PyTorch statement.  It lets the
 # CPU test-suite exercise exactly the control flow a GPU run takes.
 EMULATE = os.environ.get("DTTT_EMULATE", "0") == "1"
+# DTTT_GEMM_PAIR=1: products of at least PAIR_MIN rows and columns run on CTA pairs (tcgen05 cta_group::2)
+PAIR = os.environ.get("DTTT_GEMM_PAIR", "0") == "1"
+PAIR_MIN = 256
+_lib.register("dttt_gemm_pair_bf16", ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 6 + [ctypes.c_int] * 4
+              + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p])
 
 
 def _kernel_ok(x: torch.Tensor) -> bool:
@@ -100,6 +105,17 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
         assert out.shape == torch.Size(shape) and out.stride(-1) == 1, (out.shape, shape)
     c_batch = out.stride(0) if out.dim() == 3 else 0
     st = _lib.status_tensor(a.device)
+    if PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN:
+        # CTA pairs (csrc/gemm_pair_tcgen05.cu): each CTA of a cluster loads half of B, one instruction covers 256 x 256
+        rc = _lib.lib().dttt_gemm_pair_bf16(
+            ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),
+            M, N, K, batch, a.stride(-2), b.stride(-2), out.stride(-2), a_batch, b_batch, c_batch,
+            1 if ta else 0, 0 if tb else 1, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0,
+            float(alpha), ctypes.c_void_p(st.data_ptr()), ctypes.c_void_p(_lib.stream_ptr()))
+        if rc != 0:
+            raise _lib.KernelError(f"dttt_gemm_pair_bf16 launch failed rc={rc} for M={M} N={N} K={K} batch={batch} ta={ta} tb={tb}")
+        LAUNCHES += 1
+        return out
     rc = _lib.lib().dttt_gemm_bf16(
         ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),
         M, N, K, batch, a.stride(-2), b.stride(-2), out.stride(-2), a_batch, b_batch, c_batch,
