@@ -59,7 +59,7 @@ def _segment_reference(q, k, v, kp, vp, C, W, first, reach, patterns, scale):
     from dttt_b200.ops import attention as A, reference as ref
     B, S, T = q.shape[:3]
     WC = W * C
-    pad = lambda own, prev: torch.cat([torch.zeros_like(own[:, :WC]) if prev is None else prev, own], 1)
+    pad = lambda own, prev: torch.cat([own.new_zeros((B, WC) + tuple(own.shape[2:])) if prev is None else prev, own], 1)
     kc, vc = pad(k[:, 1], kp), pad(v[:, 1], vp)
     outs = []
     for s in range(S):
@@ -100,7 +100,7 @@ def test_segment_form_matches_chunk_by_chunk(B, S, chunks, C, W, first, reach, w
     f = [t.float().clone().requires_grad_(True) for t in (q, k, v)] + ([t.float().clone().requires_grad_(True) for t in (kp, vp)] if with_prev else [])
     want_o = _segment_reference(f[0], f[1], f[2], f[3] if with_prev else None, f[4] if with_prev else None, C, W, first, reach, patterns, scale)
     WC = W * C
-    pad = lambda own, prev: torch.cat([torch.zeros_like(own[:, :WC]) if prev is None else prev, own], 1)
+    pad = lambda own, prev: torch.cat([own.new_zeros((B, WC) + tuple(own.shape[2:])) if prev is None else prev, own], 1)
     want_tk, want_tv = pad(f[1][:, 1], f[3] if with_prev else None)[:, T:], pad(f[2][:, 1], f[4] if with_prev else None)[:, T:]
     want = torch.autograd.grad([want_o, want_tk, want_tv], f, [go.float(), gtk.float(), gtv.float()])
     assert (o.float() - want_o).abs().max().item() < 2e-2
