@@ -71,8 +71,8 @@ def param_spec(cfg: ModelConfig, tp: int = 1) -> "OrderedDict[str, Tuple[Tuple[i
     """Ordered ``name -> (shape, init kind)``; the order is the checkpoint's leaf order.  ``tp > 1``: the shapes one rank
     of a tensor-parallel group holds (``tp_layout``)."""
     if tp > 1:
-        if cfg.memory == "gdn" or cfg.num_key_value_heads % tp or cfg.intermediate_size % tp:
-            raise ValueError(f"tensor parallel {tp}: needs the fast-weight memory and kv heads / MLP width divisible by it")
+        if cfg.num_key_value_heads % tp or cfg.intermediate_size % tp:
+            raise ValueError(f"tensor parallel {tp}: needs kv heads and MLP width divisible by it")
         out = OrderedDict()
         for n, (shape, kind) in param_spec(cfg).items():
             lay = tp_layout(n)

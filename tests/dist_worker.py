@@ -21,7 +21,9 @@ def main():
     fsdp = int(os.environ.get("TEST_FSDP", "0"))
     tp = int(os.environ.get("TEST_TP", "1"))
     mesh = make_mesh(fsdp, tp, torch.device("cpu"))
-    eng = Engine(tiny_model(), tiny_train(batch_size=4, fsdp_size=fsdp, tp_size=tp), mesh, torch.device("cpu"))
+    mkw = dict(memory="gdn", gdn_heads=2, gdn_head_dim=8, gdn_conv=4, gdn_alternate=True, gdn_chunk=4) if os.environ.get("TEST_GDN") else {}
+    tkw = dict(segment_chunks=2) if os.environ.get("TEST_SEGMENTS") else {}
+    eng = Engine(tiny_model(**mkw), tiny_train(batch_size=4, fsdp_size=fsdp, tp_size=tp, **tkw), mesh, torch.device("cpu"))
     ids = torch.randint(0, 120, (4, 32), generator=torch.Generator().manual_seed(0))
     n = 4 // mesh.batch_ranks
     mine = ids[mesh.batch_index * n:(mesh.batch_index + 1) * n]

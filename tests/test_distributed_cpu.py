@@ -8,7 +8,7 @@ import sys
 import pytest
 import torch
 
-from util import ROOT, make_engine
+from util import ROOT, make_engine, tiny_model
 
 WORKER = os.path.join(ROOT, "tests", "dist_worker.py")
 
@@ -46,18 +46,21 @@ def test_sharded_training_matches_one_process(tmp_path, world, fsdp):
         assert torch.equal(eng.store.gather_full(k), v), k
 
 
-@pytest.mark.parametrize("world,fsdp", [(2, 1), (4, 2)])
-def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp):
+@pytest.mark.parametrize("world,fsdp,variant", [(2, 1, ""), (4, 2, ""), (2, 1, "gdn"), (2, 1, "segments")])
+def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp, variant):
     """tp = 2: trunk projections split over the group (heads / MLP columns), sequences split for everything else.  The loss sum,
     every parameter's gradient (slices re-assembled, whole parameters summed over the group) and the checkpoint must equal the
     single-process ones."""
     from dttt_b200.ttt.scan import Batch
     from dttt_b200.utils import rng
-    r = launch(world, "tp_grads", tmp_path, {"TEST_FSDP": str(fsdp), "TEST_TP": "2"})
+    extra = {"gdn": {"TEST_GDN": "1"}, "segments": {"TEST_SEGMENTS": "1"}}.get(variant, {})
+    r = launch(world, "tp_grads", tmp_path, {"TEST_FSDP": str(fsdp), "TEST_TP": "2", **extra})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = torch.load(tmp_path / "result.pt", weights_only=False)
     assert res["mesh"]["tp"] == 2
-    eng = make_engine(batch_size=4)
+    mc = tiny_model(memory="gdn", gdn_heads=2, gdn_head_dim=8, gdn_conv=4, gdn_alternate=True, gdn_chunk=4) if variant == "gdn" else None
+    make = lambda: make_engine(mc=mc, batch_size=4, **({"segment_chunks": 2} if variant == "segments" else {}))
+    eng = make()
     ids = torch.randint(0, 120, (4, 32), generator=torch.Generator().manual_seed(0))
     n_groups = world // 2                                         # every TP group scores the same four sequences here
     loss, w = eng.grad_of(Batch(ids), rng.split(rng.key(11), 4), 0, weight="sum")
@@ -70,7 +73,7 @@ def test_tensor_parallel_gradients_match_one_process(tmp_path, world, fsdp):
     assert all(m["finite"] == 1.0 for m in res["metrics"])
     # evaluation under tensor parallelism reports the group's whole batch, sequences in order
     import dataclasses as dc
-    ev_loss, ev = make_engine(batch_size=4).eval_step(Batch(ids), rng.split(rng.key(11), 4), 0, dc.replace(eng.lcfg, per_sequence=True))
+    ev_loss, ev = make().eval_step(Batch(ids), rng.split(rng.key(11), 4), 0, dc.replace(eng.lcfg, per_sequence=True))
     assert abs(res["ev_loss"] - float(ev_loss)) < 1e-5 and abs(res["ev_count"] - float(ev["mask_count"])) < 1e-3
     assert torch.allclose(res["ev_by_seq"], ev["loss_by_seq"], atol=1e-5)
     from dttt_b200.ckpt import store as CK
