@@ -28,9 +28,13 @@ LAUNCHES = 0                  # kernel launches issued by this module (bench acc
 # staged backward) on CPU bf16 tensors with every device kernel replaced by its PyTorch statement.  It lets the
 # CPU test-suite exercise exactly the control flow a GPU run takes.
 EMULATE = os.environ.get("DTTT_EMULATE", "0") == "1"
-# DTTT_GEMM_PAIR=1: products of at least PAIR_MIN rows and columns run on CTA pairs (tcgen05 cta_group::2)
-PAIR = os.environ.get("DTTT_GEMM_PAIR", "0") == "1"
+# Products of at least PAIR_MIN rows and PAIR_MIN_N columns that do not accumulate into their output run on CTA pairs
+# (tcgen05 cta_group::2): +12-17 % on the model's large shapes, +5-8 % at 2048 rows; narrower outputs and the long-K
+# accumulating weight gradients (which take the 256 x 256 single-CTA form) measured faster on one CTA.  DTTT_GEMM_PAIR=0 turns
+# the pairs off.
+PAIR = os.environ.get("DTTT_GEMM_PAIR", "1") == "1"
 PAIR_MIN = 256
+PAIR_MIN_N = 1024
 _lib.register("dttt_gemm_pair_bf16", ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 6 + [ctypes.c_int] * 4
               + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p])
 
@@ -105,7 +109,7 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
         assert out.shape == torch.Size(shape) and out.stride(-1) == 1, (out.shape, shape)
     c_batch = out.stride(0) if out.dim() == 3 else 0
     st = _lib.status_tensor(a.device)
-    if PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN:
+    if PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN_N and not accumulate:
         # CTA pairs (csrc/gemm_pair_tcgen05.cu): each CTA of a cluster loads half of B, one instruction covers 256 x 256
         rc = _lib.lib().dttt_gemm_pair_bf16(
             ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(out.data_ptr()),

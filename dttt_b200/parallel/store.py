@@ -57,7 +57,9 @@ class ParamStore:
         # memory (parallel.symm): the fused reduce-scatter / optimiser / all-gather kernels read and write the other
         # ranks' copies directly over NVLink.  Otherwise they are ordinary tensors and the collectives are NCCL / gloo.
         self.peer = None
-        self.fused = bool(fused_comm and trainable and self.fs > 1 and device.type == "cuda" and mesh.tp == 1)
+        # (under tensor parallelism the FSDP group of a rank is the ranks that hold the same slices; the gradients of whole
+        # parameters are first summed over the TP group by NCCL, then every group runs the same fused kernels)
+        self.fused = bool(fused_comm and trainable and self.fs > 1 and device.type == "cuda")
         if self.fused:
             from .symm import PeerBuffer
             lo_big = self.n["big"] * torch.empty(0, dtype=compute_dtype).element_size()

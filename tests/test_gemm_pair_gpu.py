@@ -9,10 +9,10 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture()
 def pair_on():
     from dttt_b200.ops import gemm
-    old = gemm.PAIR
-    gemm.PAIR = True
+    old = gemm.PAIR, gemm.PAIR_MIN_N
+    gemm.PAIR, gemm.PAIR_MIN_N = True, 256
     yield gemm
-    gemm.PAIR = old
+    gemm.PAIR, gemm.PAIR_MIN_N = old
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (1024, 2048, 2048), (384, 768, 192), (300, 520, 136), (2048, 8192, 2048)])
@@ -47,7 +47,14 @@ def test_pair_gemm_batched_and_f32_accumulate(pair_on):
     g = torch.randn(4096, 1024, device="cuda").to(torch.bfloat16)
     acc = torch.randn(512, 1024, device="cuda")
     want = acc + 0.5 * (x.float().t() @ g.float())
-    gemm.gemm_raw(x, g, True, False, torch.float32, out=acc, accumulate=True, alpha=0.5)
+    from dttt_b200.ops._lib import lib, status_tensor, stream_ptr
+    import ctypes
+    st = status_tensor(x.device)
+    vp = ctypes.c_void_p
+    # the accumulating epilogue is not routed to the pairs by default: call the entry point directly
+    rc = lib().dttt_gemm_pair_bf16(vp(x.data_ptr()), vp(g.data_ptr()), vp(acc.data_ptr()), 512, 1024, 4096, 1, x.stride(0), g.stride(0),
+                                   acc.stride(0), 0, 0, 0, 1, 1, 1, 1, 0.5, vp(st.data_ptr()), vp(stream_ptr()))
+    assert rc == 0
     torch.cuda.synchronize()
     _lib.check_status()
     assert (acc - want).abs().max().item() < 1e-2 * want.abs().max().item()
