@@ -30,32 +30,14 @@
 // tiles of the block's own sequence.  In the segment form a block of the clean stream's [previous window | segment] buffer
 // is met by every stream's chunks that have it in their window and by the clean stream's own chunk, so the gradient of a
 // clean key is accumulated once, in tensor memory, over all of them (no per-window partial gradients to add up afterwards).
-#include "ptx_sm100.cuh"
-#include "attn_common.cuh"
+#include "attn_bwd_common.cuh"
 
 #include <mutex>
 #include <cstring>
 
 namespace dttt {
 
-constexpr int BQ = 128, BKEY = 128, HD = 64;
-constexpr int MAX_ITEMS = 512;
-
-struct AttnBwdParams {
-  int n, Cq, Kn, nh, nkv, causal;
-  int Kn1;              // keys [0, Kn1) belong to the first K / V pair (and dK / dV), the rest to the second
-  int mask_mode, mask_param;
-  SegSpec sg;           // segment form: dK / dV mirror the clean buffer [B, (W + chunks) C, nkv, 64], dK2 / dV2 the streams' own keys
-  float scale;
-  const float* lse;     // [n, nh, Cq]
-  const float* delta;   // [n, nh, Cq]  rowsum(dO * O)
-  float* dQ;            // [n, Cq, nh, 64] f32, accumulated into
-  __nv_bfloat16* dK;    // [n, Kn1, nkv, 64]
-  __nv_bfloat16* dV;
-  __nv_bfloat16* dK2;   // [n, Kn - Kn1, nkv, 64]
-  __nv_bfloat16* dV2;
-  int* status;
-};
+constexpr int HD = 64;
 
 struct BwdSmem {
   static constexpr int TILE = 128 * HD * 2;                 // 16 KB: one [128, 64] bf16 tile
@@ -67,34 +49,6 @@ struct BwdSmem {
   static constexpr int ITEMS = MAX_ITEMS * 8;               // work items: (sequence, query tile | needs mask)
   static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + 2 * DS_BYTES + DQ_BYTES + AUX + MASK + ITEMS + 1024 + 1024;
 };
-
-__device__ __forceinline__ void tma_load_4d_b(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-
-// Barrier `id` over `nthreads` threads that also ANDs a per-thread flag: every participant gets the same verdict.
-__device__ __forceinline__ int bar_red_and(int id, int nthreads, int flag) {
-  int out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, %2, %3, p;\n\t"
-      "selp.b32 %0, 1, 0, q;\n\t}"
-      : "=r"(out) : "r"(flag), "r"(id), "r"(nthreads) : "memory");
-  return out;
-}
-
-// dst[tile] += smem tile, as one bulk tensor reduction (f32 add) issued by a single thread
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-               ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; eight threads per row of 64.
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
@@ -164,69 +118,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int rep = p.nh / p.nkv;
-  const int nqt = (p.Cq + BQ - 1) / BQ;
-  // ---- which key block this CTA owns: tensor pair (first / second), sequence and row inside that tensor
-  bool second;
-  int kseq, krow, klen;        // klen: rows of that tensor per sequence (for the output offset)
-  if (!p.sg.on) {
-    if (jb * BKEY >= p.Kn) return;
-    second = jb * BKEY >= p.Kn1;
-    kseq = b;
-    krow = second ? jb * BKEY - p.Kn1 : jb * BKEY;
-    klen = second ? p.Kn - p.Kn1 : p.Kn1;
-  } else {
-    // z = (sequence, stream): the clean stream's CTAs walk the clean buffer, the others their own keys
-    const int bb = b / p.sg.streams, st = b % p.sg.streams;
-    second = st != 1;
-    klen = second ? p.sg.chunks * p.Cq : (p.sg.W + p.sg.chunks) * p.Cq;
-    if (jb * BKEY >= klen) return;
-    krow = jb * BKEY;
-    kseq = second ? b : bb;                                  // own keys are [B * streams, chunks * C]; the clean buffer [B, ...]
-  }
-  // ---- the work items (one thread; a few hundred cheap tests at most)
-  if (threadIdx.x == 0) {
-    int n = 0;
-    auto consider = [&](int v, const SeqGeom& G, int kpos0) {
-      // key block = positions [kpos0, kpos0 + 127] of sequence v's key axis
-      for (int qt = 0; qt < nqt; ++qt) {
-        const int i0 = qt * BQ, i1 = min(i0 + BQ - 1, p.Cq - 1);
-        const RowMask a = row_mask(G.mode, G.param, i0, G.Kn, p.Cq), z = row_mask(G.mode, G.param, i1, G.Kn, p.Cq);
-        const bool any = (kpos0 <= z.e1) || (kpos0 + BKEY - 1 >= a.s2 && kpos0 <= z.e2);
-        if (!any) continue;
-        const bool all = (kpos0 + BKEY - 1 <= a.e1) || (kpos0 >= z.s2 && kpos0 + BKEY - 1 <= a.e2);
-        const bool ragged = kpos0 + BKEY > G.Kn;
-        if (n < MAX_ITEMS) items[n] = make_int2(v, qt * 2 + ((all && !ragged) ? 0 : 1));
-        ++n;
-      }
-    };
-    if (!p.sg.on) {
-      const SeqGeom G = seq_geom(p.sg, b, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
-      consider(b, G, jb * BKEY);
-    } else {
-      const int bb = b / p.sg.streams, st = b % p.sg.streams;
-      const int per_b = p.sg.streams * p.sg.chunks;
-      if (second) {
-        const int c = krow / p.Cq;
-        const int v = bb * per_b + st * p.sg.chunks + c;
-        const SeqGeom G = seq_geom(p.sg, v, p.Cq, 0, 0, 0, 0);
-        consider(v, G, G.Kn - p.Cq + (krow - c * p.Cq));
-      } else {
-        // a block of the clean buffer: row krow = chunk (krow / C - W) of the segment (negative: the previous segment's window)
-        const int kc = krow / p.Cq - p.sg.W;
-        for (int c = max(kc, 0); c < min(kc + p.sg.W + 1, p.sg.chunks); ++c)
-          for (int s2 = 0; s2 < p.sg.streams; ++s2) {
-            const int v = bb * per_b + s2 * p.sg.chunks + c;
-            const SeqGeom G = seq_geom(p.sg, v, p.Cq, 0, 0, 0, 0);
-            const int kpos0 = krow - G.row0;
-            // the stream reads this buffer up to its window (nv chunks), the clean stream (and a reading stream) one chunk further
-            const int reach_rows = G.nv * p.Cq + ((s2 == 1 || G.mode == MASK_READ) ? p.Cq : 0);
-            if (kpos0 < 0 || kpos0 >= reach_rows) continue;
-            consider(v, G, kpos0);
-          }
-      }
-    }
-    *n_items_slot = n;
-  }
+  // ---- which key block this CTA owns, and the work items that see it (one thread; a few hundred cheap tests at most)
+  const OwnedBlock own = owned_block(p, jb, b);
+  if (!own.live) return;
+  const bool second = own.second;
+  const int kseq = own.kseq, krow = own.krow, klen = own.klen;
+  if (threadIdx.x == 0) *n_items_slot = build_work_items(p, own, jb, b, items);
   // (published by the __syncthreads below)
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
@@ -344,11 +241,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr float LOG2E = 1.4426950408889634f;
     bool ok = n_it > 0;
-    // position of this CTA's first key row on the key axis of work item `item` (the pattern is stated on that axis)
-    auto key_pos0 = [&](const SeqGeom& G) -> int {
-      if (!p.sg.on) return jb * BKEY;
-      return second ? G.Kn - p.Cq + (krow % p.Cq) : krow - G.row0;
-    };
     auto load_aux = [&](int it, float& val, int& e1, int& s2, int& e2) {
       const int2 item = items[it % nq_it];
       const int h = hk * rep + it / nq_it, qt = item.y >> 1;
@@ -358,7 +250,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
         // the keys query qi sees, as positions RELATIVE to this block's first row; rows past the sequence see nothing
         const SeqGeom G = seq_geom(p.sg, item.x, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
-        const int k0 = key_pos0(G);
+        const int k0 = key_pos0(p, own, jb, G);
         const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
         e1 = rm.e1 - k0; s2 = rm.s2 - k0; e2 = rm.e2 - k0;
       } else {
@@ -546,12 +438,12 @@ static EncodeTiledFnB bwd_encode_fn() {
   return fn;
 }
 
-// f32 [n, rows, heads, 64], box = 32 x 1 head x 128 rows x 1, 128-byte swizzle: the dQ accumulation target of the bulk reduction
-static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int heads) {
+// f32 [n, rows, heads, hd], box = 32 x 1 head x 128 rows x 1, 128-byte swizzle: the dQ accumulation target of the bulk reduction
+static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int heads, int hd) {
   EncodeTiledFnB enc = bwd_encode_fn();
   if (!enc) return -1;
-  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
-  cuuint64_t strides[3] = {(cuuint64_t)HD * 4, (cuuint64_t)heads * HD * 4, (cuuint64_t)rows * heads * HD * 4};
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)hd * 4, (cuuint64_t)heads * hd * 4, (cuuint64_t)rows * heads * hd * 4};
   cuuint32_t box[4] = {32, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -560,12 +452,12 @@ static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int he
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
-static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads, long long batch_stride = 0) {
+static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int heads, int hd, long long batch_stride = 0) {
   EncodeTiledFnB enc = bwd_encode_fn();
   if (!enc) return -1;
-  if (batch_stride <= 0) batch_stride = (long long)rows * heads * HD;
-  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
-  cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)heads * HD * 2, (cuuint64_t)batch_stride * 2};
+  if (batch_stride <= 0) batch_stride = (long long)rows * heads * hd;
+  cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)rows, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)heads * hd * 2, (cuuint64_t)batch_stride * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -579,9 +471,15 @@ static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int he
 using namespace dttt;
 
 namespace dttt {
+// the head-dimension-128 kernel (attn_bwd128_tcgen05.cu): same maps with 128-wide rows, same parameter block
+int attn_bwd128_launch(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
+                       const CUtensorMap& mk2, const CUtensorMap& mv2, const CUtensorMap& mdq, const AttnBwdParams& p, const void* O,
+                       const void* dO, float* delta, long long q_rows, cudaStream_t stream);
+
 static int launch_bwd(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, const CUtensorMap& mk, const CUtensorMap& mv,
                       const CUtensorMap& mk2, const CUtensorMap& mv2, const CUtensorMap& mdq, const AttnBwdParams& p,
-                      const void* O, const void* dO, float* delta, long long q_rows, cudaStream_t stream) {
+                      const void* O, const void* dO, float* delta, long long q_rows, int d, cudaStream_t stream) {
+  if (d == 128) return attn_bwd128_launch(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, q_rows, stream);
   attn_bwd_delta_kernel<<<(unsigned)((q_rows * 8 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, q_rows, p.Cq, p.nh);
   static bool attr = false;
@@ -592,7 +490,7 @@ static int launch_bwd(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, 
 }
 }  // namespace dttt
 
-// Q, O, dO [n, Cq, nh, 64] (bf16, contiguous); keys / values as one or two pairs like dttt_attn_fwd (K2 == null: one pair):
+// Every last dimension below is the head dimension d, 64 or 128.  Q, O, dO [n, Cq, nh, 64] (bf16, contiguous); keys / values as one or two pairs like dttt_attn_fwd (K2 == null: one pair):
 // K / V [n, Kn1, nkv, 64] with `k_bs` / `v_bs` elements between sequences, K2 / V2 [n, Kn2, nkv, 64]; dK / dV [n, Kn1, nkv, 64]
 // and dK2 / dV2 [n, Kn2, nkv, 64] contiguous outputs; lse [n, nh, Cq] f32 from the forward; delta [n, nh, Cq] f32 scratch
 // (written here); dQ [n, Cq, nh, 64] f32, must be zero on entry (accumulated into).  mode / param: the own-chunk pattern as in
@@ -603,7 +501,7 @@ extern "C" int dttt_attn_bwd_masked(const void* Q, const void* K, const void* V,
                                     long long k2_bs, long long v2_bs, float scale, int mode, int param, int* status,
                                     cudaStream_t stream) {
   const int Kn = Kn1 + (K2 ? Kn2 : 0);
-  if (d != HD || nh % nkv || n <= 0 || Cq <= 0 || Kn < Cq || mode < 0 || mode > MASK_READ) return -2;
+  if ((d != 64 && d != 128) || nh % nkv || n <= 0 || Cq <= 0 || Kn < Cq || mode < 0 || mode > MASK_READ) return -2;
   if (mode >= MASK_SPLIT && (Cq % BKEY || param <= 0 || param > Cq)) return -3;
   if (mode == MASK_READ && Kn < 2 * Cq) return -3;
   if (K2 && Kn1 % BKEY) return -4;
@@ -612,16 +510,16 @@ extern "C" int dttt_attn_bwd_masked(const void* Q, const void* K, const void* V,
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
   CUtensorMap mq, mdo, mk, mv, mk2, mv2, mdq;
   int r;
-  if ((r = make_map4f(&mdq, dQ, n, Cq, nh))) return 500 + r;
-  if ((r = make_map4b(&mq, Q, n, Cq, nh))) return 100 + r;
-  if ((r = make_map4b(&mdo, dO, n, Cq, nh))) return 200 + r;
+  if ((r = make_map4f(&mdq, dQ, n, Cq, nh, d))) return 500 + r;
+  if ((r = make_map4b(&mq, Q, n, Cq, nh, d))) return 100 + r;
+  if ((r = make_map4b(&mdo, dO, n, Cq, nh, d))) return 200 + r;
   if (Kn1 > 0) {
-    if ((r = make_map4b(&mk, K, n, Kn1, nkv, k_bs))) return 300 + r;
-    if ((r = make_map4b(&mv, V, n, Kn1, nkv, v_bs))) return 400 + r;
+    if ((r = make_map4b(&mk, K, n, Kn1, nkv, d, k_bs))) return 300 + r;
+    if ((r = make_map4b(&mv, V, n, Kn1, nkv, d, v_bs))) return 400 + r;
   }
   if (K2) {
-    if ((r = make_map4b(&mk2, K2, n, Kn2, nkv, k2_bs))) return 600 + r;
-    if ((r = make_map4b(&mv2, V2, n, Kn2, nkv, v2_bs))) return 700 + r;
+    if ((r = make_map4b(&mk2, K2, n, Kn2, nkv, d, k2_bs))) return 600 + r;
+    if ((r = make_map4b(&mv2, V2, n, Kn2, nkv, d, v2_bs))) return 700 + r;
     if (Kn1 == 0) { mk = mk2; mv = mv2; }
   } else {
     mk2 = mk; mv2 = mv;
@@ -634,7 +532,7 @@ extern "C" int dttt_attn_bwd_masked(const void* Q, const void* K, const void* V,
   p.dK = reinterpret_cast<__nv_bfloat16*>(dK); p.dV = reinterpret_cast<__nv_bfloat16*>(dV);
   p.dK2 = reinterpret_cast<__nv_bfloat16*>(dK2); p.dV2 = reinterpret_cast<__nv_bfloat16*>(dV2); p.status = status;
   dim3 grid((Kn + BKEY - 1) / BKEY, nkv, n);
-  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * Cq * nh, stream);
+  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * Cq * nh, d, stream);
 }
 
 extern "C" int dttt_attn_bwd(const void* Q, const void* K, const void* V, const void* K2, const void* V2, const void* O, const void* dO,
@@ -656,20 +554,20 @@ extern "C" int dttt_attn_bwd_segment(const void* Q, const void* Kc, const void* 
                                      int B, int streams, int chunks, int C, int W, int first, int reach, int nh, int nkv, int d,
                                      long long kc_bs, long long vc_bs, const int* modes, const int* params, float scale, int* status,
                                      cudaStream_t stream) {
-  if (d != HD || nh % nkv || B <= 0 || streams < 2 || streams > MAX_STREAMS || chunks <= 0 || C % BKEY || W < 0) return -2;
+  if ((d != 64 && d != 128) || nh % nkv || B <= 0 || streams < 2 || streams > MAX_STREAMS || chunks <= 0 || C % BKEY || W < 0) return -2;
   if (streams * (W + 1) * (C / BQ) > MAX_ITEMS) return -5;
   static thread_local bool ctx_bound = false;
   if (!ctx_bound) { int dev = 0; cudaGetDevice(&dev); cudaSetDevice(dev); cudaFree(0); ctx_bound = true; }
   const int n = B * streams * chunks;
   CUtensorMap mq, mdo, mk, mv, mk2, mv2, mdq;
   int r;
-  if ((r = make_map4f(&mdq, dQ, n, C, nh))) return 500 + r;
-  if ((r = make_map4b(&mq, Q, n, C, nh))) return 100 + r;
-  if ((r = make_map4b(&mdo, dO, n, C, nh))) return 200 + r;
-  if ((r = make_map4b(&mk, Kc, B, (W + chunks) * C, nkv, kc_bs))) return 300 + r;
-  if ((r = make_map4b(&mv, Vc, B, (W + chunks) * C, nkv, vc_bs))) return 400 + r;
-  if ((r = make_map4b(&mk2, Ko, B * streams, chunks * C, nkv))) return 600 + r;
-  if ((r = make_map4b(&mv2, Vo, B * streams, chunks * C, nkv))) return 700 + r;
+  if ((r = make_map4f(&mdq, dQ, n, C, nh, d))) return 500 + r;
+  if ((r = make_map4b(&mq, Q, n, C, nh, d))) return 100 + r;
+  if ((r = make_map4b(&mdo, dO, n, C, nh, d))) return 200 + r;
+  if ((r = make_map4b(&mk, Kc, B, (W + chunks) * C, nkv, d, kc_bs))) return 300 + r;
+  if ((r = make_map4b(&mv, Vc, B, (W + chunks) * C, nkv, d, vc_bs))) return 400 + r;
+  if ((r = make_map4b(&mk2, Ko, B * streams, chunks * C, nkv, d))) return 600 + r;
+  if ((r = make_map4b(&mv2, Vo, B * streams, chunks * C, nkv, d))) return 700 + r;
   AttnBwdParams p;
   memset(&p, 0, sizeof(p));
   p.n = n; p.Cq = C; p.nh = nh; p.nkv = nkv; p.scale = scale;
@@ -682,5 +580,5 @@ extern "C" int dttt_attn_bwd_segment(const void* Q, const void* Kc, const void* 
   p.dK = reinterpret_cast<__nv_bfloat16*>(dKc); p.dV = reinterpret_cast<__nv_bfloat16*>(dVc);
   p.dK2 = reinterpret_cast<__nv_bfloat16*>(dKo); p.dV2 = reinterpret_cast<__nv_bfloat16*>(dVo); p.status = status;
   dim3 grid((W + chunks) * C / BKEY, nkv, B * streams);
-  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * C * nh, stream);
+  return launch_bwd(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, (long long)n * C * nh, d, stream);
 }

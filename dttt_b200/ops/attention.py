@@ -381,7 +381,7 @@ def _fast_bwd(g, tensors, saved, needs, scale, pattern):
     q, K, V = tensors
     if saved and kernels.available("attention_bwd") and kernels.attention_bwd_supported(q, K):
         return kernels.attention_bwd(g, q, K, V, saved[0], saved[1], scale, pattern)
-    # shapes the backward kernel does not cover (head dimension 128 today): differentiate the tensor-core statement
+    # shapes the kernels do not cover (CPU tensors, f32): differentiate the tensor-core statement
     with torch.enable_grad():
         qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, K, V))
         o = _ref_for_staged(qq, kk, vv, scale, pattern)

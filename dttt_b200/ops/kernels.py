@@ -429,9 +429,9 @@ def _int_array(vals):
 
 
 def attention_segment_supported(q, W: int, patterns) -> bool:
-    """``q [B, S, T, nh, d]``: the one-launch segment form covers head dimension 64, chunks that are multiples of 128 tokens,
+    """``q [B, S, T, nh, d]``: the one-launch segment form covers head dimensions 64 and 128, chunks that are multiples of 128 tokens,
     every pattern but the sub-block read, and work lists of at most 512 (stream, chunk, tile) entries per key block."""
-    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 64 and available("attention_segment")
+    return (q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128) and available("attention_segment")
             and all(parse_pattern(p)[0] < 4 for p in patterns))
 
 
@@ -514,7 +514,8 @@ _SYMBOL.update(attention_bwd="dttt_attn_bwd", attention_segment="dttt_attn_bwd_s
 
 
 def attention_bwd_supported(q, k) -> bool:
-    return attention_supported(q, k) and q.shape[-1] == 64
+    """Head dimensions 64 (``csrc/attn_bwd_tcgen05.cu``) and 128 (``csrc/attn_bwd128_tcgen05.cu``)."""
+    return attention_supported(q, k)
 
 
 def attention_bwd(g, q, k, v, o, lse, scale, causal, k2=None, v2=None):

@@ -76,11 +76,11 @@ def test_attn_fwd_large_magnitude(variant):
     (1, 100, 100, 2, 1, True),
     (1, 1024, 3072, 8, 2, True),
 ])
-def test_attn_bwd(n, Cq, Kn, nh, nkv, causal):
+@pytest.mark.parametrize("d", [64, 128])
+def test_attn_bwd(n, Cq, Kn, nh, nkv, causal, d):
     from dttt_b200.ops import _lib, kernels
     assert kernels.available("attention_bwd")
     torch.manual_seed(5)
-    d = 64
     q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
     k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
     v = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
@@ -100,12 +100,12 @@ def test_attn_bwd(n, Cq, Kn, nh, nkv, causal):
 
 
 @pytest.mark.parametrize("n,Cq,Kw,nh,nkv,causal", [(2, 256, 512, 4, 2, True), (2, 256, 512, 4, 2, False), (1, 1024, 2048, 8, 2, True), (3, 128, 128, 2, 1, True)])
-def test_two_segment_keys_equal_the_concatenation(n, Cq, Kw, nh, nkv, causal):
+@pytest.mark.parametrize("d", [64, 128])
+def test_two_segment_keys_equal_the_concatenation(n, Cq, Kw, nh, nkv, causal, d):
     """Window keys (a strided slice of a longer window buffer) and own keys passed as separate tensors: forward and backward
     must equal the single-tensor call on their concatenation."""
     from dttt_b200.ops import _lib, kernels
     torch.manual_seed(6)
-    d = 64
     q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
     win_k = torch.randn(n, Kw + 256, nkv, d, device="cuda", dtype=torch.bfloat16)
     win_v = torch.randn(n, Kw + 256, nkv, d, device="cuda", dtype=torch.bfloat16)
