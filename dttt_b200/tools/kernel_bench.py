@@ -4,6 +4,9 @@
     python -m dttt_b200.tools.kernel_bench rmsnorm|rope|swiglu|adamw --rows R --dim D
     python -m dttt_b200.tools.kernel_bench attn --seqs 8 --cq 1024 --kn 9216 --heads 32 --kv-heads 8 --head-dim 64 [--causal]
     python -m dttt_b200.tools.kernel_bench ce --rows 2048 --k 2048 --vocab 128256
+    python -m dttt_b200.tools.kernel_bench gemm_pair                                 (one CTA per tile / CTA pair / cuBLAS)
+    python -m dttt_b200.tools.kernel_bench segment --seqs 2 --cq 1024 --window 7 --chunks 8   (one-launch prefix attention)
+    python -m dttt_b200.tools.kernel_bench gdn --seqs 4 --cq 1024 --heads 16 --head-dim 128   (blocked gated delta rule)
     python -m dttt_b200.tools.kernel_bench suite            (the shapes of the 1B model)
 
 Timing: CUDA events on the launching stream, 3 warm-up launches, best of ``--iters``; between timed launches a
@@ -135,9 +138,127 @@ def bench_elementwise(a, out):
         out({"kernel": name, "rows": R, "dim": D, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_copy_bw": nbytes / (ms * 1e-3) / hbm, "peaks": src})
 
 
+def _sdpa_fast(q, k, v, scale, causal):
+    """The library path the attention kernels are compared with: torch SDPA with grouped heads; ``causal`` is aligned to the end
+    of the key axis (query i sees keys j <= i + Kn - Cq)."""
+    import torch.nn.functional as F
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if causal and k.shape[1] != q.shape[1]:
+        from torch.nn.attention.bias import causal_lower_right
+        o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=causal_lower_right(q.shape[1], k.shape[1]), scale=scale, enable_gqa=True)
+    else:
+        o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=bool(causal), scale=scale, enable_gqa=True)
+    return o.transpose(1, 2)
+
+
+def bench_gemm_pair(a, out):
+    """The plain GEMM on one CTA per tile against the CTA-pair form (``csrc/gemm_pair_tcgen05.cu``: two SMs share each B tile)
+    and cuBLAS, on the model's shapes."""
+    from dttt_b200.ops import gemm
+    _, flops, src = peaks()
+    shapes = [(8192, 8192, 8192, 1, 0, 0), (49152, 2048, 2048, 1, 0, 0), (49152, 8192, 2048, 1, 0, 0), (49152, 2048, 8192, 1, 0, 0),
+              (2048, 8192, 2048, 1, 0, 0), (2048, 2048, 8192, 1, 0, 0), (1024, 8192, 2048, 4, 0, 0), (49152, 2048, 8192, 1, 0, 1),
+              (2048, 3072, 2048, 1, 0, 0), (2048, 512, 2048, 1, 0, 0)]
+    was = gemm.PAIR
+    for M, N, K, B, ta, tb in shapes:
+        lead = (B,) if B > 1 else ()
+        x = torch.randn(*lead, *((K, M) if ta else (M, K)), device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(*lead, *((N, K) if tb else (K, N)), device="cuda", dtype=torch.bfloat16)
+        res = {"kernel": "gemm single CTA / CTA pair", "M": M, "N": N, "K": K, "batch": B, "ta": ta, "tb": tb, "peaks": src}
+        fl = 2.0 * M * N * K * B
+        for pair, name in ((False, "single"), (True, "pair")):
+            gemm.PAIR = pair
+            ms = timeit(lambda: gemm.gemm_raw(x, w, bool(ta), bool(tb)), a.iters)
+            res["ms_" + name], res["tflops_" + name] = ms, fl / ms / 1e9
+        X, Y = (x.transpose(-1, -2) if ta else x), (w.transpose(-1, -2) if tb else w)
+        mt = timeit(lambda: torch.matmul(X, Y), a.iters)
+        res.update(ms_cublas=mt, tflops_cublas=fl / mt / 1e9, pair_vs_single=res["ms_single"] / res["ms_pair"], pair_vs_cublas=mt / res["ms_pair"],
+                   frac_of_cublas_peak=fl / (res["ms_pair"] * 1e-3) / flops)
+        out(res)
+    gemm.PAIR = was
+
+
+def bench_segment(a, out):
+    """One prefix layer's attention over a segment: every chunk of the three streams in ONE launch (``dttt_attn_fwd_segment`` /
+    ``dttt_attn_bwd_segment``, the clean keys read in place from the window buffer) against one masked call per chunk on
+    window keys gathered with ``torch.cat`` (what the layer did before)."""
+    from dttt_b200.ops import attention as A, kernels
+    B, S, C, W, nh, nkv, d = a.seqs, 3, a.cq, a.window, a.heads, a.kv_heads, a.head_dim
+    chunks = a.chunks
+    T = chunks * C
+    pats = ("full", "full", "causal")
+    r = lambda *s: torch.randn(*s, device="cuda", dtype=torch.bfloat16)
+    q, k, v, g = r(B, S, T, nh, d), r(B, S, T, nkv, d), r(B, S, T, nkv, d), r(B, S, T, nh, d)
+    kc = torch.cat([r(B, W * C, nkv, d), k[:, 1]], 1)
+    vc = torch.cat([r(B, W * C, nkv, d), v[:, 1]], 1)
+    scale = d ** -0.5
+    _, flops, src = peaks()
+    pairs = 0
+    for c in range(chunks):
+        nv = A.valid_window_chunks(c + W, W, None)
+        pairs += 2 * (nv + 1) * C * C + (nv * C * C + C * (C + 1) // 2)
+    fl = 4.0 * B * nh * d * pairs
+    fwd = lambda: kernels.attention_fwd_segment(q, kc, vc, k, v, C, W, W, None, pats, scale)
+    ms = timeit(fwd, a.iters, a.once)
+    o, lse = fwd()
+    bwd = lambda: kernels.attention_bwd_segment(g, q, kc, vc, k, v, o, lse, C, W, W, None, pats, scale)
+    mb = timeit(bwd, a.iters, a.once)
+
+    def per_chunk(with_bwd):
+        for c in range(chunks):
+            nv = A.valid_window_chunks(c + W, W, None)
+            sl = slice(c * C, (c + 1) * C)
+            kw, vw = kc[:, (W + c - nv) * C:(W + c) * C], vc[:, (W + c - nv) * C:(W + c) * C]
+            for s_, pat in enumerate(pats):
+                oo, ll = kernels.attention_fwd(q[:, s_, sl], kw, vw, scale, pat, k2=k[:, s_, sl], v2=v[:, s_, sl])
+                if with_bwd:
+                    kernels.attention_bwd(g[:, s_, sl], q[:, s_, sl], kw, vw, oo, ll, scale, pat, k2=k[:, s_, sl], v2=v[:, s_, sl])
+    res = {"kernel": "attention, segment form", "seqs": B, "streams": S, "chunks": chunks, "C": C, "W": W, "heads": nh, "kv_heads": nkv,
+           "head_dim": d, "ms_fwd": ms, "tflops_fwd": fl / ms / 1e9, "ms_bwd": mb, "tflops_bwd": 2.5 * fl / mb / 1e9,
+           "frac_of_cublas_peak_fwd": fl / (ms * 1e-3) / flops, "frac_of_cublas_peak_bwd": 2.5 * fl / (mb * 1e-3) / flops, "peaks": src}
+    if a.compare and not a.once:
+        m1 = timeit(lambda: per_chunk(False), a.iters)
+        m2 = timeit(lambda: per_chunk(True), a.iters)
+        res.update(ms_fwd_per_chunk_calls=m1, ms_bwd_per_chunk_calls=m2 - m1, fwd_speedup=m1 / ms, bwd_speedup=(m2 - m1) / mb)
+    out(res)
+
+
+def bench_gdn(a, out):
+    """Gated delta rule over one chunk: the blocked WY kernel (``csrc/gdn_chunked.cu``, f32, one CTA per 32 value rows of a head)
+    against the same block algebra in PyTorch (batched small GEMMs + triangular solves, differentiated by autograd)."""
+    from dttt_b200.ops import gdn_scan, kernels
+    B, C, nh, D = a.seqs, a.cq, a.heads, a.head_dim
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=gen)
+    k = torch.nn.functional.normalize(r(B, C, nh, D), dim=-1)
+    v, beta, la, S0 = r(B, C, nh, D), torch.sigmoid(r(B, C, nh)), -0.05 * torch.rand(B, C, nh, device="cuda", generator=gen), 0.1 * r(B, nh, D, D)
+    gS = r(B, nh, D, D)
+    hbm, _, src = peaks()
+    ms = timeit(lambda: kernels.gdn_chunk_fwd(k, v, beta, la, S0), a.iters, a.once)
+    mb = timeit(lambda: kernels.gdn_chunk_bwd(k, v, beta, la, S0, gS), a.iters, a.once)
+    fl = B * nh * (C // 64) * 2.0 * (64 * 64 * D + 64 * D * D + 64 * 64 * D + 64 * D * D)        # K K^T, K S^T, solve, U^T K
+    res = {"kernel": "gdn_chunk (WY blocks of 64)", "seqs": B, "C": C, "heads": nh, "head_dim": D, "ms_fwd": ms, "ms_bwd": mb,
+           "gflops_fwd": fl / ms / 1e6, "peaks": src}
+    if a.compare and not a.once:
+        was = kernels.gdn_chunk_supported
+        kernels.gdn_chunk_supported = lambda *_: False
+        try:
+            leaves = [t.clone().requires_grad_(True) for t in (k, v, beta, la, S0)]
+            with torch.no_grad():
+                mt = timeit(lambda: gdn_scan.delta_rule_chunked(k, v, beta, la, S0), a.iters)
+
+            def both():
+                S = gdn_scan.delta_rule_chunked(*leaves)
+                torch.autograd.grad(S, leaves, gS)
+            mtb = timeit(both, a.iters)
+        finally:
+            kernels.gdn_chunk_supported = was
+        res.update(ms_fwd_torch=mt, ms_fwd_bwd_torch=mtb, fwd_speedup=mt / ms, fwd_bwd_speedup=mtb / (ms + mb))
+    out(res)
+
+
 def bench_attn(a, out):
     from dttt_b200.ops import kernels
-    from dttt_b200.ops.attention import _sdpa_fast
     n, Cq, Kn, nh, nkv, d = a.seqs, a.cq, a.kn, a.heads, a.kv_heads, a.head_dim
     q = torch.randn(n, Cq, nh, d, device="cuda", dtype=torch.bfloat16)
     k = torch.randn(n, Kn, nkv, d, device="cuda", dtype=torch.bfloat16)
@@ -260,7 +381,7 @@ def bench_ce(a, out):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m dttt_b200.tools.kernel_bench")
-    ap.add_argument("cmd", choices=["gemm", "gemm_forms", "attn", "attn2", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
+    ap.add_argument("cmd", choices=["gemm", "gemm_forms", "gemm_pair", "attn", "attn2", "segment", "gdn", "ce", "rmsnorm", "rope", "swiglu", "adamw", "suite"])
     ap.add_argument("--seqs", type=int, default=8); ap.add_argument("--cq", type=int, default=1024); ap.add_argument("--kn", type=int, default=9216)
     ap.add_argument("--heads", type=int, default=32); ap.add_argument("--kv-heads", type=int, default=8); ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--vocab", type=int, default=128256); ap.add_argument("--causal", action="store_true"); ap.add_argument("--variant", type=int, default=0); ap.add_argument("--bwd", action="store_true")
@@ -269,6 +390,7 @@ def main(argv=None):
     ap.add_argument("--f32acc", action="store_true"); ap.add_argument("--compare", action="store_true")
     ap.add_argument("--rows", type=int, default=49152); ap.add_argument("--dim", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10); ap.add_argument("--once", action="store_true")
+    ap.add_argument("--window", type=int, default=8, help="segment: window chunks"); ap.add_argument("--chunks", type=int, default=8, help="segment: chunks per segment")
     ap.add_argument("--out", default="")
     ap.add_argument("--tile-form", type=int, default=-1, help="plain GEMM tile form: -1 per shape, 0 128 x 256, 1 256 x 256")
     a = ap.parse_args(argv)
@@ -287,6 +409,14 @@ def main(argv=None):
         bench_attn(a, out)
     elif a.cmd == "gemm_forms":
         bench_gemm_forms(a, out)
+    elif a.cmd == "gemm_pair":
+        bench_gemm_pair(a, out)
+    elif a.cmd == "segment":
+        bench_segment(a, out)
+    elif a.cmd == "gdn":
+        a.heads = 16 if a.heads == 32 else a.heads
+        a.head_dim = 128 if a.head_dim == 64 else a.head_dim
+        bench_gdn(a, out)
     elif a.cmd == "attn2":
         bench_attn2(a, out)
     elif a.cmd == "ce":
@@ -304,6 +434,13 @@ def main(argv=None):
         for n, Cq, Kn, causal in ((8, 1024, 9216, True), (8, 1024, 9216, False), (16, 1024, 1024, True), (8, 1024, 4096, True)):
             a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim, a.bwd = n, Cq, Kn, causal, 32, 8, 64, True
             bench_attn(a, out)
+        a.seqs, a.cq, a.kn, a.causal, a.heads, a.kv_heads, a.head_dim = 8, 1024, 9216, True, 16, 4, 128
+        bench_attn(a, out)
+        bench_gemm_pair(a, out)
+        a.seqs, a.cq, a.heads, a.kv_heads, a.head_dim, a.window, a.chunks = 2, 1024, 32, 8, 64, 7, 8
+        bench_segment(a, out)
+        a.seqs, a.cq, a.heads, a.head_dim = 4, 1024, 16, 128
+        bench_gdn(a, out)
         a.rows, a.k, a.vocab = 2048, 2048, 128256
         bench_ce(a, out)
         for cmd, R, D in (("rmsnorm", 49152, 2048), ("swiglu", 49152, 8192), ("rope", 49152, 2048), ("adamw", 16384, 8192)):
