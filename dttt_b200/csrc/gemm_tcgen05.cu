@@ -61,6 +61,15 @@ struct GemmParams {
   void* peer_a[DTTT_MAX_TP];      // MODE 3: rank r's gather buffer [M, K] (entry self_rank is the local one)
   int* peer_flags[DTTT_MAX_TP];   // rank r's flag words: [0, tp) "shard of rank s is in place", [tp, 2 tp) "partials of rank s have landed"
   int* ready;               // MODE 3: local [tiles_m] words, epoch of the last completed copy of that m-block
+  // MODE 5: the weight (the B operand, [wg_rows, wg_row_elems] bf16, dense) is gathered from the ranks' flat shards: element e of
+  // the flat parameter space lives at peer_a[e / wg_shard_elems] + (e % wg_shard_elems); `ready` has one word per 64 weight rows
+  int n_rotate;             // tile columns are visited starting at this n-block
+  int wg_on_k;              // 0: weight rows are output columns (K-major B); 1: weight rows are the contraction index (N-major B)
+  int wg_rows, wg_rot;      // rows of the weight; 64-row block the copies (and the visiting order) start at
+  long long wg_flat_off;    // flat index of the weight's first element
+  long long wg_shard_elems; // elements of the flat space per rank
+  long long wg_row_elems;   // elements per weight row
+  void* wg_dst;             // local dense copy of the weight that the TMA reads
   void* peer_c[DTTT_MAX_TP];      // MODE 4: rank r's slot buffer [tp][rows_per_rank][N] bf16
   int* done_counter;        // MODE 4: local CTA counter, never reset
   int done_target;          // MODE 4: its value once every CTA of this launch has finished
@@ -77,7 +86,14 @@ struct GemmParams {
 //      are already here; the TMA producer waits (bounded) on a per-m-block ready word before touching a pulled block
 //   4  the GEMM with the reduce-scatter of C fused in: every finished tile is stored straight into the slot
 //      [this rank] of the rank that owns those rows; the last CTA to finish raises this rank's flag at every peer
-constexpr int EPI_STORE = 0, EPI_CE_PARTIAL = 1, EPI_CE_DLOGITS = 2, EPI_AG = 3, EPI_RS = 4;
+//   5  the GEMM with the all-gather of a sharded WEIGHT (the B operand) fused in: four copy warps per CTA pull the weight,
+//      64 rows at a time, from the flat parameter shards of the ranks that own them (peer loads over NVLink, the own part
+//      from local memory) into a dense local buffer; the TMA producer waits (bounded) on the ready words of the rows a
+//      tile (or, when the weight's rows are the contraction index, a k-block) needs.  Tiles and k-blocks are visited
+//      starting at the block the copies start at.  The shards must not change while any rank runs the kernel
+//      (the optimiser step is separated from the passes by collectives).
+constexpr int EPI_STORE = 0, EPI_CE_PARTIAL = 1, EPI_CE_DLOGITS = 2, EPI_AG = 3, EPI_RS = 4, EPI_WG = 5;
+constexpr int WG_ROWS = 64;
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   int v;
@@ -156,10 +172,11 @@ __device__ __forceinline__ void tile_coords(int tile, const GemmParams& p, int& 
   tm = first_m + (r % rows);
   tn = r / rows;
   if (p.m_rotate) tm = (tm + p.m_rotate) % p.tiles_m;
+  if (p.n_rotate) tn = (tn + p.n_rotate) % p.tiles_n;
 }
 
 template <int BN, int MODE>
-__global__ void __launch_bounds__(MODE == 3 ? 320 : 192, 1)
+__global__ void __launch_bounds__((MODE == EPI_AG || MODE == EPI_WG) ? 320 : 192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                  const GemmParams p) {
   using L = SmemLayout<BN>;
@@ -213,7 +230,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
             fence_async_proxy();
           }
         }
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        if constexpr (MODE == EPI_WG) {
+          if (!p.wg_on_k) {
+            // the weight rows of this tile's columns: wait for the copy warps (of whichever CTAs took those blocks)
+            const int nblk = (p.wg_rows + WG_ROWS - 1) / WG_ROWS;
+            for (int j = 0; j < BN / WG_ROWS && ok; ++j) {
+              const int blk = n0 / WG_ROWS + j;
+              if (blk < nblk && !wait_flag_ge<false>(p.ready + blk, p.epoch, abort_word, p.status, ERR_WAIT_PEER)) ok = false;
+            }
+            if (!ok) break;
+            fence_async_proxy();
+          }
+        }
+        for (int kb_ = 0; kb_ < kblocks; ++kb_, ++it) {
+          int kb = kb_;
+          if constexpr (MODE == EPI_WG) {
+            if (p.wg_on_k) {
+              // k-blocks are 64 weight rows each: start at the block the copies start at; after this CTA's first tile
+              // every block has been seen ready
+              kb = kb_ + p.wg_rot;
+              if (kb >= kblocks) kb -= kblocks;
+              if (tile == (int)blockIdx.x) {
+                if (!wait_flag_ge<false>(p.ready + kb, p.epoch, abort_word, p.status, ERR_WAIT_PEER)) { ok = false; break; }
+                fence_async_proxy();
+              }
+            }
+          }
           const int s = it % L::STAGES;
           const uint32_t ph = (it / L::STAGES) & 1;
           if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -312,6 +354,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         __threadfence();
         asm volatile("bar.sync 4, 128;" ::: "memory");
         if (ct == 0) { fence_async_proxy(); st_release_gpu(p.ready + tm, p.epoch); }
+      }
+    }
+    if constexpr (MODE == EPI_WG) {
+      const int ct = threadIdx.x - 192;                              // 0..127
+      const int nblk = (p.wg_rows + WG_ROWS - 1) / WG_ROWS;
+      const long long vec_per_blk = (long long)WG_ROWS * p.wg_row_elems / 8;
+      const long long vec_total = (long long)p.wg_rows * p.wg_row_elems / 8;
+      const long long shard_vecs = p.wg_shard_elems / 8, flat0 = p.wg_flat_off / 8;
+      for (int i = blockIdx.x; i < nblk; i += gridDim.x) {
+        int blk = i + p.wg_rot;
+        if (blk >= nblk) blk -= nblk;
+        const long long v_lo = (long long)blk * vec_per_blk;
+        const long long v_hi = min(v_lo + vec_per_blk, vec_total);
+        uint4* to = reinterpret_cast<uint4*>(p.wg_dst);
+        for (long long v0 = v_lo + ct; v0 < v_hi; v0 += 128 * 8) {
+          uint4 buf[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const long long v = v0 + u * 128;
+            if (v < v_hi) {
+              const long long f = flat0 + v;                         // 16-byte vector index in the flat space
+              const int r = (int)(f / shard_vecs);
+              buf[u] = ld_relaxed_sys_v4(reinterpret_cast<const uint4*>(p.peer_a[r]) + (f - (long long)r * shard_vecs));
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (v0 + u * 128 < v_hi) to[v0 + u * 128] = buf[u];
+        }
+        __threadfence();
+        asm volatile("bar.sync 4, 128;" ::: "memory");
+        if (ct == 0) { fence_async_proxy(); st_release_gpu(p.ready + blk, p.epoch); }
       }
     }
   } else {
@@ -815,7 +889,7 @@ static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const G
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   int grid = (int)(tiles < cap ? tiles : cap);
-  gemm_bf16_kernel<BN, MODE><<<grid, MODE == EPI_AG ? 320 : 192, MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+  gemm_bf16_kernel<BN, MODE><<<grid, (MODE == EPI_AG || MODE == EPI_WG) ? 320 : 192, MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
@@ -1069,6 +1143,55 @@ extern "C" int dttt_gemm_ag_bf16(void* const* peer_a, int* const* peer_flags, in
   p.a_row_bytes = (long long)K * 2; p.lda_bytes = lda * 2; p.ready = ready;
   for (int i = 0; i < tp; ++i) { p.peer_a[i] = peer_a[i]; p.peer_flags[i] = peer_flags[i]; }
   return launch_gemm<256, EPI_AG>(mapA, mapB, p, 0, stream);
+}
+
+// C = A x W^T (`on_k` = 0: W [N, K], rows = output columns) or C = A x W (`on_k` = 1: W [K, N], rows = contraction index) where
+// the weight W is gathered inside the kernel from the ranks' flat parameter shards.
+//   peer_shards[r]  rank r's shard of the flat bf16 parameter space (`shard_elems` elements; entry `self` is local)
+//   flat_off        flat index of W's first element (a multiple of 8); W is dense, `w_rows` rows of `w_cols` elements
+//   w_dst           local dense buffer [w_rows, w_cols] bf16 that receives the whole weight (valid after the call, stream order)
+//   ready           local ints, one per 64 weight rows, zero at allocation; epoch grows by one per call on these words
+// The shards must hold their final values on every rank before any rank launches, and must not change until all have finished.
+extern "C" int dttt_gemm_wg_bf16(const void* A, void* const* peer_shards, void* w_dst, int* ready, void* C, int M, int N, int K,
+                                 long long lda, long long ldc, int on_k, long long flat_off, long long shard_elems, int world,
+                                 int self, int epoch, int c_is_f32, int accumulate, int max_ctas, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const int w_rows = on_k ? K : N, w_cols = on_k ? N : K;
+  if (world < 1 || world > DTTT_MAX_TP || self < 0 || self >= world || (K % 8) || (N % 8) || (lda % 8) || (flat_off % 8) ||
+      (shard_elems % 8) || shard_elems <= 0)
+    return -2;
+  if (on_k && (K % BK)) return -3;                      // a k-block is one 64-row copy block
+  if (flat_off + (long long)w_rows * w_cols > shard_elems * world) return -4;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(w_dst) & 15)) return -2;
+  bind_thread_context();
+  const int bn = 256;
+  CUtensorMap mapA, mapB;
+  int r;
+  if ((r = make_map(&mapA, A, K, M, 1, lda, 0, BM))) return 100 + r;
+  if (!on_k) r = make_map(&mapB, w_dst, K, N, 1, K, 0, bn);
+  else       r = make_map(&mapB, w_dst, N, K, 1, N, 0, BK);
+  if (r) return 200 + r;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = M; p.N = N; p.K = K; p.batch = 1; p.b_mn_major = on_k;
+  p.ldc = ldc; p.c_is_f32 = c_is_f32; p.accumulate = accumulate; p.alpha = 1.f; p.C = C; p.status = status;
+  p.tiles_m = (M + BM - 1) / BM; p.tiles_n = (N + bn - 1) / bn;
+  p.tp = world; p.self_rank = self; p.epoch = epoch; p.ready = ready;
+  p.wg_on_k = on_k; p.wg_rows = w_rows; p.wg_flat_off = flat_off; p.wg_shard_elems = shard_elems; p.wg_row_elems = w_cols;
+  p.wg_dst = w_dst;
+  // start where this rank's own part of the weight begins (if it owns any of it)
+  const long long own_lo = (long long)self * shard_elems, own_hi = own_lo + shard_elems;
+  const long long w_lo = flat_off, w_hi = flat_off + (long long)w_rows * w_cols;
+  const long long blk_elems = (long long)WG_ROWS * w_cols;
+  const int nblk = (w_rows + WG_ROWS - 1) / WG_ROWS;
+  int rot = 0;
+  if (own_lo < w_hi && own_hi > w_lo) rot = own_lo > w_lo ? (int)((own_lo - w_lo + blk_elems - 1) / blk_elems) : 0;
+  else rot = (int)((long long)self * nblk / world);      // owns none of it: the ranks start at different blocks of the owners
+  if (rot >= nblk) rot = 0;
+  if (!on_k) { p.n_rotate = rot * WG_ROWS / bn; rot = p.n_rotate * (bn / WG_ROWS); }
+  p.wg_rot = rot;
+  for (int i = 0; i < world; ++i) p.peer_a[i] = peer_shards[i];
+  return launch_gemm<256, EPI_WG>(mapA, mapB, p, max_ctas, stream);
 }
 
 // Partial product of this rank, reduce-scattered by rows: slot[self] of the owner of each row block receives

@@ -113,6 +113,8 @@ class Engine:
         self.store = ParamStore(self.spec, self.mesh, self.dtype, self.device, trainable=trainable,
                                 fused_comm=train_cfg.fused_comm, tp_ctx=self.tp_ctx)
         self.n_params = count_params(model_cfg)
+        if train_cfg.shard_compute and trainable:
+            self.store.enable_shard_compute([n for n in self.spec if n.startswith("prefix.") and n.endswith(".weight")])
         if init:
             self.init_weights(train_cfg.seed)
         self.opt = None

@@ -136,6 +136,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if getattr(w, "tp", None) is not None:
         from ..parallel.tp import tp_linear
         return tp_linear(x, w, bias)
+    if getattr(w, "wg", None) is not None:
+        from ..parallel.wgather import wg_linear
+        return wg_linear(x, w, bias)
     if w.dim() == 3:
         y = mm(x, w.to(x.dtype) if w.dtype != x.dtype else w)
     else:

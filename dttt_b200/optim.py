@@ -106,8 +106,10 @@ class ShardedAdamW:
             me = st.mesh.fsdp_index
             for name, a, b, decay, scale in self.segs:
                 space, off = st.space_of_master_index(a)
+                # (a matrix gathered per use keeps only this rank's slice current: the same kernel with this rank as the only peer)
+                table, world, who = (st._lo_self_tables[space], 1, 0) if name in st.sharded_names else (st._lo_tables[space], st.fs, me)
                 symm.adamw_allgather(st.master[a:b], self.m[a:b], self.v[a:b], g[a:b], lr * scale, self.b1, self.b2, self.eps,
-                                     decay, bc1, bc2, factor, st._lo_tables[space], st.fs, me, off, space == "big" and st.dtype == torch.bfloat16)
+                                     decay, bc1, bc2, factor, table, world, who, off, space == "big" and st.dtype == torch.bfloat16)
             st.barrier()                                     # every rank's stores have landed before anyone reads
             self.wrote_compute = True
         for name, a, b, decay, scale in ([] if st.fused else self.segs):

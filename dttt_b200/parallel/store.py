@@ -79,9 +79,43 @@ class ParamStore:
             self.lo = {"big": torch.zeros(self.n["big"], dtype=compute_dtype, device=device),
                        "small": torch.zeros(self.n["small"], dtype=f32, device=device)}
             self.grad = {k: torch.zeros(self.n[k], dtype=f32, device=device) for k in ("big", "small")} if trainable else None
+        self.sharded_names: set = set()        # matrices whose compute copy is gathered per use (enable_shard_compute)
+        self.wgather = None
         ns = self.shard_n["big"] + self.shard_n["small"]
         self.master = torch.zeros(ns, dtype=f32, device=device)                   # [big shard | small shard]
         self.grad_shard = torch.zeros(ns, dtype=f32, device=device) if trainable else None
+
+    # ---- per-use weight gather (parallel.wgather)
+    def enable_shard_compute(self, names) -> None:
+        """From now on the compute copies of ``names`` (stacked matrices ``[layers, in, out]`` of the big space) are kept
+        current only inside each rank's own flat slice: the optimiser stops pushing them to the peers and every product
+        with one of them gathers it inside the GEMM (``parallel.wgather``).  Needs the peer-memory layout (``fused``)."""
+        if not self.fused or self.mesh.tp > 1 or self.dtype != torch.bfloat16:
+            raise ValueError("shard_compute needs fused_comm on a GPU FSDP group of more than one rank, bf16, no tensor parallelism")
+        import ctypes
+        from .wgather import WeightGather
+        names = [n for n in names if n in self.slots and self.slots[n][0] == "big" and len(self.slots[n][3]) == 3]
+        if not names:
+            return
+        es = 2
+        base = self._off["lo_big"]
+        table = (ctypes.c_void_p * self.fs)(*[ctypes.c_void_p(p + base + r * self.shard_n["big"] * es) for r, p in enumerate(self.peer.ptrs)])
+        biggest = max(self.slots[n][3][1] * self.slots[n][3][2] for n in names)
+        rows = max(max(self.slots[n][3][1], self.slots[n][3][2]) for n in names)
+        self.wgather = WeightGather(table, self.shard_n["big"], self.fs, self.mesh.fsdp_index, self.device, biggest, rows)
+        self.sharded_names = {n for n in names if self.wgather.supports(self.slots[n][3][1:])
+                              and self.wgather.supports(self.slots[n][3][1:][::-1])}
+        self._lo_self_tables = {k: (ctypes.c_void_p * 1)(ctypes.c_void_p(self.peer.local + self._off["lo_" + k])) for k in ("big", "small")}
+
+    def forget_foreign_compute(self) -> None:
+        """Overwrite, in this rank's compute buffer, what other ranks own of the per-use gathered matrices (NaN), so that
+        anything that read them without gathering would show.  A test aid; the training path never reads those ranges."""
+        lo, hi = self.shard_range("big")
+        for n in self.sharded_names:
+            _, off, cnt, _ = self.slots[n]
+            for a, b in ((off, min(off + cnt, lo)), (max(off, hi), off + cnt)):
+                if a < b:
+                    self.lo["big"][a:b].fill_(float("nan"))
 
     # ---- geometry
     def tp_replicated_ranges(self) -> Dict[str, List[Tuple[int, int]]]:
@@ -262,6 +296,9 @@ class ComputeWeights:
             lay = self.store.tp_layout.get(name)
             if lay is not None and not name.endswith("bias"):
                 t.tp = (lay[0], self.store.tp_ctx)
+            if name in self.store.sharded_names and layer is not None:
+                _, off, _, shape = self.store.slots[name]
+                t.wg = (self.store.wgather, off + layer * shape[1] * shape[2])
             self._leaves[key] = t
         return t
 

@@ -359,8 +359,9 @@ class TrainConfig:
     tp_size: int = 1                      # tensor-parallel group size inside a node (heads / MLP width / vocab)
     compute_dtype: str = "bfloat16"       # bfloat16 | float32 (CPU checks)
     fused_comm: bool = True               # fused compute+collective kernels over peer memory (else NCCL)
+    shard_compute: bool = False           # prefix matrices: bf16 copies current only in the owner's slice, gathered inside each GEMM
 
-    _ADDED = ("tp_size", "compute_dtype", "fused_comm")
+    _ADDED = ("tp_size", "compute_dtype", "fused_comm", "shard_compute")
 
     def __post_init__(self):
         c = self

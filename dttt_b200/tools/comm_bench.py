@@ -54,6 +54,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", type=int, default=49152)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--out", default="")
+    ap.add_argument("--only", default="", help="run one family: tp (gemm_ag / gemm_rs), wg (weight-gather GEMM), optim")
     a = ap.parse_args(argv)
     sys.path.insert(0, ROOT)
     from dttt_b200.ops import _lib, gemm
@@ -73,10 +74,50 @@ def main(argv=None) -> int:
             print(lines[-1], flush=True)
 
     M = a.rows - a.rows % (128 * world)
-    ws = tp.Workspace(group, dev, nbytes=6 << 30)
     rows = M // world
+    want = lambda fam: a.only in ("", fam)
+    # ---- FSDP weight all-gather -> GEMM: the weight lies in a flat space cut evenly over the ranks
+    if want("wg"):
+        import ctypes
+        from dttt_b200.parallel.wgather import WeightGather
+        for name, K, N in (("qkv", 2048, 3072), ("mlp_up", 2048, 8192), ("mlp_down", 8192, 2048)):
+            n_w = K * N
+            shard_w = n_w // world
+            pbw = symm.PeerBuffer(n_w * 2, group, dev)
+            pbw.tensor(0, n_w, torch.bfloat16).normal_(0, 0.02)
+            table = (ctypes.c_void_p * world)(*[ctypes.c_void_p(p_ + r_ * shard_w * 2) for r_, p_ in enumerate(pbw.ptrs)])
+            wgr = WeightGather(table, shard_w, world, rank, dev, n_w, max(K, N))
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            mine = pbw.tensor(rank * shard_w * 2, shard_w, torch.bfloat16)
+            full = torch.empty(n_w, device=dev, dtype=torch.bfloat16)
+            torch.cuda.synchronize(); dist.barrier(group=group)
+            t_f = timed(lambda: wgr.gemm(x, (K, N), 0, False), a.iters, group)
+
+            def base_wg():
+                dist.all_gather_into_tensor(full, mine, group=group)
+                gemm.gemm_raw(x, full.view(K, N), False, False)
+            t_b = timed(base_wg, a.iters, group)
+            t_g = timed(lambda: gemm.gemm_raw(x, full.view(K, N), False, False), a.iters, group)
+            fl = 2.0 * M * K * N
+            link = (n_w - shard_w) * 2.0
+            roof = max(fl / flops, link / NVLINK) * 1e3
+            out({"kernel": "gemm_wg (weight all-gather -> GEMM)", "case": name, "M": M, "K": K, "N": N, "ms": t_f, "ms_nccl_then_gemm": t_b,
+                 "ms_gemm_alone": t_g, "speedup_vs_unfused": t_b / t_f, "roofline_ms": roof, "frac_of_roofline": roof / t_f,
+                 "tflops": fl / t_f / 1e9, "nvlink_gbs_in": link / t_f / 1e6})
+            torch.cuda.synchronize(); dist.barrier(group=group)
+            del wgr, pbw
+    if not (want("tp") or want("optim")):
+        torch.cuda.synchronize()
+        _lib.check_status()
+        if a.out and rank == 0:
+            with open(a.out, "w") as fh:
+                fh.write("\n".join(lines) + "\n")
+        dist.barrier(group=group)
+        dist.destroy_process_group()
+        return 0
+    ws = tp.Workspace(group, dev, nbytes=6 << 30)
     # ---- all-gather -> GEMM (column parallel): QKV and MLP up of the 1B model
-    for name, K, N in (("qkv", 2048, 3072), ("mlp_up", 2048, 8192)):
+    for name, K, N in ((("qkv", 2048, 3072), ("mlp_up", 2048, 8192)) if want("tp") else ()):
         Nl = N // world
         xs = torch.randn(rows, K, device=dev, dtype=torch.bfloat16)
         w = (torch.randn(K, Nl, device=dev) * 0.02).to(torch.bfloat16)
@@ -94,7 +135,7 @@ def main(argv=None) -> int:
              "speedup_vs_unfused": t_b / t_f, "roofline_ms": roof, "frac_of_roofline": roof / t_f, "tflops": fl / t_f / 1e9,
              "nvlink_gbs_in": link / t_f / 1e6})
     # ---- GEMM -> reduce-scatter (row parallel): attention out and MLP down
-    for name, K, N in (("attn_out", 2048, 2048), ("mlp_down", 8192, 2048)):
+    for name, K, N in ((("attn_out", 2048, 2048), ("mlp_down", 8192, 2048)) if want("tp") else ()):
         Kl = K // world
         x = torch.randn(M, Kl, device=dev, dtype=torch.bfloat16)
         w = (torch.randn(Kl, N, device=dev) * 0.02).to(torch.bfloat16)
@@ -112,6 +153,15 @@ def main(argv=None) -> int:
         out({"kernel": "gemm_rs (GEMM -> reduce-scatter) + slot_reduce", "case": name, "M": M, "K_local": Kl, "N": N, "ms": t_f,
              "ms_gemm_then_nccl": t_b, "speedup_vs_unfused": t_b / t_f, "roofline_ms": roof, "frac_of_roofline": roof / t_f,
              "tflops": fl / t_f / 1e9, "nvlink_gbs_out": link / t_f / 1e6})
+    if not want("optim"):
+        torch.cuda.synchronize()
+        _lib.check_status()
+        if a.out and rank == 0:
+            with open(a.out, "w") as fh:
+                fh.write("\n".join(lines) + "\n")
+        dist.barrier(group=group)
+        dist.destroy_process_group()
+        return 0
     # ---- optimiser step collectives: reduce-scatter + sum of squares, AdamW + all-gather (1.4 B parameters)
     n = 1437157376 // (64 * world) * (64 * world)
     shard = n // world
