@@ -209,6 +209,8 @@ class Engine:
                         v = v.pow(2)
                     sum_stats[k] = sum_stats.get(k, 0) + v.detach().float()
             del cw, net, loss
+            if self.tp_ctx is not None:
+                self.tp_ctx.last_gather = None                 # the shared gather of the last layer input goes with the pass
         # one global normaliser: micro-batches and data ranks together are one batch
         if noise:
             for k, g in st.grad.items():

@@ -241,6 +241,7 @@ class TPContext:
     def __init__(self, group, size: int, index: int, device: torch.device, workspace_bytes: int = 2 << 30):
         self.group, self.size, self.index, self.device = group, size, index, device
         self.ws: Optional[Workspace] = Workspace(group, device, workspace_bytes) if device.type == "cuda" else None
+        self.last_gather = None            # (key, rows, gathered copy) of the latest column-parallel gather (_gathered_product)
 
 
 def _all_gather_rows(x: torch.Tensor, ctx: TPContext) -> torch.Tensor:
@@ -295,6 +296,21 @@ def _ref_linear(x2: torch.Tensor, w: torch.Tensor, kind: str, tpc: TPContext) ->
     return _ScatterRows.apply(mm(x2, wc), tpc)
 
 
+def _gathered_product(tpc: "TPContext", x2: torch.Tensor, w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(gather_rows(x2) @ w, gathered rows)`` for a column-parallel weight.  Consecutive products of the SAME rows (Q, K and V
+    of a layer; gate and up) gather once: the first call runs the fused all-gather GEMM and keeps a copy of the gathered rows,
+    the following ones are plain GEMMs on that copy.  The rows are recognised by storage address, layout and version counter;
+    the context keeps the tensor alive meanwhile, so the address cannot have been handed to another tensor."""
+    key = (x2.data_ptr(), tuple(x2.shape), tuple(x2.stride()), x2._version)
+    last = tpc.last_gather
+    if last is not None and last[0] == key:
+        return _gemm.gemm_raw(last[2], w, False, False), last[2]
+    y, view = ag_gemm(tpc.ws, x2, w)
+    full = view.clone()
+    tpc.last_gather = (key, x2, full)
+    return y, full
+
+
 class _TPLinear(torch.autograd.Function):
     """Fused forward and first-order backward (``ag_gemm`` / ``gemm_rs``); a backward that is being recorded (the inner
     step under the meta-gradient) is computed from ``_ref_linear`` instead, so it can be differentiated again.  The
@@ -305,8 +321,8 @@ class _TPLinear(torch.autograd.Function):
         ctx.kind, ctx.tpc = kind, tpc
         ctx.target = getattr(w, "grad_target", None)
         if kind == "col":
-            y, full = ag_gemm(tpc.ws, x2, w)
-            ctx.save_for_backward(x2, w, full.clone())
+            y, full = _gathered_product(tpc, x2, w)
+            ctx.save_for_backward(x2, w, full)
         else:
             y = gemm_rs(tpc.ws, x2, w)
             ctx.save_for_backward(x2, w)
@@ -361,7 +377,7 @@ def tp_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     if fused and (torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad)):
         y2 = _TPLinear.apply(x2, w, kind, tpc)
     elif fused:
-        y2 = ag_gemm(tpc.ws, x2, w)[0] if kind == "col" else gemm_rs(tpc.ws, x2, w)
+        y2 = _gathered_product(tpc, x2, w)[0] if kind == "col" else gemm_rs(tpc.ws, x2, w)
     else:
         y2 = _ref_linear(x2, w, kind, tpc)
     if kind == "col":
