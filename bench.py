@@ -228,6 +228,7 @@ def main() -> int:
     ap.add_argument("--fsdp", type=int, default=0)
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shard-compute", action="store_true", help="prefix matrices gathered inside each GEMM instead of kept replicated")
     ap.add_argument("--keep-prefix-layers", type=int, default=-1, help="prefix layers whose activations stay resident (-1: the config's)")
     ap.add_argument("--keep-suffix-chunks", type=int, default=-1, help="chunk steps per segment whose graph stays resident (-1: the config's)")
     args = ap.parse_args()
@@ -277,7 +278,7 @@ def main() -> int:
         return cpu_baseline(args, spec, mc, mesh, W, K)
     tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
                      seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
-                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **extra)
+                     outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, shard_compute=args.shard_compute, **extra)
     eng = Engine(mc, tc, mesh, dev)
 
     # synthetic data: distinct tokens for every step, on pinned host memory
@@ -311,12 +312,13 @@ def main() -> int:
         note = "out of memory with resident graphs: recompute regions instead"
         tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
                          seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
-                         outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, **extra)
+                         outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, shard_compute=args.shard_compute, **extra)
         eng = Engine(mc, tc, mesh, dev)
         torch.cuda.reset_peak_memory_stats()
         for s in range(W):
             m = eng.train_step(host[s].to(dev, non_blocking=True), s)
-    launches0 = gemm.LAUNCHES + kernels.LAUNCHES
+    from dttt_b200.parallel import wgather
+    launches0 = gemm.LAUNCHES + kernels.LAUNCHES + wgather.LAUNCHES
 
     def timed(first_step: int, e2e: bool):
         staged = None if e2e else [host[first_step + i].to(dev) for i in range(K)]
@@ -337,7 +339,7 @@ def main() -> int:
     clocks = ClockSampler(local)
     clocks.start()
     ms_dev, last = timed(W, e2e=False)
-    launches = gemm.LAUNCHES + kernels.LAUNCHES - launches0
+    launches = gemm.LAUNCHES + kernels.LAUNCHES + wgather.LAUNCHES - launches0
     ck = clocks.stop()
     ms_e2e = None
     if not args.no_e2e:

@@ -81,10 +81,14 @@ def build(force: bool = False, verbose: bool = False) -> str:
             print(log, file=sys.stderr)
     newest = max(os.path.getmtime(o) for o in objs)
     if force or not os.path.exists(LIBPATH) or os.path.getmtime(LIBPATH) < newest:
-        cmd = [nvcc, "-shared", "-o", LIBPATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+        tmp = LIBPATH + f".{os.getpid()}.tmp"             # link beside the target, then rename: a reader never sees half a library
+        cmd = [nvcc, "-shared", "-o", tmp, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
+            if os.path.exists(tmp):
+                os.remove(tmp)
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIBPATH)
     return LIBPATH
 
 

@@ -70,6 +70,8 @@ struct GemmParams {
   long long wg_shard_elems; // elements of the flat space per rank
   long long wg_row_elems;   // elements per weight row
   void* wg_dst;             // local dense copy of the weight that the TMA reads
+  int wg_parts;             // CTAs that share the copy of one 64-row block (so every CTA's copy warps pull something)
+  int* wg_cnt;              // per block: parts finished so far in this launch (the last one resets it and raises the ready word)
   void* peer_c[DTTT_MAX_TP];      // MODE 4: rank r's slot buffer [tp][rows_per_rank][N] bf16
   int* done_counter;        // MODE 4: local CTA counter, never reset
   int done_target;          // MODE 4: its value once every CTA of this launch has finished
@@ -362,11 +364,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const long long vec_per_blk = (long long)WG_ROWS * p.wg_row_elems / 8;
       const long long vec_total = (long long)p.wg_rows * p.wg_row_elems / 8;
       const long long shard_vecs = p.wg_shard_elems / 8, flat0 = p.wg_flat_off / 8;
-      for (int i = blockIdx.x; i < nblk; i += gridDim.x) {
-        int blk = i + p.wg_rot;
+      const long long vec_per_part = (vec_per_blk + p.wg_parts - 1) / p.wg_parts;
+      for (int i = blockIdx.x; i < nblk * p.wg_parts; i += gridDim.x) {
+        int blk = i / p.wg_parts + p.wg_rot;
+        const int part = i % p.wg_parts;
         if (blk >= nblk) blk -= nblk;
-        const long long v_lo = (long long)blk * vec_per_blk;
-        const long long v_hi = min(v_lo + vec_per_blk, vec_total);
+        const long long b_lo = (long long)blk * vec_per_blk;
+        const long long v_lo = b_lo + part * vec_per_part;
+        const long long v_hi = min(min(v_lo + vec_per_part, b_lo + vec_per_blk), vec_total);
         uint4* to = reinterpret_cast<uint4*>(p.wg_dst);
         for (long long v0 = v_lo + ct; v0 < v_hi; v0 += 128 * 8) {
           uint4 buf[8];
@@ -385,7 +390,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         }
         __threadfence();
         asm volatile("bar.sync 4, 128;" ::: "memory");
-        if (ct == 0) { fence_async_proxy(); st_release_gpu(p.ready + blk, p.epoch); }
+        if (ct == 0) {
+          fence_async_proxy();
+          if (atomicAdd(p.wg_cnt + blk, 1) == p.wg_parts - 1) {       // the last part of this block
+            __threadfence();
+            p.wg_cnt[blk] = 0;
+            st_release_gpu(p.ready + blk, p.epoch);
+          }
+        }
       }
     }
   } else {
@@ -1151,8 +1163,9 @@ extern "C" int dttt_gemm_ag_bf16(void* const* peer_a, int* const* peer_flags, in
 //   flat_off        flat index of W's first element (a multiple of 8); W is dense, `w_rows` rows of `w_cols` elements
 //   w_dst           local dense buffer [w_rows, w_cols] bf16 that receives the whole weight (valid after the call, stream order)
 //   ready           local ints, one per 64 weight rows, zero at allocation; epoch grows by one per call on these words
+//   cnt             local ints, as many, zero at allocation (how many CTAs have finished their part of a block; back to zero on exit)
 // The shards must hold their final values on every rank before any rank launches, and must not change until all have finished.
-extern "C" int dttt_gemm_wg_bf16(const void* A, void* const* peer_shards, void* w_dst, int* ready, void* C, int M, int N, int K,
+extern "C" int dttt_gemm_wg_bf16(const void* A, void* const* peer_shards, void* w_dst, int* ready, int* cnt, void* C, int M, int N, int K,
                                  long long lda, long long ldc, int on_k, long long flat_off, long long shard_elems, int world,
                                  int self, int epoch, int c_is_f32, int accumulate, int max_ctas, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
@@ -1190,6 +1203,18 @@ extern "C" int dttt_gemm_wg_bf16(const void* A, void* const* peer_shards, void* 
   if (rot >= nblk) rot = 0;
   if (!on_k) { p.n_rotate = rot * WG_ROWS / bn; rot = p.n_rotate * (bn / WG_ROWS); }
   p.wg_rot = rot;
+  // every CTA's copy warps should have something to pull: split a block's copy over several CTAs (at least 1024 vectors each)
+  {
+    const long long tiles = (long long)p.tiles_m * p.tiles_n;
+    const int sms = num_sms();
+    const int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+    const int grid = (int)(tiles < cap ? tiles : cap);
+    int parts = (grid + nblk - 1) / nblk;
+    const long long vec_per_blk = blk_elems / 8;
+    while (parts > 1 && vec_per_blk / parts < 1024) --parts;
+    p.wg_parts = parts < 1 ? 1 : (parts > 16 ? 16 : parts);
+    p.wg_cnt = cnt;
+  }
   for (int i = 0; i < world; ++i) p.peer_a[i] = peer_shards[i];
   return launch_gemm<256, EPI_WG>(mapA, mapB, p, max_ctas, stream);
 }

@@ -23,7 +23,7 @@ from ..ops import _lib
 
 _vp, _ll, _i = ctypes.c_void_p, ctypes.c_longlong, ctypes.c_int
 _PP = ctypes.POINTER(_vp)
-_lib.register("dttt_gemm_wg_bf16", _i, [_vp, _PP, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _ll, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp])
+_lib.register("dttt_gemm_wg_bf16", _i, [_vp, _PP, _vp, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _i, _ll, _ll, _i, _i, _i, _i, _i, _i, _vp, _vp])
 
 ROW_BLOCK = 64          # weight rows per copy block / ready word (WG_ROWS in the kernel)
 LAUNCHES = 0
@@ -38,6 +38,7 @@ class WeightGather:
         self.table, self.shard_elems, self.world, self.rank, self.device = shard_table, int(shard_elems), world, rank, device
         self.stage = torch.empty(max_weight_elems, dtype=torch.bfloat16, device=device)
         self.ready = torch.zeros(-(-max_rows // ROW_BLOCK) + 8, dtype=torch.int32, device=device)
+        self.count = torch.zeros_like(self.ready)       # parts of a block copied so far (the kernel leaves it at zero)
         self.epoch = 0
 
     def gemm(self, a: torch.Tensor, w_shape, flat_off: int, transpose_w: bool, out_dtype=torch.bfloat16,
@@ -60,7 +61,7 @@ class WeightGather:
         self.epoch += 1
         st = _lib.status_tensor(a.device)
         rc = _lib.lib().dttt_gemm_wg_bf16(_vp(a.data_ptr()), self.table, _vp(self.stage.data_ptr()), _vp(self.ready.data_ptr()),
-                                          _vp(out.data_ptr()), M, N, K, a.stride(0), out.stride(0), on_k, int(flat_off), self.shard_elems,
+                                          _vp(self.count.data_ptr()), _vp(out.data_ptr()), M, N, K, a.stride(0), out.stride(0), on_k, int(flat_off), self.shard_elems,
                                           self.world, self.rank, self.epoch, 1 if out.dtype == torch.float32 else 0,
                                           1 if accumulate else 0, int(max_ctas), _vp(st.data_ptr()),
                                           _vp(torch.cuda.current_stream().cuda_stream))
