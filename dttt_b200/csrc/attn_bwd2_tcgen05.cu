@@ -17,6 +17,7 @@
 // The tensor pipe works one block ahead of the arithmetic.  Every wait is bounded; on a timeout all roles leave
 // through the common exit and TMEM is freed.
 #include "ptx_sm100.cuh"
+#include "host_check.h"
 
 #include <mutex>
 
@@ -334,6 +335,7 @@ static int make_in_map(CUtensorMap* map, const void* ptr, int n, int rows, int h
   cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)heads * HD * 2, (cuuint64_t)rows * heads * HD * 2};
   cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (int c = check_map(ptr, 4, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -348,6 +350,7 @@ static int make_out_map(CUtensorMap* map, void* ptr, long long rows, int Kn) {
   cuuint64_t strides[1] = {(cuuint64_t)Kn * 2};
   cuuint32_t box[2] = {BKEY, BQ};
   cuuint32_t estr[2] = {1, 1};
+  if (int c = check_map(ptr, 2, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;

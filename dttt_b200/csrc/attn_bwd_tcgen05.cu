@@ -31,6 +31,7 @@
 // is met by every stream's chunks that have it in their window and by the clean stream's own chunk, so the gradient of a
 // clean key is accumulated once, in tensor memory, over all of them (no per-window partial gradients to add up afterwards).
 #include "attn_bwd_common.cuh"
+#include "host_check.h"
 
 #include <mutex>
 #include <cstring>
@@ -446,6 +447,7 @@ static int make_map4f(CUtensorMap* map, const void* ptr, int n, int rows, int he
   cuuint64_t strides[3] = {(cuuint64_t)hd * 4, (cuuint64_t)heads * hd * 4, (cuuint64_t)rows * heads * hd * 4};
   cuuint32_t box[4] = {32, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (int c = check_map(ptr, 4, dims, strides, 4)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -460,6 +462,7 @@ static int make_map4b(CUtensorMap* map, const void* ptr, int n, int rows, int he
   cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)heads * hd * 2, (cuuint64_t)batch_stride * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (int c = check_map(ptr, 4, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

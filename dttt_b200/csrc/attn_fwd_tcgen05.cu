@@ -17,6 +17,7 @@
 // S(j+1) is issued before the softmax of block j finishes, so the tensor pipe and the exponentials overlap.
 // Every wait is bounded (ptx_sm100.cuh): on a timeout the roles leave through the common exit and TMEM is freed.
 #include "ptx_sm100.cuh"
+#include "host_check.h"
 #include "attn_common.cuh"
 
 #include <mutex>
@@ -591,6 +592,7 @@ static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int hea
   cuuint64_t strides[3] = {(cuuint64_t)d * 2, (cuuint64_t)heads * d * 2, (cuuint64_t)batch_stride * 2};
   cuuint32_t box[4] = {64, 1, 128, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (int c = check_map(ptr, 4, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -15,6 +15,7 @@
 //   * the follower's epilogue threads arriving on the leader's "accumulator drained" barrier.
 // Every wait is bounded; a CTA that gives up sets the status word, and its partner's waits then run out the same way.
 #include "ptx_sm100.cuh"
+#include "host_check.h"
 
 #include <cstring>
 #include <mutex>
@@ -280,6 +281,7 @@ static int make_map(CUtensorMap* map, const void* ptr, long long inner, long lon
   cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * 2, (cuuint64_t)(batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
+  if (int c = check_map(ptr, 3, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;

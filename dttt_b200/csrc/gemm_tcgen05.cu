@@ -18,6 +18,7 @@
 // tile i+1.  Every wait is bounded (ptx_sm100.cuh); on a timeout all roles leave through the
 // common exit, the status word says which wait gave up and TMEM is freed.
 #include "ptx_sm100.cuh"
+#include "host_check.h"
 
 #include <mutex>
 #include <unordered_map>
@@ -836,6 +837,7 @@ static int make_map(CUtensorMap* map, const void* ptr, long long inner, long lon
   cuuint64_t strides[2] = {(cuuint64_t)outer_stride_elems * 2, (cuuint64_t)(batch > 1 ? batch_stride_elems : outer_stride_elems * outer) * 2};
   cuuint32_t box[3] = {64, (cuuint32_t)box_outer, 1};
   cuuint32_t estr[3] = {1, 1, 1};
+  if (int c = check_map(ptr, 3, dims, strides, 2)) return c;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1153,8 +1155,18 @@ extern "C" int dttt_gemm_ag_bf16(void* const* peer_a, int* const* peer_flags, in
   p.tp = tp; p.self_rank = self; p.epoch = epoch; p.rows_per_rank = M / tp;
   p.m_rotate = self * (p.rows_per_rank / BM);
   p.a_row_bytes = (long long)K * 2; p.lda_bytes = lda * 2; p.ready = ready;
-  for (int i = 0; i < tp; ++i) { p.peer_a[i] = peer_a[i]; p.peer_flags[i] = peer_flags[i]; }
+  for (int i = 0; i < tp; ++i) {
+    if (int c = check_extent(peer_a[i], (unsigned long long)(M - 1) * lda * 2 + (unsigned long long)K * 2)) return c;
+    if (int c = check_extent(peer_flags[i], (unsigned long long)2 * tp * 4)) return c;
+    p.peer_a[i] = peer_a[i]; p.peer_flags[i] = peer_flags[i];
+  }
   return launch_gemm<256, EPI_AG>(mapA, mapB, p, 0, stream);
+}
+
+// The host-side range check of host_check.h, whatever DTTT_DEBUG says: 0 if [ptr, ptr + bytes) lies inside one device
+// allocation (or its range cannot be queried), -70 if it does not.  Nothing is launched.
+extern "C" int dttt_debug_extent_check(const void* ptr, long long bytes) {
+  return dttt::extent_inside_allocation(ptr, (unsigned long long)bytes);
 }
 
 // C = A x W^T (`on_k` = 0: W [N, K], rows = output columns) or C = A x W (`on_k` = 1: W [K, N], rows = contraction index) where
@@ -1215,7 +1227,11 @@ extern "C" int dttt_gemm_wg_bf16(const void* A, void* const* peer_shards, void* 
     p.wg_parts = parts < 1 ? 1 : (parts > 16 ? 16 : parts);
     p.wg_cnt = cnt;
   }
-  for (int i = 0; i < world; ++i) p.peer_a[i] = peer_shards[i];
+  for (int i = 0; i < world; ++i) {
+    if (int c = check_extent(peer_shards[i], (unsigned long long)shard_elems * 2)) return c;
+    p.peer_a[i] = peer_shards[i];
+  }
+  if (int c = check_extent(w_dst, (unsigned long long)w_rows * w_cols * 2)) return c;
   return launch_gemm<256, EPI_WG>(mapA, mapB, p, max_ctas, stream);
 }
 
@@ -1245,7 +1261,11 @@ extern "C" int dttt_gemm_rs_bf16(const void* A, const void* B, void* const* peer
   p.ldc = N; p.c_is_f32 = 0; p.alpha = 1.f; p.status = status;
   p.tiles_m = M / BM; p.tiles_n = (N + bn - 1) / bn;
   p.tp = tp; p.self_rank = self; p.epoch = epoch; p.rows_per_rank = M / tp;
-  for (int i = 0; i < tp; ++i) { p.peer_c[i] = peer_c[i]; p.peer_flags[i] = peer_flags[i]; }
+  for (int i = 0; i < tp; ++i) {
+    if (int c = check_extent(peer_c[i], (unsigned long long)M * N * 2)) return c;           // [tp][M / tp][N] bf16
+    if (int c = check_extent(peer_flags[i], (unsigned long long)2 * tp * 4)) return c;
+    p.peer_c[i] = peer_c[i]; p.peer_flags[i] = peer_flags[i];
+  }
   // every rank starts with its own rows and walks the owners in ring order, so at any moment the ranks write to
   // different owners instead of all converging on one GPU's inbound links
   p.m_rotate = self * (p.rows_per_rank / BM);
