@@ -33,6 +33,7 @@ EMULATE = os.environ.get("DTTT_EMULATE", "0") == "1"
 # accumulating weight gradients (which take the 256 x 256 single-CTA form) measured faster on one CTA.  DTTT_GEMM_PAIR=0 turns
 # the pairs off.
 PAIR = os.environ.get("DTTT_GEMM_PAIR", "1") == "1"
+SHAPE_LOG = None        # a dict while a profile wants the launches counted by problem shape (tools/step_profile.py)
 PAIR_MIN = 256
 PAIR_MIN_N = 1024
 _lib.register("dttt_gemm_pair_bf16", ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 6 + [ctypes.c_int] * 4
@@ -109,6 +110,9 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
         assert out.shape == torch.Size(shape) and out.stride(-1) == 1, (out.shape, shape)
     c_batch = out.stride(0) if out.dim() == 3 else 0
     st = _lib.status_tensor(a.device)
+    if SHAPE_LOG is not None:
+        key = (M, N, K, batch, int(ta), int(tb), int(accumulate))
+        SHAPE_LOG[key] = SHAPE_LOG.get(key, 0) + 1
     if PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN_N and not accumulate:
         # CTA pairs (csrc/gemm_pair_tcgen05.cu): each CTA of a cluster loads half of B, one instruction covers 256 x 256
         rc = _lib.lib().dttt_gemm_pair_bf16(

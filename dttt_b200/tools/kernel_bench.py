@@ -253,7 +253,8 @@ def bench_gdn(a, out):
             mtb = timeit(both, a.iters)
         finally:
             kernels.gdn_chunk_supported = was
-        res.update(ms_fwd_torch=mt, ms_fwd_bwd_torch=mtb, fwd_speedup=mt / ms, fwd_bwd_speedup=mtb / (ms + mb))
+        res.update(ms_fwd_token_recurrence_kernel=mt, ms_fwd_bwd_torch_blocks=mtb, fwd_speedup_vs_recurrence=mt / ms,
+                   fwd_bwd_speedup_vs_torch=mtb / (ms + mb))
     out(res)
 
 

@@ -48,6 +48,7 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         print(f"warm-up step {s}: {time.time() - t0:.3f} s", flush=True)
     prof.enable(True)
+    gemm.SHAPE_LOG = {}
     n0 = gemm.LAUNCHES, kernels.LAUNCHES
     t0 = time.time()
     eng.train_step(ids, 2)
@@ -57,6 +58,12 @@ def main(argv=None) -> int:
           f"other kernels {kernels.LAUNCHES - n0[1]}")
     print(prof.format_report(prof.report()))
     prof.enable(False)
+    shapes, gemm.SHAPE_LOG = gemm.SHAPE_LOG, None
+    tot = sum(2.0 * M * N * K * B * n for (M, N, K, B, *_), n in shapes.items())
+    print(f"GEMM launches by problem (M, N, K, batch, A^T, B^T, f32 +=): {sum(shapes.values())} launches, {tot / 1e12:.1f} TFLOP")
+    for key, n in sorted(shapes.items(), key=lambda kv: -2.0 * kv[0][0] * kv[0][1] * kv[0][2] * kv[0][3] * kv[1])[:40]:
+        M, N, K, B = key[:4]
+        print(f"  {str(key):46s} n={n:5d}  {2.0 * M * N * K * B * n / 1e12:8.2f} TFLOP  ({100 * 2.0 * M * N * K * B * n / tot:4.1f} %)")
     print(f"peak device memory: {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB")
     if a.kernels or a.trace:
         from torch.profiler import ProfilerActivity, profile
