@@ -987,7 +987,17 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
       (a_batch % 8) || (b_batch % 8))
     return -2;
   bind_thread_context();
-  const int bn = (N > 128) ? 256 : 128;
+  int bn = (N > 128) ? 256 : 128;
+  if (bn == 256 && !use_256_rows(M, N, K, batch, max_ctas)) {
+    // Small grids: 128-wide tiles when they fill the SMs so much better that the waves they need (at about 0.55 of a 256-wide
+    // tile's time each) come to less than 0.85 of the 256-wide waves.  E.g. 2048 x 512: 32 tiles on 148 SMs become 64.
+    const int sms = num_sms();
+    const int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+    const long long tm = (M + BM - 1) / BM;
+    const long long t256 = tm * ((N + 255) / 256) * batch, t128 = tm * ((N + 127) / 128) * batch;
+    const long long w256 = (t256 + cap - 1) / cap, w128 = (t128 + cap - 1) / cap;
+    if (w256 <= 4 && 0.55 * (double)w128 < 0.85 * (double)w256) bn = 128;
+  }
   CUtensorMap mapA, mapB;
   int r;
   if (!a_mn_major) r = make_map(&mapA, A, K, M, batch, lda, a_batch, BM);
