@@ -30,7 +30,7 @@ struct Smem {
   static constexpr int DQ_BYTES = 128 * 64 * 4;              // 64 columns of the dQ tile at a time
   static constexpr int AUX = 2 * 2 * 128 * 4;
   static constexpr int MASK = 2 * 3 * 128 * 4;
-  static constexpr int ITEMS = MAX_ITEMS * 8;
+  static constexpr int ITEMS = MAX_ITEMS * 16;
   static constexpr int TOTAL = 4 * TILE + DS_BYTES + DQ_BYTES + AUX + MASK + ITEMS + 1024 + 1024;
 };
 
@@ -82,7 +82,7 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   int* sE1 = reinterpret_cast<int*>(sDel + 2 * 128);
   int* sS2 = sE1 + 2 * 128;
   int* sE2 = sS2 + 2 * 128;
-  int2* items = reinterpret_cast<int2*>(sE2 + 2 * 128);
+  int4* items = reinterpret_cast<int4*>(sE2 + 2 * 128);      // see build_work_items
   uint64_t* bars = reinterpret_cast<uint64_t*>(items + MAX_ITEMS);
   static_assert(4 * L::TILE + L::DS_BYTES + L::DQ_BYTES + L::AUX + L::MASK + L::ITEMS + 256 + 1024 <= L::TOTAL, "shared-memory layout");
   static_assert(L::TOTAL <= 227 * 1024, "shared memory per CTA");
@@ -141,16 +141,18 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         tma_load_4d_b(sK + db * SUB, second ? &mapK2 : &mapK, kv_full, db * 64, hk, krow, kseq);
         tma_load_4d_b(sV + db * SUB, second ? &mapV2 : &mapV, kv_full, db * 64, hk, krow, kseq);
       }
+      int ii = 0, h = hk * rep;                              // item index and head of step `it`
       for (int it = 0; it < n_it; ++it) {
         if (!mbar_wait_bounded(st_empty, (it & 1) ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
-        const int2 item = items[it % nq_it];
-        const int h = hk * rep + it / nq_it, qt = item.y >> 1;
+        const int4 item = items[ii];
+        const int qt = item_qt(item);
         mbar_expect_tx(st_full, 2 * L::TILE);
 #pragma unroll
         for (int db = 0; db < 2; ++db) {
           tma_load_4d_b(sQ + db * SUB, &mapQ, st_full, db * 64, h, qt * BQ, item.x);
           tma_load_4d_b(sDO + db * SUB, &mapdO, st_full, db * 64, h, qt * BQ, item.x);
         }
+        if (++ii == nq_it) { ii = 0; ++h; }
       }
     }
     __syncwarp();
@@ -218,29 +220,26 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr float LOG2E = 1.4426950408889634f;
     bool ok = n_it > 0;
-    auto load_aux = [&](int it, float& val, int& e1, int& s2, int& e2) {
-      const int2 item = items[it % nq_it];
-      const int h = hk * rep + it / nq_it, qt = item.y >> 1;
-      const int qi = qt * BQ + (tid & 127);
+    auto load_aux = [&](const int4& item, int h, float& val, int& e1, int& s2, int& e2) {
+      const int qi = item_qt(item) * BQ + (tid & 127);
       const long long base = ((long long)item.x * p.nh + h) * p.Cq;
       if (tid < 128) {
         val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
-        const SeqGeom G = seq_geom(p.sg, item.x, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
-        const int k0 = key_pos0(p, own, jb, G);
-        const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
-        e1 = rm.e1 - k0; s2 = rm.s2 - k0; e2 = rm.e2 - k0;
+        if (item.y & 1) {                                    // positions relative to this block's first row
+          const RowMask rm = item_row_mask(p, item, qi);
+          e1 = rm.e1; s2 = rm.s2; e2 = rm.e2;
+        }
       } else {
         val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
       }
     };
     // the dQ tile of step `it` (lanes = queries, 128 columns) goes to global memory 64 columns at a time: TMEM -> shared
     // memory (two [128 x 32] f32 boxes) -> two bulk tensor reductions (f32 add); rows past the sequence end are clipped
-    auto reduce_dq = [&](int it) -> bool {
+    auto reduce_dq = [&](int it, const int4& item, int h) -> bool {
       int got = 1;
       if (lane == 0) got = mbar_wait_bounded(dq_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
-      const int2 item = items[it % nq_it];
-      const int h = hk * rep + it / nq_it, qt = item.y >> 1;
+      const int qt = item_qt(item);
 #pragma unroll 1
       for (int pass = 0; pass < 2; ++pass) {
         if (tid == 0) bulk_wait_read0();                     // the previous reduction has finished reading the staging tile
@@ -265,22 +264,29 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       }
       return true;
     };
+    int ii = 0, h = hk * rep;                                // item index and head of step `it`
+    int4 item = make_int4(0, 0, 0, 0), prev_item = item;
+    int prev_h = h;
     if (ok) {
-      float v0;
+      item = items[0];
+      float v0 = 0.f;
       int a0 = 0, a1 = 0, a2 = 0;
-      load_aux(0, v0, a0, a1, a2);
+      load_aux(item, h, v0, a0, a1, a2);
       if (tid < 128) { sLSE[tid] = v0; sE1[tid] = a0; sS2[tid] = a1; sE2[tid] = a2; } else sDel[tid - 128] = v0;
     }
     for (int it = 0; it < n_it && ok; ++it) {
+      int ii_n = ii + 1, h_n = h;                            // the next step's item and head: counters, not divisions
+      if (ii_n == nq_it) { ii_n = 0; ++h_n; }
       float vnext = 0.f;
       int n1 = 0, n2 = 0, n3 = 0;
-      if (it + 1 < n_it) load_aux(it + 1, vnext, n1, n2, n3);
+      int4 next_item = item;
+      if (it + 1 < n_it) { next_item = items[ii_n]; load_aux(next_item, h_n, vnext, n1, n2, n3); }
       const float* lse2 = sLSE + (it & 1) * 128;
       const float* del = sDel + (it & 1) * 128;
       const int* e1s = sE1 + (it & 1) * 128;
       const int* s2s = sS2 + (it & 1) * 128;
       const int* e2s = sE2 + (it & 1) * 128;
-      const bool need_mask = (items[it % nq_it].y & 1) != 0;
+      const bool need_mask = (item.y & 1) != 0;
 #pragma unroll 1
       for (int hf = 0; hf < 2 && ok; ++hf) {
         int got = 1;
@@ -338,15 +344,17 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         fence_async_proxy();
         tc_fence_before();
         mbar_arrive(&pds_ready[hf]);
-        if (hf == 0 && it > 0) ok = reduce_dq(it - 1);       // the previous step's dQ, while the tensor core runs this step's products
+        if (hf == 0 && it > 0) ok = reduce_dq(it - 1, prev_item, prev_h);     // the previous step's dQ, under this step's products
       }
       if (!ok) break;
       if (it + 1 < n_it) {
         const int nx = ((it + 1) & 1) * 128;
         if (tid < 128) { sLSE[nx + tid] = vnext; sE1[nx + tid] = n1; sS2[nx + tid] = n2; sE2[nx + tid] = n3; } else sDel[nx + tid - 128] = vnext;
       }
+      prev_item = item; prev_h = h;
+      item = next_item; ii = ii_n; h = h_n;
     }
-    if (ok) ok = reduce_dq(n_it - 1);
+    if (ok) ok = reduce_dq(n_it - 1, prev_item, prev_h);
     if (tid == 0) bulk_wait0();                              // the last dQ reduction has been performed
     // dK, dV of the block: this warp's 64 of the 128 columns, 32 at a time
     if (ok) {

@@ -51,6 +51,9 @@ __device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const 
   asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
                ::"l"(map), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -83,9 +86,11 @@ __device__ __forceinline__ OwnedBlock owned_block(const AttnBwdParams& p, int jb
   return o;
 }
 
-// Fills `items` (.x = sequence, .y = query tile * 2 + needs-mask) with every (sequence, query tile) that sees at least one key
-// of the block; returns how many there are (which may exceed MAX_ITEMS: the caller reports that).  One thread runs this.
-__device__ inline int build_work_items(const AttnBwdParams& p, const OwnedBlock& o, int jb, int z, int2* items) {
+// Fills `items` with every (sequence, query tile) that sees at least one key of the block: .x = sequence, .y = query tile * 2 +
+// needs-mask + (stream << 24), .z = position of the block's first key on that sequence's key axis, .w = that sequence's number of
+// keys (what the math warps need for the mask, so that no step recomputes the geometry).  Returns how many there are (which
+// may exceed MAX_ITEMS: the caller reports that).  One thread runs this.
+__device__ inline int build_work_items(const AttnBwdParams& p, const OwnedBlock& o, int jb, int z, int4* items) {
   const int nqt = (p.Cq + BQ - 1) / BQ;
   int n = 0;
   auto consider = [&](int v, const SeqGeom& G, int kpos0) {
@@ -97,7 +102,7 @@ __device__ inline int build_work_items(const AttnBwdParams& p, const OwnedBlock&
       if (!any) continue;
       const bool all = (kpos0 + BKEY - 1 <= a.e1) || (kpos0 >= zz.s2 && kpos0 + BKEY - 1 <= a.e2);
       const bool ragged = kpos0 + BKEY > G.Kn;
-      if (n < MAX_ITEMS) items[n] = make_int2(v, qt * 2 + ((all && !ragged) ? 0 : 1));
+      if (n < MAX_ITEMS) items[n] = make_int4(v, qt * 2 + ((all && !ragged) ? 0 : 1) + (G.stream << 24), kpos0, G.Kn);
       ++n;
     }
   };
@@ -130,10 +135,14 @@ __device__ inline int build_work_items(const AttnBwdParams& p, const OwnedBlock&
   return n;
 }
 
-// Position of the owned block's first key row on the key axis of sequence geometry G (the pattern is stated on that axis).
-__device__ __forceinline__ int key_pos0(const AttnBwdParams& p, const OwnedBlock& o, int jb, const SeqGeom& G) {
-  if (!p.sg.on) return jb * BKEY;
-  return o.second ? G.Kn - p.Cq + (o.krow % p.Cq) : o.krow - G.row0;
+// The visible keys of query row `qi` of a work item, as positions relative to the owned block's first row.
+__device__ __forceinline__ RowMask item_row_mask(const AttnBwdParams& p, const int4& item, int qi) {
+  const int stream = item.y >> 24;
+  const int mode = p.sg.on ? p.sg.mode[stream] : p.mask_mode, param = p.sg.on ? p.sg.param[stream] : p.mask_param;
+  RowMask rm = row_mask(mode, param, min(qi, p.Cq - 1), item.w, p.Cq);
+  rm.e1 -= item.z; rm.s2 -= item.z; rm.e2 -= item.z;
+  return rm;
 }
+__device__ __forceinline__ int item_qt(const int4& item) { return (item.y & 0xffffff) >> 1; }
 
 }  // namespace dttt

@@ -35,6 +35,7 @@
 
 #include <mutex>
 #include <cstring>
+#include <cstdlib>
 
 namespace dttt {
 
@@ -47,7 +48,7 @@ struct BwdSmem {
   static constexpr int AUX = 2 * 2 * 128 * 4;               // LSE and D, two buffers
   static constexpr int DQ_BYTES = 128 * HD * 4;                // f32 dQ tile staged for the bulk reduction
   static constexpr int MASK = 2 * 3 * 128 * 4;              // per query column: e1, s2, e2 (two buffers)
-  static constexpr int ITEMS = MAX_ITEMS * 8;               // work items: (sequence, query tile | needs mask)
+  static constexpr int ITEMS = MAX_ITEMS * 16;              // work items (build_work_items)
   static constexpr int TOTAL = 2 * TILE + STAGES * 2 * TILE + 2 * DS_BYTES + DQ_BYTES + AUX + MASK + ITEMS + 1024 + 1024;
 };
 
@@ -81,7 +82,12 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ O, const
   }
 }
 
-__global__ void __launch_bounds__(320, 1)
+// G2 = false: eight math warps process the two 64-query halves of a step one after the other (320 threads).
+// G2 = true: sixteen math warps in two groups of eight, group h owning half h of every step and dQ columns [32 h, 32 h + 32)
+// (576 threads, at most 112 registers each: a warp's 32 columns are read in two passes of 16).  The elementwise phase is bound by
+// latency (TMEM loads, special-function unit, barriers), not by issue slots, so twice the warps nearly halve it.
+template <bool G2>
+__global__ void __launch_bounds__(G2 ? 576 : 320, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
                 const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                 const __grid_constant__ CUtensorMap mapK2, const __grid_constant__ CUtensorMap mapV2,
@@ -99,11 +105,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   int* sE1 = reinterpret_cast<int*>(sDel + 2 * 128);         // [2][128] per query column: last key of the prefix interval
   int* sS2 = sE1 + 2 * 128;                                  // [2][128] second interval
   int* sE2 = sS2 + 2 * 128;
-  int2* items = reinterpret_cast<int2*>(sE2 + 2 * 128);      // .x = sequence, .y = query tile * 2 + needs-mask
+  int4* items = reinterpret_cast<int4*>(sE2 + 2 * 128);      // see build_work_items
   uint64_t* bars = reinterpret_cast<uint64_t*>(items + MAX_ITEMS);
   // everything carved above plus the barrier block must fit what the launcher asks for (1024 bytes of alignment slack included)
   static_assert(2 * L::TILE + L::STAGES * 2 * L::TILE + 2 * L::DS_BYTES + L::DQ_BYTES + L::AUX + L::MASK + L::ITEMS + 256 + 1024 <= L::TOTAL,
                 "shared-memory layout exceeds BwdSmem::TOTAL");
+  static_assert(L::TOTAL <= 227 * 1024, "shared memory per CTA");
   uint64_t* kv_full = bars;
   uint64_t* st_full = bars + 1;                              // [2]
   uint64_t* st_empty = st_full + 2;                          // [2]
@@ -128,6 +135,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   // (published by the __syncthreads below)
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t C_S = 0, C_DP = 128, C_DV = 256, C_DK = 320, C_DQ = 384;
+  constexpr int NMATH = G2 ? 512 : 256;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -136,7 +144,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_init(&s_full[s], 1); mbar_init(&pds_ready[s], 256);
     }
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, NMATH);
     mbar_init(acc_final, 1);
     *abort_word = 0;
     fence_mbar_init();
@@ -160,15 +168,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_expect_tx(kv_full, 2 * L::TILE);
       tma_load_4d_b(sK, second ? &mapK2 : &mapK, kv_full, 0, hk, krow, kseq);
       tma_load_4d_b(sV, second ? &mapV2 : &mapV, kv_full, 0, hk, krow, kseq);
+      int ii = 0, h = hk * rep;                              // item index and head of step `it`
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
         if (!mbar_wait_bounded(&st_empty[s], ((it >> 1) & 1) ^ 1, abort_word, p.status, ERR_WAIT_EMPTY)) break;
-        const int2 item = items[it % nq_it];
-        const int h = hk * rep + it / nq_it, qt = item.y >> 1;
+        const int4 item = items[ii];
+        const int qt = item_qt(item);
         uint8_t* sQ = sST + s * 2 * L::TILE;
         mbar_expect_tx(&st_full[s], 2 * L::TILE);
         tma_load_4d_b(sQ, &mapQ, &st_full[s], 0, h, qt * BQ, item.x);
         tma_load_4d_b(sQ + L::TILE, &mapdO, &st_full[s], 0, h, qt * BQ, item.x);
+        if (++ii == nq_it) { ii = 0; ++h; }
       }
     }
     __syncwarp();
@@ -233,124 +243,170 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     __syncwarp();
   } else {
     // ---------------------------------------------------------------- softmax backward, dQ reduction, dK / dV stores
-    const int w = warp - 2;                                  // 0..7
+    const int w = warp - 2;                                  // 0..7 (or 0..15)
     const int quarter = warp & 3;                            // TMEM lane quarter of this warp
-    const int sub = w >> 2;                                  // which 32 of a half's 64 query columns
-    const int tid = threadIdx.x - 64;                        // 0..255
+    const int sub = (w >> 2) & 1;                            // which 32 of a half's 64 query columns
+    const int grp = G2 ? (w >> 3) : 0;                       // G2: the 64-query half (and dQ column half) this warp works on
+    const int gt = (threadIdx.x - 64) & 255;                 // thread within its group of eight warps
     const int kr = quarter * 32 + lane;                      // key row within the block == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const int bar_a = 1 + 3 * grp, bar_b = 2 + 3 * grp, bar_c = 3 + 3 * grp;     // named barriers of this group (256 threads)
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr float LOG2E = 1.4426950408889634f;
     bool ok = n_it > 0;
-    auto load_aux = [&](int it, float& val, int& e1, int& s2, int& e2) {
-      const int2 item = items[it % nq_it];
-      const int h = hk * rep + it / nq_it, qt = item.y >> 1;
-      const int qi = qt * BQ + (tid & 127);
+    // LSE, D and (for tiles that need the mask) the visible key intervals of the step's queries.  G1: thread t < 128 serves query
+    // t (LSE, intervals), thread 128 + t its D.  G2: group h serves queries 64 h ... 64 h + 63 the same way with 64 + 64 threads.
+    constexpr int NQ = G2 ? 64 : 128;                        // queries a group serves
+    const int q_loc = grp * 64 + (gt & (NQ - 1));            // query row within the tile this thread serves (gt < 2 NQ)
+    auto load_aux = [&](const int4& item, int h, float& val, int& e1, int& s2, int& e2) {
+      const int qi = item_qt(item) * BQ + q_loc;
       const long long base = ((long long)item.x * p.nh + h) * p.Cq;
-      if (tid < 128) {
+      if (gt < NQ) {
         val = (qi < p.Cq) ? p.lse[base + qi] * LOG2E : 1e30f;
-        // the keys query qi sees, as positions RELATIVE to this block's first row; rows past the sequence see nothing
-        const SeqGeom G = seq_geom(p.sg, item.x, p.Cq, p.Kn, p.Kn1, p.mask_mode, p.mask_param);
-        const int k0 = key_pos0(p, own, jb, G);
-        const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
-        e1 = rm.e1 - k0; s2 = rm.s2 - k0; e2 = rm.e2 - k0;
-      } else {
+        if (item.y & 1) {                                    // positions RELATIVE to this block's first row
+          const RowMask rm = item_row_mask(p, item, qi);
+          e1 = rm.e1; s2 = rm.s2; e2 = rm.e2;
+        }
+      } else if (gt < 2 * NQ) {
         val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
       }
     };
-    // add the dQ tile of step `it` (lanes = queries) into global memory: the eight warps copy it from TMEM into a
-    // shared-memory tile and one thread issues a single bulk tensor reduction (f32 add) for the whole 128 x 64 tile;
-    // rows past the end of the sequence are clipped by the tensor map
-    auto reduce_dq = [&](int it) -> bool {
+    auto store_aux = [&](int buf, float val, int e1, int s2, int e2) {
+      const int x = buf * 128 + q_loc;
+      if (gt < NQ) { sLSE[x] = val; sE1[x] = e1; sS2[x] = s2; sE2[x] = e2; } else if (gt < 2 * NQ) sDel[x] = val;
+    };
+    // add the dQ tile of a step (lanes = queries) into global memory: the warps copy it from TMEM into shared memory (two
+    // [128 x 32] f32 boxes, rows of 128 bytes with the 16-byte pieces XOR-swizzled by row: the tensor map's 128-byte swizzle,
+    // which also spreads the lanes' stores over the banks) and one thread per box issues a bulk tensor reduction (f32 add);
+    // rows past the end of the sequence are clipped by the tensor map.  G2: each group owns one box.
+    auto reduce_dq = [&](int it, const int4& item, int h) -> bool {
       int got = 1;
       if (lane == 0) got = mbar_wait_bounded(dq_full, it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
-      if (tid == 0) bulk_wait_read0();                       // the previous reduction has finished reading the tile
-      if (!bar_red_and(3, 256, got)) return false;
+      if (gt == 0) bulk_wait_read0();                        // the previous reduction has finished reading the tile
+      if (!bar_red_and(bar_c, 256, got)) return false;
       tc_fence_after();
-      uint32_t r[32];
-      tmem_ld_32x32(tmem + C_DQ + lane_addr + sub * 32, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(dq_empty);
-      // two [128 x 32] f32 boxes (one per 32-column half), rows of 128 bytes with the 16-byte pieces XOR-swizzled by row
-      // (the tensor map's 128-byte swizzle), which also spreads the lanes' stores over the banks
-      float* row = sDQ + sub * (128 * 32) + kr * 32;          // the lane index doubles as the query row here
+      const int qt = item_qt(item);
+      if constexpr (!G2) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + C_DQ + lane_addr + sub * 32, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_empty);
+        float* row = sDQ + sub * (128 * 32) + kr * 32;        // the lane index doubles as the query row here
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        *reinterpret_cast<float4*>(row + 4 * (j ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                                             __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-      fence_async_proxy();
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      if (tid == 0) {
-        const int2 item = items[it % nq_it];
-        const int h = hk * rep + it / nq_it, qt = item.y >> 1;
-        tma_reduce_add_4d(&mapdQ, sDQ, 0, h, qt * BQ, item.x);
-        tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, 32, h, qt * BQ, item.x);
-        bulk_commit();
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<float4*>(row + 4 * (j ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        fence_async_proxy();
+        bar_sync_named(bar_b, 256);
+        if (gt == 0) {
+          tma_reduce_add_4d(&mapdQ, sDQ, 0, h, qt * BQ, item.x);
+          tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, 32, h, qt * BQ, item.x);
+          bulk_commit();
+        }
+      } else {
+        uint32_t r[16];
+        tmem_ld_32x16(tmem + C_DQ + lane_addr + grp * 32 + sub * 16, r);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(dq_empty);
+        float* row = sDQ + grp * (128 * 32) + kr * 32;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<float4*>(row + 4 * ((sub * 4 + j) ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        fence_async_proxy();
+        bar_sync_named(bar_b, 256);
+        if (gt == 0) {
+          tma_reduce_add_4d(&mapdQ, sDQ + grp * (128 * 32), grp * 32, h, qt * BQ, item.x);
+          bulk_commit();
+        }
       }
       return true;
     };
+    // P^T and dS^T (bf16 pairs) of W query columns starting at tile column c0, from the raw S^T / dP^T columns
+    auto softmax_bwd_cols = [&](auto& sr, auto& dr, int c0, int width, uint32_t* pp, uint32_t* dd, const float* lse2, const float* del,
+                                const int* e1s, const int* s2s, const int* e2s, bool need_mask) {
+#pragma unroll
+      for (int i = 0; i < width; i += 4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);     // broadcast reads
+        const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);      // D * scale
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4], dv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
+          if (need_mask) {
+            const int q = c0 + i + u;                        // query column; visible: kr <= e1 or s2 <= kr <= e2 (block-relative)
+            if (kr > e1s[q] && (kr < s2s[q] || kr > e2s[q])) pe = 0.f;
+          }
+          pv[u] = pe;
+          dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u += 2) {
+          __nv_bfloat162 pb = __floats2bfloat162_rn(pv[u], pv[u + 1]);
+          __nv_bfloat162 db = __floats2bfloat162_rn(dv[u], dv[u + 1]);
+          pp[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&pb);
+          dd[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&db);
+        }
+      }
+    };
+    int ii = 0, h = hk * rep;                                // item index and head of step `it`
+    int4 item = make_int4(0, 0, 0, 0), prev_item = item;
+    int prev_h = h;
     if (ok) {
-      float v0;
+      item = items[0];
+      float v0 = 0.f;
       int a0 = 0, a1 = 0, a2 = 0;
-      load_aux(0, v0, a0, a1, a2);
-      if (tid < 128) { sLSE[tid] = v0; sE1[tid] = a0; sS2[tid] = a1; sE2[tid] = a2; } else sDel[tid - 128] = v0;
+      load_aux(item, h, v0, a0, a1, a2);
+      store_aux(0, v0, a0, a1, a2);
     }
     for (int it = 0; it < n_it && ok; ++it) {
+      // the next step's item and head (counters, not divisions), and its LSE / D / intervals on their way
+      int ii_n = ii + 1, h_n = h;
+      if (ii_n == nq_it) { ii_n = 0; ++h_n; }
       float vnext = 0.f;
       int n1 = 0, n2 = 0, n3 = 0;
-      if (it + 1 < n_it) load_aux(it + 1, vnext, n1, n2, n3);
+      int4 next_item = item;
+      if (it + 1 < n_it) { next_item = items[ii_n]; load_aux(next_item, h_n, vnext, n1, n2, n3); }
       const float* lse2 = sLSE + (it & 1) * 128;
       const float* del = sDel + (it & 1) * 128;
       const int* e1s = sE1 + (it & 1) * 128;
       const int* s2s = sS2 + (it & 1) * 128;
       const int* e2s = sE2 + (it & 1) * 128;
-      const bool need_mask = (items[it % nq_it].y & 1) != 0;
+      const bool need_mask = (item.y & 1) != 0;
       uint8_t* ds_tile = sDS + (it & 1) * L::DS_BYTES;
 #pragma unroll 1
-      for (int hf = 0; hf < 2 && ok; ++hf) {
+      for (int hf = grp; hf < (G2 ? grp + 1 : 2) && ok; ++hf) {
         int got = 1;
         if (lane == 0) got = mbar_wait_bounded(&s_full[hf], it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
-        // one verdict for all eight warps (they meet at barriers below); at hf == 0 it also publishes this step's LSE / D
-        if (!bar_red_and(1, 256, got)) { ok = false; break; }
+        // one verdict for the group's eight warps (they meet at barriers below); it also publishes this step's LSE / D
+        if (!bar_red_and(bar_a, 256, got)) { ok = false; break; }
         tc_fence_after();
         const int c0 = hf * 64 + sub * 32;                   // first query column of this warp in this half
         uint32_t pp[16], dd[16];
-        {
+        if constexpr (!G2) {
           uint32_t sr[32], dr[32];
           tmem_ld_32x32(tmem + C_S + lane_addr + c0, sr);
           tmem_ld_32x32(tmem + C_DP + lane_addr + c0, dr);
           tmem_ld_wait();
+          softmax_bwd_cols(sr, dr, c0, 32, pp, dd, lse2, del, e1s, s2s, e2s, need_mask);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);     // broadcast reads
-            const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);      // D * scale
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
-            float pv[4], dv[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              float pe = ex2_approx(fmaf(__uint_as_float(sr[i + u]), sl2, -lv[u]));
-              if (need_mask) {
-                const int q = c0 + i + u;                    // query column; visible: kr <= e1 or s2 <= kr <= e2 (block-relative)
-                if (kr > e1s[q] && (kr < s2s[q] || kr > e2s[q])) pe = 0.f;
-              }
-              pv[u] = pe;
-              dv[u] = pe * fmaf(__uint_as_float(dr[i + u]), p.scale, -dl[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u += 2) {
-              __nv_bfloat162 pb = __floats2bfloat162_rn(pv[u], pv[u + 1]);
-              __nv_bfloat162 db = __floats2bfloat162_rn(dv[u], dv[u + 1]);
-              pp[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&pb);
-              dd[(i + u) / 2] = *reinterpret_cast<uint32_t*>(&db);
-            }
+          for (int ps = 0; ps < 2; ++ps) {
+            uint32_t sr[16], dr[16];
+            tmem_ld_32x16(tmem + C_S + lane_addr + c0 + ps * 16, sr);
+            tmem_ld_32x16(tmem + C_DP + lane_addr + c0 + ps * 16, dr);
+            tmem_ld_wait();
+            softmax_bwd_cols(sr, dr, c0 + ps * 16, 16, pp + ps * 8, dd + ps * 8, lse2, del, e1s, s2s, e2s, need_mask);
           }
         }
-        // both warps of a lane quarter have read this half's columns: the packed results may now overwrite them
+        // every warp that reads this half's columns has read them: the packed results may now overwrite them
         tc_fence_before();
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        bar_sync_named(bar_b, 256);
         tc_fence_after();
         tmem_st_32x16(tmem + C_S + lane_addr + hf * 64 + sub * 16, pp);     // 32 queries -> 16 columns of bf16 pairs
         tmem_st_32x16(tmem + C_DP + lane_addr + hf * 64 + sub * 16, dd);
@@ -365,34 +421,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         fence_async_proxy();
         tc_fence_before();
         mbar_arrive(&pds_ready[hf]);
-        if (hf == 0 && it > 0) ok = reduce_dq(it - 1);       // the previous step's dQ, while this step's half 1 is computed
+        // the previous step's dQ, while the tensor core works on this step's products
+        if ((G2 || hf == 0) && it > 0) ok = reduce_dq(it - 1, prev_item, prev_h);
       }
       if (!ok) break;
-      // next step's LSE / D into the other buffer (its last readers passed barrier 1 of this step)
-      if (it + 1 < n_it) {
-        const int nx = ((it + 1) & 1) * 128;
-        if (tid < 128) { sLSE[nx + tid] = vnext; sE1[nx + tid] = n1; sS2[nx + tid] = n2; sE2[nx + tid] = n3; } else sDel[nx + tid - 128] = vnext;
-      }
+      // next step's LSE / D into the other buffer (its last readers passed this group's first barrier of this step)
+      if (it + 1 < n_it) store_aux((it + 1) & 1, vnext, n1, n2, n3);
+      prev_item = item; prev_h = h;
+      item = next_item; ii = ii_n; h = h_n;
     }
-    if (ok) ok = reduce_dq(n_it - 1);
-    if (tid == 0) bulk_wait0();                              // the last dQ reduction has been performed
-    // dK, dV of the block
+    if (ok) ok = reduce_dq(n_it - 1, prev_item, prev_h);
+    if (gt == 0) bulk_wait0();                               // the last dQ reduction has been performed
+    // dK, dV of the block: a warp's 32 (G2: 16) of the 64 columns
+    constexpr int CW = G2 ? 16 : 32;
+    const int col = G2 ? grp * 32 + sub * 16 : sub * 32;
     if (ok) {
       int got = 1;
       if (lane == 0) got = mbar_wait_bounded(acc_final, 0, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       if (got) {
         tc_fence_after();
-        uint32_t rv[32], rk[32];
-        tmem_ld_32x32(tmem + C_DV + lane_addr + sub * 32, rv);
-        tmem_ld_32x32(tmem + C_DK + lane_addr + sub * 32, rk);
+        uint32_t rv[CW], rk[CW];
+        if constexpr (G2) {
+          tmem_ld_32x16(tmem + C_DV + lane_addr + col, rv);
+          tmem_ld_32x16(tmem + C_DK + lane_addr + col, rk);
+        } else {
+          tmem_ld_32x32(tmem + C_DV + lane_addr + col, rv);
+          tmem_ld_32x32(tmem + C_DK + lane_addr + col, rk);
+        }
         tmem_ld_wait();
         if (krow + kr < klen) {
           __nv_bfloat16* outK = second ? p.dK2 : p.dK;
           __nv_bfloat16* outV = second ? p.dV2 : p.dV;
-          const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * 32;
+          const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + col;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
+          for (int i = 0; i < CW; i += 8) {
             uint4 v, k;
             __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
             __nv_bfloat162* kb = reinterpret_cast<__nv_bfloat162*>(&k);
@@ -408,10 +471,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
     } else if (n_it == 0 && krow + kr < klen) {
       // no query sees this key block: its gradients are zero
-      const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * 32;
+      const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + col;
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int i = 0; i < 32; i += 8) {
+      for (int i = 0; i < CW; i += 8) {
         *reinterpret_cast<uint4*>((second ? p.dV2 : p.dV) + o + i) = z;
         *reinterpret_cast<uint4*>((second ? p.dK2 : p.dK) + o + i) = z;
       }
@@ -485,9 +548,16 @@ static int launch_bwd(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo, 
   if (d == 128) return attn_bwd128_launch(grid, mq, mdo, mk, mv, mk2, mv2, mdq, p, O, dO, delta, q_rows, stream);
   attn_bwd_delta_kernel<<<(unsigned)((q_rows * 8 + 255) / 256), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(O), reinterpret_cast<const __nv_bfloat16*>(dO), delta, q_rows, p.Cq, p.nh);
+  // sixteen math warps unless DTTT_ATTN_BWD_WARPS=8 asks for the eight-warp form
+  static const bool sixteen = [] { const char* e = getenv("DTTT_ATTN_BWD_WARPS"); return !(e && e[0] == '8'); }();
   static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL); attr = true; }
-  attn_bwd_kernel<<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
+  if (!attr) {
+    cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+    cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::TOTAL);
+    attr = true;
+  }
+  if (sixteen) attn_bwd_kernel<true><<<grid, 576, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
+  else attn_bwd_kernel<false><<<grid, 320, BwdSmem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -9,10 +9,10 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture()
 def pair_on():
     from dttt_b200.ops import gemm
-    old = gemm.PAIR, gemm.PAIR_MIN_N
-    gemm.PAIR, gemm.PAIR_MIN_N = True, 256
+    old = gemm.PAIR, gemm.PAIR_MIN_N, gemm.PAIR_MIN_TILES
+    gemm.PAIR, gemm.PAIR_MIN_N, gemm.PAIR_MIN_TILES = True, 256, 0
     yield gemm
-    gemm.PAIR, gemm.PAIR_MIN_N = old
+    gemm.PAIR, gemm.PAIR_MIN_N, gemm.PAIR_MIN_TILES = old
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (1024, 2048, 2048), (384, 768, 192), (300, 520, 136), (2048, 8192, 2048)])
