@@ -18,6 +18,8 @@
 // Every wait is bounded (ptx_sm100.cuh); on a timeout the roles leave through the common exit and TMEM is freed.
 #include "attn_bwd_common.cuh"
 
+#include <cstdlib>
+
 namespace dttt {
 namespace b128 {
 
@@ -63,7 +65,11 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfl
   }
 }
 
-__global__ void __launch_bounds__(320, 1)
+// W16 = false: eight math warps, 32 query columns of a half per thread.  W16 = true: sixteen math warps, 16 columns per thread
+// (576 threads, at most 96 registers): the halves of a step cannot overlap here (they share their score columns), so the
+// elementwise phase is on the critical path and twice the warps shorten it.
+template <bool W16>
+__global__ void __launch_bounds__(W16 ? 576 : 320, 1)
 attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapdO,
                    const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
                    const __grid_constant__ CUtensorMap mapK2, const __grid_constant__ CUtensorMap mapV2,
@@ -108,13 +114,15 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
   if (threadIdx.x == 0) *n_items_slot = build_work_items(p, own, jb, b, items);
   constexpr uint32_t TMEM_COLS = 512;
   constexpr uint32_t C_S = 0, C_DP = 64, C_DV = 128, C_DK = 256, C_DQ = 384;
+  constexpr int NM = W16 ? 512 : 256;                        // math threads
+  constexpr int CW = W16 ? 16 : 32;                          // query columns of a half per thread
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     mbar_init(st_full, 1); mbar_init(st_empty, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&pds_ready[s], 256); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&pds_ready[s], NM); }
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 256);
+    mbar_init(dq_empty, NM);
     mbar_init(acc_final, 1);
     *abort_word = 0;
     fence_mbar_init();
@@ -213,7 +221,7 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
     // ---------------------------------------------------------------- softmax backward, dQ reduction, dK / dV stores
     const int w = warp - 2;
     const int quarter = warp & 3;
-    const int sub = w >> 2;                                  // which 32 of a half's 64 query columns
+    const int sub = w >> 2;                                  // which CW of a half's 64 query columns
     const int tid = threadIdx.x - 64;
     const int kr = quarter * 32 + lane;                      // key row within the block == TMEM lane
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
@@ -229,9 +237,13 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
           const RowMask rm = item_row_mask(p, item, qi);
           e1 = rm.e1; s2 = rm.s2; e2 = rm.e2;
         }
-      } else {
+      } else if (tid < 256) {
         val = (qi < p.Cq) ? p.delta[base + qi] * p.scale : 0.f;
       }
+    };
+    auto store_aux = [&](int buf, float val, int e1, int s2, int e2) {
+      const int x = buf * 128 + (tid & 127);
+      if (tid < 128) { sLSE[x] = val; sE1[x] = e1; sS2[x] = s2; sE2[x] = e2; } else if (tid < 256) sDel[x] = val;
     };
     // the dQ tile of step `it` (lanes = queries, 128 columns) goes to global memory 64 columns at a time: TMEM -> shared
     // memory (two [128 x 32] f32 boxes) -> two bulk tensor reductions (f32 add); rows past the sequence end are clipped
@@ -243,19 +255,22 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
 #pragma unroll 1
       for (int pass = 0; pass < 2; ++pass) {
         if (tid == 0) bulk_wait_read0();                     // the previous reduction has finished reading the staging tile
-        if (!bar_red_and(3, 256, got)) return false;
+        if (!bar_red_and(3, NM, got)) return false;
         tc_fence_after();
-        uint32_t r[32];
-        tmem_ld_32x32(tmem + C_DQ + lane_addr + pass * 64 + sub * 32, r);
+        uint32_t r[CW];
+        if constexpr (W16) tmem_ld_32x16(tmem + C_DQ + lane_addr + pass * 64 + sub * CW, r);
+        else tmem_ld_32x32(tmem + C_DQ + lane_addr + pass * 64 + sub * CW, r);
         tmem_ld_wait();
         if (pass == 1) { tc_fence_before(); mbar_arrive(dq_empty); }
-        float* row = sDQ + sub * (128 * 32) + kr * 32;        // the lane index doubles as the query row here
+        // this thread's CW columns lie in box (sub * CW) / 32 at 16-byte piece ((sub * CW) % 32) / 4 of the row
+        float* row = sDQ + ((sub * CW) / 32) * (128 * 32) + kr * 32;        // the lane index doubles as the query row here
+        const int j0 = ((sub * CW) % 32) / 4;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<float4*>(row + 4 * (j ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        for (int j = 0; j < CW / 4; ++j)
+          *reinterpret_cast<float4*>(row + 4 * ((j0 + j) ^ (kr & 7))) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                                      __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
         fence_async_proxy();
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        bar_sync_named(2, NM);
         if (tid == 0) {
           tma_reduce_add_4d(&mapdQ, sDQ, pass * 64, h, qt * BQ, item.x);
           tma_reduce_add_4d(&mapdQ, sDQ + 128 * 32, pass * 64 + 32, h, qt * BQ, item.x);
@@ -272,7 +287,7 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       float v0 = 0.f;
       int a0 = 0, a1 = 0, a2 = 0;
       load_aux(item, h, v0, a0, a1, a2);
-      if (tid < 128) { sLSE[tid] = v0; sE1[tid] = a0; sS2[tid] = a1; sE2[tid] = a2; } else sDel[tid - 128] = v0;
+      store_aux(0, v0, a0, a1, a2);
     }
     for (int it = 0; it < n_it && ok; ++it) {
       int ii_n = ii + 1, h_n = h;                            // the next step's item and head: counters, not divisions
@@ -292,18 +307,23 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         int got = 1;
         if (lane == 0) got = mbar_wait_bounded(&s_full[hf], it & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
         got = __shfl_sync(0xffffffffu, got, 0);
-        // one verdict for all eight warps; at hf == 0 it also publishes this step's LSE / D / mask bounds
-        if (!bar_red_and(1, 256, got)) { ok = false; break; }
+        // one verdict for all math warps; at hf == 0 it also publishes this step's LSE / D / mask bounds
+        if (!bar_red_and(1, NM, got)) { ok = false; break; }
         tc_fence_after();
-        const int c0 = hf * 64 + sub * 32;                   // first query column (within the tile) of this warp in this half
-        uint32_t pp[16], dd[16];
+        const int c0 = hf * 64 + sub * CW;                   // first query column (within the tile) of this warp in this half
+        uint32_t pp[CW / 2], dd[CW / 2];
         {
-          uint32_t sr[32], dr[32];
-          tmem_ld_32x32(tmem + C_S + lane_addr + sub * 32, sr);
-          tmem_ld_32x32(tmem + C_DP + lane_addr + sub * 32, dr);
+          uint32_t sr[CW], dr[CW];
+          if constexpr (W16) {
+            tmem_ld_32x16(tmem + C_S + lane_addr + sub * CW, sr);
+            tmem_ld_32x16(tmem + C_DP + lane_addr + sub * CW, dr);
+          } else {
+            tmem_ld_32x32(tmem + C_S + lane_addr + sub * CW, sr);
+            tmem_ld_32x32(tmem + C_DP + lane_addr + sub * CW, dr);
+          }
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
+          for (int i = 0; i < CW; i += 4) {
             const float4 l4 = *reinterpret_cast<const float4*>(lse2 + c0 + i);
             const float4 d4 = *reinterpret_cast<const float4*>(del + c0 + i);
             const float lv[4] = {l4.x, l4.y, l4.z, l4.w}, dl[4] = {d4.x, d4.y, d4.z, d4.w};
@@ -327,18 +347,23 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
             }
           }
         }
-        // both warps of a lane quarter have read this half's columns: the packed results may now overwrite them
+        // every warp that reads this half's columns has read them: the packed results may now overwrite them
         tc_fence_before();
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        bar_sync_named(2, NM);
         tc_fence_after();
-        tmem_st_32x16(tmem + C_S + lane_addr + sub * 16, pp);       // 32 queries -> 16 columns of bf16 pairs
-        tmem_st_32x16(tmem + C_DP + lane_addr + sub * 16, dd);
+        if constexpr (W16) {
+          tmem_st_32x8(tmem + C_S + lane_addr + sub * 8, pp);        // 16 queries -> 8 columns of bf16 pairs
+          tmem_st_32x8(tmem + C_DP + lane_addr + sub * 8, dd);
+        } else {
+          tmem_st_32x16(tmem + C_S + lane_addr + sub * 16, pp);      // 32 queries -> 16 columns of bf16 pairs
+          tmem_st_32x16(tmem + C_DP + lane_addr + sub * 16, dd);
+        }
         {
-          // dS^T row kr, queries c0..c0+31, into the M-major A tile: 64-query block hf, 128-byte rows indexed by key
+          // dS^T row kr, queries c0..c0+CW-1, into the M-major A tile: 64-query block hf, 128-byte rows indexed by key
           uint8_t* base = sDS + hf * (128 * 128) + (kr / 8) * 1024 + (kr % 8) * 128;
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(base + (((sub * 4 + q) ^ (kr % 8)) * 16)) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+          for (int q = 0; q < CW / 8; ++q)
+            *reinterpret_cast<uint4*>(base + (((sub * (CW / 8) + q) ^ (kr % 8)) * 16)) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
         }
         tmem_st_wait();
         fence_async_proxy();
@@ -347,16 +372,14 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
         if (hf == 0 && it > 0) ok = reduce_dq(it - 1, prev_item, prev_h);     // the previous step's dQ, under this step's products
       }
       if (!ok) break;
-      if (it + 1 < n_it) {
-        const int nx = ((it + 1) & 1) * 128;
-        if (tid < 128) { sLSE[nx + tid] = vnext; sE1[nx + tid] = n1; sS2[nx + tid] = n2; sE2[nx + tid] = n3; } else sDel[nx + tid - 128] = vnext;
-      }
+      if (it + 1 < n_it) store_aux((it + 1) & 1, vnext, n1, n2, n3);
       prev_item = item; prev_h = h;
       item = next_item; ii = ii_n; h = h_n;
     }
     if (ok) ok = reduce_dq(n_it - 1, prev_item, prev_h);
     if (tid == 0) bulk_wait0();                              // the last dQ reduction has been performed
-    // dK, dV of the block: this warp's 64 of the 128 columns, 32 at a time
+    // dK, dV of the block: this warp's 64 (W16: 32) of the 128 columns, 32 at a time
+    constexpr int OUT_COLS = W16 ? 32 : 64;
     if (ok) {
       int got = 1;
       if (lane == 0) got = mbar_wait_bounded(acc_final, 0, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
@@ -364,8 +387,8 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       if (got) {
         tc_fence_after();
 #pragma unroll 1
-        for (int part = 0; part < 2; ++part) {
-          const int col = sub * 64 + part * 32;
+        for (int part = 0; part < OUT_COLS / 32; ++part) {
+          const int col = sub * OUT_COLS + part * 32;
           uint32_t rv[32], rk[32];
           tmem_ld_32x32(tmem + C_DV + lane_addr + col, rv);
           tmem_ld_32x32(tmem + C_DK + lane_addr + col, rk);
@@ -392,10 +415,10 @@ attn_bwd128_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_consta
       }
     } else if (n_it == 0 && krow + kr < klen) {
       // no query sees this key block: its gradients are zero
-      const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * 64;
+      const long long o = (((long long)kseq * klen + krow + kr) * p.nkv + hk) * HD + sub * OUT_COLS;
       const uint4 z = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int i = 0; i < 64; i += 8) {
+      for (int i = 0; i < OUT_COLS; i += 8) {
         *reinterpret_cast<uint4*>((second ? p.dV2 : p.dV) + o + i) = z;
         *reinterpret_cast<uint4*>((second ? p.dK2 : p.dK) + o + i) = z;
       }
@@ -416,9 +439,16 @@ int attn_bwd128_launch(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mdo,
   using namespace b128;
   delta_kernel<<<(unsigned)((q_rows * 16 + 255) / 256), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(O),
                                                                           reinterpret_cast<const __nv_bfloat16*>(dO), delta, q_rows, p.Cq, p.nh);
+  // sixteen math warps unless DTTT_ATTN_BWD_WARPS=8 asks for the eight-warp form
+  static const bool sixteen = [] { const char* e = getenv("DTTT_ATTN_BWD_WARPS"); return !(e && e[0] == '8'); }();
   static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(attn_bwd128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::TOTAL); attr = true; }
-  attn_bwd128_kernel<<<grid, 320, Smem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
+  if (!attr) {
+    cudaFuncSetAttribute(attn_bwd128_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::TOTAL);
+    cudaFuncSetAttribute(attn_bwd128_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::TOTAL);
+    attr = true;
+  }
+  if (sixteen) attn_bwd128_kernel<true><<<grid, 576, Smem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
+  else attn_bwd128_kernel<false><<<grid, 320, Smem::TOTAL, stream>>>(mq, mdo, mk, mv, mk2, mv2, mdq, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
