@@ -14,14 +14,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(device, dtype, steps):
+def _run(device, dtype, steps, head_dim=64, qk_norm=False):
     from dttt_b200.engine import Engine
     from dttt_b200.ops import gemm, kernels
     from dttt_b200.schema import ModelConfig, TrainConfig
     from dttt_b200.ttt.scan import Batch
     from dttt_b200.utils import rng
     mc = ModelConfig(vocab_size=4096, hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=4,
-                     num_key_value_heads=2, head_dim=64, suffix_len=2, chunk_size=128, window_chunks=2, qk_norm=False,
+                     num_key_value_heads=2, head_dim=head_dim, suffix_len=2, chunk_size=128, window_chunks=2, qk_norm=qk_norm,
                      mask_token_id=4095, pad_token_id=4094, eos_token_id=4094)
     tc = TrainConfig(seq_len=512, batch_size=4, steps=steps, lr=2e-3, end_lr=2e-3, warmup_steps=2, inner_lr_warmup_steps=0,
                      inner_task="causal", outer_shift=True, cart_window=64, fused_ce_block=2048, compute_dtype=dtype, seed=7)
@@ -55,3 +55,16 @@ def test_twenty_steps_bf16_kernels_track_the_f32_statement():
     assert cpu[0] - cpu[-1] > 0.05                                # the model learned something, so the comparison means something
     for s, (a, b) in enumerate(zip(gpu, cpu)):
         assert abs(a - b) / b < (0.01 if s == steps - 1 else 0.02), (s, a, b)
+
+
+def test_head_dimension_128_with_qk_norm_tracks_the_f32_statement():
+    """The reference model's own geometry in small (heads of 128, QK-norm): forward `attn_fwd2_kernel<128>`, backward
+    `attn_bwd128_kernel`, the second order on the row kernel.  Ten steps, 2 % at every step."""
+    from dttt_b200.ops import _lib
+    steps = 10
+    gpu, launches = _run("cuda", "bfloat16", steps, head_dim=128, qk_norm=True)
+    _lib.check_status()
+    cpu, _ = _run("cpu", "float32", steps, head_dim=128, qk_norm=True)
+    assert launches > 500
+    for s_, (a, b) in enumerate(zip(gpu, cpu)):
+        assert abs(a - b) / b < 0.02, (s_, a, b)
