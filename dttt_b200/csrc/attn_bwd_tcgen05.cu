@@ -20,8 +20,10 @@
 //   warp 0      TMA: K, V once; Q and dO tiles into two stages
 //   warp 1      tcgen05.mma issuer, TMEM owner
 //   warps 2-9   two per TMEM lane quarter: softmax-backward math, then the step's dQ tile goes through shared memory
-//               into global memory as ONE bulk tensor reduction (cp.reduce.async.bulk.tensor, f32 add), then the
+//               into global memory by bulk tensor reductions (cp.reduce.async.bulk.tensor, f32 add), then the
 //               final dK / dV stores
+//   warps 10-17 (the default, sixteen-warp form) a second group of eight: group h owns the 64-query half h of every step and
+//               the 32-column half h of the dQ tile, so the elementwise work of both halves runs at the same time
 // TMEM columns: S^T / P^T [0,128)  dP^T / dS^T [128,256)  dV [256,320)  dK [320,384)  dQ [384,448).
 // Every wait is bounded (ptx_sm100.cuh); on a timeout the roles leave through the common exit and TMEM is freed.
 //
