@@ -229,8 +229,8 @@ def main() -> int:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--shard-compute", action="store_true", help="prefix matrices gathered inside each GEMM instead of kept replicated")
-    ap.add_argument("--keep-prefix-layers", type=int, default=-1, help="prefix layers whose activations stay resident (-1: the config's)")
-    ap.add_argument("--keep-suffix-chunks", type=int, default=-1, help="chunk steps per segment whose graph stays resident (-1: the config's)")
+    ap.add_argument("--keep-prefix-layers", type=int, default=-1, help="prefix layers whose activations stay resident (-1: the config's, -2: as many as fit)")
+    ap.add_argument("--keep-suffix-chunks", type=int, default=-1, help="chunk steps per segment whose graph stays resident (-1: the config's, -2: as many as fit)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -264,8 +264,10 @@ def main() -> int:
     micro = min(args.micro or spec["micro"], per_gpu)
     accum = per_gpu // micro
     T = spec["seq_len"]
-    extra = dict(spec["extra"], **({"keep_prefix_layers": args.keep_prefix_layers} if args.keep_prefix_layers >= 0 else {}),
-                 **({"keep_suffix_chunks": args.keep_suffix_chunks} if args.keep_suffix_chunks >= 0 else {}))
+    # (-2 on the command line: "as many as fit", which the engine resolves from the memory model and the free bytes)
+    pick = lambda v: {} if v == -1 else {"k": -1 if v == -2 else v}
+    extra = dict(spec["extra"], **{("keep_prefix_layers" if k == "k" else k): v for k, v in pick(args.keep_prefix_layers).items()},
+                 **{("keep_suffix_chunks" if k == "k" else k): v for k, v in pick(args.keep_suffix_chunks).items()})
     # resident graphs need the whole part: with less than RESIDENT_MIN_FREE_GIB free on any rank the regions recompute instead
     free = torch.tensor([torch.cuda.mem_get_info(dev)[0] / 2 ** 30 if on_gpu else 0.0], device=dev)
     if world > 1:
@@ -356,7 +358,7 @@ def main() -> int:
                    "parallelism": f"dp{mesh.dp}xfsdp{mesh.fsdp}xtp{mesh.tp}", "micro_batch_per_gpu": micro, "grad_accum": accum,
                    "l2": "per-step working set (3 GB bf16 weights + activations) >> 126 MB L2; no explicit flush",
                    "params": eng.n_params, "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
-                   "keep_prefix_layers": extra.get("keep_prefix_layers", 0), "keep_suffix_chunks": extra.get("keep_suffix_chunks", 0),
+                   "keep_prefix_layers": eng.tc.keep_prefix_layers, "keep_suffix_chunks": eng.tc.keep_suffix_chunks,
                    **({"note": note} if note else {})},
         "clocks": ck, "gpu_launches": launches, "final_loss": last.get("main_loss") if last else None,
         "eval_loss": held_out_loss(eng, mc, spec, micro, T),

@@ -301,36 +301,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 //               so tile A's products run while tile B's softmax computes and the other way round
 //   warps 2-5   softmax of tile A, warps 6-9 of tile B: one thread per row holds the 128 scores of the block in
 //               registers, writes P (bf16 pairs) back over the first 64 columns of its S row
-//   (W16: warps 2-9 serve tile A and 10-17 tile B, TWO threads per row with 64 of the block's 128 key columns
-//               each; they agree on the row maximum through shared memory once per block.  A scheduler's special-function
-//               unit takes 8 cycles per warp-wide ex2, and with one warp per scheduler and tile it idles whenever that warp
-//               loads, reduces or stores; four warps per scheduler keep it fed)
+//   (Two threads per row on sixteen softmax warps, agreeing on the row maximum through shared memory once per block, was
+//               built and measured: 1.276 against 1.085 ms at 8 x 1024 x 9216 causal with heads of 64, 0.731 against 0.649 ms
+//               with heads of 128 - slower, the exchange and its barrier cost more than the extra warps hide - and taken out.)
 // The running maximum is only raised when a row's block maximum exceeds it by more than 2^8 (in the exponent's
 // units), so most blocks skip the read-modify-write of the O row; the final O / l and the LSE are exact either way.
 // TMEM columns: S_A / P_A [0,128)  S_B / P_B [128,256)  O_A [256,256+D)  O_B [256+D,256+2D).
-// Barrier `id` over `nthreads` threads that also ANDs a per-thread flag: every participant gets the same verdict.
-__device__ __forceinline__ int bar_red_and_n(int id, int nthreads, int flag) {
-  int out;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %1, 0;\n\t"
-      "bar.red.and.pred q, %2, %3, p;\n\t"
-      "selp.b32 %0, 1, 0, q;\n\t}"
-      : "=r"(out) : "r"(flag), "r"(id), "r"(nthreads) : "memory");
-  return out;
-}
-
 template <int D>
 struct Attn2Smem {
   static constexpr int Q_BYTES = 2 * AQ * D * 2;
   static constexpr int KV_BYTES = 2 * AK * D * 2;
   static constexpr int STAGES = (D == 64) ? 4 : 2;
-  static constexpr int XCH = 2 * 2 * 2 * 128 * 4;            // [buffer][tile][half][row] floats the two threads of a row exchange
-  static constexpr int TOTAL = Q_BYTES + STAGES * KV_BYTES + XCH + 1024 + 1024;
+  static constexpr int TOTAL = Q_BYTES + STAGES * KV_BYTES + 1024 + 1024;
 };
 
-template <int D, bool W16>
-__global__ void __launch_bounds__(W16 ? 576 : 320, 1)
+template <int D>
+__global__ void __launch_bounds__(320, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                  const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapK2,
                  const __grid_constant__ CUtensorMap mapV2, const AttnParams p) {
@@ -340,8 +326,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = sQ + L::Q_BYTES;
-  float* xch = reinterpret_cast<float*>(sKV + L::STAGES * L::KV_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + L::STAGES * L::KV_BYTES + L::XCH);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + L::STAGES * L::KV_BYTES);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;
   uint64_t* kv_empty = kv_full + L::STAGES;
@@ -387,7 +372,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < L::STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], W16 ? 256 : 128); mbar_init(&o_final[t], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 128); mbar_init(&o_final[t], 1); }
     *abort_word = 0;
     fence_mbar_init();
     tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
@@ -474,125 +459,6 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       }
     }
     __syncwarp();
-  } else if constexpr (W16) {
-    // ---------------------------------------------------------------- softmax + epilogue, two threads per row
-    const int sw = warp - 2;                                // 0..15
-    const int t = sw >> 3;                                  // tile of this group of eight warps
-    const int half = (sw >> 2) & 1;                         // which 64 of a block's 128 key columns (and which half of the O row)
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int qi = q0 + t * AQ + row;
-    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_addr = tmem + t * 128 + lane_addr;
-    const uint32_t o_addr = tmem + O_COL + t * D + lane_addr + half * (D / 2);
-    const float sl2 = p.scale * 1.4426950408889634f;
-    const RowMask rm = row_mask(G.mode, G.param, min(qi, p.Cq - 1), G.Kn, p.Cq);
-    const int bar_id = 1 + t;                               // named barrier of this tile's 256 threads
-    float m = -1e30f, l = 0.f;                              // m: the row's reference maximum (both threads hold the same); l: this thread's part of the sum
-    bool ok = true;
-    const int nbt = nb[t];
-    for (int j = 0; j < nbt; ++j) {
-      int got = 1;
-      if (lane == 0) got = mbar_wait_bounded(&s_full[t], j & 1, abort_word, p.status, ERR_WAIT_TMEM_FULL) ? 1 : 0;
-      got = __shfl_sync(0xffffffffu, got, 0);
-      if (!got) { ok = false; }                             // (the verdict is made uniform at the barrier below)
-      tc_fence_after();
-      uint32_t sr[64];
-      if (got) {
-        tmem_ld_32x32(s_addr + half * 64, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-        tmem_ld_32x32(s_addr + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) sr[i] = __float_as_uint(MASKED);
-      }
-      const int kbase = blk(j) * AK + half * 64;             // key position of this thread's first column
-      const bool whole = (kbase + 63 <= rm.e1) || (kbase >= rm.s2 && kbase + 63 <= rm.e2);
-      if (!whole) {
-        const int hi1 = rm.e1 - kbase, lo2 = rm.s2 - kbase, hi2 = rm.e2 - kbase;
-#pragma unroll
-        for (int i = 0; i < 64; ++i)
-          if (i > hi1 && (i < lo2 || i > hi2)) sr[i] = __float_as_uint(MASKED);
-      }
-      float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
-#pragma unroll
-      for (int i = 4; i < 64; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));     mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
-      }
-      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // the two threads of a row exchange their maxima (buffers alternate by block, so one barrier per block is enough); the
-      // barrier also means both have their scores in registers, so the packed P may overwrite the S columns afterwards
-      float* xb = xch + (((j & 1) * 2 + t) * 2) * 128;
-      xb[half * 128 + row] = mx;
-      if (!bar_red_and_n(bar_id, 256, ok ? 1 : 0)) { ok = false; break; }
-      mx = fmaxf(mx, xb[(half ^ 1) * 128 + row]);
-      // raise the reference maximum only on a large jump (the same decision in both warps of the rows: they see the same maxima)
-      if (__any_sync(0xffffffffu, (mx - m) * sl2 > 8.f)) {
-        const float m_new = fmaxf(m, mx);
-        const float alpha = exp2f((m - m_new) * sl2);
-        m = m_new;
-        l *= alpha;
-        if (j > 0) {
-#pragma unroll 1
-          for (int c = 0; c < D / 2; c += 16) {              // this thread's half of the O row, 16 columns at a time (registers)
-            uint32_t o[16];
-            tmem_ld_32x16(o_addr + c, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x16(o_addr + c, o);
-          }
-        }
-      }
-      const float mneg = -m * sl2;
-      float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-      for (int i = 0; i < 64; i += 2) {                     // packed in place: pair i / 2 goes where score i / 2 was
-        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), sl2, mneg));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), sl2, mneg));
-        sum0 += p0; sum1 += p1;
-        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        sr[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
-      }
-      l += sum0 + sum1;
-      tmem_st_32x32(s_addr + half * 32, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&p_ready[t]);
-    }
-    if (nbt > 0) {
-      int got = 1;
-      if (ok && lane == 0) got = mbar_wait_bounded(&o_final[t], 0, abort_word, p.status, ERR_WAIT_TMEM_EMPTY) ? 1 : 0;
-      got = __shfl_sync(0xffffffffu, got, 0) && ok;
-      // the row's sum: both parts (buffer parity continues the block sequence)
-      float* xb = xch + (((nbt & 1) * 2 + t) * 2) * 128;
-      xb[half * 128 + row] = l;
-      if (ok && bar_red_and_n(bar_id, 256, got)) {
-        l += xb[(half ^ 1) * 128 + row];
-        tc_fence_after();
-        const float inv = 1.f / l;
-        __nv_bfloat16* out = p.O + (((long long)b * p.Cq + qi) * p.nh + h) * D + half * (D / 2);
-#pragma unroll 1
-        for (int c = 0; c < D / 2; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_addr + c, r);
-          tmem_ld_wait();
-          if (qi < p.Cq) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 v;
-              __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                vb[q] = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * q]) * inv, __uint_as_float(r[i + 2 * q + 1]) * inv);
-              *reinterpret_cast<uint4*>(out + c + i) = v;
-            }
-          }
-        }
-        if (half == 0 && qi < p.Cq && p.lse) p.lse[((long long)b * p.nh + h) * p.Cq + qi] = m * p.scale + logf(l);
-      }
-    }
   } else {
     // ---------------------------------------------------------------- softmax + epilogue
     const int t = (warp - 2) >> 2;                          // tile of this warpgroup
@@ -741,19 +607,12 @@ static int make_map4(CUtensorMap* map, const void* ptr, int n, int rows, int hea
 }  // namespace dttt
 
 namespace dttt {
-// eight softmax warps (one thread per row); DTTT_ATTN_FWD_WARPS=16 selects sixteen (two threads per row)
 template <int D>
 static int launch_fwd2(dim3 grid, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mk2,
                        const CUtensorMap& mv2, const AttnParams& p, cudaStream_t stream) {
-  static const bool sixteen = [] { const char* e = getenv("DTTT_ATTN_FWD_WARPS"); return e && e[0] == '1' && e[1] == '6'; }();
   static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(attn_fwd2_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<D>::TOTAL);
-    cudaFuncSetAttribute(attn_fwd2_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<D>::TOTAL);
-    attr = true;
-  }
-  if (sixteen) attn_fwd2_kernel<D, true><<<grid, 576, Attn2Smem<D>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
-  else attn_fwd2_kernel<D, false><<<grid, 320, Attn2Smem<D>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
+  if (!attr) { cudaFuncSetAttribute(attn_fwd2_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Attn2Smem<D>::TOTAL); attr = true; }
+  attn_fwd2_kernel<D><<<grid, 320, Attn2Smem<D>::TOTAL, stream>>>(mq, mk, mv, mk2, mv2, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -18,12 +18,11 @@ import torch
 
 
 def _state_after_chunk(k, v, beta, log_alpha, S0):
-    """The new state alone (nothing kept for a backward): the token-recurrence kernel (``csrc/gdn_scan.cu``) runs it about five
-    times faster than the blocked form (0.51 against 2.56 ms for 4 x 16 heads of 128 over 1024 tokens), whose point is the
-    block-state checkpoints its backward needs."""
+    """The new state alone (nothing kept for a backward), on the blocked kernel.  (The token-recurrence kernel
+    ``csrc/gdn_scan.cu`` is five times faster on this shape, 0.51 against 2.56 ms, but a 32k training run that took its forward
+    from it ended with a non-finite loss while the same run on the blocked kernel is finite; until that is understood the
+    recurrence kernel stays a cross-check for tests.)"""
     from . import kernels
-    if kernels.available("gdn"):
-        return kernels.gdn_chunked(k, v, beta, log_alpha, S0)
     return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
 
 
