@@ -17,23 +17,15 @@ from __future__ import annotations
 import torch
 
 
-def _state_after_chunk(k, v, beta, log_alpha, S0):
-    """The new state alone (nothing kept for a backward), on the blocked kernel.  (The token-recurrence kernel
-    ``csrc/gdn_scan.cu`` is five times faster on this shape, 0.51 against 2.56 ms, but a 32k training run that took its forward
-    from it ended with a non-finite loss while the same run on the blocked kernel is finite; until that is understood the
-    recurrence kernel stays a cross-check for tests.)"""
-    from . import kernels
-    return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
-
-
 class _ChunkKernel(torch.autograd.Function):
     """The chunk update on the CUDA kernels: the forward keeps only its inputs, the backward re-creates the block states
     (``csrc/gdn_chunked.cu``) and runs the reverse sweep."""
 
     @staticmethod
     def forward(ctx, k, v, beta, log_alpha, S0):
+        from . import kernels
         ctx.save_for_backward(k, v, beta, log_alpha, S0)
-        return _state_after_chunk(k, v, beta, log_alpha, S0)
+        return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -53,10 +45,7 @@ def delta_rule_chunked(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, log
     if kernels.gdn_chunk_supported(k, v, min(block, k.shape[1])):
         if torch.is_grad_enabled() and any(t.requires_grad for t in (k, v, beta, log_alpha, S0)):
             return _ChunkKernel.apply(k, v, beta, log_alpha, S0)
-        return _state_after_chunk(k, v, beta, log_alpha, S0)
-    if (k.is_cuda and kernels.available("gdn") and k.shape[-1] in (64, 128) and v.shape[-1] == k.shape[-1]
-            and not (torch.is_grad_enabled() and any(t.requires_grad for t in (k, v, beta, log_alpha, S0)))):
-        return kernels.gdn_chunked(k, v, beta, log_alpha, S0, block)
+        return kernels.gdn_chunk_fwd(k, v, beta, log_alpha, S0)
     B, C, nh, dk = k.shape
     L = min(block, C)
     assert C % L == 0, (C, L)

@@ -702,24 +702,6 @@ def threefry_uniform(keys, n, thresh=None):
 
 
 # =============================================================================== gated delta rule
-_lib.register("dttt_gdn_update", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp])
-_SYMBOL.update(gdn="dttt_gdn_update")
-
-
-def gdn_chunked(k, v, beta, log_alpha, S0, block=64):
-    """The state after one chunk of the gated delta rule (exact token recurrence, f32; no autograd): ``k / v [B, C, nh, D]``,
-    ``beta / log_alpha [B, C, nh]``, ``S0 [B, nh, D, D]``.  Head dimensions other than 64 / 128 (or unequal key / value
-    widths) are not covered: the caller's chunked PyTorch form handles them."""
-    B, C, nh, D = k.shape
-    if D not in (64, 128) or v.shape[-1] != D:
-        raise NotImplementedError("gdn kernel: head dimension 64 or 128 with equal key and value widths")
-    f = lambda t: t.float().contiguous()
-    out = torch.empty(B, nh, D, D, dtype=torch.float32, device=k.device)
-    _check(_lib.lib().dttt_gdn_update(_p(f(k)), _p(f(v)), _p(f(beta)), _p(f(log_alpha)), _p(f(S0)), _p(out), B, C, nh, D, _stream()),
-           "gdn_update")
-    return out
-
-
 # ---- the blocked (WY) form: forward with optional block-state checkpoints, and the backward
 _lib.register("dttt_gdn_chunk_state_elems", _ll, [_i, _i, _i, _i])
 _lib.register("dttt_gdn_chunk_fwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp])

@@ -244,8 +244,6 @@ def bench_gdn(a, out):
         kernels.gdn_chunk_supported = lambda *_: False
         try:
             leaves = [t.clone().requires_grad_(True) for t in (k, v, beta, la, S0)]
-            with torch.no_grad():
-                mt = timeit(lambda: gdn_scan.delta_rule_chunked(k, v, beta, la, S0), a.iters)
 
             def both():
                 S = gdn_scan.delta_rule_chunked(*leaves)
@@ -253,8 +251,7 @@ def bench_gdn(a, out):
             mtb = timeit(both, a.iters)
         finally:
             kernels.gdn_chunk_supported = was
-        res.update(ms_fwd_token_recurrence_kernel=mt, ms_fwd_bwd_torch_blocks=mtb, fwd_speedup_vs_recurrence=mt / ms,
-                   fwd_bwd_speedup_vs_torch=mtb / (ms + mb))
+        res.update(ms_fwd_bwd_torch_blocks=mtb, fwd_bwd_speedup_vs_torch=mtb / (ms + mb))
     out(res)
 
 

@@ -268,18 +268,3 @@ def test_cart_band_and_threefry_match_the_host_statements():
     assert torch.equal(u.cpu(), u_ref)
     th = torch.tensor([0.1, 0.5, 0.9], device="cuda")
     assert torch.equal(kernels.threefry_uniform(keys, 1000, th).cpu(), u_ref < th.cpu()[:, None])
-
-
-@pytest.mark.parametrize("D,C", [(64, 100), (128, 256)])
-def test_gdn_update_kernel_matches_the_token_recurrence(D, C):
-    from dttt_b200.ops import kernels, reference as ref
-    torch.manual_seed(23)
-    B, nh = 2, 3
-    k = torch.nn.functional.normalize(torch.randn(B, C, nh, D, device="cuda"), dim=-1)
-    v = torch.randn(B, C, nh, D, device="cuda")
-    beta = torch.rand(B, C, nh, device="cuda")
-    log_alpha = -0.05 * torch.rand(B, C, nh, device="cuda")
-    S0 = 0.1 * torch.randn(B, nh, D, D, device="cuda")
-    out = kernels.gdn_chunked(k, v, beta, log_alpha, S0)
-    want = ref.gdn_update_sequential(k, v, beta, torch.exp(log_alpha), S0)
-    assert _rel(out, want) < 1e-4
