@@ -294,31 +294,35 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
-    oom = False
-    try:
-        for s in range(W):
-            m = eng.train_step(host[s].to(dev, non_blocking=True), s)
-    except torch.OutOfMemoryError:
-        if world > 1 or not (extra.get("keep_prefix_layers") or extra.get("keep_suffix_chunks")):
-            raise
-        oom = True
-    if oom:
-        # a single GPU that cannot hold the resident graphs after all: start over with recompute regions
-        # (outside the handler, so that the failed step's frames and their tensors are gone)
-        import gc
+    def make_config():
+        return TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
+                           seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
+                           outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, shard_compute=args.shard_compute, **extra)
+
+    # Warm-up.  A single GPU that cannot hold the resident graphs it was asked (or planned) to keep starts over with half of
+    # them, down to none (recompute regions); each retry happens outside the handler, so that the failed step's frames and
+    # their tensors are gone.  Several ranks do not retry: they would have to agree on it.
+    import gc
+    while True:
+        oom = False
+        try:
+            for s in range(W):
+                m = eng.train_step(host[s].to(dev, non_blocking=True), s)
+        except torch.OutOfMemoryError:
+            kept = (eng.tc.keep_prefix_layers, eng.tc.keep_suffix_chunks)
+            if world > 1 or not any(kept):
+                raise
+            oom = True
+        if not oom:
+            break
         del eng
         m = None
         gc.collect()
         torch.cuda.empty_cache()
-        extra.update(keep_prefix_layers=0, keep_suffix_chunks=0)
-        note = "out of memory with resident graphs: recompute regions instead"
-        tc = TrainConfig(model_config=spec["model"], seq_len=T, batch_size=micro * mesh.batch_ranks, grad_accum=accum, steps=10_000,
-                         seed=0, lr=1e-3, end_lr=1e-4, warmup_steps=5000, inner_lr_warmup_steps=5000, inner_task="causal",
-                         outer_shift=True, second_order=True, fsdp_size=args.fsdp, tp_size=args.tp, shard_compute=args.shard_compute, **extra)
-        eng = Engine(mc, tc, mesh, dev)
+        extra.update(keep_prefix_layers=kept[0] // 2, keep_suffix_chunks=kept[1] // 2)
+        note = f"out of memory with {kept[0]} resident prefix layers and {kept[1]} chunk steps: {kept[0] // 2} and {kept[1] // 2} instead"
+        eng = Engine(mc, make_config(), mesh, dev)
         torch.cuda.reset_peak_memory_stats()
-        for s in range(W):
-            m = eng.train_step(host[s].to(dev, non_blocking=True), s)
     from dttt_b200.parallel import wgather
     launches0 = gemm.LAUNCHES + kernels.LAUNCHES + wgather.LAUNCHES
 
