@@ -36,12 +36,15 @@ CONFIGS = {
     # 180 GB; the reference recomputes per layer and per chunk on its 96 GB parts
     "8k": dict(model="configs/b200_1b_8k", seq_len=8192, mean_doc=2048, seqs_per_gpu=32, micro=2,
                extra=dict(keep_prefix_layers=12, keep_suffix_chunks=8)),
+    # 32k: one sequence per pass; four of a segment's eight chunk steps keep their graphs (126 GiB; all eight do not fit)
     "32k": dict(model="configs/b200_1b_32k", seq_len=32768, mean_doc=8192, seqs_per_gpu=4, micro=1,
-                extra=dict(segment_chunks=8, inner_norm_alpha=1.0, inner_norm_cap=128.0, inner_lr=0.82, self_prior=0.1)),
+                extra=dict(segment_chunks=8, inner_norm_alpha=1.0, inner_norm_cap=128.0, inner_lr=0.82, self_prior=0.1,
+                           keep_suffix_chunks=4)),
     "128k": dict(model="configs/b200_1b_128k", seq_len=131072, mean_doc=32768, seqs_per_gpu=1, micro=1,
                  extra=dict(segment_chunks=8, truncate_fast_weight=True, inner_norm_alpha=1.0, inner_norm_cap=128.0,
                             inner_lr=0.82, self_prior=0.1)),
-    "gdn": dict(model="configs/b200_1b_gdn", seq_len=32768, mean_doc=8192, seqs_per_gpu=4, micro=1, extra=dict(segment_chunks=8)),
+    "gdn": dict(model="configs/b200_1b_gdn", seq_len=32768, mean_doc=8192, seqs_per_gpu=4, micro=1,
+                extra=dict(segment_chunks=8, keep_prefix_layers=4, keep_suffix_chunks=8)),       # 136 GiB on one GPU
     "tiny": dict(model="configs/tiny_baseline", seq_len=512, mean_doc=200, seqs_per_gpu=2, micro=2, extra=dict(cart_window=64)),
 }
 
