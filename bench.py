@@ -106,7 +106,7 @@ def reference_arm(args) -> int:
     root = _reference_root()
     why = None
     if not os.path.isdir(os.path.join(root, "ttt")):
-        why = ("reference not installed: pip install of /root/reference needs the hatchling build backend, which is neither in "
+        why = ("reference not installed: pip install of the reference tree needs the hatchling build backend, which is neither in "
                "the image nor in the offline wheelhouse; baseline/_ref is empty")
     else:
         import importlib.util
