@@ -83,7 +83,11 @@ def resolve_keep(tc: TrainConfig, mc: ModelConfig, free_bytes: float, seqs_per_p
     regions = seqs_per_pass * (n_prefix * 3 * seq_len * mc.hidden_size * 2 + (seq_len // mc.chunk_size) * (carried["fast_weight"] + carried["kv"]))
     transients = 19e9 * tokens / 16384 * (mc.hidden_size / 2048)
     budget = free_bytes - regions - transients - 15e9
-    kept = lambda layers, chunks: seqs_per_pass * MM.kept_bytes(c, seq_len, layers, chunks, tc.segment_chunks)
+    # a chunk step of the method arm (normalised write, self-prior: `write_chunk`) records about twice the graph of the plain
+    # step the memory model describes (measured at 32k: 13.1 GiB per kept step and segment against 6.8)
+    step_factor = 1.0 if loss_config(tc).write.plain else 1.95
+    kept = lambda layers, chunks: seqs_per_pass * (MM.kept_bytes(c, seq_len, layers, 0, tc.segment_chunks)
+                                                   + step_factor * MM.kept_bytes(c, seq_len, 0, chunks, tc.segment_chunks))
     chunks = tc.keep_suffix_chunks
     if chunks < 0:
         chunks = max((k for k in range(per_segment + 1) if kept(0, k) <= budget), default=0)
