@@ -91,3 +91,11 @@ def test_keep_knobs_below_zero_are_filled_in_from_the_memory_model():
     fixed = resolve_keep(tc.replace(keep_suffix_chunks=3), mc, 154e9, 2)
     assert fixed.keep_suffix_chunks == 3 and fixed.keep_prefix_layers == 12
     assert resolve_keep(tc.replace(keep_prefix_layers=0, keep_suffix_chunks=0), mc, 0.0, 2).keep_prefix_layers == 0
+    # 32k, one sequence per pass, the method arm (normalised write + self-prior): a kept chunk step costs about twice the plain
+    # one, and the plan must stay inside what was measured to fit (four steps per segment: 126 GiB; eight: out of memory)
+    mc32 = ModelConfig.load(os.path.join(ROOT, "configs/b200_1b_32k"))
+    long_ = TrainConfig(model_config="configs/b200_1b_32k", seq_len=32768, batch_size=1, segment_chunks=8, keep_prefix_layers=-1,
+                        keep_suffix_chunks=-1, inner_task="causal", outer_shift=True)
+    plain = resolve_keep(long_, mc32, 160e9, 1)
+    method = resolve_keep(long_.replace(inner_norm_alpha=1.0, inner_norm_cap=128.0, self_prior=0.1), mc32, 160e9, 1)
+    assert plain.keep_suffix_chunks == 8 and 3 <= method.keep_suffix_chunks <= 6
