@@ -479,29 +479,44 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got) { ok = false; break; }
       tc_fence_after();
-      uint32_t sr[128];
-      tmem_ld_32x32(s_addr + 0, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-      tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
-      tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sr[64]));
-      tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sr[96]));
-      tmem_ld_wait();
       const int kbase = blk(j) * AK;
       const bool whole = (kbase + AK - 1 <= rm.e1) || (kbase >= rm.s2 && kbase + AK - 1 <= rm.e2);
-      if (!whole) {
-        // columns of this block the row sees: [0, hi1] (prefix interval) and [lo2, hi2] (second interval)
-        const int hi1 = rm.e1 - kbase, lo2 = rm.s2 - kbase, hi2 = rm.e2 - kbase;
+      // columns of this block the row sees: [0, hi1] (prefix interval) and [lo2, hi2] (second interval)
+      const int hi1 = rm.e1 - kbase, lo2 = rm.s2 - kbase, hi2 = rm.e2 - kbase;
+      // One pass over the block: its scores from TMEM, exponentials against the reference maximum `m_ref`, the block maximum
+      // tracked alongside (the two interleave; a separate maximum pass would sit in front of the first ex2), P packed.
+      float sum0, sum1, mx;
+      uint32_t pk[64];
+      auto exp_block = [&](float m_ref) {
+        uint32_t sr[128];
+        tmem_ld_32x32(s_addr + 0, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+        tmem_ld_32x32(s_addr + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+        tmem_ld_32x32(s_addr + 64, reinterpret_cast<uint32_t(&)[32]>(sr[64]));
+        tmem_ld_32x32(s_addr + 96, reinterpret_cast<uint32_t(&)[32]>(sr[96]));
+        tmem_ld_wait();
+        if (!whole) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i > hi1 && (i < lo2 || i > hi2)) sr[i] = __float_as_uint(MASKED);
-      }
-      float mx0 = __uint_as_float(sr[0]), mx1 = __uint_as_float(sr[1]), mx2 = __uint_as_float(sr[2]), mx3 = __uint_as_float(sr[3]);
+          for (int i = 0; i < 128; ++i)
+            if (i > hi1 && (i < lo2 || i > hi2)) sr[i] = __float_as_uint(MASKED);
+        }
+        const float mneg = -m_ref * sl2;
+        float mx0 = -3.4e38f, mx1 = -3.4e38f, s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[i]));     mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2])); mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
-      }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // raise the reference maximum only on a large jump (warp-uniform decision: the TMEM accesses are collective)
+        for (int i = 0; i < 128; i += 2) {
+          const float a0 = __uint_as_float(sr[i]), a1 = __uint_as_float(sr[i + 1]);
+          mx0 = fmaxf(mx0, a0); mx1 = fmaxf(mx1, a1);
+          const float p0 = ex2_approx(fmaf(a0, sl2, mneg));
+          const float p1 = ex2_approx(fmaf(a1, sl2, mneg));
+          s0 += p0; s1 += p1;
+          __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+          pk[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
+        }
+        sum0 = s0; sum1 = s1; mx = fmaxf(mx0, mx1);
+      };
+      exp_block(m);
+      // Only when the block raises the maximum by more than 2^8 in the exponent's units - rare after the first blocks - is the
+      // reference raised and the block done again from its scores, which are still in TMEM (P has not been stored yet).
+      // (warp-uniform decision: the TMEM accesses are collective)
       if (__any_sync(0xffffffffu, (mx - m) * sl2 > 8.f)) {
         const float m_new = fmaxf(m, mx);
         const float alpha = exp2f((m - m_new) * sl2);
@@ -518,17 +533,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
             tmem_st_32x32(o_addr + c, o);
           }
         }
-      }
-      const float mneg = -m * sl2;
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pk[64];
-#pragma unroll
-      for (int i = 0; i < 128; i += 2) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[i]), sl2, mneg));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[i + 1]), sl2, mneg));
-        sum0 += p0; sum1 += p1;
-        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-        pk[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
+        exp_block(m);
       }
       l += sum0 + sum1;
       tmem_st_32x32(s_addr + 0, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
