@@ -245,6 +245,44 @@ class Net:
             return hn, kv_own, (xs, ps)
         return hn, kv_own, None
 
+    def suffix_forward_streams(self, h: torch.Tensor, pos: torch.Tensor, pos_q: Optional[torch.Tensor],
+                               kv: Sequence[Tuple[torch.Tensor, torch.Tensor]], W, n_valid: int, owns: Sequence[str],
+                               return_prime: bool = False):
+        """Several streams of one chunk through the suffix in ONE pass: ``h [B, S, C, H]`` with stream ``CLEAN`` (index 1) the
+        clean one, ``pos / pos_q [B, S, C]`` (key and query positions per stream), the same window ``kv`` and the same fast
+        weights ``W`` for all of them, one own-chunk pattern per stream.  Equal to ``suffix_forward`` stream by stream (the
+        read and the clean pass of a chunk step use the same memory when no row takes the self-prior), but every projection
+        sees ``S`` times the rows, the fast-weight products ``S C`` rows per sequence, and on the GPU the attention of all
+        streams is one launch (``ops.attention.segment_attention`` over a one-chunk segment).  Returns ``(final_norm(h)
+        [B, S, C, H], kv_own of the clean stream per layer, (xs, p_outs) of the clean stream per fast layer or None)``.
+        Not for the GDN memory or the sub-block read."""
+        cfg = self.cfg
+        B, S, C, H = h.shape
+        Wn = cfg.window_chunks
+        kv_own, xs, ps = [], [], []
+        f = 0
+        for i in range(cfg.suffix_len):
+            q, k, v = self.qkv("suffix", i, self.norm("suffix.attn_norm.weight", i, h), pos, pos_q)      # [B, S, C, heads, d]
+            kw, vw = kv[i]
+            if kw.shape[1] == Wn * C and A.segment_attention_ok(q, C, Wn, owns):
+                # a one-chunk segment whose window holds `n_valid` chunks: first = n_valid makes exactly those visible
+                a, _, _ = A.segment_attention(q, k, v, (kw, vw) if Wn else None, C, Wn, n_valid, None, owns, self.scale)
+            else:
+                a = torch.stack([A.attend_window(q[:, s], k[:, s], v[:, s], kw, vw, n_valid, C, self.scale, own=owns[s])
+                                 for s in range(S)], dim=1)
+            h = h + Fn.linear(a.flatten(-2), self.p("suffix.attn.o.weight", i))
+            if cfg.fast_mask[i]:
+                x_p = self.norm("prime_norm.weight", f, h)
+                p_out = self.norm("prime_post_norm.weight", f, self.fast_mlp(W[f], x_p.flatten(1, 2)).unflatten(1, (S, C)))
+                h = h + p_out
+                if return_prime:
+                    xs.append(x_p[:, CLEAN]); ps.append(p_out[:, CLEAN])
+                f += 1
+            h = h + self.mlp("suffix", i, self.norm("suffix.mlp_norm.weight", i, h))
+            kv_own.append((k[:, CLEAN], v[:, CLEAN]))
+        hn = self.norm("final_norm.weight", None, h)
+        return hn, kv_own, ((xs, ps) if return_prime else None)
+
     # ---- whole sequence with a FIXED memory (tests, evaluation tools; reference Model.hidden)
     def hidden(self, ids: torch.Tensor, pos: Optional[torch.Tensor] = None, W=None) -> torch.Tensor:
         """Final-normed hidden states ``[B, T, H]`` for clean ``ids [B, T]`` with the KV window applied and a fixed

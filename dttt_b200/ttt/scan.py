@@ -37,6 +37,7 @@ from .regions import region
 # sequence (0.9 GB per chunk and sequence at 1B) still fit beside the working set and the extra forward pass (about 15 % of a
 # step) is not worth paying; from 64 chunks (128k tokens of 1024-token chunks in segments of 8) they no longer do.
 NEST_SEGMENTS_FROM = 8
+STREAMS_TOGETHER = True      # the read and the clean pass of a chunk step in one pass through the suffix where they share the memory
 
 
 class Batch(NamedTuple):
@@ -436,9 +437,28 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
                 soft_mask = (masked_t & (first > 0) & (ok_a & ok_b)[None]).float()
         extras = IN.InnerExtras(soft_ids, soft_q, soft_mask, k["mtp_t"], k["mtp_m"])
 
-    # B. clean -> next KV window; with memory gdn also the state written from this chunk
-    with prof.range("step.B_clean"):
-        resB = sf(hc, mem if use_gdn else Wc, update=use_gdn, prime=clean_prime, own=clean_own)
+    # B. clean -> next KV window; with memory gdn also the state written from this chunk.  When the read (A) uses the very
+    # memory the clean pass uses (no self-prior rows, no sub-block read, no GDN state), A, its extra views and B go through
+    # the suffix together (Net.suffix_forward_streams): the same arithmetic on two or more times the rows per launch.
+    together = (STREAMS_TOGETHER and not use_gdn and sp_flags is None and not rb and read_own is None and Wc is not None
+                and net.tp_size == 1)
+    hA = None
+    hV_together = []
+    if together:
+        with prof.range("step.AB_together"):
+            hs = torch.stack([ho, hc] + list(hv), dim=1)                                  # OUTER = 0, CLEAN = 1, extra outer views
+            n_s = hs.shape[1]
+            pos_s = p[:, None].expand(B, n_s, C)
+            pq = p if p_q_outer is None else p_q_outer
+            pos_q_s = torch.stack([pq, p] + [pq] * len(hv), dim=1)
+            owns_s = ["full", clean_own] + ["full"] * len(hv)
+            hn_s, own_kv_s, extra_s = net.suffix_forward_streams(hs, pos_s, pos_q_s, kv, Wc, nv, owns_s, return_prime=clean_prime)
+        hA = hn_s[:, 0]
+        hV_together = [hn_s[:, 2 + i] for i in range(len(hv))]
+        resB = (hn_s[:, 1], own_kv_s, extra_s)
+    else:
+        with prof.range("step.B_clean"):
+            resB = sf(hc, mem if use_gdn else Wc, update=use_gdn, prime=clean_prime, own=clean_own)
     own_kv = resB[1]
     kv_next = [(torch.cat([ck[:, C:], ok], dim=1), torch.cat([cv[:, C:], ov], dim=1)) if ck.shape[1] else (ck, cv)
                for (ck, cv), (ok, ov) in zip(kv, own_kv)]
@@ -515,8 +535,9 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
         sel = [tuple(torch.where(sp_flags.view(B, 1, 1), b_, a_) for a_, b_ in zip(wa, wb)) for wa, wb in zip(W, W_next)]
         W_read = IN.cast_fast(sel, net.dtype)
     read_kv = own_kv if rb else None
-    with prof.range("step.A_read"):
-        hA = sf(ho, W_read, p_q_outer, own="full", own_mask=read_own, own_kv=read_kv)[0]
+    if hA is None:
+        with prof.range("step.A_read"):
+            hA = sf(ho, W_read, p_q_outer, own="full", own_mask=read_own, own_kv=read_kv)[0]
     tok, wgt, tm = k["tok"], k["wgt"], k["tm"]
     ce_seq = mask_seq = torch.zeros(B, device=dev)
     if cfg.per_sequence:
@@ -533,7 +554,7 @@ def _suffix_step(net: Net, cfg: LossConfig, kv, memv, ho, hc, hi, ht, hv, k, W0,
         mask2 = k["tm2"].float().sum()
     mask_count = tm.float().sum()
     for i, hvi in enumerate(hv):
-        hV = sf(hvi, W_read, p_q_outer)[0]
+        hV = hV_together[i] if hV_together else sf(hvi, W_read, p_q_outer)[0]
         ce_sum = ce_sum + CE.weighted_ce(hV.reshape(B * C, -1), lm_w, tok.reshape(-1), k["wv"][i].reshape(-1).float(), fb)
         mask_count = mask_count + k["tmv"][i].float().sum()
     if cfg.per_token:
