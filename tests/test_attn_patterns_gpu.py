@@ -78,6 +78,10 @@ def _segment_reference(q, k, v, kp, vp, C, W, first, reach, patterns, scale):
     (2, 2, 5, 128, 3, 2, 2, True, ("full", "full")),
     (1, 4, 2, 128, 4, 0, None, False, ("full", "block:64", "split:32", "causal")),
     (1, 3, 8, 128, 8, 8, None, True, ("full", "full", "causal")),
+    # the suffix's use: the read and the clean pass of ONE chunk, `first` = number of valid window chunks
+    (2, 2, 1, 128, 2, 1, None, True, ("full", "full")),
+    (2, 2, 1, 256, 2, 0, None, True, ("full", "full")),
+    (1, 3, 1, 128, 4, 4, None, True, ("full", "full", "full")),
 ])
 @pytest.mark.parametrize("d", [64, 128])
 def test_segment_form_matches_chunk_by_chunk(B, S, chunks, C, W, first, reach, with_prev, patterns, d):
