@@ -195,11 +195,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               for (int j = 0; j < 32; j += 4) {
                 float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
                                        __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                if (p.accumulate) {
-                  const float4 o = *reinterpret_cast<float4*>(out + j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(out + j) = v;
+                if (p.accumulate) red_add_f32x4(out + j, v);       // C += tile as a vector reduction at L2 (no load to wait for)
+                else *reinterpret_cast<float4*>(out + j) = v;
               }
             } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {

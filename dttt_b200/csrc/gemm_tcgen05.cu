@@ -523,11 +523,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
               for (int j = 0; j < 32; j += 4) {
                 float4 v = make_float4(xform(__uint_as_float(r[j]), col + j), xform(__uint_as_float(r[j + 1]), col + j + 1),
                                        xform(__uint_as_float(r[j + 2]), col + j + 2), xform(__uint_as_float(r[j + 3]), col + j + 3));
-                if (p.accumulate) {
-                  float4 o = *reinterpret_cast<float4*>(out + j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(out + j) = v;
+                // C += tile: a vector reduction performed at L2 instead of load - add - store (nothing waits for a load; each
+                // element is touched by one thread of one tile in a launch, so the result is the same sum)
+                if (p.accumulate) red_add_f32x4(out + j, v);
+                else *reinterpret_cast<float4*>(out + j) = v;
               }
             } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {
@@ -751,11 +750,8 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               for (int j = 0; j < 32; j += 4) {
                 float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
                                        __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                if (p.accumulate) {
-                  const float4 o = *reinterpret_cast<float4*>(out + j);
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *reinterpret_cast<float4*>(out + j) = v;
+                if (p.accumulate) red_add_f32x4(out + j, v);       // see the 128-row kernel's epilogue
+                else *reinterpret_cast<float4*>(out + j) = v;
               }
             } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {

@@ -36,6 +36,7 @@ PAIR = os.environ.get("DTTT_GEMM_PAIR", "1") == "1"
 SHAPE_LOG = None        # a dict while a profile wants the launches counted by problem shape (tools/step_profile.py)
 PAIR_MIN = 256
 PAIR_MIN_N = 1024
+PAIR_ACCUMULATE = os.environ.get("DTTT_GEMM_PAIR_ACC", "0") == "1"     # CTA pairs also for C += products (weight gradients)
 PAIR_MIN_TILES = 100    # below about 100 pair tiles (74 pairs of SMs) one CTA per 128-wide tile fills the machine better
 _lib.register("dttt_gemm_pair_bf16", ctypes.c_int, [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4 + [ctypes.c_longlong] * 6 + [ctypes.c_int] * 4
               + [ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p])
@@ -114,7 +115,7 @@ def gemm_raw(a: torch.Tensor, b: torch.Tensor, ta: bool, tb: bool, out_dtype: to
     if SHAPE_LOG is not None:
         key = (M, N, K, batch, int(ta), int(tb), int(accumulate))
         SHAPE_LOG[key] = SHAPE_LOG.get(key, 0) + 1
-    if (PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN_N and not accumulate
+    if (PAIR and max_ctas == 0 and M >= PAIR_MIN and N >= PAIR_MIN_N and (PAIR_ACCUMULATE or not accumulate)
             and -(-M // 256) * -(-N // 256) * batch >= PAIR_MIN_TILES):
         # CTA pairs (csrc/gemm_pair_tcgen05.cu): each CTA of a cluster loads half of B, one instruction covers 256 x 256
         rc = _lib.lib().dttt_gemm_pair_bf16(
