@@ -514,6 +514,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col = n0 + c;
+        if constexpr (MODE == EPI_STORE) {
+          // C += tile with whole 128-byte lines per reduction: the warp's 32 x 32 f32 piece goes through its staging area
+          // (16-byte pieces XOR-swizzled by row) so that eight lanes cover one row's 128 bytes and an instruction four
+          // rows, instead of 32 lanes adding 16 bytes to 32 different rows.  (Warp-uniform condition.)
+          if (p.c_is_f32 && p.accumulate && n0 + c + 32 <= p.N && (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 4)) & 15) == 0) {
+            uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<float4*>(stg + lane * 128 + ((q ^ (lane & 7)) * 16)) =
+                  make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
+                              __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
+            __syncwarp();
+            const int piece = lane & 7;
+            const int row0 = tm * BM + quarter * 32;
+            float* tile_out = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch + col + piece * 4;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = i * 4 + (lane >> 3);
+              const float4 v = *reinterpret_cast<const float4*>(stg + rr * 128 + ((piece ^ (rr & 7)) * 16));
+              if (row0 + rr < p.M) red_add_f32x4(tile_out + (long long)(row0 + rr) * p.ldc, v);
+            }
+            __syncwarp();
+            continue;
+          }
+        }
         if (row_ok && col < p.N) {
           const bool full_chunk = (col + 32 <= p.N);
           if (p.c_is_f32) {
@@ -893,13 +918,14 @@ template <int BN, int MODE>
 static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, int max_ctas, cudaStream_t stream) {
   once_per_device((BN == 256 ? 0 : 8) + MODE, [] {
     cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL);
+                         (MODE == EPI_RS || MODE == EPI_STORE) ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL);
   });
   const int sms = num_sms();
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   int grid = (int)(tiles < cap ? tiles : cap);
-  gemm_bf16_kernel<BN, MODE><<<grid, (MODE == EPI_AG || MODE == EPI_WG) ? 320 : 192, MODE == EPI_RS ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+  gemm_bf16_kernel<BN, MODE><<<grid, (MODE == EPI_AG || MODE == EPI_WG) ? 320 : 192,
+                               (MODE == EPI_RS || MODE == EPI_STORE) ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -63,6 +63,25 @@ def test_gemm_f32_accumulate_and_views():
     assert _rel(out, 1.0 + 0.5 * (a.float() @ b.float())) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,batch", [(1000, 520, 264, 1), (136, 96, 72, 1), (4096, 2048, 512, 1), (304, 264, 136, 3)])
+@pytest.mark.parametrize("ta", [False, True])
+def test_gemm_f32_accumulate_ragged_edges(M, N, K, batch, ta):
+    """C += A B into f32 (the weight-gradient form: whole-line reductions staged through shared memory) with rows, columns and
+    contraction lengths that are not multiples of the tile, twice into the same buffer, batched too."""
+    from dttt_b200.ops import _lib, gemm
+    torch.manual_seed(M + N)
+    lead = (batch,) if batch > 1 else ()
+    a = torch.randn(*lead, *((K, M) if ta else (M, K)), device="cuda").to(torch.bfloat16)
+    b = torch.randn(*lead, K, N, device="cuda").to(torch.bfloat16)
+    out = torch.full((*lead, M, N), 0.25, device="cuda")
+    for _ in range(2):
+        gemm.gemm_raw(a, b, ta, False, torch.float32, out=out, accumulate=True)
+    torch.cuda.synchronize()
+    _lib.check_status()
+    want = 0.25 + 2.0 * ((a.transpose(-1, -2) if ta else a).float() @ b.float())
+    assert _rel(out, want) < 1e-5
+
+
 def test_mm_autograd_double_backward():
     from dttt_b200.ops import gemm
     torch.manual_seed(2)
