@@ -158,11 +158,66 @@ def _torch_mm(a, b, ta, tb, out_dtype):
     return r if out_dtype is None or r.dtype == out_dtype else r.to(out_dtype)
 
 
+# Fast-weight gradients summed in f32 by the GEMM epilogue (False: every contribution is a bf16 tensor that autograd adds up).
+CAST_ACC = os.environ.get("DTTT_CAST_ACC", "1") == "1"
+
+
+class _CastAcc(torch.autograd.Function):
+    """The bf16 compute copy of an f32 per-sequence weight.  The copy carries ``grad_acc``, a one-slot holder: in a backward
+    that is not being recorded every product that owes the copy a gradient adds it into one f32 buffer through the GEMM's
+    accumulating epilogue (``_MM.backward``) and hands autograd nothing; this node's backward, which runs once all of them
+    have reported, returns the buffer.  It replaces one bf16 tensor per contribution, the additions between them and the
+    cast back to f32 (the meta-gradient reaches a chunk's fast weights through the read, the clean stream and the write:
+    reference src/ttt/chunk_scan.py:604-625)."""
+
+    @staticmethod
+    def forward(ctx, w, holder, lo):
+        ctx.set_materialize_grads(False)
+        ctx.holder = holder
+        return w.to(torch.bfloat16) if lo is None else lo.view_as(lo)
+
+    @staticmethod
+    def backward(ctx, g):
+        acc, ctx.holder[0] = ctx.holder[0], None
+        if acc is None:
+            return (None if g is None else g.to(torch.float32)), None, None
+        if g is not None:
+            acc = acc + g if torch.is_grad_enabled() else acc.add_(g)
+        return acc, None, None
+
+
+def cast_acc(w: torch.Tensor, lo: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``w.to(bfloat16)`` for an f32 ``[B, in, out]`` weight that wants its gradient summed in f32 (see ``_CastAcc``);
+    ``lo``: that copy if the kernel that produced ``w`` already wrote it."""
+    holder = [None]
+    c = _CastAcc.apply(w, holder, None if lo is None else lo.detach())
+    c.grad_acc = holder
+    return c
+
+
+def _acc_into(holder, shape, a, b, ta, tb) -> bool:
+    """Add ``op(a) @ op(b)`` to the f32 buffer of ``holder`` (created by the first product); False if this backward has to
+    return an ordinary gradient instead (it is being recorded, or it is the inner step's own gradient)."""
+    from .functional import _INNER_BACKWARD
+    if holder is None or torch.is_grad_enabled() or _INNER_BACKWARD[0] or not (_kernel_ok(a) and _kernel_ok(b)):
+        return False
+    M = a.shape[-1] if ta else a.shape[-2]
+    N = b.shape[-2] if tb else b.shape[-1]
+    if a.dim() != len(shape) or b.dim() != len(shape) or (a.shape[0], M, N) != tuple(shape):
+        return False
+    if holder[0] is None:
+        holder[0] = gemm_raw(a, b, ta, tb, torch.float32)
+    else:
+        gemm_raw(a, b, ta, tb, torch.float32, out=holder[0], accumulate=True)
+    return True
+
+
 class _MM(torch.autograd.Function):
     @staticmethod
     def forward(ctx, a, b, ta, tb, out_dtype):
         ctx.save_for_backward(a, b)
         ctx.ta, ctx.tb = ta, tb
+        ctx.acc_a, ctx.acc_b = getattr(a, "grad_acc", None), getattr(b, "grad_acc", None)
         return gemm_raw(a, b, ta, tb, out_dtype)
 
     @staticmethod
@@ -173,13 +228,17 @@ class _MM(torch.autograd.Function):
         ga = gb = None
         # y = op(a) op(b);  d op(a) = g op(b)^T,  d op(b) = op(a)^T g
         if ctx.needs_input_grad[0]:
-            ga = mm(b, g, tb, True) if ta else mm(g, b, False, not tb)
-            if ga.dim() > a.dim():
-                ga = ga.sum(0)
+            args = (b, g, tb, True) if ta else (g, b, False, not tb)
+            if not _acc_into(ctx.acc_a, a.shape, *args):
+                ga = mm(*args)
+                if ga.dim() > a.dim():
+                    ga = ga.sum(0)
         if ctx.needs_input_grad[1]:
-            gb = mm(g, a, True, ta) if tb else mm(a, g, not ta, False)
-            if gb.dim() > b.dim():
-                gb = gb.sum(0)
+            args = (g, a, True, ta) if tb else (a, g, not ta, False)
+            if not _acc_into(ctx.acc_b, b.shape, *args):
+                gb = mm(*args)
+                if gb.dim() > b.dim():
+                    gb = gb.sum(0)
         return ga, gb, None, None, None
 
 

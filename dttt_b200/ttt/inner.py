@@ -101,7 +101,22 @@ def inner_lr(step: int, lr: float, warmup_steps: int) -> float:
 
 
 def cast_fast(W: FastW, dtype: torch.dtype) -> FastW:
-    return [tuple(t if t.dtype == dtype else t.to(dtype) for t in w) for w in W]
+    """The compute-dtype copies of the fast weights.  f32 -> bf16 copies whose gradient will be wanted go through
+    ``ops.gemm.cast_acc``: the products that use them then sum their gradient contributions in one f32 buffer."""
+    from ..ops import gemm
+
+    def one(t):
+        if t.dtype == dtype:
+            return t
+        lo = getattr(t, "lo_copy", None)               # written by the step kernel that produced t (one use only)
+        if lo is not None:
+            t.lo_copy = None
+            lo = lo if dtype == torch.bfloat16 and lo.shape == t.shape else None
+        if (gemm.CAST_ACC and dtype == torch.bfloat16 and t.dtype == torch.float32 and t.dim() == 3 and t.requires_grad
+                and torch.is_grad_enabled() and (t.is_cuda or gemm.EMULATE) and not gemm._FORCE_TORCH):
+            return gemm.cast_acc(t, lo)
+        return t.to(dtype) if lo is None or (t.requires_grad and torch.is_grad_enabled()) else lo
+    return [tuple(one(t) for t in w) for w in W]
 
 
 def flat(W: FastW) -> List[torch.Tensor]:
@@ -388,6 +403,8 @@ GRAD_VIA_CAST = [True]
 # The plain step as one autograd node with fused kernels (False: the chain of differentiable torch ops; "force": also
 # for CPU tensors, where the node's pieces are torch statements -- used by the tests).
 FUSED_PLAIN_STEP = [True]
+# The fused step also writes the bf16 copy of the new weights (False: the next chunk casts them in a pass of its own).
+LO_COPY = [True]
 
 
 def _seq_ops(t: torch.Tensor):
@@ -416,14 +433,22 @@ class _PlainStep(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, clip, eta, n, *Wg):
+        from ..ops import kernels
         W, g = Wg[:n], Wg[n:]
         sumsq, axpy, _, _ = _seq_ops(W[0])
         norm = torch.sqrt(sumsq(list(g)) + 1e-8)
         s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
-        new = [axpy(W[i], g[i], s * eta[i // 3]) for i in range(n)]
+        los = []
+        if axpy is kernels.seq_axpy and LO_COPY[0] and all(w.dtype == torch.float32 for w in W):
+            # the kernel writes the bf16 copy of W' in the same pass: the next chunk's cast has nothing left to do
+            pairs = [axpy(W[i], g[i], s * eta[i // 3], want_lo=True) for i in range(n)]
+            new, los = [p_[0] for p_ in pairs], [p_[1] for p_ in pairs]
+            ctx.mark_non_differentiable(*los)
+        else:
+            new = [axpy(W[i], g[i], s * eta[i // 3]) for i in range(n)]
         ctx.save_for_backward(eta, norm, s, *g)
         ctx.clip, ctx.n = clip, n
-        return (*new, norm)
+        return (*new, norm, *los)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -461,7 +486,10 @@ def inner_apply(W: FastW, g: List[torch.Tensor], model, lr: float, clip: float, 
             eta = eta * torch.exp(net.p("inner_step_log").float())
         if FUSED_PLAIN_STEP[0] and (Wl[0].is_cuda or FUSED_PLAIN_STEP[0] == "force"):
             out = _PlainStep.apply(float(clip), eta, len(Wl), *Wl, *g)           # the kernels read bf16 or f32 gradients
-            return unflat(list(out[:-1])), out[-1]
+            n = len(Wl)
+            for t, lo in zip(out[:n], out[n + 1:]):
+                t.lo_copy = lo
+            return unflat(list(out[:n])), out[n]
         g = [x.float() for x in g]
         norm = seq_norm(g)
         s = torch.clamp(clip / norm, max=1.0) if clip > 0 else torch.ones_like(norm)
