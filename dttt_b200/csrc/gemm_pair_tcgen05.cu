@@ -17,6 +17,7 @@
 #include "ptx_sm100.cuh"
 #include "host_check.h"
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -31,13 +32,15 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_BYTES = (BN / 2) * BK * 2;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;                 // 32 KB per CTA
-constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+constexpr int STAGING_BYTES = 4 * 4096;                        // epilogue: 32 rows x 128 bytes per warp (whole-line stores)
+constexpr int SMEM_TOTAL = STAGES * STAGE_BYTES + 1024 + STAGING_BYTES + 1024;
 
 struct Params {
   int M, N, K, batch;
   int a_mn_major, b_mn_major;
   long long ldc, c_batch;
   int c_is_f32, accumulate;
+  int per_lane_stores;         // 1: 16 bytes per lane and row instead of whole lines (DTTT_GEMM_LINES=0; for comparisons)
   float alpha;
   void* C;
   int* status;
@@ -180,8 +183,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.M;
       const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+      // bf16 stores as whole 128-byte lines (warp-uniform condition; ragged column edges take the per-lane path below)
+      const bool lines = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      uint8_t* stg = bar_base + 1024 + quarter * 4096;
+      const int row0 = tm * 2 * BM + (int)rank * BM + quarter * 32;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
+        if (lines && (c & 32) == 0 && n0 + c + 64 <= p.N) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_32x32(taddr + c + 32, r1);
+          tmem_ld_wait();
+          stage_put_bf16x32(stg, lane, 0, r0, p.alpha);
+          stage_put_bf16x32(stg, lane, 1, r1, p.alpha);
+          __syncwarp();
+          stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch + (long long)row0 * p.ldc + n0 + c,
+                              p.ldc, p.M - row0);
+          __syncwarp();
+          c += 32;
+          continue;
+        }
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
@@ -311,6 +333,7 @@ extern "C" int dttt_gemm_pair_bf16(const void* A, const void* B, void* C, int M,
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K; p.batch = batch; p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.ldc = ldc; p.c_batch = c_batch; p.c_is_f32 = c_is_f32; p.accumulate = accumulate; p.alpha = alpha; p.C = C; p.status = status;
+  { static const int per_lane = (getenv("DTTT_GEMM_LINES") && atoi(getenv("DTTT_GEMM_LINES")) == 0) ? 1 : 0; p.per_lane_stores = per_lane; }
   p.tiles_m = (M + 2 * BM - 1) / (2 * BM);
   p.tiles_n = (N + BN - 1) / BN;
   static std::mutex mu;

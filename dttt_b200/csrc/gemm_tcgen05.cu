@@ -40,6 +40,7 @@ struct GemmParams {
   long long ldc;        // elements
   long long c_batch;    // elements
   int c_is_f32;
+  int per_lane_stores;  // 1: the bf16 store epilogue writes 16 bytes per lane and row (DTTT_GEMM_LINES=0; for comparisons)
   int accumulate;       // C += result
   float alpha;
   void* C;
@@ -508,8 +509,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if constexpr (MODE == EPI_CE_DLOGITS) return coef * (__expf(acc_v - lse) - (colj == y ? 1.f : 0.f));
         else return acc_v * p.alpha;
       };
+      // bf16 stores as whole 128-byte lines (warp-uniform condition; ragged column edges take the per-lane path below)
+      bool lines = false;
+      if constexpr (MODE == EPI_STORE)
+        lines = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
+                ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
+        if constexpr (MODE == EPI_STORE) {
+          if (lines && (c & 32) == 0 && n0 + c + 64 <= p.N) {
+            uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
+            const int row0 = tm * BM + quarter * 32;
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(taddr + c, r0);
+            tmem_ld_32x32(taddr + c + 32, r1);
+            tmem_ld_wait();
+            stage_put_bf16x32(stg, lane, 0, r0, p.alpha);
+            stage_put_bf16x32(stg, lane, 1, r1, p.alpha);
+            __syncwarp();
+            stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch + (long long)row0 * p.ldc + n0 + c,
+                                p.ldc, p.M - row0);
+            __syncwarp();
+            c += 32;
+            continue;
+          }
+        }
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
@@ -1034,6 +1058,7 @@ extern "C" int dttt_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.a_mn_major = a_mn_major; p.b_mn_major = b_mn_major;
   p.ldc = ldc; p.c_batch = c_batch; p.c_is_f32 = c_is_f32; p.accumulate = accumulate; p.alpha = alpha;
+  { static const int per_lane = (getenv("DTTT_GEMM_LINES") && atoi(getenv("DTTT_GEMM_LINES")) == 0) ? 1 : 0; p.per_lane_stores = per_lane; }
   p.C = C; p.status = status;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + bn - 1) / bn;

@@ -14,6 +14,8 @@ per-sequence gradients and one backward pass serves the whole batch.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import List, NamedTuple, Optional, Sequence, Tuple
 
@@ -404,7 +406,7 @@ GRAD_VIA_CAST = [True]
 # for CPU tensors, where the node's pieces are torch statements -- used by the tests).
 FUSED_PLAIN_STEP = [True]
 # The fused step also writes the bf16 copy of the new weights (False: the next chunk casts them in a pass of its own).
-LO_COPY = [True]
+LO_COPY = [os.environ.get("DTTT_LO_COPY", "1") == "1"]
 
 
 def _seq_ops(t: torch.Tensor):
