@@ -183,25 +183,40 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.M;
       const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
-      // bf16 stores as whole 128-byte lines (warp-uniform condition; ragged column edges take the per-lane path below)
-      const bool lines = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
-                         ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      // stores and reductions as whole 128-byte lines (warp-uniform conditions; ragged column edges, odd strides and bf16
+      // accumulation take the per-lane path below)
+      const bool lines16 = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      const bool lines32 = !p.per_lane_stores && p.c_is_f32 && (p.ldc & 3) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 4)) & 15) == 0;
       uint8_t* stg = bar_base + 1024 + quarter * 4096;
       const int row0 = tm * 2 * BM + (int)rank * BM + quarter * 32;
+      const long long tile_off = (long long)b * p.c_batch + (long long)row0 * p.ldc + n0;
+      const float alpha = p.alpha;
+      auto scale = [alpha](float v, int) { return v * alpha; };
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
-        if (lines && (c & 32) == 0 && n0 + c + 64 <= p.N) {
+        if (lines16 && (c & 32) == 0 && n0 + c + 64 <= p.N) {
           uint32_t r0[32], r1[32];
           tmem_ld_32x32(taddr + c, r0);
           tmem_ld_32x32(taddr + c + 32, r1);
           tmem_ld_wait();
-          stage_put_bf16x32(stg, lane, 0, r0, p.alpha);
-          stage_put_bf16x32(stg, lane, 1, r1, p.alpha);
+          stage_put_bf16x32(stg, lane, 0, r0, scale);
+          stage_put_bf16x32(stg, lane, 1, r1, scale);
           __syncwarp();
-          stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch + (long long)row0 * p.ldc + n0 + c,
-                              p.ldc, p.M - row0);
+          stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + tile_off + c, p.ldc, p.M - row0);
           __syncwarp();
           c += 32;
+          continue;
+        }
+        if (lines32 && n0 + c + 32 <= p.N) {
+          uint32_t r0[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_wait();
+          stage_put_f32x32(stg, lane, r0, scale);
+          __syncwarp();
+          stage_flush_f32x32(stg, lane, reinterpret_cast<float*>(p.C) + tile_off + c, p.ldc, p.M - row0, p.accumulate != 0);
+          __syncwarp();
           continue;
         }
         uint32_t r[32];

@@ -509,60 +509,47 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         if constexpr (MODE == EPI_CE_DLOGITS) return coef * (__expf(acc_v - lse) - (colj == y ? 1.f : 0.f));
         else return acc_v * p.alpha;
       };
-      // bf16 stores as whole 128-byte lines (warp-uniform condition; ragged column edges take the per-lane path below)
-      bool lines = false;
-      if constexpr (MODE == EPI_STORE)
-        lines = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
-                ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      // stores and reductions as whole 128-byte lines (warp-uniform conditions; ragged column edges, odd strides and bf16
+      // accumulation take the per-lane path below): the warp's piece goes through its staging area so that eight lanes
+      // cover one row's 128 bytes and an instruction four rows, instead of 32 lanes touching 16 bytes of 32 rows
+      const bool lines16 = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      const bool lines32 = !p.per_lane_stores && p.c_is_f32 && (p.ldc & 3) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 4)) & 15) == 0;
+      uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
+      const int row0 = tm * BM + quarter * 32;
+      const long long tile_off = (long long)b * p.c_batch + (long long)row0 * p.ldc + n0;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
-        if constexpr (MODE == EPI_STORE) {
-          if (lines && (c & 32) == 0 && n0 + c + 64 <= p.N) {
-            uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
-            const int row0 = tm * BM + quarter * 32;
-            uint32_t r0[32], r1[32];
-            tmem_ld_32x32(taddr + c, r0);
-            tmem_ld_32x32(taddr + c + 32, r1);
-            tmem_ld_wait();
-            stage_put_bf16x32(stg, lane, 0, r0, p.alpha);
-            stage_put_bf16x32(stg, lane, 1, r1, p.alpha);
-            __syncwarp();
-            stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)b * p.c_batch + (long long)row0 * p.ldc + n0 + c,
-                                p.ldc, p.M - row0);
-            __syncwarp();
-            c += 32;
-            continue;
-          }
+        if (lines16 && (c & 32) == 0 && n0 + c + 64 <= p.N) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_32x32(taddr + c + 32, r1);
+          tmem_ld_wait();
+          const int col0 = n0 + c;
+          stage_put_bf16x32(stg, lane, 0, r0, [&](float v, int j) { return xform(v, col0 + j); });
+          stage_put_bf16x32(stg, lane, 1, r1, [&](float v, int j) { return xform(v, col0 + 32 + j); });
+          __syncwarp();
+          stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + tile_off + c, p.ldc, p.M - row0);
+          __syncwarp();
+          c += 32;
+          continue;
+        }
+        if (lines32 && n0 + c + 32 <= p.N) {
+          uint32_t r0[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_wait();
+          const int col0 = n0 + c;
+          stage_put_f32x32(stg, lane, r0, [&](float v, int j) { return xform(v, col0 + j); });
+          __syncwarp();
+          stage_flush_f32x32(stg, lane, reinterpret_cast<float*>(p.C) + tile_off + c, p.ldc, p.M - row0, p.accumulate != 0);
+          __syncwarp();
+          continue;
         }
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
         const int col = n0 + c;
-        if constexpr (MODE == EPI_STORE) {
-          // C += tile with whole 128-byte lines per reduction: the warp's 32 x 32 f32 piece goes through its staging area
-          // (16-byte pieces XOR-swizzled by row) so that eight lanes cover one row's 128 bytes and an instruction four
-          // rows, instead of 32 lanes adding 16 bytes to 32 different rows.  (Warp-uniform condition.)
-          if (p.c_is_f32 && p.accumulate && n0 + c + 32 <= p.N && (p.ldc & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 4)) & 15) == 0) {
-            uint8_t* stg = bar_base + L::BAR_BYTES + quarter * (32 * 256);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-              *reinterpret_cast<float4*>(stg + lane * 128 + ((q ^ (lane & 7)) * 16)) =
-                  make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
-                              __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
-            __syncwarp();
-            const int piece = lane & 7;
-            const int row0 = tm * BM + quarter * 32;
-            float* tile_out = reinterpret_cast<float*>(p.C) + (long long)b * p.c_batch + col + piece * 4;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = i * 4 + (lane >> 3);
-              const float4 v = *reinterpret_cast<const float4*>(stg + rr * 128 + ((piece ^ (rr & 7)) * 16));
-              if (row0 + rr < p.M) red_add_f32x4(tile_out + (long long)(row0 + rr) * p.ldc, v);
-            }
-            __syncwarp();
-            continue;
-          }
-        }
         if (row_ok && col < p.N) {
           const bool full_chunk = (col + 32 <= p.N);
           if (p.c_is_f32) {
@@ -657,7 +644,7 @@ struct Smem256 {
   static constexpr int B_BYTES = 256 * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = 3;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 1024;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 8 * 4096 + 1024;   // stages, barriers, epilogue staging (8 warps), slack
 };
 
 __global__ void __launch_bounds__(320, 1)
@@ -784,8 +771,41 @@ gemm256_bf16_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       const uint32_t taddr = tmem_base + half * BN + ((uint32_t)(quarter * 32) << 16);
       const bool row_ok = row < p.M;
       const long long row_off = (long long)b * p.c_batch + (long long)row * p.ldc;
+      // whole-line stores and reductions through a staging area, as in the 128-row kernel's epilogue
+      const bool lines16 = !p.per_lane_stores && !p.c_is_f32 && !p.accumulate && (p.ldc & 7) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 2)) & 15) == 0;
+      const bool lines32 = !p.per_lane_stores && p.c_is_f32 && (p.ldc & 3) == 0 &&
+                           ((reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)(p.c_batch * 4)) & 15) == 0;
+      uint8_t* stg = bar_base + 1024 + (warp - 2) * 4096;
+      const int row0 = tm * 2 * BM + half * BM + quarter * 32;
+      const long long tile_off = (long long)b * p.c_batch + (long long)row0 * p.ldc + n0;
+      const float alpha = p.alpha;
+      auto scale = [alpha](float v, int) { return v * alpha; };
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
+        if (lines16 && (c & 32) == 0 && n0 + c + 64 <= p.N) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_32x32(taddr + c + 32, r1);
+          tmem_ld_wait();
+          stage_put_bf16x32(stg, lane, 0, r0, scale);
+          stage_put_bf16x32(stg, lane, 1, r1, scale);
+          __syncwarp();
+          stage_flush_bf16x64(stg, lane, reinterpret_cast<__nv_bfloat16*>(p.C) + tile_off + c, p.ldc, p.M - row0);
+          __syncwarp();
+          c += 32;
+          continue;
+        }
+        if (lines32 && n0 + c + 32 <= p.N) {
+          uint32_t r0[32];
+          tmem_ld_32x32(taddr + c, r0);
+          tmem_ld_wait();
+          stage_put_f32x32(stg, lane, r0, scale);
+          __syncwarp();
+          stage_flush_f32x32(stg, lane, reinterpret_cast<float*>(p.C) + tile_off + c, p.ldc, p.M - row0, p.accumulate != 0);
+          __syncwarp();
+          continue;
+        }
         uint32_t r[32];
         tmem_ld_32x32(taddr + c, r);
         tmem_ld_wait();
@@ -942,14 +962,14 @@ template <int BN, int MODE>
 static int launch_gemm(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, int max_ctas, cudaStream_t stream) {
   once_per_device((BN == 256 ? 0 : 8) + MODE, [] {
     cudaFuncSetAttribute(gemm_bf16_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (MODE == EPI_RS || MODE == EPI_STORE) ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL);
+                         SmemLayout<BN>::TOTAL_RS);
   });
   const int sms = num_sms();
   long long tiles = (long long)p.batch * p.tiles_m * p.tiles_n;
   int cap = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
   int grid = (int)(tiles < cap ? tiles : cap);
   gemm_bf16_kernel<BN, MODE><<<grid, (MODE == EPI_AG || MODE == EPI_WG) ? 320 : 192,
-                               (MODE == EPI_RS || MODE == EPI_STORE) ? SmemLayout<BN>::TOTAL_RS : SmemLayout<BN>::TOTAL, stream>>>(mapA, mapB, p);
+                               SmemLayout<BN>::TOTAL_RS, stream>>>(mapA, mapB, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

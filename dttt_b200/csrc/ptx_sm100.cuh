@@ -106,22 +106,33 @@ __device__ __forceinline__ void red_add_f32x4(float* addr, const float4& v) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// A warp's 32 rows x 64 bf16 columns (lane = row, as tcgen05.ld delivers them) leave as whole 128-byte lines: the rows go
-// through a 4 KB staging area, 16-byte pieces XOR-swizzled by row (no bank conflicts either way), and come back with eight
-// lanes per row, so that one store instruction writes four complete lines instead of 16 bytes of 32 different rows.
-// `half` selects columns [32 half, 32 half + 32) of the piece; callers put both halves, __syncwarp(), flush, __syncwarp().
-__device__ __forceinline__ void stage_put_bf16x32(uint8_t* stg, int lane, int half, const uint32_t (&r)[32], float alpha) {
+// A warp's 32 rows x 128 bytes (lane = row, as tcgen05.ld delivers them: 64 bf16 or 32 f32 columns) leave as whole 128-byte
+// lines: the rows go through a 4 KB staging area, 16-byte pieces XOR-swizzled by row (no bank conflicts either way), and
+// come back with eight lanes per row, so that one instruction writes (or adds to) four complete lines instead of 16 bytes
+// of 32 different rows.  `f(value, j)` maps accumulator column j of the 32 just loaded to the stored value.  Callers put
+// (both halves for bf16), __syncwarp(), flush, __syncwarp().
+template <class F>
+__device__ __forceinline__ void stage_put_bf16x32(uint8_t* stg, int lane, int half, const uint32_t (&r)[32], F f) {
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     uint4 v;
     __nv_bfloat162* vb = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      vb[e] = __floats2bfloat162_rn(__uint_as_float(r[8 * q + 2 * e]) * alpha, __uint_as_float(r[8 * q + 2 * e + 1]) * alpha);
+      vb[e] = __floats2bfloat162_rn(f(__uint_as_float(r[8 * q + 2 * e]), 8 * q + 2 * e), f(__uint_as_float(r[8 * q + 2 * e + 1]), 8 * q + 2 * e + 1));
     *reinterpret_cast<uint4*>(stg + lane * 128 + (((half * 4 + q) ^ (lane & 7)) * 16)) = v;
   }
 }
-// out0: element (first row of the piece, first of its 64 columns), 16-byte aligned, ld a multiple of 8; rows >= rows_valid are skipped
+template <class F>
+__device__ __forceinline__ void stage_put_f32x32(uint8_t* stg, int lane, const uint32_t (&r)[32], F f) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    *reinterpret_cast<float4*>(stg + lane * 128 + ((q ^ (lane & 7)) * 16)) =
+        make_float4(f(__uint_as_float(r[4 * q]), 4 * q), f(__uint_as_float(r[4 * q + 1]), 4 * q + 1),
+                    f(__uint_as_float(r[4 * q + 2]), 4 * q + 2), f(__uint_as_float(r[4 * q + 3]), 4 * q + 3));
+}
+// out0: element (first row of the piece, first of its columns), 16-byte aligned, ld * element size a multiple of 16;
+// rows >= rows_valid are skipped
 __device__ __forceinline__ void stage_flush_bf16x64(const uint8_t* stg, int lane, __nv_bfloat16* out0, long long ld, int rows_valid) {
   const int piece = lane & 7;
 #pragma unroll
@@ -129,6 +140,19 @@ __device__ __forceinline__ void stage_flush_bf16x64(const uint8_t* stg, int lane
     const int rr = i * 4 + (lane >> 3);
     const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((piece ^ (rr & 7)) * 16));
     if (rr < rows_valid) *reinterpret_cast<uint4*>(out0 + (long long)rr * ld + piece * 8) = v;
+  }
+}
+__device__ __forceinline__ void stage_flush_f32x32(const uint8_t* stg, int lane, float* out0, long long ld, int rows_valid, bool accumulate) {
+  const int piece = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + (lane >> 3);
+    const float4 v = *reinterpret_cast<const float4*>(stg + rr * 128 + ((piece ^ (rr & 7)) * 16));
+    if (rr < rows_valid) {
+      float* o = out0 + (long long)rr * ld + piece * 4;
+      if (accumulate) red_add_f32x4(o, v);                       // C += tile, performed at L2
+      else *reinterpret_cast<float4*>(o) = v;
+    }
   }
 }
 

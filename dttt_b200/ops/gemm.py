@@ -160,6 +160,8 @@ def _torch_mm(a, b, ta, tb, out_dtype):
 
 # Fast-weight gradients summed in f32 by the GEMM epilogue (False: every contribution is a bf16 tensor that autograd adds up).
 CAST_ACC = os.environ.get("DTTT_CAST_ACC", "1") == "1"
+ACC_MISSES = None       # a dict while a profile wants to know which products could not use the buffer (tools/step_profile.py)
+ACC_DIRECT = [0]        # ordinary gradients that reached a tracked copy's backward node
 
 
 class _CastAcc(torch.autograd.Function):
@@ -182,6 +184,7 @@ class _CastAcc(torch.autograd.Function):
         if acc is None:
             return (None if g is None else g.to(torch.float32)), None, None
         if g is not None:
+            ACC_DIRECT[0] += 1
             acc = acc + g if torch.is_grad_enabled() else acc.add_(g)
         return acc, None, None
 
@@ -199,11 +202,14 @@ def _acc_into(holder, shape, a, b, ta, tb) -> bool:
     """Add ``op(a) @ op(b)`` to the f32 buffer of ``holder`` (created by the first product); False if this backward has to
     return an ordinary gradient instead (it is being recorded, or it is the inner step's own gradient)."""
     from .functional import _INNER_BACKWARD
-    if holder is None or torch.is_grad_enabled() or _INNER_BACKWARD[0] or not (_kernel_ok(a) and _kernel_ok(b)):
+    if holder is None or torch.is_grad_enabled() or _INNER_BACKWARD[0]:
         return False
     M = a.shape[-1] if ta else a.shape[-2]
     N = b.shape[-2] if tb else b.shape[-1]
-    if a.dim() != len(shape) or b.dim() != len(shape) or (a.shape[0], M, N) != tuple(shape):
+    if not (_kernel_ok(a) and _kernel_ok(b)) or a.dim() != len(shape) or b.dim() != len(shape) or (a.shape[0], M, N) != tuple(shape):
+        if ACC_MISSES is not None:
+            key = (tuple(a.shape), str(a.dtype), tuple(b.shape), str(b.dtype), ta, tb, tuple(shape))
+            ACC_MISSES[key] = ACC_MISSES.get(key, 0) + 1
         return False
     if holder[0] is None:
         holder[0] = gemm_raw(a, b, ta, tb, torch.float32)

@@ -26,6 +26,7 @@ def main(argv=None) -> int:
     ap.add_argument("--trace", default="")
     ap.add_argument("--shapes", action="store_true", help="also group the framework ops by input shapes")
     ap.add_argument("--top", type=int, default=60, help="rows of the by-shape table")
+    ap.add_argument("--stacks", action="store_true", help="attribute the ATen ops' device time to the package's source lines")
     ap.add_argument("--keep-prefix-layers", type=int, default=0)
     ap.add_argument("--keep-suffix-chunks", type=int, default=0)
     a = ap.parse_args(argv)
@@ -49,6 +50,8 @@ def main(argv=None) -> int:
         print(f"warm-up step {s}: {time.time() - t0:.3f} s", flush=True)
     prof.enable(True)
     gemm.SHAPE_LOG = {}
+    gemm.ACC_MISSES = {}
+    gemm.ACC_DIRECT[0] = 0
     n0 = gemm.LAUNCHES, kernels.LAUNCHES
     t0 = time.time()
     eng.train_step(ids, 2)
@@ -64,10 +67,14 @@ def main(argv=None) -> int:
     for key, n in sorted(shapes.items(), key=lambda kv: -2.0 * kv[0][0] * kv[0][1] * kv[0][2] * kv[0][3] * kv[1])[:40]:
         M, N, K, B = key[:4]
         print(f"  {str(key):46s} n={n:5d}  {2.0 * M * N * K * B * n / 1e12:8.2f} TFLOP  ({100 * 2.0 * M * N * K * B * n / tot:4.1f} %)")
+    print(f"fast-weight gradient buffer: {gemm.ACC_DIRECT[0]} ordinary gradients reached a tracked copy; products that could not "
+          f"use the buffer: {gemm.ACC_MISSES}")
+    gemm.ACC_MISSES = None
     print(f"peak device memory: {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB")
     if a.kernels or a.trace:
         from torch.profiler import ProfilerActivity, profile
-        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=a.shapes) as p:
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=a.shapes or a.stacks,
+                     with_stack=a.stacks) as p:
             eng.train_step(ids, 3)
             torch.cuda.synchronize()
         ka = p.key_averages()
@@ -84,6 +91,31 @@ def main(argv=None) -> int:
             for e in sorted(ks, key=lambda e: -e.self_device_time_total)[:a.top]:
                 if e.key.startswith(("aten::", "_")):
                     print(f"  {e.key[:28]:28s} n={e.count:5d} {e.self_device_time_total / 1e3:8.1f} ms  {str(e.input_shapes)[:150]}")
+        if a.stacks:
+            # ATen ops by the innermost frame of this package that issued them; ops run by the autograd engine have no
+            # Python frame and are listed under the backward node that contains them
+            agg = {}
+            for e in p.events():
+                if not e.name.startswith("aten::") or e.self_device_time_total <= 0:
+                    continue
+                where = next((f for f in (e.stack or []) if "dttt_b200" in f), None)
+                if where is None:
+                    par, names = e.cpu_parent, []
+                    while par is not None and len(names) < 2:
+                        if not par.name.startswith("aten::"):
+                            names.append(par.name[:60])
+                        par = par.cpu_parent
+                    where = " < ".join(names) or "(engine)"
+                else:
+                    where = where.split("dttt_b200/")[-1][:70]
+                key = (e.name, where, str(e.input_shapes)[:80])
+                t = agg.setdefault(key, [0, 0.0])
+                t[0] += 1
+                t[1] += e.self_device_time_total
+            tot = sum(v[1] for v in agg.values()) / 1e3
+            print(f"ATen ops by source ({tot:.1f} ms of device time):")
+            for (name, where, shp), (n, us) in sorted(agg.items(), key=lambda kv: -kv[1][1])[:a.top]:
+                print(f"  {name[:22]:22s} n={n:5d} {us / 1e3:7.2f} ms  {where:72s} {shp}")
         if a.trace:
             p.export_chrome_trace(a.trace)
     return 0

@@ -436,6 +436,7 @@ class _PlainStep(torch.autograd.Function):
     @staticmethod
     def forward(ctx, clip, eta, n, *Wg):
         from ..ops import kernels
+        ctx.set_materialize_grads(False)               # the bf16 copies below never receive a gradient: no zeros for them
         W, g = Wg[:n], Wg[n:]
         sumsq, axpy, _, _ = _seq_ops(W[0])
         norm = torch.sqrt(sumsq(list(g)) + 1e-8)
