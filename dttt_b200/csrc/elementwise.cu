@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <cstdlib>
 
 namespace {
 
@@ -441,13 +442,145 @@ extern "C" int dttt_rmsnorm_fwd(const void* x, const float* w, void* y, float* r
   return (int)cudaGetLastError();
 }
 
+// The same backward with the rows streamed through shared memory by cp.async: every warp keeps STAGES - 1 rows of x and dy
+// in flight while it works on one, and holds nothing of a row in registers between its two passes (the register form
+// above needs 228 registers at D = 2048, which leaves eight warps per SM and their loads exposed).  A lane reads back
+// exactly the 16-byte pieces it copied itself, so cp.async.wait_group is all the synchronisation the data needs.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int MAXC, int STAGES>
+__global__ void __launch_bounds__(256, 1)
+rmsnorm_bwd_async_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
+                         const float* __restrict__ rstd, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, long long rows, int D) {
+  extern __shared__ __align__(16) uint8_t smem_async[];
+  float* sdw = reinterpret_cast<float*>(smem_async);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int row_bytes = D * 2;
+  uint8_t* ring = smem_async + (size_t)D * 4 + (size_t)wid * STAGES * 2 * row_bytes;      // this warp's stages: [x row | dy row]
+  const long long warps = (long long)gridDim.x * nw;
+  const long long first = (long long)blockIdx.x * nw + wid;
+  const int nchunk = D / 8;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  float acc[MAXC][8];
+#pragma unroll
+  for (int j = 0; j < MAXC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+  auto issue = [&](long long row, int stage) {
+    if (row < rows) {
+      uint8_t* dst = ring + (size_t)stage * 2 * row_bytes;
+      const uint8_t* xs = reinterpret_cast<const uint8_t*>(x + row * D);
+      const uint8_t* gs = reinterpret_cast<const uint8_t*>(dy + row * D);
+#pragma unroll
+      for (int j = 0; j < MAXC; ++j) {
+        const int c = lane + 32 * j;
+        if (c < nchunk) {
+          cp_async16(dst + c * 16, xs + c * 16);
+          cp_async16(dst + row_bytes + c * 16, gs + c * 16);
+        }
+      }
+    }
+    cp_async_commit();                                       // one group per call, empty past the end: the counting stays uniform
+  };
+  long long next = first;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) { issue(next, s); next += warps; }
+  int stage = 0;
+  for (long long row = first; row < rows; row += warps) {
+    issue(next, (stage + STAGES - 1) % STAGES);              // the stage read in the previous iteration (its loads have been consumed)
+    next += warps;
+    cp_async_wait<STAGES - 1>();                             // this row's group has landed
+    const uint4* xr = reinterpret_cast<const uint4*>(ring + (size_t)stage * 2 * row_bytes);
+    const uint4* gr = reinterpret_cast<const uint4*>(ring + (size_t)stage * 2 * row_bytes + row_bytes);
+    const float r = rstd[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+        float fx[8], fg[8];
+        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xh = fx[i] * r;
+          dot += ww[i] * fg[i] * xh;
+          acc[j][i] += fg[i] * xh;
+        }
+      }
+    }
+    dot = warp_sum(dot) / D;
+    uint4* dr = reinterpret_cast<uint4*>(dx + row * D);
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+        float fx[8], fg[8], o[8];
+        unpack8(xr[c], fx); unpack8(gr[c], fg);
+        const float4 w0 = reinterpret_cast<const float4*>(w)[2 * c], w1 = reinterpret_cast<const float4*>(w)[2 * c + 1];
+        const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = r * (ww[i] * fg[i] - fx[i] * r * dot);
+        dr[c] = pack8(o);
+      }
+    }
+    stage = (stage + 1) % STAGES;
+  }
+  cp_async_wait<0>();
+  if (dw) {
+#pragma unroll
+    for (int j = 0; j < MAXC; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) atomicAdd(&sdw[c * 8 + i], acc[j][i]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(&dw[i], sdw[i]);
+  }
+}
+
 extern "C" int dttt_rmsnorm_bwd(const void* x, const float* w, const void* dy, const float* rstd, void* dx, float* dw,
                                 long long rows, int D, cudaStream_t s) {
   if (D % 8 || D > 8192) return -2;
+  {
+    // Rows of 1024 .. 2048 elements, a chunk's worth of them (measured at D = 2048: 4096 rows 54 -> 38 us, but 49152 rows
+    // 161 -> 206 us, crossing near 16 k rows): the streamed form.  DTTT_RMS_BWD_ASYNC=0 turns it off, =2 takes it for any size.
+    static const int use_async = getenv("DTTT_RMS_BWD_ASYNC") ? atoi(getenv("DTTT_RMS_BWD_ASYNC")) : 1;
+    constexpr int ST = 3, WPB = 8;
+    if (use_async && D % 256 == 0 && D >= 1024 && D <= 2048 && rows >= 148 * WPB && (rows <= 12288 || use_async == 2) &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy)) & 15) == 0) {
+      const size_t smem = (size_t)D * 4 + (size_t)WPB * ST * 2 * D * 2;
+      static bool attr_set[64] = {};
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(rmsnorm_bwd_async_kernel<8, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(8192 + WPB * ST * 2 * 4096)) != cudaSuccess)
+          return -3;
+        attr_set[dev] = true;
+      }
+      long long blocks = (rows + WPB - 1) / WPB;
+      const int grid = (int)(blocks > 148 ? 148 : blocks);
+      rmsnorm_bwd_async_kernel<8, ST><<<grid, WPB * 32, smem, s>>>((const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, rstd,
+                                                                    (__nv_bfloat16*)dx, dw, rows, D);
+      return (int)cudaGetLastError();
+    }
+  }
   const int wpb = 8;
   long long blocks = (rows + wpb - 1) / wpb;
-  int grid = (int)(blocks > 148 * 4 ? 148 * 4 : (blocks < 1 ? 1 : blocks));
   const int chunks = (D / 8 + 31) / 32;
+  // every block ends with D atomic adds into dw, so no more blocks than can be resident: one per SM from 8 chunks per lane
+  // on (228 registers), two at 4, four below
+  const int per_sm = chunks >= 8 ? 1 : (chunks >= 4 ? 2 : 4);
+  int grid = (int)(blocks > 148 * per_sm ? 148 * per_sm : (blocks < 1 ? 1 : blocks));
   size_t smem = (size_t)D * sizeof(float);
 #define LAUNCH(MC) rmsnorm_bwd_kernel<MC><<<grid, wpb * 32, smem, s>>>((const __nv_bfloat16*)x, w, (const __nv_bfloat16*)dy, \
                                                                       rstd, (__nv_bfloat16*)dx, dw, rows, D)
@@ -458,6 +591,66 @@ extern "C" int dttt_rmsnorm_bwd(const void* x, const float* w, const void* dy, c
   else if (chunks <= 16) LAUNCH(16);
   else LAUNCH(32);
 #undef LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// The same rotation from a table of (cos, sin) per (row, frequency): the angles depend on the position only, so one table
+// serves every head, both of q and k, every layer and the backward of a chunk; the kernel that applies it is a plain
+// streaming pass (the direct kernel above spends most of its time in sincosf on angles of up to 1e5 radians).
+__global__ void rope_table_kernel(const long long* __restrict__ pos, const float* __restrict__ inv_freq, long long rows,
+                                  int half, float2* __restrict__ tab) {
+  const long long total = rows * half;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long row = t / half;
+    const int i = (int)(t - row * half);
+    float s, c;
+    sincosf((float)pos[row] * inv_freq[i], &s, &c);
+    tab[t] = make_float2(c, s);
+  }
+}
+
+__global__ void rope_apply_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                  const float2* __restrict__ tab, long long rows, int heads, int d, float sign) {
+  const int slices = d / 16;
+  const int half = d / 2;
+  const long long total = rows * heads * slices;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int sl = (int)(t % slices);
+    const long long rh = t / slices;
+    const long long row = rh / heads;
+    const __nv_bfloat16* base = x + rh * d;
+    float a[8], b[8], oa[8], ob[8];
+    unpack8(*reinterpret_cast<const uint4*>(base + sl * 8), a);
+    unpack8(*reinterpret_cast<const uint4*>(base + half + sl * 8), b);
+    const float4* cs = reinterpret_cast<const float4*>(tab + row * half + sl * 8);     // 8 (cos, sin) pairs = 64 bytes
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = cs[i];
+      const float s0 = v.y * sign, s1 = v.w * sign;
+      oa[2 * i] = a[2 * i] * v.x - b[2 * i] * s0;
+      ob[2 * i] = b[2 * i] * v.x + a[2 * i] * s0;
+      oa[2 * i + 1] = a[2 * i + 1] * v.z - b[2 * i + 1] * s1;
+      ob[2 * i + 1] = b[2 * i + 1] * v.z + a[2 * i + 1] * s1;
+    }
+    __nv_bfloat16* ob_ = out + rh * d;
+    *reinterpret_cast<uint4*>(ob_ + sl * 8) = pack8(oa);
+    *reinterpret_cast<uint4*>(ob_ + half + sl * 8) = pack8(ob);
+  }
+}
+
+extern "C" int dttt_rope_table(const long long* pos, const float* inv_freq, long long rows, int d, void* tab, cudaStream_t s) {
+  if (d % 16) return -2;
+  const long long total = rows * (d / 2);
+  rope_table_kernel<<<grid_for(total, 256, 148 * 16), 256, 0, s>>>(pos, inv_freq, rows, d / 2, (float2*)tab);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int dttt_rope_apply(const void* x, void* out, const void* tab, long long rows, int heads, int d, float sign,
+                               cudaStream_t s) {
+  if (d % 16) return -2;
+  long long total = rows * heads * (d / 16);
+  rope_apply_kernel<<<grid_for(total, 256, 148 * 32), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (const float2*)tab,
+                                                                  rows, heads, d, sign);
   return (int)cudaGetLastError();
 }
 

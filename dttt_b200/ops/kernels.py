@@ -6,6 +6,7 @@ sections below as their symbols are found.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 from typing import Dict
 
@@ -59,6 +60,8 @@ _vp, _ll, _i, _f = _ct.c_void_p, _ct.c_longlong, _ct.c_int, _ct.c_float
 _lib.register("dttt_rmsnorm_fwd", _i, [_vp, _vp, _vp, _vp, _ll, _i, _f, _vp])
 _lib.register("dttt_rmsnorm_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _vp])
 _lib.register("dttt_rope", _i, [_vp, _vp, _vp, _vp, _ll, _i, _i, _f, _vp])
+_lib.register("dttt_rope_table", _i, [_vp, _vp, _ll, _i, _vp, _vp])
+_lib.register("dttt_rope_apply", _i, [_vp, _vp, _vp, _ll, _i, _i, _f, _vp])
 _lib.register("dttt_swiglu_fwd", _i, [_vp, _vp, _vp, _ll, _vp])
 _lib.register("dttt_swiglu_bwd", _i, [_vp, _vp, _vp, _vp, _vp, _ll, _vp])
 _lib.register("dttt_adamw", _i, [_vp, _vp, _vp, _vp, _ll, _f, _f, _f, _f, _f, _f, _f, _f, _vp])
@@ -193,6 +196,28 @@ def rms_norm(x, w, eps):
 
 
 # ---- rotary embedding
+# (cos, sin) per (row, frequency) of the positions last seen: one table serves q and k, every head and layer of a chunk and
+# the backward (DTTT_ROPE_TABLE=0: every call computes its angles itself).  An entry keeps its position tensor alive, so a
+# recycled address cannot pass for it, and the version counter catches in-place edits.
+ROPE_TABLE = os.environ.get("DTTT_ROPE_TABLE", "1") == "1"
+_ROPE_TABLES: "collections.OrderedDict" = collections.OrderedDict()
+_ROPE_TABLES_MAX = 8
+
+
+def _rope_table(pc, inv_freq, rows, d):
+    key = (pc.data_ptr(), pc.numel(), pc._version, inv_freq.data_ptr(), inv_freq._version, d, _lib.stream_ptr())
+    hit = _ROPE_TABLES.get(key)
+    if hit is not None:
+        _ROPE_TABLES.move_to_end(key)
+        return hit[2]
+    tab = torch.empty(rows, d // 2, 2, dtype=torch.float32, device=pc.device)
+    _check(_lib.lib().dttt_rope_table(_p(pc), _p(inv_freq), rows, d, _p(tab), _stream()), "rope_table")
+    _ROPE_TABLES[key] = (pc, inv_freq, tab)
+    while len(_ROPE_TABLES) > _ROPE_TABLES_MAX:
+        _ROPE_TABLES.popitem(last=False)
+    return tab
+
+
 def _rope_run(x, pos, inv_freq, sign):
     xc = x.contiguous()
     heads, d = xc.shape[-2], xc.shape[-1]
@@ -204,6 +229,10 @@ def _rope_run(x, pos, inv_freq, sign):
         ang = pc.float().unsqueeze(-1) * inv_freq
         emb = torch.cat([ang, ang], dim=-1)
         return _ref.apply_rope(xc, emb.cos(), sign * emb.sin())
+    if ROPE_TABLE and inv_freq.dtype == torch.float32 and inv_freq.is_contiguous() and inv_freq.numel() == d // 2:
+        tab = _rope_table(pc, inv_freq, rows, d)
+        _check(_lib.lib().dttt_rope_apply(_p(xc), _p(out), _p(tab), rows, heads, d, float(sign), _stream()), "rope_apply")
+        return out
     _check(_lib.lib().dttt_rope(_p(xc), _p(out), _p(pc), _p(inv_freq), rows, heads, d, float(sign), _stream()), "rope")
     return out
 

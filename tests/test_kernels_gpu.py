@@ -96,7 +96,7 @@ def test_mm_autograd_double_backward():
     assert _rel(ga, ga_r) < 3e-2 and _rel(gb2, gb2_r) < 5e-2
 
 
-@pytest.mark.parametrize("rows,D", [(1000, 2048), (77, 64), (4096, 128), (33, 8192)])
+@pytest.mark.parametrize("rows,D", [(1000, 2048), (77, 64), (4096, 128), (33, 8192), (3001, 2048), (1500, 1280), (1184, 1024)])
 def test_rmsnorm(rows, D):
     from dttt_b200.ops import kernels, reference as ref
     torch.manual_seed(3)
@@ -124,6 +124,24 @@ def test_rmsnorm_second_order_matches_reference():
     (dxr,) = torch.autograd.grad((ref.rms_norm(x32, w.detach(), 1e-6) * r).sum(), x32, create_graph=True)
     (ddxr,) = torch.autograd.grad(dxr.pow(2).sum(), x32)
     assert _rel(ddx, ddxr) < 0.1
+
+
+def test_rope_table_follows_the_positions():
+    """The cached (cos, sin) table is keyed on the position tensor: other positions of the same shape, and the same tensor
+    edited in place, must not be served from it."""
+    from dttt_b200.ops import kernels
+    torch.manual_seed(6)
+    x = torch.randn(500, 8, 64, device="cuda", dtype=torch.bfloat16)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, 32, device="cuda").float() / 32))).contiguous()
+    pos = torch.randint(0, 100000, (500,), device="cuda")
+    for _ in range(2):
+        got = kernels._rope_run(x, pos, inv, 1.0)
+        assert _rel(got, kernels._rope_ref(x.float(), pos, inv)) < 1e-2
+    pos2 = torch.randint(0, 100000, (500,), device="cuda")
+    assert _rel(kernels._rope_run(x, pos2, inv, -1.0), kernels._rope_ref(x.float(), -pos2, inv)) < 1e-2
+    pos.add_(17)
+    assert _rel(kernels._rope_run(x, pos, inv, 1.0), kernels._rope_ref(x.float(), pos, inv)) < 1e-2
+    kernels._ROPE_TABLES.clear()
 
 
 @pytest.mark.parametrize("d,heads", [(64, 8), (128, 4), (32, 3)])
