@@ -181,6 +181,8 @@ class _CastAcc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         acc, ctx.holder[0] = ctx.holder[0], None
+        if acc is not None and ctx.holder[1] != _graph_task():
+            acc = None                                  # left behind by an earlier backward that never reached this node
         if acc is None:
             return (None if g is None else g.to(torch.float32)), None, None
         if g is not None:
@@ -189,10 +191,13 @@ class _CastAcc(torch.autograd.Function):
         return acc, None, None
 
 
+_graph_task = getattr(torch._C, "_current_graph_task_id", lambda: -1)     # which backward pass is running (-1: none)
+
+
 def cast_acc(w: torch.Tensor, lo: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``w.to(bfloat16)`` for an f32 ``[B, in, out]`` weight that wants its gradient summed in f32 (see ``_CastAcc``);
     ``lo``: that copy if the kernel that produced ``w`` already wrote it."""
-    holder = [None]
+    holder = [None, -1]                                  # the buffer, and the backward pass that is filling it
     c = _CastAcc.apply(w, holder, None if lo is None else lo.detach())
     c.grad_acc = holder
     return c
@@ -211,8 +216,11 @@ def _acc_into(holder, shape, a, b, ta, tb) -> bool:
             key = (tuple(a.shape), str(a.dtype), tuple(b.shape), str(b.dtype), ta, tb, tuple(shape))
             ACC_MISSES[key] = ACC_MISSES.get(key, 0) + 1
         return False
-    if holder[0] is None:
-        holder[0] = gemm_raw(a, b, ta, tb, torch.float32)
+    task = _graph_task()
+    if holder[0] is None or holder[1] != task:
+        # the first product of this backward pass (a buffer of another pass, one that took a gradient w.r.t. something
+        # downstream of the weights and so never ran the copy's own node, is dropped)
+        holder[0], holder[1] = gemm_raw(a, b, ta, tb, torch.float32), task
     else:
         gemm_raw(a, b, ta, tb, torch.float32, out=holder[0], accumulate=True)
     return True

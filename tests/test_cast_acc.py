@@ -98,3 +98,16 @@ def test_copy_written_by_the_step_kernel_is_used_once(monkeypatch):
     x = torch.randn(2, 4, 8).bfloat16()
     gemm.mm(x, c).float().sum().backward()
     assert wg.grad is not None and wg.grad.dtype == torch.float32
+
+
+def test_a_partial_backward_leaves_nothing_behind(monkeypatch):
+    """A gradient taken w.r.t. an activation only runs the products' backward, not the copy's own node; what those products
+    put into the buffer must not be counted again by a later full backward over the same graph."""
+    monkeypatch.setattr(gemm, "EMULATE", True)
+    W = torch.randn(2, 8, 16).requires_grad_(True)
+    x = torch.randn(2, 4, 8).bfloat16().requires_grad_(True)
+    y = gemm.mm(x, gemm.cast_acc(W)).float().sum()
+    torch.autograd.grad(y, [x], retain_graph=True)
+    y.backward()
+    ref = torch.matmul(x.detach().float().transpose(1, 2), torch.ones(2, 4, 16))
+    assert _rel(W.grad, ref) < 1e-2
