@@ -73,8 +73,11 @@ def main(argv=None) -> int:
     print(f"peak device memory: {torch.cuda.max_memory_allocated() / 2 ** 30:.1f} GiB")
     if a.kernels or a.trace:
         from torch.profiler import ProfilerActivity, profile
+        extra = {}
+        if a.stacks:                                      # Python frames are only attached with the verbose tracer
+            extra["experimental_config"] = torch._C._profiler._ExperimentalConfig(verbose=True)
         with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=a.shapes or a.stacks,
-                     with_stack=a.stacks) as p:
+                     with_stack=a.stacks, **extra) as p:
             eng.train_step(ids, 3)
             torch.cuda.synchronize()
         ka = p.key_averages()
