@@ -205,13 +205,18 @@ _ROPE_TABLES_MAX = 8
 
 
 def _rope_table(pc, inv_freq, rows, d):
-    key = (pc.data_ptr(), pc.numel(), pc._version, inv_freq.data_ptr(), inv_freq._version, d, _lib.stream_ptr())
-    hit = _ROPE_TABLES.get(key)
+    try:
+        key = (pc.data_ptr(), pc.numel(), pc._version, inv_freq.data_ptr(), inv_freq._version, d, _lib.stream_ptr())
+    except RuntimeError:                               # inference tensors keep no version counter: nothing to key a cache on
+        key = None
+    hit = _ROPE_TABLES.get(key) if key is not None else None
     if hit is not None:
         _ROPE_TABLES.move_to_end(key)
         return hit[2]
     tab = torch.empty(rows, d // 2, 2, dtype=torch.float32, device=pc.device)
     _check(_lib.lib().dttt_rope_table(_p(pc), _p(inv_freq), rows, d, _p(tab), _stream()), "rope_table")
+    if key is None:
+        return tab
     _ROPE_TABLES[key] = (pc, inv_freq, tab)
     while len(_ROPE_TABLES) > _ROPE_TABLES_MAX:
         _ROPE_TABLES.popitem(last=False)
