@@ -689,6 +689,11 @@ def write_chunk(W: FastW, model, h_inner, tokens, inner_mask, kv, pos, n_valid: 
 
 def drift_stats(W_final: FastW, W0: FastW) -> dict:
     """``||W - W0|| / ||W0||`` over all leaves and sequences (reference inner_loop.py:722-732)."""
-    d = torch.sqrt(sum((a.float() - b.float()).pow(2).sum() for a, b in zip(flat(W_final), flat(W0))))
-    i = torch.sqrt(sum(b.float().pow(2).sum() for b in flat(W0)))
+    # one reduction pass per leaf; a W0 leaf that is one template broadcast over the batch is reduced once and scaled
+    def sq(t):
+        if t.dim() == 3 and t.stride(0) == 0 and t.shape[0] > 1:
+            return torch.linalg.vector_norm(t[0].float()).pow(2) * t.shape[0]
+        return torch.linalg.vector_norm(t.float()).pow(2)
+    d = torch.sqrt(sum(sq(a.float() - b.float()) for a, b in zip(flat(W_final), flat(W0))))
+    i = torch.sqrt(sum(sq(b) for b in flat(W0)))
     return {"ttt_drift_rel": d / (i + 1e-12), "ttt_delta_norm": d, "ttt_init_norm": i}
