@@ -238,16 +238,19 @@ def loss_fn(net: Net, batch: Batch, key: torch.Tensor, step: int, cfg: LossConfi
             kvp_next.append((tk, tv))
         kvp = kvp_next if n_seg > 1 else None
         hch = h.unflatten(2, (n_seg_chunks, C))                                     # [B, NS, ncs, C, H]
+        # every (stream, chunk) slice is taken from one unbind per axis: its backward stacks the slices' gradients in one pass,
+        # where indexing ``hch[:, s, j]`` inside the loop would build a zero tensor of the whole segment per slice and add it up
+        hsj = [hs.unbind(1) for hs in hch.unbind(1)]                                # hsj[s][j]: [B, C, H]
 
         # ---- suffix: chunk by chunk
         for j in range(n_seg_chunks):
             c = g * n_seg_chunks + j
-            ho, hc = hch[:, OUTER, j], hch[:, CLEAN, j]
+            ho, hc = hsj[OUTER][j], hsj[CLEAN][j]
             hi = None
             if has_inner:
-                hi = hch[:, INNER, j] if V == 1 else hch[:, INNER:INNER + V, j]
-            ht = hch[:, INNER + n_inner, j] if cfg.distill else None
-            hv = [hch[:, NS - VO + 1 + k, j] for k in range(VO - 1)]
+                hi = hsj[INNER][j] if V == 1 else torch.stack([hsj[INNER + v][j] for v in range(V)], 1)
+            ht = hsj[INNER + n_inner][j] if cfg.distill else None
+            hv = [hsj[NS - VO + 1 + k][j] for k in range(VO - 1)]
             consts = plan.at(c)
             nv = consts["nv"]
 
